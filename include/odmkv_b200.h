@@ -1,0 +1,211 @@
+/*
+ * odmkv_b200 -- C ABI of the B200 (sm_100a) implementation of ODM-KV's
+ * compress-then-decode path: risk scoring, per-layer Lagrangian bit allocation,
+ * Lloyd-Max quantise-and-pack into bit-width banks, and decode attention that reads the
+ * packed banks directly.
+ *
+ * The reference (yiiwang118/ODM-KV) is pure Python/PyTorch and has no FFI; each entry point
+ * below names the reference function whose arithmetic it replaces (paths relative to the
+ * reference project root).  A Python caller binds these with ctypes.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - the library allocates nothing on the device: callers pass outputs and workspaces
+ *     (sizes come from the *_workspace_bytes queries, which are pure host arithmetic);
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and nothing
+ *     synchronises unless stated;
+ *   - return value: 0 ok; negative = argument / shape / workspace error detected on the host
+ *     before any launch; positive = CUDA runtime error code of a failed launch;
+ *   - dtype codes for cache tensors: 0 = fp16, 1 = bf16, 2 = fp32;
+ *   - head_dim is 128 throughout (the only value the reference's experiments use);
+ *   - quantised levels are 2, 3, 4 and 8 bits ("level index" 0..3 in that order); level 16 is
+ *     the exact (verbatim) bank and level 0 the evicted list.
+ */
+#ifndef ODMKV_B200_H
+#define ODMKV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ODMKV_ABI_VERSION 1
+#define ODMKV_HEAD_DIM 128
+#define ODMKV_NUM_QLEVELS 4   /* 2, 3, 4, 8 bits */
+#define ODMKV_NUM_CLASSES 6   /* evicted, 2, 3, 4, 8, exact-16 (class index = position in this list) */
+#define ODMKV_SEG_ALIGN 16    /* every (batch, head) segment of a bank starts on a multiple of 16 slots */
+#define ODMKV_TILE 128        /* tokens per quantise tile */
+#define ODMKV_MAX_LEVELS 8    /* candidate widths of one Lagrangian problem */
+
+#define ODMKV_OK 0
+#define ODMKV_ERR_ARG (-1)
+#define ODMKV_ERR_SHAPE (-2)
+#define ODMKV_ERR_WORKSPACE (-3)
+#define ODMKV_ERR_UNSUPPORTED (-4)
+#define ODMKV_ERR_LIMIT (-5)
+
+int odmkv_abi_version(void);
+/* host string for a status code returned by any entry point */
+const char *odmkv_status_string(int status);
+
+/* ------------------------------------------------------------------------------------------
+ * Scorer.  Replaces RiskScorer.score_prefill (kvquant/scorer.py:385-404) together with
+ * _expected_core_internals (kvquant/scorer.py:285-318) and _pad_sinks_and_normalize with grain
+ * "global" (kvquant/scorer.py:321-325): per sample, softmax over the positions after the sinks
+ * of mu.k/sqrt(d), mean over the G query heads of a KV head, then
+ * s = (p + eps)^2 (|v|^2 + |k|^2/d |v - o|^2); sink slots receive the maximum over the sample.
+ *   K, V   [B, H, T, 128] contiguous, dtype code `dtype`
+ *   mu     [B, H*G, 128] fp32 -- the averaged-RoPE'd mean query (query head index is KV-major)
+ *   scores [B, H, T] fp32 out
+ * T <= n_sink gives all ones (kvquant/scorer.py:388-389).
+ */
+size_t odmkv_score_workspace_bytes(int B, int H, int G, int T);
+int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu, int B, int H, int G, int T,
+                        int n_sink, float eps, float *scores, void *workspace, size_t workspace_bytes,
+                        void *stream);
+
+/* RiskScorer.score_with_attn (kvquant/scorer.py:406-416): same risk formula for R independent
+ * rows of T tokens each with externally supplied attention weights p (the decode-buffer flush).
+ *   K, V [R, T, 128]; p [R, T] fp32; scores [R, T] fp32 out.  T <= 1024. */
+int odmkv_score_with_attn(const void *K, const void *V, int dtype, const float *p, int R, int T, float eps,
+                          float *scores, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Allocator.  Replaces optimal_scores_to_bits (kvquant/allocator.py:459-663) for P independent
+ * problems of n scores each (one problem = one (layer, sample): all KV heads flattened).
+ */
+typedef struct odmkv_alloc_report {
+    double lam;            /* final lambda (the last midpoint) */
+    double gap_before;     /* (avg - target) * n_active before gap closure */
+    long long counts[ODMKV_MAX_LEVELS]; /* tokens per candidate level after gap closure */
+    int n_active;          /* non-sink tokens */
+    int evaluations;       /* number of assignment passes (66 when hi = 1 suffices) */
+    int moved;             /* tokens moved by gap closure */
+    int ties_lambda;       /* tokens whose two adjacent-level costs differ by < 1e-6 at the final lambda */
+    int ties_cut;          /* gap-closure cuts that fall between two equal scores */
+    int done;              /* 1 when the schedule completed */
+} odmkv_alloc_report;
+
+size_t odmkv_alloc_workspace_bytes(int P, int n);
+/*   scores    [P, n] fp32
+ *   sink_mask [n] uint8 or NULL (shared by all problems; nonzero = pinned to sink_bits)
+ *   levels    host int[K] ascending candidate widths, eps host float64[K] (eviction cost already
+ *             applied to the 0 level, i.e. allocator.py:550-552 done by the caller)
+ *   bits      [P, n] int32 out;  reports [P] out (device) */
+int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, int n, const int *levels,
+                        const double *eps, int K, double target_avg_bits, int sink_bits, int32_t *bits,
+                        odmkv_alloc_report *reports, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Stepwise form for KV heads sharded over ranks: every rank evaluates its shard, the per-level
+ * counts (and, during gap closure, the selection histograms) are summed over ranks by the caller
+ * (an all-reduce on `exchange`, int64 [P, exchange_len]) between `eval` and `update`.
+ * odmkv_alloc_step_* mirror exactly what odmkv_allocate_bits runs internally.
+ *   idx_base: global index of this shard's first score inside the flattened problem. */
+size_t odmkv_alloc_exchange_len(void);
+int odmkv_alloc_begin(const float *scores, const uint8_t *sink_mask, int P, int n_local, long long idx_base,
+                      const int *levels, const double *eps, int K, double target_avg_bits, int sink_bits,
+                      void *workspace, size_t workspace_bytes, long long *exchange, void *stream);
+int odmkv_alloc_eval(void *workspace, long long *exchange, void *stream);
+int odmkv_alloc_update(void *workspace, const long long *exchange_reduced, void *stream);
+/* host: number of eval/update rounds odmkv_alloc_* needs before odmkv_alloc_finish for K levels */
+int odmkv_alloc_num_rounds(int K);
+int odmkv_alloc_finish(void *workspace, int32_t *bits, odmkv_alloc_report *reports, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Quantise-and-pack.  Replaces TurboQuantAdaptiveKVCacheState.append
+ * (kvquant/tq_adaptive_backend.py:350-374), QuantizedBank.append (149-174),
+ * TurboQuantMSE.quantize (kvquant/tq_backend.py:185-197) and _pack_indices (103-125).
+ *
+ * A "chunk" is the packed form of one [B, H, T] block of tokens.  Per class c it holds a bank
+ * whose slots are ordered (b, h, t) -- the row order of the reference's mask.nonzero() -- with
+ * each (b, h) segment starting on a multiple of 16 slots (padding slots have pos = -1).
+ *
+ * Step 1 (plan): count classes, lay out segments.
+ *   bits      [B, H, T] int32 with values in {0, 2, 3, 4, 8, 16}
+ *   seg_start [6, B*H] int32 out, seg_count [6, B*H] int32 out
+ *   totals    [6] int32 out (device): padded slots per class -- the caller reads it back to size
+ *             the banks
+ *   plan workspace keeps per-tile bases for step 2.
+ */
+size_t odmkv_pack_plan_workspace_bytes(int B, int H, int T);
+int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start, int32_t *seg_count,
+                    int32_t *totals, void *plan_workspace, size_t plan_workspace_bytes, void *stream);
+
+/* Bank storage of one chunk; all device pointers, sized from `totals` (cap[c] slots).
+ * Code bytes per slot: 32 (2-bit, four codes per byte, little-endian as the reference),
+ * 48 (3-bit: 32 bytes of the low two bits in the 2-bit layout followed by 16 bytes of the third
+ * bit, coordinate 8j+i in bit i of byte j), 64 (4-bit, two nibbles per byte), 128 (8-bit). */
+typedef struct odmkv_chunk {
+    uint8_t *k_codes[ODMKV_NUM_QLEVELS];
+    uint8_t *v_codes[ODMKV_NUM_QLEVELS];
+    float *k_norm[ODMKV_NUM_QLEVELS];
+    float *v_norm[ODMKV_NUM_QLEVELS];
+    int32_t *pos[ODMKV_NUM_QLEVELS];  /* token position t, -1 for padding */
+    void *exact_k;                    /* [cap16, 128] cache dtype */
+    void *exact_v;
+    int32_t *exact_pos;
+    int32_t *evicted_pos;             /* [cap0] */
+    const int32_t *seg_start;         /* [6, B*H] */
+    const int32_t *seg_count;         /* [6, B*H] */
+    int32_t cap[ODMKV_NUM_CLASSES];   /* slots allocated per class (>= totals) */
+    int32_t B, H, T, t_offset;        /* t_offset is added to every stored position */
+} odmkv_chunk;
+
+/* Step 2: norm, normalise, rotate (one ascending fp32 FMA chain per coordinate), nearest centroid
+ * (searchsorted + neighbour pick, lower index on ties), pack, write into the banks.
+ *   pi_k, pi_v [128, 128] fp32 row-major (y = pi x);  codebooks [4][256] fp32 ascending
+ *   (level index li uses the first 2^bits(li) entries). `chunk` is a HOST struct. */
+int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
+                        const float *pi_v, const float *codebooks, const odmkv_chunk *chunk,
+                        const void *plan_workspace, void *stream);
+
+/* Encode-and-pack only: nearest centroid + pack of already rotated coordinates (the stand-in for
+ * the absent kvquant/tq_triton.mse_nearest_centroid followed by _pack_indices).
+ *   y [n, 128] fp32; codebook [2^bits] fp32; out [n, bytes(bits)] in this library's slot layout. */
+int odmkv_encode_pack(const float *y, long long n, int bits, const float *codebook, uint8_t *out, void *stream);
+
+/* Dequantise a chunk into dense [B, H, T_dense, 128] tensors (positions index the T axis).
+ * Replaces TurboQuantMSE.dequantize (kvquant/tq_backend.py:199-203), QuantizedBank.materialize_into
+ * (kvquant/tq_adaptive_backend.py:205-242) and ExactBank.materialize_into (66-71).
+ *   out_dtype: 0/1/2 as above (fp32 gives the values before the cast to the cache dtype)
+ *   include_exact: also scatter the exact bank.  Evicted rows are not touched. */
+int odmkv_dequant_chunk(const odmkv_chunk *chunk, int in_dtype, const float *pi_k, const float *pi_v,
+                        const float *codebooks, void *K_out, void *V_out, int out_dtype, int T_dense,
+                        int include_exact, void *stream);
+
+/* Export one quantised bank in the reference's bank layout (kvquant/tq_adaptive_backend.py:74-174,
+ * kvquant/tq_backend.py:103-125): rows compacted in (b, h, t) order, 3-bit codes as nibbles.
+ *   class_idx 1..4; indices_k/v [N, ref_bytes] uint8, norms [N] fp32, positions [N, 3] int64;
+ *   row_start [B*H] int32 = exclusive prefix sum of seg_count for that class. */
+int odmkv_export_bank(const odmkv_chunk *chunk, int class_idx, const int32_t *row_start, uint8_t *indices_k,
+                      uint8_t *indices_v, float *norms_k, float *norms_v, int64_t *positions, void *stream);
+/* positions of the exact (class 5) or evicted (class 0) list, same row order */
+int odmkv_export_positions(const odmkv_chunk *chunk, int class_idx, const int32_t *row_start,
+                           int64_t *positions, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode attention over packed chunks.  Replaces, for q_len = 1, the attention call the
+ * reference's wrapper forwards to after masking evicted keys (kvquant/attention_patch.py:30-55)
+ * and the dense dequantised cache it reads: out = softmax(q K_hat^T * scale) V_hat over every
+ * stored token of every chunk plus a dense tail of recent tokens, evicted tokens absent.
+ *   q    [B, H*G, 128] dtype q_dtype;   out [B, H*G, 128] dtype out_dtype
+ *   chunks: HOST array of n_chunks descriptors sharing B and H
+ *   tail_k/tail_v [B, H, tail_cap, 128] cache dtype (may be NULL when tail_len = 0): the first
+ *   tail_len tokens of every (b, h) are attended exactly
+ *   lse  [B, H*G] fp32 out or NULL (log-sum-exp of the scaled logits)
+ *   n_splits: CTAs per (b, h); 0 lets the library choose.
+ */
+size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits);
+int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head);
+int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                      const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                      const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                      int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                      void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ODMKV_B200_H */

@@ -1,0 +1,567 @@
+// Per-layer Lagrangian bit allocation on the device (sm_100a).
+//
+// Replaces optimal_scores_to_bits (kvquant/allocator.py:459-663).  One "problem" is the flattened
+// score tensor of one (layer, sample).  The search runs as a fixed schedule of rounds; every round
+// is one pass over the scores that accumulates a few integers (level counts, or a 16-bit radix
+// histogram during gap closure), followed by a tiny state update:
+//   rounds 0..73      assignment passes: widen hi (x10 while avg > target, at most 8 times),
+//                     64 bisection halvings in fp64, one final pass that records the choice;
+//   closure rounds    per level pair: four radix-select passes that find the k-th smallest
+//                     (score, index) key among the tokens at a level, one pass that moves them.
+// The arithmetic that decides a token's level is three separately rounded fp32 operations
+// (s*eps_k, lambda*b_k, their sum) and a first-minimum argmin, exactly as the reference's
+// broadcasted torch expression; the average is fl32(total bits) / fl32(n) with an exact integer
+// total.  On one GPU the state update runs in the last block of each pass; with KV heads sharded
+// over ranks the caller sums the accumulator over ranks between `eval` and `update`.
+#include "common.cuh"
+
+namespace odmkv {
+
+constexpr int kMaxL = ODMKV_MAX_LEVELS;
+constexpr int kAccHead = 16;                 // counts[8], ties, tie_sel, tie_unsel, spare
+constexpr int kHistBins = 1 << 16;
+constexpr int kAccLen = kAccHead + kHistBins;
+constexpr int kEvalRounds = 74;              // 1 + 8 widenings + 64 halvings + 1 final
+constexpr int kAllocThreads = 256;
+constexpr int kPerThread = 8;
+
+struct AllocCfg {
+    float eps32[kMaxL];
+    float bits32[kMaxL];
+    int levels[kMaxL];
+    int K;
+    int sink_bits;
+    double target;
+};
+
+struct AllocProblem {
+    double lo, hi, lam, gap, gap_before;
+    long long level_counts[kMaxL];
+    unsigned long long sel_prefix;
+    long long sel_k;
+    long long n_move;
+    int phase;       // 0 widen, 1 bisect, 2 final pass pending, 3 select, 4 apply, 5 done
+    int iter, evals, n_active;
+    int dir, step, sel_level, sel_to, sel_pass;
+    int moved, ties_lambda, ties_cut;
+    unsigned ticket;
+    unsigned max_finite_bits;
+    int any_nonfinite, any_finite;
+};
+
+struct AllocWs {
+    AllocProblem *prob;          // [P]
+    unsigned long long *acc;     // [P][kAccLen]
+    uint8_t *chosen;             // [P][n]
+    AllocCfg *cfg;               // device copy (for the stepwise entry points)
+    // host-side header kept at the start of the workspace is mirrored in AllocHeader
+};
+
+struct AllocHeader {  // lives at the start of the workspace on the device; the host keeps its own copy
+    const float *scores;
+    const uint8_t *sink_mask;
+    int P, n;
+    long long idx_base;
+};
+
+inline size_t alloc_ws_layout(int P, int n, AllocWs *ws, unsigned char *base) {
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+    size_t o_hdr = take(sizeof(AllocHeader)), o_cfg = take(sizeof(AllocCfg)), o_prob = take(sizeof(AllocProblem) * (size_t)P);
+    size_t o_acc = take(sizeof(unsigned long long) * (size_t)P * kAccLen), o_ch = take((size_t)P * n);
+    (void)o_hdr;
+    if (ws && base) {
+        ws->cfg = (AllocCfg *)(base + o_cfg);
+        ws->prob = (AllocProblem *)(base + o_prob);
+        ws->acc = (unsigned long long *)(base + o_acc);
+        ws->chosen = (uint8_t *)(base + o_ch);
+    }
+    return off;
+}
+
+// clamp(min=0); when some scores are finite every non-finite one (nan or +inf) becomes the largest
+// finite score; when none is finite, nan -> 0 and +inf -> FLT_MAX  (kvquant/allocator.py:543-547)
+__device__ inline float sanitize(float s, const AllocProblem &pr) {
+    if (s != s) return pr.any_finite ? __uint_as_float(pr.max_finite_bits) : 0.0f;
+    s = fmaxf(s, 0.0f);
+    if (isinf(s)) s = pr.any_finite ? __uint_as_float(pr.max_finite_bits) : 3.402823466e+38f;
+    return s;
+}
+
+__global__ void alloc_init_kernel(AllocProblem *prob, unsigned long long *acc, int P, int K) {
+    const int p = blockIdx.x;
+    if (threadIdx.x == 0) {
+        AllocProblem z = {};
+        z.lo = 0.0; z.hi = 1.0; z.lam = 1.0;
+        z.phase = K == 1 ? 2 : 0;
+        z.sel_level = -1;
+        prob[p] = z;
+    }
+    for (int i = threadIdx.x; i < kAccLen; i += blockDim.x) acc[(size_t)p * kAccLen + i] = 0ull;
+}
+
+__global__ void alloc_stats_kernel(const float *__restrict__ scores, const uint8_t *__restrict__ sink_mask, int n,
+                                   AllocProblem *prob) {
+    const int p = blockIdx.y;
+    unsigned best = 0;
+    int nonfinite = 0, finite = 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        if (sink_mask && sink_mask[i]) continue;
+        float s = scores[(size_t)p * n + i];
+        if (s != s) { nonfinite = 1; continue; }
+        s = fmaxf(s, 0.0f);
+        if (isinf(s)) nonfinite = 1;
+        else { finite = 1; best = max(best, __float_as_uint(s)); }
+    }
+    best = __reduce_max_sync(0xffffffffu, best);
+    nonfinite = __any_sync(0xffffffffu, nonfinite);
+    finite = __any_sync(0xffffffffu, finite);
+    if ((threadIdx.x & 31) == 0) {
+        if (finite) { atomicMax(&prob[p].max_finite_bits, best); prob[p].any_finite = 1; }
+        if (nonfinite) prob[p].any_nonfinite = 1;
+    }
+}
+
+// next gap-closure pair with something to move; sets phase 3 (select) or 5 (done)
+__device__ inline void setup_step(AllocProblem &pr, const AllocCfg &cfg) {
+    const int K = cfg.K;
+    while (pr.step >= 0 && pr.step <= K - 2) {
+        const int lower = pr.step, upper = pr.step + 1;
+        const double delta = (double)cfg.bits32[upper] - (double)cfg.bits32[lower];
+        if (delta > 0) {
+            const int from = pr.dir > 0 ? upper : lower;
+            long long want = (long long)(pr.gap / delta + 0.5);
+            long long nm = pr.level_counts[from] < want ? pr.level_counts[from] : want;
+            if (nm > 0) {
+                pr.sel_level = from;
+                pr.sel_to = pr.dir > 0 ? lower : upper;
+                pr.sel_k = nm;
+                pr.n_move = nm;
+                pr.sel_prefix = 0ull;
+                pr.sel_pass = 0;
+                pr.phase = 3;
+                return;
+            }
+        }
+        pr.step += pr.dir > 0 ? 1 : -1;
+    }
+    pr.sel_level = -1;
+    pr.phase = 5;
+}
+
+// State update of one problem after a pass; called by a whole block (blockDim.x == kAllocThreads).
+__device__ void update_problem(AllocProblem *prp, unsigned long long *acc, const AllocCfg &cfg) {
+    __shared__ unsigned long long part[kAllocThreads];
+    __shared__ int sh_phase;
+    const int tid = threadIdx.x;
+    if (tid == 0) sh_phase = prp->phase;
+    __syncthreads();
+    const int phase = sh_phase;
+    if (phase <= 2) {
+        if (tid == 0) {
+            AllocProblem pr = *prp;
+            long long total = 0, nact = 0, counts[kMaxL];
+            for (int k = 0; k < cfg.K; ++k) {
+                counts[k] = (long long)acc[k];
+                total += counts[k] * (long long)cfg.levels[k];
+                nact += counts[k];
+            }
+            const double avg = (double)((float)total / (float)nact);
+            pr.evals += 1;
+            if (phase == 0) {
+                if (avg > cfg.target && pr.hi < 1e8) { pr.hi *= 10.0; pr.lam = pr.hi; }
+                else { pr.phase = 1; pr.iter = 0; pr.lam = (pr.lo + pr.hi) * 0.5; }
+            } else if (phase == 1) {
+                if (avg > cfg.target) pr.lo = pr.lam; else pr.hi = pr.lam;
+                pr.iter += 1;
+                pr.lam = (pr.lo + pr.hi) * 0.5;
+                if (pr.iter == 64) pr.phase = 2;
+            } else {
+                pr.n_active = (int)nact;
+                for (int k = 0; k < cfg.K; ++k) pr.level_counts[k] = counts[k];
+                pr.ties_lambda = (int)acc[8];
+                double gap = (avg - cfg.target) * (double)nact;
+                pr.gap_before = gap;
+                if (cfg.K > 1 && fabs(gap) > 0.5) {
+                    pr.dir = gap > 0 ? 1 : -1;
+                    pr.gap = fabs(gap);
+                    pr.step = pr.dir > 0 ? 0 : cfg.K - 2;
+                    setup_step(pr, cfg);
+                } else {
+                    pr.phase = 5;
+                }
+            }
+            *prp = pr;
+        }
+        if (tid < kAccHead) acc[tid] = 0ull;
+    } else if (phase == 3) {
+        // find the 16-bit digit holding the sel_k-th smallest key of the current prefix bucket
+        unsigned long long *hist = acc + kAccHead;
+        const long long k = prp->sel_k;
+        const int per = kHistBins / kAllocThreads;
+        unsigned long long s = 0;
+        for (int i = 0; i < per; ++i) s += hist[tid * per + i];
+        part[tid] = s;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long run = 0;
+            for (int i = 0; i < kAllocThreads; ++i) { unsigned long long v = part[i]; part[i] = run; run += v; }
+        }
+        __syncthreads();
+        const unsigned long long before = part[tid];
+        if ((long long)before < k && k <= (long long)(before + s)) {
+            unsigned long long run = before;
+            for (int i = 0; i < per; ++i) {
+                unsigned long long h = hist[tid * per + i];
+                if ((long long)run < k && k <= (long long)(run + h)) {
+                    AllocProblem pr = *prp;
+                    pr.sel_prefix = (pr.sel_prefix << 16) | (unsigned long long)(tid * per + i);
+                    pr.sel_k = k - (long long)run;
+                    pr.sel_pass += 1;
+                    if (pr.sel_pass == 4) pr.phase = 4;
+                    *prp = pr;
+                    break;
+                }
+                run += h;
+            }
+        }
+        __syncthreads();
+        for (int i = tid; i < kAccLen; i += kAllocThreads) acc[i] = 0ull;
+    } else if (phase == 4) {
+        if (tid == 0) {
+            AllocProblem pr = *prp;
+            if (acc[9] > 0 && acc[10] > 0) pr.ties_cut += 1;
+            const int lower = pr.step, upper = pr.step + 1;
+            const double delta = (double)cfg.bits32[upper] - (double)cfg.bits32[lower];
+            pr.moved += (int)pr.n_move;
+            pr.level_counts[pr.sel_level] -= pr.n_move;
+            pr.level_counts[pr.sel_to] += pr.n_move;
+            pr.gap -= (double)pr.n_move * delta;
+            if (pr.gap <= 0.5) { pr.phase = 5; pr.sel_level = -1; }
+            else { pr.step += pr.dir > 0 ? 1 : -1; setup_step(pr, cfg); }
+            *prp = pr;
+        }
+        if (tid < kAccHead) acc[tid] = 0ull;
+    }
+    __syncthreads();
+}
+
+__device__ inline unsigned long long make_key(float s, long long gidx, bool invert) {
+    unsigned long long key = ((unsigned long long)__float_as_uint(s) << 32) | (unsigned long long)(unsigned)gidx;
+    return invert ? ~key : key;
+}
+
+// One pass over the scores of every problem.  FUSED: the last block of a problem updates its state.
+template <bool FUSED>
+__global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *__restrict__ scores,
+                                                                   const uint8_t *__restrict__ sink_mask, int n,
+                                                                   long long idx_base, AllocWs ws, const AllocCfg cfg) {
+    __shared__ unsigned long long sh_cnt[kAccHead];
+    __shared__ int sh_last;
+    const int p = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
+    AllocProblem *prp = ws.prob + p;
+    unsigned long long *acc = ws.acc + (size_t)p * kAccLen;
+    const AllocProblem pr = *prp;   // state is only written between passes
+    const int phase = pr.phase;
+    if (phase == 5) return;
+    const float *sc = scores + (size_t)p * n;
+    uint8_t *chosen = ws.chosen + (size_t)p * n;
+    if (tid < kAccHead) sh_cnt[tid] = 0ull;
+    __syncthreads();
+    const long long base = (long long)blockIdx.x * (kAllocThreads * kPerThread);
+
+    if (phase <= 2) {
+        const float lam32 = (float)pr.lam;
+        float lamb[kMaxL];
+#pragma unroll
+        for (int k = 0; k < kMaxL; ++k) lamb[k] = k < cfg.K ? __fmul_rn(lam32, cfg.bits32[k]) : 0.f;
+        unsigned cnt[kMaxL];
+#pragma unroll
+        for (int k = 0; k < kMaxL; ++k) cnt[k] = 0;
+        unsigned ties = 0;
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            long long i = base + u * kAllocThreads + tid;
+            if (i >= n) continue;
+            if (sink_mask && sink_mask[i]) { if (phase == 2) chosen[i] = 255; continue; }
+            const float s = sanitize(sc[i], pr);
+            float best = __fadd_rn(__fmul_rn(s, cfg.eps32[0]), lamb[0]);
+            float cost[kMaxL];
+            cost[0] = best;
+            int arg = 0;
+#pragma unroll
+            for (int k = 1; k < kMaxL; ++k) {
+                if (k < cfg.K) {
+                    float c = __fadd_rn(__fmul_rn(s, cfg.eps32[k]), lamb[k]);
+                    cost[k] = c;
+                    if (c < best) { best = c; arg = k; }
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kMaxL; ++k) cnt[k] += (arg == k);
+            if (phase == 2) {
+                chosen[i] = (uint8_t)arg;
+#pragma unroll
+                for (int k = 0; k < kMaxL; ++k) {
+                    if (k == arg) {
+                        if (k >= 1 && fabs((double)cost[k - 1] - (double)cost[k]) < 1e-6) ties++;
+                        if (k + 1 < cfg.K && fabs((double)cost[k] - (double)cost[k + 1 < kMaxL ? k + 1 : k]) < 1e-6) ties++;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < kMaxL; ++k) {
+            unsigned v = __reduce_add_sync(0xffffffffu, cnt[k]);
+            if (lane == 0 && v) atomicAdd(&sh_cnt[k], (unsigned long long)v);
+        }
+        unsigned tv = __reduce_add_sync(0xffffffffu, ties);
+        if (lane == 0 && tv) atomicAdd(&sh_cnt[8], (unsigned long long)tv);
+        __syncthreads();
+        if (tid < kAccHead && sh_cnt[tid]) atomicAdd(&acc[tid], sh_cnt[tid]);
+    } else if (phase == 3) {
+        const bool inv = pr.dir < 0;
+        const int shift_digit = 48 - 16 * pr.sel_pass;
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            long long i = base + u * kAllocThreads + tid;
+            if (i >= n) continue;
+            if (chosen[i] != (uint8_t)pr.sel_level) continue;
+            unsigned long long key = make_key(sanitize(sc[i], pr), idx_base + i, inv);
+            if (pr.sel_pass > 0 && (key >> (shift_digit + 16)) != pr.sel_prefix) continue;
+            atomicAdd(&acc[kAccHead + ((key >> shift_digit) & 0xffffull)], 1ull);
+        }
+    } else {  // phase 4: move every candidate whose key is <= the selected key
+        const bool inv = pr.dir < 0;
+        const unsigned long long cut = pr.sel_prefix;
+        const unsigned cut_score = (unsigned)((inv ? ~cut : cut) >> 32);
+        unsigned same_sel = 0, same_unsel = 0;
+#pragma unroll
+        for (int u = 0; u < kPerThread; ++u) {
+            long long i = base + u * kAllocThreads + tid;
+            if (i >= n) continue;
+            if (chosen[i] != (uint8_t)pr.sel_level) continue;
+            const float s = sanitize(sc[i], pr);
+            unsigned long long key = make_key(s, idx_base + i, inv);
+            const bool sel = key <= cut;
+            if (sel) chosen[i] = (uint8_t)pr.sel_to;
+            if (__float_as_uint(s) == cut_score) { if (sel) same_sel++; else same_unsel++; }
+        }
+        unsigned a = __reduce_add_sync(0xffffffffu, same_sel), b = __reduce_add_sync(0xffffffffu, same_unsel);
+        if (lane == 0) {
+            if (a) atomicAdd(&acc[9], (unsigned long long)a);
+            if (b) atomicAdd(&acc[10], (unsigned long long)b);
+        }
+    }
+
+    if (FUSED) {
+        __syncthreads();
+        if (tid == 0) {
+            __threadfence();
+            unsigned t = atomicAdd(&prp->ticket, 1u);
+            sh_last = (t == gridDim.x - 1);
+        }
+        __syncthreads();
+        if (sh_last) {
+            __threadfence();
+            if (tid == 0) prp->ticket = 0;
+            update_problem(prp, acc, cfg);
+        }
+    }
+}
+
+// stepwise path: copy the accumulator out / consume the rank-summed accumulator
+__global__ void alloc_export_acc_kernel(const unsigned long long *__restrict__ acc, long long *__restrict__ exchange, int len) {
+    const int p = blockIdx.y;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < len) exchange[(size_t)p * len + i] = (long long)acc[(size_t)p * kAccLen + i];
+}
+__global__ void __launch_bounds__(kAllocThreads) alloc_update_kernel(AllocWs ws, const long long *__restrict__ reduced, int len,
+                                                                      const AllocCfg cfg) {
+    const int p = blockIdx.x;
+    unsigned long long *acc = ws.acc + (size_t)p * kAccLen;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) acc[i] = (unsigned long long)reduced[(size_t)p * len + i];
+    __syncthreads();
+    update_problem(ws.prob + p, acc, cfg);
+}
+
+__global__ void alloc_emit_kernel(const uint8_t *__restrict__ sink_mask, int n, AllocWs ws, const AllocCfg cfg,
+                                  int32_t *__restrict__ bits, odmkv_alloc_report *__restrict__ reports) {
+    const int p = blockIdx.y;
+    const uint8_t *chosen = ws.chosen + (size_t)p * n;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        uint8_t c = chosen[i];
+        bits[(size_t)p * n + i] = (c == 255 || (sink_mask && sink_mask[i])) ? cfg.sink_bits : cfg.levels[c < kMaxL ? c : 0];
+    }
+    if (reports && blockIdx.x == 0 && threadIdx.x == 0) {
+        const AllocProblem &pr = ws.prob[p];
+        odmkv_alloc_report r = {};
+        r.lam = pr.lam;
+        r.gap_before = pr.gap_before;
+        for (int k = 0; k < kMaxL; ++k) r.counts[k] = k < cfg.K ? pr.level_counts[k] : 0;
+        r.n_active = pr.n_active;
+        r.evaluations = pr.evals;
+        r.moved = pr.moved;
+        r.ties_lambda = pr.ties_lambda;
+        r.ties_cut = pr.ties_cut;
+        r.done = pr.phase == 5;
+        reports[p] = r;
+    }
+}
+
+static int make_cfg(const int *levels, const double *eps, int K, double target, int sink_bits, AllocCfg *cfg) {
+    if (!levels || !eps) return ODMKV_ERR_ARG;
+    if (K < 1 || K > kMaxL) return ODMKV_ERR_LIMIT;
+    for (int k = 0; k < K; ++k) {
+        if (k > 0 && levels[k] <= levels[k - 1]) return ODMKV_ERR_ARG;
+        cfg->levels[k] = levels[k];
+        cfg->bits32[k] = (float)levels[k];
+        cfg->eps32[k] = (float)eps[k];
+    }
+    for (int k = K; k < kMaxL; ++k) { cfg->levels[k] = 0; cfg->bits32[k] = 0.f; cfg->eps32[k] = 0.f; }
+    cfg->K = K;
+    cfg->sink_bits = sink_bits;
+    double t = target;
+    if (t < (double)levels[0]) t = (double)levels[0];
+    if (t > (double)levels[K - 1]) t = (double)levels[K - 1];
+    cfg->target = t;
+    return ODMKV_OK;
+}
+
+static inline int closure_rounds(int K) { return K > 1 ? 5 * (K - 1) : 0; }
+
+// host-side mirror of what a stepwise caller needs between calls
+struct AllocHostCtx {
+    AllocHeader hdr;
+    AllocCfg cfg;
+    int round;
+};
+
+}  // namespace odmkv
+
+using namespace odmkv;
+
+extern "C" {
+
+size_t odmkv_alloc_workspace_bytes(int P, int n) {
+    if (P <= 0 || n <= 0) return 0;
+    return alloc_ws_layout(P, n, nullptr, nullptr) + 256;
+}
+
+static int alloc_begin_impl(const float *scores, const uint8_t *sink_mask, int P, int n, const AllocCfg &cfg, AllocWs *ws,
+                            void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (!scores || !workspace) return ODMKV_ERR_ARG;
+    if (P <= 0 || n <= 0 || P > 65535) return ODMKV_ERR_SHAPE;
+    if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    if (workspace_bytes < alloc_ws_layout(P, n, ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
+    alloc_init_kernel<<<P, 256, 0, st>>>(ws->prob, ws->acc, P, cfg.K);
+    int blocks = (n + 256 * 8 - 1) / (256 * 8);
+    if (blocks > 1024) blocks = 1024;
+    alloc_stats_kernel<<<dim3(blocks, P), 256, 0, st>>>(scores, sink_mask, n, ws->prob);
+    return launch_status();
+}
+
+int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, int n, const int *levels,
+                        const double *eps, int K, double target_avg_bits, int sink_bits, int32_t *bits,
+                        odmkv_alloc_report *reports, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!bits) return ODMKV_ERR_ARG;
+    AllocCfg cfg;
+    int rc = make_cfg(levels, eps, K, target_avg_bits, sink_bits, &cfg);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    AllocWs ws;
+    rc = alloc_begin_impl(scores, sink_mask, P, n, cfg, &ws, workspace, workspace_bytes, st);
+    if (rc) return rc;
+    const int nblk = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
+    const int rounds = (K > 1 ? kEvalRounds : 1) + closure_rounds(K);
+    for (int r = 0; r < rounds; ++r)
+        alloc_pass_kernel<true><<<dim3(nblk, P), kAllocThreads, 0, st>>>(scores, sink_mask, n, 0ll, ws, cfg);
+    int eb = (n + 255) / 256;
+    if (eb > 2048) eb = 2048;
+    alloc_emit_kernel<<<dim3(eb, P), 256, 0, st>>>(sink_mask, n, ws, cfg, bits, reports);
+    return launch_status();
+}
+
+// ---- stepwise (rank-sharded) form ------------------------------------------------------------
+// The workspace starts with a small host-readable header region that this library only writes
+// from the host side through cudaMemcpyAsync; the per-call context lives in a static table keyed
+// by the workspace pointer so that eval/update/finish need no extra arguments.
+}  // extern "C"
+
+#include <map>
+#include <mutex>
+namespace odmkv {
+static std::mutex g_ctx_mu;
+static std::map<void *, AllocHostCtx> g_ctx;
+}  // namespace odmkv
+
+extern "C" {
+
+size_t odmkv_alloc_exchange_len(void) { return (size_t)kAccLen; }
+int odmkv_alloc_num_rounds(int K) { return K > 1 ? kEvalRounds + closure_rounds(K) : 1; }
+
+int odmkv_alloc_begin(const float *scores, const uint8_t *sink_mask, int P, int n_local, long long idx_base,
+                      const int *levels, const double *eps, int K, double target_avg_bits, int sink_bits,
+                      void *workspace, size_t workspace_bytes, long long *exchange, void *stream) {
+    if (!exchange) return ODMKV_ERR_ARG;
+    AllocHostCtx ctx;
+    int rc = make_cfg(levels, eps, K, target_avg_bits, sink_bits, &ctx.cfg);
+    if (rc) return rc;
+    AllocWs ws;
+    rc = alloc_begin_impl(scores, sink_mask, P, n_local, ctx.cfg, &ws, workspace, workspace_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+    ctx.hdr.scores = scores; ctx.hdr.sink_mask = sink_mask; ctx.hdr.P = P; ctx.hdr.n = n_local; ctx.hdr.idx_base = idx_base;
+    ctx.round = 0;
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    g_ctx[workspace] = ctx;
+    return ODMKV_OK;
+}
+
+static int get_ctx(void *workspace, AllocHostCtx *out, AllocWs *ws) {
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    auto it = g_ctx.find(workspace);
+    if (it == g_ctx.end()) return ODMKV_ERR_ARG;
+    *out = it->second;
+    alloc_ws_layout(out->hdr.P, out->hdr.n, ws, (unsigned char *)workspace);
+    return ODMKV_OK;
+}
+
+int odmkv_alloc_eval(void *workspace, long long *exchange, void *stream) {
+    AllocHostCtx ctx; AllocWs ws;
+    int rc = get_ctx(workspace, &ctx, &ws);
+    if (rc) return rc;
+    if (!exchange) return ODMKV_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int n = ctx.hdr.n, P = ctx.hdr.P;
+    const int nblk = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
+    alloc_pass_kernel<false><<<dim3(nblk, P), kAllocThreads, 0, st>>>(ctx.hdr.scores, ctx.hdr.sink_mask, n, ctx.hdr.idx_base, ws, ctx.cfg);
+    alloc_export_acc_kernel<<<dim3((kAccLen + 255) / 256, P), 256, 0, st>>>(ws.acc, exchange, kAccLen);
+    return launch_status();
+}
+
+int odmkv_alloc_update(void *workspace, const long long *exchange_reduced, void *stream) {
+    AllocHostCtx ctx; AllocWs ws;
+    int rc = get_ctx(workspace, &ctx, &ws);
+    if (rc) return rc;
+    if (!exchange_reduced) return ODMKV_ERR_ARG;
+    alloc_update_kernel<<<ctx.hdr.P, kAllocThreads, 0, (cudaStream_t)stream>>>(ws, exchange_reduced, kAccLen, ctx.cfg);
+    return launch_status();
+}
+
+int odmkv_alloc_finish(void *workspace, int32_t *bits, odmkv_alloc_report *reports, void *stream) {
+    AllocHostCtx ctx; AllocWs ws;
+    int rc = get_ctx(workspace, &ctx, &ws);
+    if (rc) return rc;
+    if (!bits) return ODMKV_ERR_ARG;
+    const int n = ctx.hdr.n;
+    int eb = (n + 255) / 256;
+    if (eb > 2048) eb = 2048;
+    alloc_emit_kernel<<<dim3(eb, ctx.hdr.P), 256, 0, (cudaStream_t)stream>>>(ctx.hdr.sink_mask, n, ws, ctx.cfg, bits, reports);
+    {
+        std::lock_guard<std::mutex> lk(g_ctx_mu);
+        g_ctx.erase(workspace);
+    }
+    return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,451 @@
+// Decode attention over packed chunks (sm_100a) -- split-K flash decoding in code space.
+//
+// Replaces the q_len = 1 attention call behind the reference's wrapper
+// (kvquant/attention_patch.py:30-55) and the dense dequantised cache it reads
+// (kvquant/tq_adaptive_backend.py:205-242).  Identity used: with q' = pi_k q,
+//   q . k_hat_j = norm^K_j * sum_i q'_i c[idxK_{j,i}],
+//   out = (sum_j p_j norm^V_j c[idxV_j]) pi_v  +  sum_{j exact} p_j v_j,
+// so every quantised token is consumed as codes + two norms; rotation is applied once to the
+// queries (prologue kernel) and once to the merged accumulator (merge kernel).  Evicted tokens are
+// in no bank and therefore absent, which is what the reference's fake-key mask achieves.
+//
+// Grid: (n_splits, B*H).  Each CTA takes the same fraction of every (chunk, class) segment of its
+// (b, h), keeps per-warp running (max, sum, accumulators) for the G query heads of the KV head and
+// writes one partial; the merge kernel combines partials with a log-sum-exp merge.
+#include "common.cuh"
+
+namespace odmkv {
+
+constexpr int kDecThreads = 128;
+constexpr int kDecWarps = kDecThreads / 32;
+
+struct DecodeChunks {
+    odmkv_chunk ch[kMaxChunks];
+    int n;
+};
+
+struct DecodeArgs {
+    const float *qrot;   // [B*H*G, 128] pi_k q
+    const float *qf;     // [B*H*G, 128] q as fp32
+    const void *tail_k;
+    const void *tail_v;
+    const float *codebooks;
+    float *part_ml;      // [BH, nsplit, GP, 2]
+    float *part_acc;     // [BH, nsplit, GP, 2, 128]  (rotated-space, exact-space)
+    int tail_len, tail_cap;
+    int B, H, G, nsplit;
+    float scale;
+};
+
+// rotate the queries once: qrot[r][i] = sum_j pi_k[i][j] q[r][j]; also keep q as fp32
+template <int QDT>
+__global__ void rotate_q_kernel(const void *__restrict__ q, const float *__restrict__ pi_k, float *__restrict__ qrot,
+                                float *__restrict__ qf) {
+    __shared__ float qs[kD];
+    const int r = blockIdx.x, i = threadIdx.x;
+    qs[i] = Elem<QDT>::to_f32(reinterpret_cast<const typename Elem<QDT>::T *>(q)[(size_t)r * kD + i]);
+    __syncthreads();
+    float acc = 0.f;
+    const float4 *row = reinterpret_cast<const float4 *>(pi_k + (size_t)i * kD);
+#pragma unroll 8
+    for (int j4 = 0; j4 < kD / 4; ++j4) {
+        float4 p = row[j4];
+        acc = fmaf(p.x, qs[4 * j4], acc);
+        acc = fmaf(p.y, qs[4 * j4 + 1], acc);
+        acc = fmaf(p.z, qs[4 * j4 + 2], acc);
+        acc = fmaf(p.w, qs[4 * j4 + 3], acc);
+    }
+    qrot[(size_t)r * kD + i] = acc;
+    qf[(size_t)r * kD + i] = qs[i];
+}
+
+// per-warp online-softmax state for GP query heads; each lane owns coordinates 4*lane .. 4*lane+3
+template <int GP>
+struct WarpState {
+    float m[GP], l[GP];
+    float ar[GP][4];  // code-space accumulator (to be rotated by pi_v)
+    float ae[GP][4];  // exact-space accumulator
+};
+
+// fold the logits of up to 32 tokens (one per lane) into the running state; returns p per head
+template <int GP>
+__device__ inline void softmax_step(WarpState<GP> &st, const float (&logit)[GP], bool valid, float (&p)[GP]) {
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+        float x = valid ? logit[g] : -INFINITY;
+        float mx = warp_max(x);
+        float mn = fmaxf(st.m[g], mx);
+        float corr = (st.m[g] == -INFINITY) ? 0.f : __expf(st.m[g] - mn);
+        float pv = (valid && mn > -INFINITY) ? __expf(x - mn) : 0.f;
+        st.l[g] = st.l[g] * corr + warp_sum(pv);
+        st.m[g] = mn;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) { st.ar[g][d] *= corr; st.ae[g][d] *= corr; }
+        p[g] = pv;
+    }
+}
+
+// dot products of one packed code row (held in registers as NW words) with the rotated queries
+template <int LI, int GP>
+__device__ inline void code_dot(const uint32_t *w, const float *__restrict__ lut, const float *__restrict__ qs, float (&dot)[GP]) {
+#pragma unroll
+    for (int g = 0; g < GP; ++g) dot[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < kD; ++i) {
+        int code;
+        if (LI == 0) code = (w[i >> 4] >> (2 * (i & 15))) & 3;
+        else if (LI == 1) code = ((w[i >> 4] >> (2 * (i & 15))) & 3) | (((w[8 + (i >> 5)] >> (i & 31)) & 1) << 2);
+        else if (LI == 2) code = (w[i >> 3] >> (4 * (i & 7))) & 15;
+        else code = (w[i >> 2] >> (8 * (i & 3))) & 255;
+        const float c = lut[code];
+#pragma unroll
+        for (int g4 = 0; g4 < GP / 4; ++g4) {
+            float4 qv = *reinterpret_cast<const float4 *>(qs + i * GP + 4 * g4);
+            dot[4 * g4] = fmaf(c, qv.x, dot[4 * g4]);
+            dot[4 * g4 + 1] = fmaf(c, qv.y, dot[4 * g4 + 1]);
+            dot[4 * g4 + 2] = fmaf(c, qv.z, dot[4 * g4 + 2]);
+            dot[4 * g4 + 3] = fmaf(c, qv.w, dot[4 * g4 + 3]);
+        }
+    }
+}
+
+// the four codes of coordinates 4*lane .. 4*lane+3 of a staged row
+template <int LI>
+__device__ inline void lane_codes(const uint8_t *__restrict__ row, int lane, int (&code)[4]) {
+    if (LI == 0) {
+        uint32_t b = row[lane];
+#pragma unroll
+        for (int d = 0; d < 4; ++d) code[d] = (b >> (2 * d)) & 3;
+    } else if (LI == 1) {
+        uint32_t b = row[lane], h = row[32 + (lane >> 1)] >> ((lane & 1) * 4);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) code[d] = ((b >> (2 * d)) & 3) | (((h >> d) & 1) << 2);
+    } else if (LI == 2) {
+        uint32_t b = *reinterpret_cast<const uint16_t *>(row + 2 * lane);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) code[d] = (b >> (4 * d)) & 15;
+    } else {
+        uint32_t b = *reinterpret_cast<const uint32_t *>(row + 4 * lane);
+#pragma unroll
+        for (int d = 0; d < 4; ++d) code[d] = (b >> (8 * d)) & 255;
+    }
+}
+
+// one group of up to 32 slots of a quantised bank
+template <int LI, int GP>
+__device__ inline void process_codes(WarpState<GP> &st, const odmkv_chunk &ch, int s_begin, int s_end, const float *__restrict__ lut,
+                                     const float *__restrict__ qs, uint8_t *__restrict__ stage, float scale, int lane) {
+    constexpr int NB = LI == 0 ? 32 : LI == 1 ? 48 : LI == 2 ? 64 : 128;
+    constexpr int NW = NB / 4;
+    const int s = s_begin + lane;
+    const bool valid = s < s_end;
+    float logit[GP], p[GP];
+    uint32_t w[NW];
+    if (valid) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(ch.k_codes[LI] + (size_t)s * NB);
+#pragma unroll
+        for (int v = 0; v < NW / 4; ++v) {
+            uint4 t = src[v];
+            w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+        }
+        float dot[GP];
+        code_dot<LI, GP>(w, lut, qs, dot);
+        const float kn = ch.k_norm[LI][s] * scale;
+#pragma unroll
+        for (int g = 0; g < GP; ++g) logit[g] = dot[g] * kn;
+    } else {
+#pragma unroll
+        for (int g = 0; g < GP; ++g) logit[g] = 0.f;
+    }
+    softmax_step<GP>(st, logit, valid, p);
+    // stage this group's value codes, one row per lane
+    __syncwarp();
+    if (valid) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(ch.v_codes[LI] + (size_t)s * NB);
+        uint4 *dst = reinterpret_cast<uint4 *>(stage + lane * NB);
+#pragma unroll
+        for (int v = 0; v < NW / 4; ++v) dst[v] = src[v];
+        const float vn = ch.v_norm[LI][s];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) p[g] *= vn;
+    }
+    __syncwarp();
+    const int cnt = min(32, s_end - s_begin);
+    for (int j = 0; j < cnt; ++j) {
+        int code[4];
+        lane_codes<LI>(stage + j * NB, lane, code);
+        float c[4];
+#pragma unroll
+        for (int d = 0; d < 4; ++d) c[d] = lut[code[d]];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+            for (int d = 0; d < 4; ++d) st.ar[g][d] = fmaf(pj, c[d], st.ar[g][d]);
+        }
+    }
+}
+
+// one group of up to 32 exact rows (cache dtype, not rotated); rows [r_begin, r_end) of a dense array
+template <int CDT, int GP>
+__device__ inline void process_exact(WarpState<GP> &st, const void *__restrict__ kbase, const void *__restrict__ vbase, size_t r_begin,
+                                     size_t r_end, const float *__restrict__ qx, float scale, int lane) {
+    const size_t r = r_begin + lane;
+    const bool valid = r < r_end;
+    float logit[GP], p[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) logit[g] = 0.f;
+    if (valid) {
+        for (int i4 = 0; i4 < kD / 4; ++i4) {
+            float4 kv = load4<CDT>(kbase, r * kD + 4 * i4);
+            const float kk[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+#pragma unroll
+                for (int g = 0; g < GP; ++g) logit[g] = fmaf(kk[e], qx[(4 * i4 + e) * GP + g], logit[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < GP; ++g) logit[g] *= scale;
+    }
+    softmax_step<GP>(st, logit, valid, p);
+    const int cnt = (int)min((size_t)32, r_end - r_begin);
+    for (int j = 0; j < cnt; ++j) {
+        float4 vv = load4<CDT>(vbase, (r_begin + j) * kD + 4 * lane);
+        const float c[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            float pj = __shfl_sync(0xffffffffu, p[g], j);
+#pragma unroll
+            for (int d = 0; d < 4; ++d) st.ae[g][d] = fmaf(pj, c[d], st.ae[g][d]);
+        }
+    }
+}
+
+template <int CDT, int GP>
+__global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeChunks chunks, const DecodeArgs a) {
+    __shared__ __align__(16) float qs[kD * GP];   // rotated queries, [i][g]
+    __shared__ __align__(16) float qx[kD * GP];   // plain queries, [i][g]
+    __shared__ float lut[4 * 256];
+    // the value-code staging rows and the end-of-kernel reduction buffer share storage
+    constexpr int kStageBytes = kDecWarps * 32 * 128, kRedBytes = kDecWarps * GP * 2 * kD * 4;
+    __shared__ __align__(16) uint8_t raw[kStageBytes > kRedBytes ? kStageBytes : kRedBytes];
+    uint8_t (*stage)[32 * 128] = reinterpret_cast<uint8_t (*)[32 * 128]>(raw);
+    float (*red_acc)[GP][2][kD] = reinterpret_cast<float (*)[GP][2][kD]>(raw);
+    __shared__ float red_m[kDecWarps][GP], red_l[kDecWarps][GP];
+
+    const int bh = blockIdx.y, split = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int BH = a.B * a.H, G = a.G;
+    for (int e = tid; e < kD * GP; e += kDecThreads) {
+        int i = e / GP, g = e % GP;
+        qs[e] = g < G ? a.qrot[((size_t)bh * G + g) * kD + i] : 0.f;
+        qx[e] = g < G ? a.qf[((size_t)bh * G + g) * kD + i] : 0.f;
+    }
+    for (int e = tid; e < 4 * 256; e += kDecThreads) lut[e] = a.codebooks[e];
+    __syncthreads();
+
+    WarpState<GP> st;
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+        st.m[g] = -INFINITY; st.l[g] = 0.f;
+#pragma unroll
+        for (int d = 0; d < 4; ++d) { st.ar[g][d] = 0.f; st.ae[g][d] = 0.f; }
+    }
+
+    for (int ci = 0; ci < chunks.n; ++ci) {
+        const odmkv_chunk &ch = chunks.ch[ci];
+        for (int c = 1; c <= 5; ++c) {
+            const int cnt = ch.seg_count[c * BH + bh];
+            if (cnt == 0) continue;
+            const int s0 = ch.seg_start[c * BH + bh];
+            const int ngroups = (cnt + 31) / 32;
+            const int g_lo = (int)((long long)ngroups * split / a.nsplit), g_hi = (int)((long long)ngroups * (split + 1) / a.nsplit);
+            for (int gi = g_lo + warp; gi < g_hi; gi += kDecWarps) {
+                const int sb = s0 + gi * 32, se = min(s0 + cnt, sb + 32);
+                if (c == 1) process_codes<0, GP>(st, ch, sb, se, lut, qs, stage[warp], a.scale, lane);
+                else if (c == 2) process_codes<1, GP>(st, ch, sb, se, lut + 256, qs, stage[warp], a.scale, lane);
+                else if (c == 3) process_codes<2, GP>(st, ch, sb, se, lut + 512, qs, stage[warp], a.scale, lane);
+                else if (c == 4) process_codes<3, GP>(st, ch, sb, se, lut + 768, qs, stage[warp], a.scale, lane);
+                else process_exact<CDT, GP>(st, ch.exact_k, ch.exact_v, (size_t)sb, (size_t)se, qx, a.scale, lane);
+            }
+        }
+    }
+    if (a.tail_len > 0) {
+        const int ngroups = (a.tail_len + 31) / 32;
+        const int g_lo = (int)((long long)ngroups * split / a.nsplit), g_hi = (int)((long long)ngroups * (split + 1) / a.nsplit);
+        const size_t base = (size_t)bh * a.tail_cap;
+        for (int gi = g_lo + warp; gi < g_hi; gi += kDecWarps) {
+            const size_t rb = base + (size_t)gi * 32, re = min(base + (size_t)a.tail_len, rb + 32);
+            process_exact<CDT, GP>(st, a.tail_k, a.tail_v, rb, re, qx, a.scale, lane);
+        }
+    }
+
+    // ---- combine the warps of this CTA
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GP; ++g) {
+        if (lane == 0) { red_m[warp][g] = st.m[g]; red_l[warp][g] = st.l[g]; }
+#pragma unroll
+        for (int d = 0; d < 4; ++d) {
+            red_acc[warp][g][0][4 * lane + d] = st.ar[g][d];
+            red_acc[warp][g][1][4 * lane + d] = st.ae[g][d];
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < GP * 2 * kD; e += kDecThreads) {
+        const int g = e / (2 * kD), rest = e % (2 * kD);
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, red_m[w][g]);
+        float v = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) {
+            float f = red_m[w][g] == -INFINITY ? 0.f : __expf(red_m[w][g] - mm);
+            v += (&red_acc[w][g][0][0])[rest] * f;
+            l += red_l[w][g] * f;
+        }
+        const size_t pi = ((size_t)bh * a.nsplit + split) * GP + g;
+        a.part_acc[pi * 2 * kD + rest] = v;
+        if (rest == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = l; }
+    }
+}
+
+// merge the split partials of one query head, rotate the code-space part by pi_v, normalise
+template <int ODT>
+__global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restrict__ part_ml, const float *__restrict__ part_acc,
+                                                           const float *__restrict__ pi_v, int G, int GP, int nsplit,
+                                                           void *__restrict__ out, float *__restrict__ lse) {
+    __shared__ float ar[kD];
+    __shared__ float w[64];
+    __shared__ float sh_ml[2];
+    const int r = blockIdx.x;          // bh * G + g
+    const int bh = r / G, g = r % G, j = threadIdx.x;
+    if (j < 32) {
+        float m = -INFINITY;
+        for (int s = j; s < nsplit; s += 32) m = fmaxf(m, part_ml[(((size_t)bh * nsplit + s) * GP + g) * 2]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = j; s < nsplit; s += 32) {
+            const float *p = part_ml + (((size_t)bh * nsplit + s) * GP + g) * 2;
+            float f = p[0] == -INFINITY ? 0.f : __expf(p[0] - m);
+            w[s] = f;
+            l += p[1] * f;
+        }
+        l = warp_sum(l);
+        if (j == 0) { sh_ml[0] = m; sh_ml[1] = l; }
+    }
+    __syncthreads();
+    float accr = 0.f, acce = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float *p = part_acc + (((size_t)bh * nsplit + s) * GP + g) * 2 * kD;
+        accr = fmaf(p[j], w[s], accr);
+        acce = fmaf(p[kD + j], w[s], acce);
+    }
+    ar[j] = accr;
+    __syncthreads();
+    float o = 0.f;
+#pragma unroll 8
+    for (int i = 0; i < kD; ++i) o = fmaf(ar[i], pi_v[(size_t)i * kD + j], o);
+    const float l = sh_ml[1];
+    o = l > 0.f ? (o + acce) / l : 0.f;
+    reinterpret_cast<typename Elem<ODT>::T *>(out)[(size_t)r * kD + j] = Elem<ODT>::from_f32(o);
+    if (lse && j == 0) lse[r] = l > 0.f ? sh_ml[0] + logf(l) : -INFINITY;
+}
+
+inline int round_gp(int G) { return G <= 4 ? 4 : 8; }
+
+struct DecodeWs {
+    float *qrot, *qf, *part_ml, *part_acc;
+};
+inline size_t decode_ws_layout(int B, int H, int G, int nsplit, DecodeWs *ws, unsigned char *base) {
+    const size_t BH = (size_t)B * H, GP = round_gp(G);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+    size_t o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nsplit * GP * 2 * 4),
+           o_acc = take(BH * nsplit * GP * 2 * kD * 4);
+    if (ws && base) {
+        ws->qrot = (float *)(base + o_qr); ws->qf = (float *)(base + o_qf);
+        ws->part_ml = (float *)(base + o_ml); ws->part_acc = (float *)(base + o_acc);
+    }
+    return off;
+}
+
+}  // namespace odmkv
+
+using namespace odmkv;
+
+extern "C" {
+
+int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
+    if (B <= 0 || H <= 0) return 1;
+    long long BH = (long long)B * H;
+    long long want = (4 * 148 + BH - 1) / BH;
+    long long by_len = (max_tokens_per_head + 255) / 256;
+    long long n = want < by_len ? want : by_len;
+    if (n < 1) n = 1;
+    if (n > 64) n = 64;
+    return (int)n;
+}
+
+size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits) {
+    if (B <= 0 || H <= 0 || G <= 0 || n_splits <= 0) return 0;
+    return decode_ws_layout(B, H, G, n_splits, nullptr, nullptr) + 256;
+}
+
+int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                      const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                      const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                      int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                      void *stream) {
+    if (!q || !pi_k || !pi_v || !codebooks || !out || !workspace) return ODMKV_ERR_ARG;
+    if (n_chunks < 0 || n_chunks > kMaxChunks) return ODMKV_ERR_LIMIT;
+    if (n_chunks > 0 && !chunks) return ODMKV_ERR_ARG;
+    if (B <= 0 || H <= 0 || G <= 0 || G > 8 || (long long)B * H > 65535) return ODMKV_ERR_SHAPE;
+    if (q_dtype < 0 || q_dtype > 2 || out_dtype < 0 || out_dtype > 2 || cache_dtype < 0 || cache_dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    if (tail_len < 0 || tail_len > tail_cap || (tail_len > 0 && (!tail_k || !tail_v))) return ODMKV_ERR_ARG;
+    if (n_splits <= 0 || n_splits > 64) return ODMKV_ERR_ARG;
+    if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    DecodeWs ws;
+    if (workspace_bytes < decode_ws_layout(B, H, G, n_splits, &ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
+    DecodeChunks dc;
+    dc.n = n_chunks;
+    for (int i = 0; i < n_chunks; ++i) {
+        if (chunks[i].B != B || chunks[i].H != H || !chunks[i].seg_start || !chunks[i].seg_count) return ODMKV_ERR_SHAPE;
+        dc.ch[i] = chunks[i];
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    const int BH = B * H, R = BH * G, GP = round_gp(G);
+    if (q_dtype == kF16) rotate_q_kernel<kF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    else if (q_dtype == kBF16) rotate_q_kernel<kBF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    else rotate_q_kernel<kF32><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    DecodeArgs a;
+    a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
+    a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
+    a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.scale = scale;
+    dim3 grid(n_splits, BH);
+#define ODMKV_DEC(CDT)                                                                           \
+    if (GP == 4) decode_main_kernel<CDT, 4><<<grid, kDecThreads, 0, st>>>(dc, a);                \
+    else decode_main_kernel<CDT, 8><<<grid, kDecThreads, 0, st>>>(dc, a);
+    if (cache_dtype == kF16) { ODMKV_DEC(kF16) } else if (cache_dtype == kBF16) { ODMKV_DEC(kBF16) } else { ODMKV_DEC(kF32) }
+#undef ODMKV_DEC
+    if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
+    else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
+    else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
+    return launch_status();
+}
+
+int odmkv_abi_version(void) { return ODMKV_ABI_VERSION; }
+
+const char *odmkv_status_string(int status) {
+    switch (status) {
+        case ODMKV_OK: return "ok";
+        case ODMKV_ERR_ARG: return "invalid argument (null pointer or inconsistent option)";
+        case ODMKV_ERR_SHAPE: return "invalid shape";
+        case ODMKV_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case ODMKV_ERR_UNSUPPORTED: return "unsupported dtype or bit width";
+        case ODMKV_ERR_LIMIT: return "size beyond a compiled-in limit";
+        default: return status > 0 ? cudaGetErrorString((cudaError_t)status) : "unknown status";
+    }
+}
+
+}  // extern "C"

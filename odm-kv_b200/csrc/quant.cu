@@ -1,0 +1,672 @@
+// Quantise-and-pack, dequantise and bank export kernels (sm_100a).
+//
+// Replaces the reference's routing + TurboQuantMSE path (kvquant/tq_adaptive_backend.py:350-374,
+// 149-174, 205-242; kvquant/tq_backend.py:103-145, 185-203).  The 128x128 rotation of a tile of
+// 128 tokens is an fp32 register-blocked product whose every output coordinate is one ascending
+// fused-multiply-add chain over the contraction index -- the same chain the CPU oracle uses, so
+// codes are reproducible bit for bit.
+#include "common.cuh"
+
+namespace odmkv {
+
+constexpr int kLd = 132;  // padded fp32 row stride in shared memory (conflict-free 128-bit reads)
+constexpr int kLdC = 144; // byte row stride of the staged codes
+
+// ----------------------------------------------------------------------------------------------
+// Plan: per-tile class counts, exclusive scans, segment table
+// ----------------------------------------------------------------------------------------------
+__global__ void count_tiles_kernel(const int32_t *__restrict__ bits, int T, int ntiles,
+                                   int32_t *__restrict__ tile_counts, int32_t *__restrict__ totals) {
+    const int tile = blockIdx.x, bh = blockIdx.y;
+    const int t = tile * kTile + threadIdx.x;
+    int c = -2;
+    if (t < T) c = class_of_bits(bits[(size_t)bh * T + t]);
+    __shared__ int cnt[4][kNumClasses];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+    for (int cc = 0; cc < kNumClasses; ++cc) {
+        unsigned m = __ballot_sync(0xffffffffu, c == cc);
+        if (lane == 0) cnt[warp][cc] = __popc(m);
+    }
+    unsigned bad = __ballot_sync(0xffffffffu, c == -1);
+    if (lane == 0 && bad) atomicAdd(&totals[6], __popc(bad));
+    __syncthreads();
+    if (threadIdx.x < kNumClasses) {
+        int s = cnt[0][threadIdx.x] + cnt[1][threadIdx.x] + cnt[2][threadIdx.x] + cnt[3][threadIdx.x];
+        tile_counts[((size_t)bh * ntiles + tile) * kNumClasses + threadIdx.x] = s;
+    }
+}
+
+__device__ inline int warp_incl_scan(int v, int lane) {
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+    }
+    return v;
+}
+
+// one block per (b, h); warp c scans the tiles of class c
+__global__ void scan_tiles_kernel(const int32_t *__restrict__ tile_counts, int ntiles, int BH,
+                                  int32_t *__restrict__ tile_base, int32_t *__restrict__ seg_count) {
+    const int bh = blockIdx.x, c = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < ntiles; base += 32) {
+        int tile = base + lane;
+        int v = tile < ntiles ? tile_counts[((size_t)bh * ntiles + tile) * kNumClasses + c] : 0;
+        int incl = warp_incl_scan(v, lane);
+        if (tile < ntiles) tile_base[((size_t)bh * ntiles + tile) * kNumClasses + c] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) seg_count[c * BH + bh] = carry;
+}
+
+// one block; warp c lays out the (b, h) segments of class c on 16-slot boundaries
+__global__ void scan_segs_kernel(const int32_t *__restrict__ seg_count, int BH, int32_t *__restrict__ seg_start,
+                                 int32_t *__restrict__ totals) {
+    const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int carry = 0;
+    for (int base = 0; base < BH; base += 32) {
+        int bh = base + lane;
+        int v = bh < BH ? ((seg_count[c * BH + bh] + kSegAlign - 1) / kSegAlign) * kSegAlign : 0;
+        int incl = warp_incl_scan(v, lane);
+        if (bh < BH) seg_start[c * BH + bh] = carry + incl - v;
+        carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) totals[c] = carry;
+}
+
+// ----------------------------------------------------------------------------------------------
+// Quantise kernel
+// ----------------------------------------------------------------------------------------------
+struct QuantArgs {
+    const void *K;
+    const void *V;
+    const int32_t *bits;
+    const float *pi_k;
+    const float *pi_v;
+    const float *codebooks;
+    const int32_t *tile_base;
+    odmkv_chunk ch;
+    int ntiles;
+};
+
+// 128x128x128 product: acc[a][b] = sum_i X[ty+16a][i] * P[tx+16b][i], ascending i, one FMA chain each
+__device__ inline void tile_product(const float *__restrict__ Xs, const float *__restrict__ Ps, int ty, int tx,
+                                    float (&acc)[8][8]) {
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+    const float *xrow = Xs + ty * kLd;
+    const float *prow = Ps + tx * kLd;
+#pragma unroll 1
+    for (int i4 = 0; i4 < kD / 4; ++i4) {
+        float4 xa[8], pb[8];
+#pragma unroll
+        for (int a = 0; a < 8; ++a) xa[a] = *reinterpret_cast<const float4 *>(xrow + a * 16 * kLd + 4 * i4);
+#pragma unroll
+        for (int b = 0; b < 8; ++b) pb[b] = *reinterpret_cast<const float4 *>(prow + b * 16 * kLd + 4 * i4);
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                float v = acc[a][b];
+                v = fmaf(xa[a].x, pb[b].x, v);
+                v = fmaf(xa[a].y, pb[b].y, v);
+                v = fmaf(xa[a].z, pb[b].z, v);
+                v = fmaf(xa[a].w, pb[b].w, v);
+                acc[a][b] = v;
+            }
+    }
+}
+
+// pack the staged codes of one row and store them at its slot
+__device__ inline void store_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ dst, int lane) {
+    if (li == 0 || li == 1) {
+        uint32_t b = (row[4 * lane] & 3) | ((row[4 * lane + 1] & 3) << 2) | ((row[4 * lane + 2] & 3) << 4) |
+                     ((row[4 * lane + 3] & 3) << 6);
+        dst[lane] = (uint8_t)b;
+        if (li == 1 && lane < 16) {
+            uint32_t h = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) h |= ((row[8 * lane + i] >> 2) & 1u) << i;
+            dst[32 + lane] = (uint8_t)h;
+        }
+    } else if (li == 2) {
+        uint32_t b0 = (row[4 * lane] & 15) | ((row[4 * lane + 1] & 15) << 4);
+        uint32_t b1 = (row[4 * lane + 2] & 15) | ((row[4 * lane + 3] & 15) << 4);
+        *reinterpret_cast<uint16_t *>(dst + 2 * lane) = (uint16_t)(b0 | (b1 << 8));
+    } else {
+        uint32_t w = row[4 * lane] | (row[4 * lane + 1] << 8) | (row[4 * lane + 2] << 16) | (row[4 * lane + 3] << 24);
+        *reinterpret_cast<uint32_t *>(dst + 4 * lane) = w;
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *PiK = reinterpret_cast<float *>(smem_raw);
+    float *PiV = PiK + kD * kLd;
+    float *Xs = PiV + kD * kLd;
+    float *cb = Xs + kD * kLd;        // [4][256]
+    float *nrm = cb + 4 * 256;        // [128]
+    int *cls = reinterpret_cast<int *>(nrm + kTile);  // [128]
+    int *slot = cls + kTile;          // [128]
+    int *wcnt = slot + kTile;         // [4][6]
+    int *flags = wcnt + 4 * kNumClasses;  // [1]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ty = tid >> 4, tx = tid & 15;
+    const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
+
+    for (int g = tid; g < kD * kD / 4; g += 256) {
+        int j = g >> 5, i4 = g & 31;
+        *reinterpret_cast<float4 *>(PiK + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(a.pi_k + j * kD + 4 * i4);
+        *reinterpret_cast<float4 *>(PiV + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(a.pi_v + j * kD + 4 * i4);
+    }
+    for (int g = tid; g < 4 * 256; g += 256) cb[g] = a.codebooks[g];
+    __syncthreads();
+
+    const long long n_work = (long long)BH * a.ntiles;
+    for (long long w = blockIdx.x; w < n_work; w += gridDim.x) {
+        const int bh = (int)(w / a.ntiles), tile = (int)(w % a.ntiles);
+        const int t0 = tile * kTile;
+        if (tid == 0) flags[0] = 0;
+        // ---- classes and slots
+        int c = -1, rank = 0;
+        if (tid < kTile) {
+            int t = t0 + tid;
+            if (t < T) c = class_of_bits(a.bits[(size_t)bh * T + t]);
+#pragma unroll
+            for (int cc = 0; cc < kNumClasses; ++cc) {
+                unsigned m = __ballot_sync(0xffffffffu, c == cc);
+                if (c == cc) rank = __popc(m & ((1u << lane) - 1u));
+                if (lane == 0) wcnt[warp * kNumClasses + cc] = __popc(m);
+            }
+        }
+        __syncthreads();
+        if (tid < kTile) {
+            int s = -1;
+            if (c >= 0) {
+                s = a.ch.seg_start[c * BH + bh] + a.tile_base[((size_t)bh * a.ntiles + tile) * kNumClasses + c] + rank;
+                for (int ww = 0; ww < warp; ++ww) s += wcnt[ww * kNumClasses + c];
+                if (c >= 1 && c <= 4) flags[0] = 1;
+            }
+            cls[tid] = c;
+            slot[tid] = s;
+        }
+        __syncthreads();
+        const bool any_q = flags[0] != 0;
+
+        for (int side = 0; side < 2; ++side) {
+            const void *src = side ? a.V : a.K;
+            const float *Ps = side ? PiV : PiK;
+            const size_t row0 = ((size_t)bh * T + t0) * kD;
+            if (any_q) {
+                // ---- load the tile as fp32
+                for (int g = tid; g < kTile * kD / 4; g += 256) {
+                    int r = g >> 5, i4 = g & 31;
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (t0 + r < T) v = load4<DT>(src, row0 + (size_t)r * kD + 4 * i4);
+                    *reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4) = v;
+                }
+                __syncthreads();
+                // ---- fp32 norm: one ascending FMA chain of squares, IEEE square root
+                if (tid < kTile) {
+                    float acc = 0.0f;
+                    const float *xr = Xs + tid * kLd;
+#pragma unroll 4
+                    for (int i4 = 0; i4 < kD / 4; ++i4) {
+                        float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i4);
+                        acc = fmaf(v.x, v.x, acc);
+                        acc = fmaf(v.y, v.y, acc);
+                        acc = fmaf(v.z, v.z, acc);
+                        acc = fmaf(v.w, v.w, acc);
+                    }
+                    nrm[tid] = __fsqrt_rn(acc);
+                }
+                __syncthreads();
+                // ---- x / (norm + 1e-10), IEEE division
+                for (int g = tid; g < kTile * kD / 4; g += 256) {
+                    int r = g >> 5, i4 = g & 31;
+                    float den = __fadd_rn(nrm[r], 1e-10f);
+                    float4 *p = reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4);
+                    float4 v = *p;
+                    v.x = __fdiv_rn(v.x, den);
+                    v.y = __fdiv_rn(v.y, den);
+                    v.z = __fdiv_rn(v.z, den);
+                    v.w = __fdiv_rn(v.w, den);
+                    *p = v;
+                }
+                __syncthreads();
+                float acc[8][8];
+                tile_product(Xs, Ps, ty, tx, acc);
+                __syncthreads();
+                // ---- nearest centroid, staged as bytes over the tile buffer
+                uint8_t *C8 = reinterpret_cast<uint8_t *>(Xs);
+#pragma unroll
+                for (int aa = 0; aa < 8; ++aa) {
+                    int r = ty + 16 * aa;
+                    int cc = cls[r];
+                    if (cc >= 1 && cc <= 4) {
+                        int li = cc - 1;
+                        const float *cbl = cb + li * 256;
+                        int k = 1 << bits_of_qlevel(li);
+#pragma unroll
+                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_centroid(acc[aa][bb], cbl, k);
+                    }
+                }
+                __syncthreads();
+            }
+            // ---- pack and store: one warp per row
+            const uint8_t *C8 = reinterpret_cast<const uint8_t *>(Xs);
+            for (int r = warp; r < kTile; r += 8) {
+                int cc = cls[r];
+                int s = slot[r];
+                if (cc < 0) continue;
+                int t_abs = a.ch.t_offset + t0 + r;
+                if (cc >= 1 && cc <= 4) {
+                    int li = cc - 1;
+                    uint8_t *dst = (side ? a.ch.v_codes[li] : a.ch.k_codes[li]) + (size_t)s * code_bytes(li);
+                    store_codes(C8 + r * kLdC, li, dst, lane);
+                    if (lane == 0) {
+                        (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
+                        if (side == 0) a.ch.pos[li][s] = t_abs;
+                    }
+                } else if (cc == 5) {
+                    const unsigned char *srow = reinterpret_cast<const unsigned char *>(src) + (row0 + (size_t)r * kD) * sizeof(typename Elem<DT>::T);
+                    unsigned char *drow = reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + (size_t)s * kD * sizeof(typename Elem<DT>::T);
+                    if constexpr (DT == kF32) {
+                        reinterpret_cast<uint4 *>(drow)[lane] = reinterpret_cast<const uint4 *>(srow)[lane];
+                    } else {
+                        reinterpret_cast<uint2 *>(drow)[lane] = reinterpret_cast<const uint2 *>(srow)[lane];
+                    }
+                    if (lane == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
+                } else if (cc == 0 && side == 0 && lane == 0) {
+                    a.ch.evicted_pos[s] = t_abs;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// zero the padding slots between a segment's last token and the next 16-slot boundary
+template <int DT>
+__global__ void fill_padding_kernel(const odmkv_chunk ch) {
+    const int BH = ch.B * ch.H;
+    const int bh = blockIdx.x, c = blockIdx.y;
+    const int cnt = ch.seg_count[c * BH + bh];
+    const int start = ch.seg_start[c * BH + bh];
+    const int pad_end = ((cnt + kSegAlign - 1) / kSegAlign) * kSegAlign;
+    for (int k = cnt + (threadIdx.x >> 5); k < pad_end; k += blockDim.x >> 5) {
+        const int s = start + k, lane = threadIdx.x & 31;
+        if (c == 0) {
+            if (lane == 0) ch.evicted_pos[s] = -1;
+        } else if (c == 5) {
+            using T = typename Elem<DT>::T;
+            T *kr = reinterpret_cast<T *>(ch.exact_k) + (size_t)s * kD;
+            T *vr = reinterpret_cast<T *>(ch.exact_v) + (size_t)s * kD;
+            for (int i = lane; i < kD; i += 32) {
+                kr[i] = Elem<DT>::from_f32(0.f);
+                vr[i] = Elem<DT>::from_f32(0.f);
+            }
+            if (lane == 0) ch.exact_pos[s] = -1;
+        } else {
+            const int li = c - 1, nb = code_bytes(li);
+            for (int i = lane; i < nb; i += 32) {
+                ch.k_codes[li][(size_t)s * nb + i] = 0;
+                ch.v_codes[li][(size_t)s * nb + i] = 0;
+            }
+            if (lane == 0) {
+                ch.k_norm[li][s] = 0.f;
+                ch.v_norm[li][s] = 0.f;
+                ch.pos[li][s] = -1;
+            }
+        }
+    }
+}
+
+// nearest centroid + pack of given rotated coordinates; one warp per row
+__global__ void encode_pack_kernel(const float *__restrict__ y, long long n, int li, const float *__restrict__ codebook,
+                                   uint8_t *__restrict__ out) {
+    __shared__ float cb[256];
+    __shared__ uint8_t stage[8][kD];
+    const int k = 1 << bits_of_qlevel(li);
+    for (int i = threadIdx.x; i < k; i += blockDim.x) cb[i] = codebook[i];
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (long long r = (long long)blockIdx.x * 8 + warp; r < n; r += (long long)gridDim.x * 8) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) stage[warp][lane + 32 * q] = (uint8_t)nearest_centroid(y[r * kD + lane + 32 * q], cb, k);
+        __syncwarp();
+        store_codes(stage[warp], li, out + (size_t)r * code_bytes(li), lane);
+        __syncwarp();
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Dequantise
+// ----------------------------------------------------------------------------------------------
+struct DequantArgs {
+    odmkv_chunk ch;
+    const float *pi_k;
+    const float *pi_v;
+    const float *codebooks;
+    void *K_out;
+    void *V_out;
+    int T_dense;
+    int tiles_before[5];  // prefix of tile counts per quantised level
+};
+
+__device__ inline int bank_end(const odmkv_chunk &ch, int c) {
+    const int BH = ch.B * ch.H;
+    int cnt = ch.seg_count[c * BH + BH - 1];
+    return ch.seg_start[c * BH + BH - 1] + ((cnt + kSegAlign - 1) / kSegAlign) * kSegAlign;
+}
+
+// largest bh with seg_start[bh] <= s
+__device__ inline int find_segment(const int32_t *__restrict__ seg_start, int BH, int s) {
+    int lo = 0, hi = BH;
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (seg_start[mid] <= s) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <int ODT>
+__global__ void __launch_bounds__(256, 1) dequant_kernel(const DequantArgs a) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    float *PkT = reinterpret_cast<float *>(smem_raw);  // PkT[j][i] = pi_k[i][j]
+    float *PvT = PkT + kD * kLd;
+    float *Xs = PvT + kD * kLd;
+    float *cb = Xs + kD * kLd;
+    float *nrm = cb + 4 * 256;
+    long long *dst_row = reinterpret_cast<long long *>(nrm + kTile);  // [128] dense row index or -1
+
+    const int tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;
+    const int BH = a.ch.B * a.ch.H;
+    for (int g = tid; g < kD * kD; g += 256) {
+        int i = g >> 7, j = g & 127;
+        PkT[j * kLd + i] = a.pi_k[g];
+        PvT[j * kLd + i] = a.pi_v[g];
+    }
+    for (int g = tid; g < 4 * 256; g += 256) cb[g] = a.codebooks[g];
+    __syncthreads();
+
+    const int n_work = a.tiles_before[4];
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x) {
+        int li = 0;
+        while (li < 3 && w >= a.tiles_before[li + 1]) ++li;
+        const int c = li + 1;
+        const int s0 = (w - a.tiles_before[li]) * kTile;
+        const int end = bank_end(a.ch, c);
+        if (s0 >= end) continue;  // uniform across the block
+        const int nb = code_bytes(li);
+        if (tid < kTile) {
+            int s = s0 + tid;
+            long long row = -1;
+            if (s < end) {
+                int t = a.ch.pos[li][s];
+                if (t >= 0) {
+                    int bh = find_segment(a.ch.seg_start + c * BH, BH, s);
+                    row = (long long)bh * a.T_dense + t;
+                }
+            }
+            dst_row[tid] = row;
+        }
+        for (int side = 0; side < 2; ++side) {
+            const uint8_t *codes = side ? a.ch.v_codes[li] : a.ch.k_codes[li];
+            const float *norms = side ? a.ch.v_norm[li] : a.ch.k_norm[li];
+            const float *Ps = side ? PvT : PkT;
+            __syncthreads();
+            {   // centroid gather: two threads per row
+                int r = tid >> 1, half = tid & 1, s = s0 + r;
+                bool ok = s < end;
+                const uint8_t *row = codes + (size_t)(ok ? s : 0) * nb;
+                const float *cbl = cb + li * 256;
+                for (int i = half * 64; i < half * 64 + 64; ++i) Xs[r * kLd + i] = ok ? cbl[extract_code(row, li, i)] : 0.f;
+                if (half == 0) nrm[r] = ok ? norms[s] : 0.f;
+            }
+            __syncthreads();
+            float acc[8][8];
+            tile_product(Xs, Ps, ty, tx, acc);
+            __syncthreads();
+#pragma unroll
+            for (int aa = 0; aa < 8; ++aa) {
+                int r = ty + 16 * aa;
+                float nn = nrm[r];
+#pragma unroll
+                for (int bb = 0; bb < 8; ++bb) Xs[r * kLd + tx + 16 * bb] = __fmul_rn(acc[aa][bb], nn);
+            }
+            __syncthreads();
+            void *out = side ? a.V_out : a.K_out;
+            for (int g = tid; g < kTile * kD / 4; g += 256) {
+                int r = g >> 5, i4 = g & 31;
+                long long row = dst_row[r];
+                if (row >= 0) store4<ODT>(out, (size_t)row * kD + 4 * i4, *reinterpret_cast<const float4 *>(Xs + r * kLd + 4 * i4));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// scatter the exact bank into the dense tensors; one warp per slot
+template <int IDT, int ODT>
+__global__ void scatter_exact_kernel(const odmkv_chunk ch, void *K_out, void *V_out, int T_dense) {
+    const int BH = ch.B * ch.H;
+    const int end = bank_end(ch, 5);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int s = blockIdx.x * (blockDim.x >> 5) + warp; s < end; s += gridDim.x * (blockDim.x >> 5)) {
+        int t = ch.exact_pos[s];
+        if (t < 0) continue;
+        int bh = find_segment(ch.seg_start + 5 * BH, BH, s);
+        size_t dst = ((size_t)bh * T_dense + t) * kD + 4 * lane;
+        store4<ODT>(K_out, dst, load4<IDT>(ch.exact_k, (size_t)s * kD + 4 * lane));
+        store4<ODT>(V_out, dst, load4<IDT>(ch.exact_v, (size_t)s * kD + 4 * lane));
+    }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Export to the reference bank layout
+// ----------------------------------------------------------------------------------------------
+__global__ void export_bank_kernel(const odmkv_chunk ch, int c, const int32_t *__restrict__ row_start,
+                                   uint8_t *__restrict__ ik, uint8_t *__restrict__ iv, float *__restrict__ nk,
+                                   float *__restrict__ nv, int64_t *__restrict__ positions) {
+    const int BH = ch.B * ch.H, bh = blockIdx.x, li = c - 1;
+    const int cnt = ch.seg_count[c * BH + bh], s0 = ch.seg_start[c * BH + bh], r0 = row_start[bh];
+    const int nb = code_bytes(li), rb = ref_code_bytes(li);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = warp; k < cnt; k += blockDim.x >> 5) {
+        const size_t s = (size_t)s0 + k, r = (size_t)r0 + k;
+        for (int side = 0; side < 2; ++side) {
+            const uint8_t *src = (side ? ch.v_codes[li] : ch.k_codes[li]) + s * nb;
+            uint8_t *dst = (side ? iv : ik) + r * rb;
+            if (li == 1) {
+                for (int j = lane; j < 64; j += 32) {
+                    int c0 = extract_code(src, 1, 2 * j), c1 = extract_code(src, 1, 2 * j + 1);
+                    dst[j] = (uint8_t)(c0 | (c1 << 4));
+                }
+            } else {
+                for (int j = lane; j < nb; j += 32) dst[j] = src[j];
+            }
+        }
+        if (lane == 0) {
+            nk[r] = ch.k_norm[li][s];
+            nv[r] = ch.v_norm[li][s];
+            positions[3 * r + 0] = bh / ch.H;
+            positions[3 * r + 1] = bh % ch.H;
+            positions[3 * r + 2] = ch.pos[li][s];
+        }
+    }
+}
+
+__global__ void export_positions_kernel(const odmkv_chunk ch, int c, const int32_t *__restrict__ row_start,
+                                        int64_t *__restrict__ positions) {
+    const int BH = ch.B * ch.H, bh = blockIdx.x;
+    const int cnt = ch.seg_count[c * BH + bh], s0 = ch.seg_start[c * BH + bh], r0 = row_start[bh];
+    const int32_t *pos = c == 0 ? ch.evicted_pos : ch.exact_pos;
+    for (int k = threadIdx.x; k < cnt; k += blockDim.x) {
+        size_t r = (size_t)r0 + k;
+        positions[3 * r + 0] = bh / ch.H;
+        positions[3 * r + 1] = bh % ch.H;
+        positions[3 * r + 2] = pos[s0 + k];
+    }
+}
+
+static int num_sms() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+constexpr size_t kQuantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + (2 * kTile + 4 * kNumClasses + 4) * sizeof(int);
+constexpr size_t kDequantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + kTile * sizeof(long long);
+
+}  // namespace odmkv
+
+using namespace odmkv;
+
+extern "C" {
+
+size_t odmkv_pack_plan_workspace_bytes(int B, int H, int T) {
+    if (B <= 0 || H <= 0 || T <= 0) return 0;
+    size_t ntiles = ((size_t)T + kTile - 1) / kTile;
+    return 2 * (size_t)B * H * ntiles * kNumClasses * sizeof(int32_t);
+}
+
+int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start, int32_t *seg_count,
+                    int32_t *totals, void *plan_workspace, size_t plan_workspace_bytes, void *stream) {
+    if (!bits || !seg_start || !seg_count || !totals || !plan_workspace) return ODMKV_ERR_ARG;
+    if (B <= 0 || H <= 0 || T <= 0 || (long long)B * H > 65535) return ODMKV_ERR_SHAPE;
+    if (plan_workspace_bytes < odmkv_pack_plan_workspace_bytes(B, H, T)) return ODMKV_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int BH = B * H, ntiles = (T + kTile - 1) / kTile;
+    int32_t *tile_counts = (int32_t *)plan_workspace;
+    int32_t *tile_base = tile_counts + (size_t)BH * ntiles * kNumClasses;
+    cudaMemsetAsync(totals, 0, 8 * sizeof(int32_t), st);
+    count_tiles_kernel<<<dim3(ntiles, BH), kTile, 0, st>>>(bits, T, ntiles, tile_counts, totals);
+    scan_tiles_kernel<<<BH, 32 * kNumClasses, 0, st>>>(tile_counts, ntiles, BH, tile_base, seg_count);
+    scan_segs_kernel<<<1, 32 * kNumClasses, 0, st>>>(seg_count, BH, seg_start, totals);
+    return launch_status();
+}
+
+static int check_chunk(const odmkv_chunk *ch) {
+    if (!ch || !ch->seg_start || !ch->seg_count) return ODMKV_ERR_ARG;
+    if (ch->B <= 0 || ch->H <= 0 || ch->T < 0 || (long long)ch->B * ch->H > 65535) return ODMKV_ERR_SHAPE;
+    for (int li = 0; li < ODMKV_NUM_QLEVELS; ++li)
+        if (ch->cap[li + 1] > 0 && (!ch->k_codes[li] || !ch->v_codes[li] || !ch->k_norm[li] || !ch->v_norm[li] || !ch->pos[li]))
+            return ODMKV_ERR_ARG;
+    if (ch->cap[5] > 0 && (!ch->exact_k || !ch->exact_v || !ch->exact_pos)) return ODMKV_ERR_ARG;
+    if (ch->cap[0] > 0 && !ch->evicted_pos) return ODMKV_ERR_ARG;
+    return ODMKV_OK;
+}
+
+int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
+                        const float *pi_v, const float *codebooks, const odmkv_chunk *chunk,
+                        const void *plan_workspace, void *stream) {
+    if (!K || !V || !bits || !pi_k || !pi_v || !codebooks || !plan_workspace) return ODMKV_ERR_ARG;
+    int rc = check_chunk(chunk);
+    if (rc) return rc;
+    if (chunk->T <= 0) return ODMKV_ERR_SHAPE;
+    if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    QuantArgs a;
+    a.K = K; a.V = V; a.bits = bits; a.pi_k = pi_k; a.pi_v = pi_v; a.codebooks = codebooks;
+    a.ch = *chunk;
+    const int BH = chunk->B * chunk->H;
+    a.ntiles = (chunk->T + kTile - 1) / kTile;
+    a.tile_base = (const int32_t *)plan_workspace + (size_t)BH * a.ntiles * kNumClasses;
+    long long n_work = (long long)BH * a.ntiles;
+    int grid = (int)(n_work < num_sms() ? n_work : num_sms());
+    dim3 pad_grid(BH, kNumClasses);
+    cudaError_t e;
+#define ODMKV_LAUNCH_Q(DT)                                                                                   \
+    e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantSmem); \
+    if (e != cudaSuccess) return (int)e;                                                                     \
+    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk);                                               \
+    quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);
+    if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
+#undef ODMKV_LAUNCH_Q
+    return launch_status();
+}
+
+int odmkv_encode_pack(const float *y, long long n, int bits, const float *codebook, uint8_t *out, void *stream) {
+    if (!y || !codebook || !out) return ODMKV_ERR_ARG;
+    int c = class_of_bits(bits);
+    if (c < 1 || c > 4) return ODMKV_ERR_UNSUPPORTED;
+    if (n <= 0) return n == 0 ? ODMKV_OK : ODMKV_ERR_SHAPE;
+    long long blocks = (n + 7) / 8;
+    int grid = (int)(blocks < 4 * num_sms() ? blocks : 4 * num_sms());
+    encode_pack_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(y, n, c - 1, codebook, out);
+    return launch_status();
+}
+
+int odmkv_dequant_chunk(const odmkv_chunk *chunk, int in_dtype, const float *pi_k, const float *pi_v,
+                        const float *codebooks, void *K_out, void *V_out, int out_dtype, int T_dense,
+                        int include_exact, void *stream) {
+    if (!pi_k || !pi_v || !codebooks || !K_out || !V_out) return ODMKV_ERR_ARG;
+    int rc = check_chunk(chunk);
+    if (rc) return rc;
+    if (in_dtype < 0 || in_dtype > 2 || out_dtype < 0 || out_dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    if (T_dense <= 0) return ODMKV_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    DequantArgs a;
+    a.ch = *chunk; a.pi_k = pi_k; a.pi_v = pi_v; a.codebooks = codebooks; a.K_out = K_out; a.V_out = V_out; a.T_dense = T_dense;
+    a.tiles_before[0] = 0;
+    for (int li = 0; li < 4; ++li) a.tiles_before[li + 1] = a.tiles_before[li] + (chunk->cap[li + 1] + kTile - 1) / kTile;
+    cudaError_t e;
+    if (a.tiles_before[4] > 0) {
+        int grid = a.tiles_before[4] < num_sms() ? a.tiles_before[4] : num_sms();
+#define ODMKV_LAUNCH_D(ODT)                                                                                      \
+    e = cudaFuncSetAttribute(dequant_kernel<ODT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDequantSmem); \
+    if (e != cudaSuccess) return (int)e;                                                                         \
+    dequant_kernel<ODT><<<grid, 256, kDequantSmem, st>>>(a);
+        if (out_dtype == kF16) { ODMKV_LAUNCH_D(kF16) } else if (out_dtype == kBF16) { ODMKV_LAUNCH_D(kBF16) } else { ODMKV_LAUNCH_D(kF32) }
+#undef ODMKV_LAUNCH_D
+    }
+    if (include_exact && chunk->cap[5] > 0) {
+        int grid = (chunk->cap[5] + 7) / 8;
+        if (grid > 8 * num_sms()) grid = 8 * num_sms();
+#define ODMKV_LAUNCH_E(IDT, ODT) scatter_exact_kernel<IDT, ODT><<<grid, 256, 0, st>>>(*chunk, K_out, V_out, T_dense);
+        if (in_dtype == kF16) {
+            if (out_dtype == kF16) { ODMKV_LAUNCH_E(kF16, kF16) } else if (out_dtype == kBF16) { ODMKV_LAUNCH_E(kF16, kBF16) } else { ODMKV_LAUNCH_E(kF16, kF32) }
+        } else if (in_dtype == kBF16) {
+            if (out_dtype == kF16) { ODMKV_LAUNCH_E(kBF16, kF16) } else if (out_dtype == kBF16) { ODMKV_LAUNCH_E(kBF16, kBF16) } else { ODMKV_LAUNCH_E(kBF16, kF32) }
+        } else {
+            if (out_dtype == kF16) { ODMKV_LAUNCH_E(kF32, kF16) } else if (out_dtype == kBF16) { ODMKV_LAUNCH_E(kF32, kBF16) } else { ODMKV_LAUNCH_E(kF32, kF32) }
+        }
+#undef ODMKV_LAUNCH_E
+    }
+    return launch_status();
+}
+
+int odmkv_export_bank(const odmkv_chunk *chunk, int class_idx, const int32_t *row_start, uint8_t *indices_k,
+                      uint8_t *indices_v, float *norms_k, float *norms_v, int64_t *positions, void *stream) {
+    int rc = check_chunk(chunk);
+    if (rc) return rc;
+    if (class_idx < 1 || class_idx > 4) return ODMKV_ERR_ARG;
+    if (!row_start || !indices_k || !indices_v || !norms_k || !norms_v || !positions) return ODMKV_ERR_ARG;
+    export_bank_kernel<<<chunk->B * chunk->H, 256, 0, (cudaStream_t)stream>>>(*chunk, class_idx, row_start, indices_k, indices_v,
+                                                                            norms_k, norms_v, positions);
+    return launch_status();
+}
+
+int odmkv_export_positions(const odmkv_chunk *chunk, int class_idx, const int32_t *row_start, int64_t *positions,
+                           void *stream) {
+    int rc = check_chunk(chunk);
+    if (rc) return rc;
+    if ((class_idx != 0 && class_idx != 5) || !row_start || !positions) return ODMKV_ERR_ARG;
+    export_positions_kernel<<<chunk->B * chunk->H, 256, 0, (cudaStream_t)stream>>>(*chunk, class_idx, row_start, positions);
+    return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,427 @@
+// Risk scorer kernels (sm_100a).
+//
+// Replaces RiskScorer.score_prefill / score_with_attn (kvquant/scorer.py:385-416) and the
+// mean-query attention of _expected_core_internals (kvquant/scorer.py:302-315).  Three streaming
+// sweeps per (sample, KV head), each split over several CTAs:
+//   1. K only:  logits of the G mean queries, |k|^2, per-split softmax statistics;
+//   2. V:       p = mean_g softmax_g, |v|^2, partial sums of p v (for o) and of p;
+//   3. V again: |v - o|^2 and the score; per-sample maximum for the sink slots.
+// A quad of lanes owns one token (32 coordinates per lane), so every 16-byte load of a row is
+// fully used and each reduction takes two shuffles.
+#include "common.cuh"
+
+namespace odmkv {
+
+constexpr int kScoreThreads = 256;
+constexpr int kTokPerIter = kScoreThreads / 4;  // tokens per CTA iteration
+constexpr int kMaxG = 16;
+
+struct ScoreWs {
+    float *logits;    // [BH, G, Tc]
+    float *pbar;      // [BH, Tc]
+    float *kn2;       // [BH, Tc]
+    float *vn2;       // [BH, Tc]
+    float *part_ml;   // [BH, nsplit, G, 2]
+    float *part_o;    // [BH, nsplit, 128]
+    float *part_ps;   // [BH, nsplit]
+    unsigned *smax;   // [B]
+};
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+inline int score_splits(int BH, int Tc) {
+    int want = (4 * 148 + BH - 1) / BH;
+    int by_len = (Tc + 511) / 512;
+    int n = want < by_len ? want : by_len;
+    if (n < 1) n = 1;
+    if (n > 64) n = 64;
+    return n;
+}
+
+inline size_t score_ws_layout(int B, int H, int G, int T, int n_sink, ScoreWs *ws, unsigned char *base) {
+    const size_t BH = (size_t)B * H, Tc = (size_t)(T > n_sink ? T - n_sink : 0);
+    const int ns = score_splits((int)BH, (int)Tc);
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    size_t o_logits = take(BH * G * Tc * 4), o_pbar = take(BH * Tc * 4), o_kn2 = take(BH * Tc * 4), o_vn2 = take(BH * Tc * 4);
+    size_t o_ml = take(BH * ns * G * 2 * 4), o_po = take(BH * ns * kD * 4), o_ps = take(BH * ns * 4), o_sm = take((size_t)B * 4);
+    if (ws && base) {
+        ws->logits = (float *)(base + o_logits); ws->pbar = (float *)(base + o_pbar); ws->kn2 = (float *)(base + o_kn2);
+        ws->vn2 = (float *)(base + o_vn2); ws->part_ml = (float *)(base + o_ml); ws->part_o = (float *)(base + o_po);
+        ws->part_ps = (float *)(base + o_ps); ws->smax = (unsigned *)(base + o_sm);
+    }
+    return off;
+}
+
+// load this lane's 32 coordinates of one row (quad lane q covers [32q, 32q+32))
+template <int DT>
+__device__ inline void load_row32(const void *base, size_t row, int q, float (&x)[32]) {
+#pragma unroll
+    for (int v = 0; v < 8; ++v) {
+        float4 f = load4<DT>(base, row * kD + 32 * q + 4 * v);
+        x[4 * v] = f.x; x[4 * v + 1] = f.y; x[4 * v + 2] = f.z; x[4 * v + 3] = f.w;
+    }
+}
+
+__device__ inline float quad_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    return v;
+}
+
+// ---- sweep 1 ---------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kScoreThreads) score_logits_kernel(const void *__restrict__ K, const float *__restrict__ mu,
+                                                                      int H, int G, int T, int n_sink, int nsplit, ScoreWs ws) {
+    __shared__ __align__(16) float mus[kMaxG * kD];
+    __shared__ float red_m[kTokPerIter], red_l[kTokPerIter];
+    const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
+    const int Tc = T - n_sink;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2;
+    const float inv_sqrt_d = 1.0f / sqrtf((float)kD);
+    for (int i = tid; i < G * kD; i += kScoreThreads) mus[i] = mu[((size_t)b * H * G + (size_t)(bh % H) * G) * kD + i];
+    __syncthreads();
+    const int per = (Tc + nsplit - 1) / nsplit;
+    const int j0 = split * per, j1 = min(Tc, j0 + per);
+    float m_run[kMaxG], l_run[kMaxG];
+#pragma unroll
+    for (int g = 0; g < kMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; }
+    // every lane of a warp runs the same number of iterations: the quad reductions below are
+    // full-warp shuffles and must not be reached by a partial warp
+    for (int jb = j0; jb < j1; jb += kTokPerIter) {
+        const int j = jb + quad;
+        const bool live = j < j1;
+        float x[32];
+        if (live) load_row32<DT>(K, (size_t)bh * T + n_sink + j, q, x);
+        else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        float kk = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) kk = fmaf(x[i], x[i], kk);
+        kk = quad_sum(kk);
+        if (q == 0 && live) ws.kn2[(size_t)bh * Tc + j] = kk;
+#pragma unroll
+        for (int g = 0; g < kMaxG; ++g) {
+            if (g < G) {
+                const float4 *mg = reinterpret_cast<const float4 *>(mus + g * kD + 32 * q);
+                float acc = 0.f;
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    float4 m4 = mg[v];
+                    acc = fmaf(x[4 * v], m4.x, acc);
+                    acc = fmaf(x[4 * v + 1], m4.y, acc);
+                    acc = fmaf(x[4 * v + 2], m4.z, acc);
+                    acc = fmaf(x[4 * v + 3], m4.w, acc);
+                }
+                acc = quad_sum(acc) * inv_sqrt_d;
+                if (q == 0 && live) {
+                    ws.logits[((size_t)bh * G + g) * Tc + j] = acc;
+                    float mn = fmaxf(m_run[g], acc);
+                    l_run[g] = l_run[g] * expf(m_run[g] - mn) + expf(acc - mn);
+                    m_run[g] = mn;
+                }
+            }
+        }
+    }
+    // block merge of the per-quad (m, l) pairs, one head at a time
+    for (int g = 0; g < G; ++g) {
+        __syncthreads();
+        if (q == 0) { red_m[quad] = m_run[g]; red_l[quad] = l_run[g]; }
+        __syncthreads();
+        if (tid < 32) {
+            float m = fmaxf(red_m[tid], red_m[tid + 32]);
+            float mm = warp_max(m);
+            float l = 0.f;
+            if (mm > -INFINITY) l = red_l[tid] * expf(red_m[tid] - mm) + red_l[tid + 32] * expf(red_m[tid + 32] - mm);
+            l = warp_sum(l);
+            if (tid == 0) {
+                float *dst = ws.part_ml + (((size_t)bh * nsplit + split) * G + g) * 2;
+                dst[0] = mm; dst[1] = l;
+            }
+        }
+    }
+}
+
+// merge the split statistics of one (b, h): final max and denominator per query head
+__device__ inline void merge_ml(const float *__restrict__ part_ml, int bh, int nsplit, int G, float *M, float *L) {
+    // called by threads g < G
+    const int g = threadIdx.x;
+    float m = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) m = fmaxf(m, part_ml[(((size_t)bh * nsplit + s) * G + g) * 2]);
+    float l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float *p = part_ml + (((size_t)bh * nsplit + s) * G + g) * 2;
+        if (p[1] > 0.f) l += p[1] * expf(p[0] - m);
+    }
+    M[g] = m; L[g] = l;
+}
+
+// ---- sweep 2 ---------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kScoreThreads) score_pv_kernel(const void *__restrict__ V, int H, int G, int T, int n_sink,
+                                                                  int nsplit, ScoreWs ws) {
+    __shared__ float M[kMaxG], L[kMaxG];
+    __shared__ float osum[kTokPerIter / 8][kD];  // one row per warp
+    __shared__ float psum[kTokPerIter / 8];
+    const int bh = blockIdx.y, split = blockIdx.x;
+    const int Tc = T - n_sink;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2, warp = tid >> 5, lane = tid & 31;
+    if (tid < G) merge_ml(ws.part_ml, bh, nsplit, G, M, L);
+    __syncthreads();
+    const int per = (Tc + nsplit - 1) / nsplit;
+    const int j0 = split * per, j1 = min(Tc, j0 + per);
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    float ps = 0.f;
+    const float inv_g = 1.0f / (float)G;
+    for (int jb = j0; jb < j1; jb += kTokPerIter) {
+        const int j = jb + quad;
+        const bool live = j < j1;
+        float x[32];
+        float p = 0.f;
+        if (live) {
+            load_row32<DT>(V, (size_t)bh * T + n_sink + j, q, x);
+            for (int g = 0; g < G; ++g) p += expf(ws.logits[((size_t)bh * G + g) * Tc + j] - M[g]) / L[g];
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        p *= inv_g;
+        float vv = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { vv = fmaf(x[i], x[i], vv); o[i] = fmaf(p, x[i], o[i]); }
+        vv = quad_sum(vv);
+        if (q == 0 && live) {
+            ws.pbar[(size_t)bh * Tc + j] = p;
+            ws.vn2[(size_t)bh * Tc + j] = vv;
+            ps += p;
+        }
+    }
+    // reduce over the 8 quads of a warp (lanes with equal q), then over warps through shared memory
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float v = o[i];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        o[i] = v;
+    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+    if (lane < 4) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) osum[warp][32 * lane + i] = o[i];
+        if (lane == 0) psum[warp] = ps;
+    }
+    __syncthreads();
+    if (tid < kD) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < kTokPerIter / 8; ++w) v += osum[w][tid];
+        ws.part_o[((size_t)bh * nsplit + split) * kD + tid] = v;
+    }
+    if (tid == 0) {
+        float v = 0.f;
+        for (int w = 0; w < kTokPerIter / 8; ++w) v += psum[w];
+        ws.part_ps[(size_t)bh * nsplit + split] = v;
+    }
+}
+
+// ---- sweep 3 ---------------------------------------------------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kScoreThreads) score_final_kernel(const void *__restrict__ V, int H, int T, int n_sink,
+                                                                     int nsplit, float eps, ScoreWs ws, float *__restrict__ scores) {
+    __shared__ __align__(16) float ob[kD];
+    __shared__ float wmax[kScoreThreads / 32];
+    const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
+    const int Tc = T - n_sink;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2, warp = tid >> 5, lane = tid & 31;
+    if (tid < kD) {
+        float v = 0.f, ps = 0.f;
+        for (int s = 0; s < nsplit; ++s) {
+            v += ws.part_o[((size_t)bh * nsplit + s) * kD + tid];
+            ps += ws.part_ps[(size_t)bh * nsplit + s];
+        }
+        ob[tid] = v / fmaxf(ps, 1e-8f);
+    }
+    __syncthreads();
+    float oq[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) oq[i] = ob[32 * q + i];
+    const int per = (Tc + nsplit - 1) / nsplit;
+    const int j0 = split * per, j1 = min(Tc, j0 + per);
+    float best = 0.f;
+    for (int jb = j0; jb < j1; jb += kTokPerIter) {
+        const int j = jb + quad;
+        const bool live = j < j1;
+        float x[32];
+        if (live) load_row32<DT>(V, (size_t)bh * T + n_sink + j, q, x);
+        else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        }
+        float ir = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { float dlt = x[i] - oq[i]; ir = fmaf(dlt, dlt, ir); }
+        ir = quad_sum(ir);
+        if (q == 0 && live) {
+            size_t e = (size_t)bh * Tc + j;
+            float p = ws.pbar[e] + eps;
+            float s = p * p * (ws.vn2[e] + (ws.kn2[e] / (float)kD) * ir);
+            scores[(size_t)bh * T + n_sink + j] = s;
+            best = fmaxf(best, s);  // NaN-free inputs assumed; scores are non-negative
+        }
+    }
+    best = warp_max(best);
+    if (lane == 0) wmax[warp] = best;
+    __syncthreads();
+    if (tid == 0) {
+        float v = wmax[0];
+        for (int w = 1; w < kScoreThreads / 32; ++w) v = fmaxf(v, wmax[w]);
+        atomicMax(ws.smax + b, __float_as_uint(v));  // order-preserving for non-negative floats
+    }
+}
+
+__global__ void score_sinks_kernel(float *__restrict__ scores, const unsigned *__restrict__ smax, int H, int T, int n_sink) {
+    const int bh = blockIdx.x;
+    if ((int)threadIdx.x < n_sink) scores[(size_t)bh * T + threadIdx.x] = __uint_as_float(smax[bh / H]);
+}
+
+__global__ void fill_ones_kernel(float *__restrict__ p, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = 1.0f;
+}
+
+// ---- score_with_attn: one CTA per row of T <= 1024 tokens ---------------------------------------
+template <int DT>
+__global__ void __launch_bounds__(kScoreThreads) score_with_attn_kernel(const void *__restrict__ K, const void *__restrict__ V,
+                                                                         const float *__restrict__ p, int T, float eps,
+                                                                         float *__restrict__ scores) {
+    __shared__ float osum[kScoreThreads / 32][kD];
+    __shared__ float psum[kScoreThreads / 32];
+    __shared__ __align__(16) float ob[kD];
+    const int row = blockIdx.x;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2, warp = tid >> 5, lane = tid & 31;
+    float o[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    float ps = 0.f;
+    for (int j = quad; j < T; j += kTokPerIter) {
+        float x[32];
+        load_row32<DT>(V, (size_t)row * T + j, q, x);
+        float pj = p[(size_t)row * T + j];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] = fmaf(pj, x[i], o[i]);
+        if (q == 0) ps += pj;
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        float v = o[i];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        o[i] = v;
+    }
+    ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 8);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 16);
+    if (lane < 4) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) osum[warp][32 * lane + i] = o[i];
+        if (lane == 0) psum[warp] = ps;
+    }
+    __syncthreads();
+    if (tid < kD) {
+        float v = 0.f, s = 0.f;
+        for (int w = 0; w < kScoreThreads / 32; ++w) { v += osum[w][tid]; s += psum[w]; }
+        ob[tid] = v / fmaxf(s, 1e-8f);
+    }
+    __syncthreads();
+    float oq[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) oq[i] = ob[32 * q + i];
+    for (int jb = 0; jb < T; jb += kTokPerIter) {
+        const int j = jb + quad;
+        const bool live = j < T;
+        float x[32], y[32];
+        if (live) {
+            load_row32<DT>(V, (size_t)row * T + j, q, x);
+            load_row32<DT>(K, (size_t)row * T + j, q, y);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { x[i] = 0.f; y[i] = 0.f; }
+        }
+        float ir = 0.f, vv = 0.f, kk = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            float dlt = x[i] - oq[i];
+            ir = fmaf(dlt, dlt, ir);
+            vv = fmaf(x[i], x[i], vv);
+            kk = fmaf(y[i], y[i], kk);
+        }
+        ir = quad_sum(ir); vv = quad_sum(vv); kk = quad_sum(kk);
+        if (q == 0 && live) {
+            float pe = p[(size_t)row * T + j] + eps;
+            scores[(size_t)row * T + j] = pe * pe * (vv + (kk / (float)kD) * ir);
+        }
+    }
+}
+
+}  // namespace odmkv
+
+using namespace odmkv;
+
+extern "C" {
+
+size_t odmkv_score_workspace_bytes(int B, int H, int G, int T) {
+    if (B <= 0 || H <= 0 || G <= 0 || T <= 0) return 0;
+    return score_ws_layout(B, H, G, T, 0, nullptr, nullptr) + 256;
+}
+
+int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu, int B, int H, int G, int T,
+                        int n_sink, float eps, float *scores, void *workspace, size_t workspace_bytes,
+                        void *stream) {
+    if (!K || !V || !mu || !scores) return ODMKV_ERR_ARG;
+    if (B <= 0 || H <= 0 || G <= 0 || G > kMaxG || T <= 0 || n_sink < 0 || n_sink > 32 || (long long)B * H > 65535) return ODMKV_ERR_SHAPE;
+    if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (T <= n_sink) {
+        size_t n = (size_t)B * H * T;
+        fill_ones_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(scores, n);
+        return launch_status();
+    }
+    if (!workspace) return ODMKV_ERR_ARG;
+    if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    ScoreWs ws;
+    size_t need = score_ws_layout(B, H, G, T, n_sink, &ws, (unsigned char *)workspace);
+    if (workspace_bytes < need) return ODMKV_ERR_WORKSPACE;
+    const int BH = B * H, Tc = T - n_sink, ns = score_splits(BH, Tc);
+    cudaMemsetAsync(ws.smax, 0, (size_t)B * 4, st);
+    dim3 grid(ns, BH);
+#define ODMKV_SCORE(DT)                                                                                    \
+    score_logits_kernel<DT><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);                 \
+    score_pv_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, G, T, n_sink, ns, ws);                          \
+    score_final_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, T, n_sink, ns, eps, ws, scores);
+    if (dtype == kF16) { ODMKV_SCORE(kF16) } else if (dtype == kBF16) { ODMKV_SCORE(kBF16) } else { ODMKV_SCORE(kF32) }
+#undef ODMKV_SCORE
+    if (n_sink > 0) score_sinks_kernel<<<BH, 32, 0, st>>>(scores, ws.smax, H, T, n_sink);
+    return launch_status();
+}
+
+int odmkv_score_with_attn(const void *K, const void *V, int dtype, const float *p, int R, int T, float eps,
+                          float *scores, void *stream) {
+    if (!K || !V || !p || !scores) return ODMKV_ERR_ARG;
+    if (R <= 0 || T <= 0 || T > 1024) return ODMKV_ERR_SHAPE;
+    if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == kF16) score_with_attn_kernel<kF16><<<R, kScoreThreads, 0, st>>>(K, V, p, T, eps, scores);
+    else if (dtype == kBF16) score_with_attn_kernel<kBF16><<<R, kScoreThreads, 0, st>>>(K, V, p, T, eps, scores);
+    else score_with_attn_kernel<kF32><<<R, kScoreThreads, 0, st>>>(K, V, p, T, eps, scores);
+    return launch_status();
+}
+
+}  // extern "C"

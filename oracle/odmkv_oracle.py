@@ -131,7 +131,7 @@ def random_rotation(dim: int, seed: int) -> np.ndarray:
     q, r = torch.linalg.qr(mat)
     diag = torch.diag(r)
     signs = torch.where(diag >= 0, torch.ones_like(diag), -torch.ones_like(diag))
-    return (q * signs.unsqueeze(0)).numpy().astype(np.float32)
+    return np.ascontiguousarray((q * signs.unsqueeze(0)).numpy(), dtype=np.float32)
 
 
 # ---------------------------------------------------------------------------
