@@ -1,0 +1,378 @@
+"""Benchmark of the compress-then-decode hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the point the headline metric is quoted on): decode attention over a packed cache at
+131 072 tokens of context, 2.0-bit average, GQA 32 query / 8 KV heads, head_dim 128, batch 8 --
+synthetic seeded K/V with four x10 key channels and four attention-sink tokens, compressed by this
+library's own score -> allocate -> quantise/pack path.  One step = one decode-attention call over
+every (sample, KV head) of the batch.  The packed cache (~0.6 GB) is larger than L2, so successive
+steps re-read it from HBM.
+
+`value` is algorithmic packed-cache bytes per second (codes + norms + exact rows that one step must
+read, summed over ranks).  The reference arm (`--impl reference`) times what the reference's decode
+step costs on the host cores: dense fp32 attention over a dequantised cache of the same shape, on a
+bounded sample, reported in the same unit (the same algorithmic bytes per unit divided by its time).
+"""
+from __future__ import annotations
+
+import argparse
+import importlib
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LEVELS = (0, 2, 3, 4, 8, 16)
+METRIC = "LUT decode-attn HBM GB/s (128K ctx, 2.0-bit avg)"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ctx", type=int, default=131072)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--group", type=int, default=4)
+    ap.add_argument("--target-bits", type=float, default=2.0)
+    ap.add_argument("--decode-impl", default="auto")
+    ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def algorithmic_bytes_per_token_head(target_bits: float) -> float:
+    """Expected bytes per stored token-head for the synthetic distribution (documentation only)."""
+    return 71.0 if target_bits <= 2.0 else 104.0
+
+
+def dense_attention_cpu(q, Kh, Vh, keep, scale):
+    """What the reference's decode step computes on the host: dense fp32 softmax(q K^T) V with evicted
+    keys masked (oracle restatement; numpy, all BLAS threads)."""
+    from oracle import odmkv_oracle as orc
+    return orc.decode_attention(q, Kh, Vh, keep, scale)
+
+
+def cpu_reference_leg(ctx, H, G, keep_frac, bytes_per_unit, steps, warmup, seed=0):
+    """Times dense fp32 decode attention on the host for a bounded sample: one sample (all KV heads) of
+    the workload's context length.  Returns (GB/s in the bench's unit, seconds per step, description)."""
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    Kh = rng.standard_normal((1, H, ctx, 128), dtype=np.float32)
+    Vh = rng.standard_normal((1, H, ctx, 128), dtype=np.float32)
+    keep = rng.random((1, H, ctx)) < keep_frac
+    q = rng.standard_normal((1, H * G, 128), dtype=np.float32)
+    scale = 1.0 / math.sqrt(128)
+    for _ in range(max(warmup, 1)):
+        dense_attention_cpu(q, Kh, Vh, keep, scale)
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        dense_attention_cpu(q, Kh, Vh, keep, scale)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    units = H  # (sample, KV head) units processed per step
+    return units * bytes_per_unit / sec / 1e9, sec, f"1 sample x {H} KV heads x {ctx} tokens, dense fp32 attention (numpy), {steps} steps"
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm
+# ------------------------------------------------------------------------------------------------
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = os.cpu_count() or 1
+    bpt = algorithmic_bytes_per_token_head(args.target_bits)
+    bytes_per_unit = bpt * args.ctx
+    steps = max(1, min(args.steps, 10))
+    gbs, sec, sample = cpu_reference_leg(args.ctx, args.kv_heads, args.group, 0.883, bytes_per_unit, steps, min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"decode attention, ctx {args.ctx}, batch {args.batch}, GQA {args.kv_heads * args.group}/{args.kv_heads}, "
+                               f"d 128, target {args.target_bits} bits", "timing": "host wall clock, bounded sample scaled per (sample, KV head) unit"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+
+def synth_kv(torch, B, H, T, G, dev, seed):
+    """Config-0 style synthetic cache on the device: N(0,1) fp16, key channels 0-3 x10, four sink tokens."""
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    K = torch.randn(B, H, T, 128, generator=g, device=dev, dtype=torch.float16)
+    V = torch.randn(B, H, T, 128, generator=g, device=dev, dtype=torch.float16)
+    e = torch.randn(128, generator=g, device=dev)
+    e = e / e.norm()
+    Qw = torch.randn(B, H * G, 64, 128, generator=g, device=dev) + 3.0 * e
+    qd = (torch.randn(B, H * G, 128, generator=g, device=dev) + 3.0 * e).to(torch.float16)
+    K[..., 0:4] *= 10.0
+    K[:, :, 0:4, :] += ((8.0 * math.sqrt(128) / 3.0) * e).to(torch.float16)
+    return K, V, Qw.mean(dim=2).float(), qd
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    pkg = importlib.import_module("odm-kv_b200")
+    ops, L = pkg.ops, pkg._lib.lib()
+    B, H, G, T = args.batch, args.kv_heads, args.group, args.ctx
+
+    # ---- build the packed cache with this library's compress path (timed: compress throughput)
+    eps = pkg.allocator.calibrate_epsilon(128, LEVELS, seed=42, device=dev)
+    eps_list = [eps[b] * (0.5 if b == 0 else 1.0) for b in LEVELS]
+    pi_k = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=42)
+    pi_v = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=2042)
+    K, V, mu, qd = synth_kv(torch, B, H, T, G, dev, seed=1000 + rank)
+    sink = torch.zeros(H, T, dtype=torch.uint8, device=dev)
+    sink[:, :4] = 1
+    sink = sink.reshape(-1)
+
+    def compress():
+        scores = ops.score_prefill(K, V, mu, 4, 1e-2)
+        bits, rep = ops.allocate_bits(scores.reshape(B, H * T), sink, LEVELS, eps_list, args.target_bits)
+        bits = bits.reshape(B, H, T)
+        bits[..., -128:] = 16
+        return ops.quantize_pack(K, V, bits, pi_k, pi_v), rep
+
+    L.odmkv_timing_enable(0)
+    chunk, rep = compress()           # warm-up + the cache the decode steps read
+    torch.cuda.synchronize()
+    stage_ms = {}
+    L.odmkv_timing_enable(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    chunk2, _ = compress()
+    e1.record()
+    torch.cuda.synchronize()
+    compress_ms = e0.elapsed_time(e1)
+    import ctypes
+    for name in ("score", "allocate", "quantize"):
+        tot, n = ctypes.c_double(), ctypes.c_longlong()
+        L.odmkv_timing_read(name.encode(), ctypes.byref(tot), ctypes.byref(n))
+        stage_ms[name] = tot.value
+    del chunk2
+    reports = ops.read_reports(rep)
+    cnt = chunk.seg_count_host().sum(axis=1)
+    stored = int(cnt[1:].sum())
+    bytes_per_step = chunk.packed_bytes()
+    del K, V
+    torch.cuda.empty_cache()
+
+    # ---- decode steps
+    n_splits = args.splits
+    q_steps = [qd.clone() for _ in range(2)]
+
+    def step(i):
+        return ops.decode_attn(q_steps[i & 1], [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+
+    for i in range(max(args.warmup, 3)):
+        out = step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    L.odmkv_timing_enable(1)
+    gathered = [torch.empty_like(out) for _ in range(world)] if world > 1 else None
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        out = step(i)
+        if world > 1:
+            dist.all_gather(gathered, out)   # the per-head output gather of a KV-head / layer sharded run
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total_ms = ev0.elapsed_time(ev1)
+    tot, n = ctypes.c_double(), ctypes.c_longlong()
+    L.odmkv_timing_read(b"decode_main", ctypes.byref(tot), ctypes.byref(n))
+    L.odmkv_timing_enable(0)
+    main_ms = tot.value / max(n.value, 1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end through the cache-state API with host buffers (pinned q in, output out)
+    q_host = qd.cpu().pin_memory()
+    out_host = torch.empty(B, H * G, 128, dtype=torch.float16).pin_memory()
+    q_dev = torch.empty_like(qd)
+
+    def e2e_step():
+        q_dev.copy_(q_host, non_blocking=True)
+        o = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+        out_host.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    # ---- max over ranks, totals over ranks
+    stats = torch.tensor([total_ms, e2e_ms, float(bytes_per_step), main_ms, compress_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, main_ms, compress_ms = mx[0].item(), mx[1].item(), mx[3].item(), mx[4].item()
+        bytes_all = sm[2].item()
+    else:
+        bytes_all = float(bytes_per_step)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = total_ms / args.steps
+    value = bytes_all / (ms_per_step * 1e-3) / 1e9
+    e2e_value = bytes_all / (e2e_ms / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_peak_gbs()
+    achieved = bytes_per_step / (main_ms * 1e-3) / 1e9
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "decode_traffic.json")
+    if os.path.exists(tpath):
+        try:
+            tj = json.load(open(tpath))
+            traffic = tj["dram_bytes_per_algorithmic_byte"] * bytes_per_step
+        except Exception:
+            traffic = None
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": ms_per_step, "us_per_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16 codes -> f32 accumulate", "data": "synthetic",
+        "config": {"workload": f"decode attention over packed cache: ctx {T}, batch {B}, GQA {H * G}/{H}, d 128, target "
+                               f"{args.target_bits} bits over {list(LEVELS)}, fp16 cache",
+                   "l2": "packed cache per rank %.0f MB > 126 MB L2, re-read every step" % (bytes_per_step / 1e6),
+                   "timing": "CUDA events on the launching stream, max over ranks",
+                   "level_counts": {str(b): int(c) for b, c in zip(LEVELS, cnt)},
+                   "stored_token_heads": stored, "bytes_per_step_per_rank": bytes_per_step,
+                   "decode_impl": args.decode_impl, "n_splits": n_splits,
+                   "multi_gpu": "each rank holds its own (sample, KV head) units; outputs all-gathered per step" if world > 1 else "single GPU"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,
+                     "frac_of_8000": achieved / 8000.0},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
+                "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps},
+        "gpu_launches": 3 * args.steps,
+        "clocks": clocks,
+        "compress": {"mtok_per_s": B * T / (compress_ms * 1e-3) / 1e6, "ms_per_layer": compress_ms, "stage_ms": stage_ms,
+                     "tokens": B * T, "alloc_evaluations": reports[0]["evaluations"], "alloc_moved": reports[0]["moved"],
+                     "ties_lambda": sum(r["ties_lambda"] for r in reports), "ties_cut": sum(r["ties_cut"] for r in reports)},
+    }
+    if not args.no_cpu_baseline and world == 1:
+        cores = os.cpu_count() or 1
+        gbs, sec, sample = cpu_reference_leg(T, H, G, stored / float(B * H * T), bytes_per_step / float(B * H), 5, 1)
+        line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
+                                "sec_per_step_of_sample": sec}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -205,6 +205,14 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
                       int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                       void *stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Optional kernel timing (no counterpart in the reference).  When enabled, the launchers bracket
+ * their dominant kernel with CUDA events on the launching stream under the names "score",
+ * "allocate", "quantize", "decode_main"; odmkv_timing_read waits for the events recorded since the
+ * last read and returns their summed duration and count. */
+void odmkv_timing_enable(int on);
+int odmkv_timing_read(const char *kernel, double *total_ms, long long *launches);
+
 #ifdef __cplusplus
 }
 #endif

@@ -91,6 +91,8 @@ _PROTOTYPES = {
                                     c_int, c_void_p]),
     "odmkv_export_bank": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "odmkv_export_positions": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p]),
+    "odmkv_timing_enable": (None, [c_int]),
+    "odmkv_timing_read": (c_int, [c_char_p, POINTER(c_double), POINTER(c_longlong)]),
     "odmkv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "odmkv_decode_default_splits": (c_int, [c_int, c_int, c_longlong]),
     "odmkv_decode_attn": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,

@@ -474,8 +474,10 @@ int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, in
     if (rc) return rc;
     const int nblk = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
     const int rounds = (K > 1 ? kEvalRounds : 1) + closure_rounds(K);
+    timing_begin("allocate", st);
     for (int r = 0; r < rounds; ++r)
         alloc_pass_kernel<true><<<dim3(nblk, P), kAllocThreads, 0, st>>>(scores, sink_mask, n, 0ll, ws, cfg);
+    timing_end(st);
     int eb = (n + 255) / 256;
     if (eb > 2048) eb = 2048;
     alloc_emit_kernel<<<dim3(eb, P), 256, 0, st>>>(sink_mask, n, ws, cfg, bits, reports);

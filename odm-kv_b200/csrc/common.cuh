@@ -37,6 +37,11 @@ __host__ __device__ inline int code_bytes(int li) { return li == 0 ? 32 : li == 
 __host__ __device__ inline int ref_code_bytes(int li) { return li == 0 ? 32 : li == 3 ? 128 : 64; }
 __host__ __device__ inline int dtype_size(int dt) { return dt == kF32 ? 4 : 2; }
 
+// optional event timing of the dominant kernels (timing.cu)
+bool timing_on();
+void timing_begin(const char *name, cudaStream_t st);
+void timing_end(cudaStream_t st);
+
 inline int launch_status() {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? ODMKV_OK : (int)e;

@@ -423,11 +423,13 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
     a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.scale = scale;
     dim3 grid(n_splits, BH);
+    timing_begin("decode_main", st);
 #define ODMKV_DEC(CDT)                                                                           \
     if (GP == 4) decode_main_kernel<CDT, 4><<<grid, kDecThreads, 0, st>>>(dc, a);                \
     else decode_main_kernel<CDT, 8><<<grid, kDecThreads, 0, st>>>(dc, a);
     if (cache_dtype == kF16) { ODMKV_DEC(kF16) } else if (cache_dtype == kBF16) { ODMKV_DEC(kBF16) } else { ODMKV_DEC(kF32) }
 #undef ODMKV_DEC
+    timing_end(st);
     if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
     else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
     else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);

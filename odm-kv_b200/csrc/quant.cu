@@ -593,7 +593,9 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantSmem); \
     if (e != cudaSuccess) return (int)e;                                                                     \
     fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk);                                               \
-    quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);
+    timing_begin("quantize", st);                                                                            \
+    quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);                                                   \
+    timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q
     return launch_status();

@@ -402,12 +402,14 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     const int BH = B * H, Tc = T - n_sink, ns = score_splits(BH, Tc);
     cudaMemsetAsync(ws.smax, 0, (size_t)B * 4, st);
     dim3 grid(ns, BH);
+    timing_begin("score", st);
 #define ODMKV_SCORE(DT)                                                                                    \
     score_logits_kernel<DT><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);                 \
     score_pv_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, G, T, n_sink, ns, ws);                          \
     score_final_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, T, n_sink, ns, eps, ws, scores);
     if (dtype == kF16) { ODMKV_SCORE(kF16) } else if (dtype == kBF16) { ODMKV_SCORE(kBF16) } else { ODMKV_SCORE(kF32) }
 #undef ODMKV_SCORE
+    timing_end(st);
     if (n_sink > 0) score_sinks_kernel<<<BH, 32, 0, st>>>(scores, ws.smax, H, T, n_sink);
     return launch_status();
 }

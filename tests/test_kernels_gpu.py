@@ -195,10 +195,13 @@ def test_allocate_bits_edge_cases(pkg, orc, cuda, golden):
     got, _ = pkg.ops.allocate_bits(torch.from_numpy(s).to(cuda), None, LEVELS, alloc_eps(eps), 2.0)
     assert np.array_equal(got.cpu().numpy()[0], want)
     ones = np.ones((1, 4096), np.float32)
-    want = orc.optimal_scores_to_bits(ones[0], LEVELS, 2.0, eps, None, eviction_cost=0.5)
-    got, rep = pkg.ops.allocate_bits(torch.from_numpy(ones).to(cuda), None, LEVELS, alloc_eps(eps), 2.0)
-    assert np.array_equal(got.cpu().numpy()[0], want)
-    assert pkg.ops.read_reports(rep)[0]["ties_cut"] >= 1
+    for target in (2.0, 2.5, 5.0):
+        info = orc.AllocInfo()
+        want = orc.optimal_scores_to_bits(ones[0], LEVELS, target, eps, None, eviction_cost=0.5, info=info)
+        got, rep = pkg.ops.allocate_bits(torch.from_numpy(ones).to(cuda), None, LEVELS, alloc_eps(eps), target)
+        assert np.array_equal(got.cpu().numpy()[0], want)
+        assert pkg.ops.read_reports(rep)[0]["ties_cut"] == info.ties_cut
+        assert target == 2.0 or info.ties_cut >= 1
     allsink = np.ones(4096, np.uint8)
     got, _ = pkg.ops.allocate_bits(torch.from_numpy(ones).to(cuda), torch.from_numpy(allsink).to(cuda), LEVELS, alloc_eps(eps), 2.0)
     assert (got.cpu().numpy() == 16).all()
