@@ -133,10 +133,14 @@ size_t odmkv_pack_plan_workspace_bytes(int B, int H, int T);
 int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start, int32_t *seg_count,
                     int32_t *totals, void *plan_workspace, size_t plan_workspace_bytes, void *stream);
 
-/* Bank storage of one chunk; all device pointers, sized from `totals` (cap[c] slots).
- * Code bytes per slot: 32 (2-bit, four codes per byte, little-endian as the reference),
- * 48 (3-bit: 32 bytes of the low two bits in the 2-bit layout followed by 16 bytes of the third
- * bit, coordinate 8j+i in bit i of byte j), 64 (4-bit, two nibbles per byte), 128 (8-bit). */
+/* Bank storage of one chunk; all device pointers, sized from `totals` (cap[c] slots, a multiple of 16).
+ * Code bytes per slot: 32 (2-bit), 48 (3-bit, a true 3 bits per code), 64 (4-bit), 128 (8-bit).
+ * The 8-bit bank is token-major (byte d of a slot = code of coordinate d).  The 2/3/4-bit banks are
+ * stored in tiles of 16 slots arranged for the tensor-core fragments of the decode kernel: lane
+ * (g, t) = (lane / 4, lane % 4) of a warp owns the 8*b bytes at tile + lane*8*b as 32 little-endian
+ * pair fields of 2*b bits; keys: bytes [0,4b) = slot g of the tile, [4b,8b) = slot g+8, field f =
+ * coordinates (32t+2f, 32t+2f+1); values: field 4m+2hi+a = coordinate 16m+g+8a of slots (2t+8hi,
+ * 2t+8hi+1).  odmkv_export_bank converts any bank to the reference's byte layout. */
 typedef struct odmkv_chunk {
     uint8_t *k_codes[ODMKV_NUM_QLEVELS];
     uint8_t *v_codes[ODMKV_NUM_QLEVELS];
@@ -157,13 +161,15 @@ typedef struct odmkv_chunk {
  * (searchsorted + neighbour pick, lower index on ties), pack, write into the banks.
  *   pi_k, pi_v [128, 128] fp32 row-major (y = pi x);  codebooks [4][256] fp32 ascending
  *   (level index li uses the first 2^bits(li) entries). `chunk` is a HOST struct. */
+size_t odmkv_quantize_workspace_bytes(const int32_t *cap /* host int32[6], slots per class */);
 int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
                         const float *pi_v, const float *codebooks, const odmkv_chunk *chunk,
-                        const void *plan_workspace, void *stream);
+                        const void *plan_workspace, void *workspace, size_t workspace_bytes, void *stream);
 
 /* Encode-and-pack only: nearest centroid + pack of already rotated coordinates (the stand-in for
  * the absent kvquant/tq_triton.mse_nearest_centroid followed by _pack_indices).
- *   y [n, 128] fp32; codebook [2^bits] fp32; out [n, bytes(bits)] in this library's slot layout. */
+ *   y [n, 128] fp32; codebook [2^bits] fp32; out [n, 16*bits] bytes: the little-endian bit stream of the
+ *   128 codes of each row (for 2, 4 and 8 bits this is the reference's byte layout). */
 int odmkv_encode_pack(const float *y, long long n, int bits, const float *codebook, uint8_t *out, void *stream);
 
 /* Dequantise a chunk into dense [B, H, T_dense, 128] tensors (positions index the T axis).
@@ -204,6 +210,17 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
                       const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
                       int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                       void *stream);
+
+/* Tensor-core variant of odmkv_decode_attn (same contract and arguments): the 2-, 3- and 4-bit banks
+ * are consumed with mma.sync m16n8k16 tiles straight from the tile layout; 8-bit, exact and tail
+ * tokens take the CUDA-core kernel in a second launch; n_splits may go up to 128.
+ *   lut_scales: host float[3] or NULL (= 1.0): per level a factor s such that fp16(c * s) carries the
+ *   centroids of the 2-, 3-, 4-bit codebooks with less rounding error; divided out again in fp32. */
+int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                          const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                          const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                          int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                          const float *lut_scales, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Optional kernel timing (no counterpart in the reference).  When enabled, the launchers bracket

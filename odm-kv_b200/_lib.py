@@ -84,13 +84,17 @@ _PROTOTYPES = {
     "odmkv_alloc_finish": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "odmkv_pack_plan_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "odmkv_pack_plan": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "odmkv_quantize_workspace_bytes": (c_size_t, [POINTER(c_int32)]),
     "odmkv_quantize_pack": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(Chunk),
-                                    c_void_p, c_void_p]),
+                                    c_void_p, c_void_p, c_size_t, c_void_p]),
     "odmkv_encode_pack": (c_int, [c_void_p, c_longlong, c_int, c_void_p, c_void_p, c_void_p]),
     "odmkv_dequant_chunk": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_void_p]),
     "odmkv_export_bank": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "odmkv_export_positions": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p]),
+    "odmkv_decode_attn_mma": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int,
+                                      c_void_p, c_size_t, POINTER(c_float), c_void_p]),
     "odmkv_timing_enable": (None, [c_int]),
     "odmkv_timing_read": (c_int, [c_char_p, POINTER(c_double), POINTER(c_longlong)]),
     "odmkv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
@@ -100,12 +104,7 @@ _PROTOTYPES = {
                                   c_void_p, c_size_t, c_void_p]),
 }
 
-# entry points that newer builds add; bound when present
-_OPTIONAL = {
-    "odmkv_decode_attn_mma": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
-                                      c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int,
-                                      c_void_p, c_size_t, c_void_p]),
-}
+_OPTIONAL: dict = {}
 
 _lib = None
 

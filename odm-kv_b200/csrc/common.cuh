@@ -116,15 +116,52 @@ __device__ inline int nearest_centroid(float y, const float *c, int k) {
     return (da <= db) ? a : b;
 }
 
-// ---- code extraction from one packed slot (natural coordinate order) ---------------------------
-// li: 0 = 2-bit, 1 = 3-bit (two-bit plane then one-bit plane), 2 = 4-bit, 3 = 8-bit
-__device__ inline int extract_code(const uint8_t *row, int li, int i) {
-    switch (li) {
-        case 0: return (row[i >> 2] >> ((i & 3) * 2)) & 3;
-        case 1: return ((row[i >> 2] >> ((i & 3) * 2)) & 3) | (((row[32 + (i >> 3)] >> (i & 7)) & 1) << 2);
-        case 2: return (row[i >> 1] >> ((i & 1) * 4)) & 15;
-        default: return row[i];
-    }
+// ---- bank layouts ---------------------------------------------------------------------------------
+// 8-bit bank (li = 3): token-major, 128 bytes per slot, byte d = code of coordinate d (keys and values).
+//
+// 2/3/4-bit banks (li = 0..2, b bits per code): slots are grouped in tiles of 16 (256*b bytes per tile).
+// A tile is laid out for the m16n8k16 tensor-core fragments of the decode kernel: lane (g, t) of a warp
+// (g = lane / 4, t = lane % 4) owns the 8*b bytes at tile + lane * 8 * b, as 32 "pair fields" of 2*b bits
+// (low code in the low bits), packed little-endian in ascending field order.
+//   keys:   bytes [0, 4b) hold row g of the tile, bytes [4b, 8b) row g + 8; field f of a row part holds
+//           coordinates (32 t + 2 f, 32 t + 2 f + 1).
+//   values: field 4 m + 2 hi + a holds coordinate 16 m + g + 8 a of tokens (2 t + 8 hi, 2 t + 8 hi + 1).
+// The "linear" layout (scratch and odmkv_encode_pack output) is the plain little-endian bit stream of the
+// 128 codes of one slot, 16*b bytes per slot.
+__host__ __device__ inline int qbits(int li) { return li == 0 ? 2 : li == 1 ? 3 : li == 2 ? 4 : 8; }
+
+__device__ inline uint32_t read_bits(const uint8_t *p, int bitoff, int nbits) {
+    const int byte = bitoff >> 3, sh = bitoff & 7;
+    uint32_t v = (uint32_t)p[byte] >> sh;
+    if (sh + nbits > 8) v |= (uint32_t)p[byte + 1] << (8 - sh);
+    return v & ((1u << nbits) - 1u);
+}
+
+// byte offset of the key row part of `slot` that holds coordinates [32 t, 32 t + 32)
+__host__ __device__ inline size_t k_part_offset(int b, long long slot, int t) {
+    const long long tile = slot >> 4;
+    const int r = (int)(slot & 15), g = r & 7, hi = r >> 3;
+    return (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b + (size_t)hi * 4 * b;
+}
+
+__device__ inline int k_code(const uint8_t *bank, int li, long long slot, int d) {
+    if (li == 3) return bank[(size_t)slot * 128 + d];
+    const int b = qbits(li);
+    return (int)read_bits(bank + k_part_offset(b, slot, d >> 5), ((d & 31) >> 1) * 2 * b + (d & 1) * b, b);
+}
+
+__device__ inline int v_code(const uint8_t *bank, int li, long long slot, int d) {
+    if (li == 3) return bank[(size_t)slot * 128 + d];
+    const int b = qbits(li);
+    const long long tile = slot >> 4;
+    const int r = (int)(slot & 15), m = d >> 4, dd = d & 15, g = dd & 7, a = dd >> 3;
+    const int t = (r & 7) >> 1, e = r & 1, hi = r >> 3;
+    return (int)read_bits(bank + (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b, (4 * m + hi * 2 + a) * 2 * b + e * b, b);
+}
+
+__device__ inline int linear_code(const uint8_t *rows, int li, long long slot, int d) {
+    const int b = qbits(li);
+    return (int)read_bits(rows + (size_t)slot * 16 * b, d * b, b);
 }
 
 __device__ inline float warp_sum(float v) {

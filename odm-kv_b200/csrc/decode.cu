@@ -12,30 +12,13 @@
 // Grid: (n_splits, B*H).  Each CTA takes the same fraction of every (chunk, class) segment of its
 // (b, h), keeps per-warp running (max, sum, accumulators) for the G query heads of the KV head and
 // writes one partial; the merge kernel combines partials with a log-sum-exp merge.
-#include "common.cuh"
+#include "decode_shared.cuh"
 
 namespace odmkv {
 
 constexpr int kDecThreads = 128;
 constexpr int kDecWarps = kDecThreads / 32;
-
-struct DecodeChunks {
-    odmkv_chunk ch[kMaxChunks];
-    int n;
-};
-
-struct DecodeArgs {
-    const float *qrot;   // [B*H*G, 128] pi_k q
-    const float *qf;     // [B*H*G, 128] q as fp32
-    const void *tail_k;
-    const void *tail_v;
-    const float *codebooks;
-    float *part_ml;      // [BH, nsplit, GP, 2]
-    float *part_acc;     // [BH, nsplit, GP, 2, 128]  (rotated-space, exact-space)
-    int tail_len, tail_cap;
-    int B, H, G, nsplit;
-    float scale;
-};
+constexpr int kMaxSlots = 160;   // partial slots per (b, h) the merge kernel accepts
 
 // rotate the queries once: qrot[r][i] = sum_j pi_k[i][j] q[r][j]; also keep q as fp32
 template <int QDT>
@@ -85,98 +68,46 @@ __device__ inline void softmax_step(WarpState<GP> &st, const float (&logit)[GP],
     }
 }
 
-// dot products of one packed code row (held in registers as NW words) with the rotated queries
-template <int LI, int GP>
-__device__ inline void code_dot(const uint32_t *w, const float *__restrict__ lut, const float *__restrict__ qs, float (&dot)[GP]) {
-#pragma unroll
-    for (int g = 0; g < GP; ++g) dot[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < kD; ++i) {
-        int code;
-        if (LI == 0) code = (w[i >> 4] >> (2 * (i & 15))) & 3;
-        else if (LI == 1) code = ((w[i >> 4] >> (2 * (i & 15))) & 3) | (((w[8 + (i >> 5)] >> (i & 31)) & 1) << 2);
-        else if (LI == 2) code = (w[i >> 3] >> (4 * (i & 7))) & 15;
-        else code = (w[i >> 2] >> (8 * (i & 3))) & 255;
-        const float c = lut[code];
-#pragma unroll
-        for (int g4 = 0; g4 < GP / 4; ++g4) {
-            float4 qv = *reinterpret_cast<const float4 *>(qs + i * GP + 4 * g4);
-            dot[4 * g4] = fmaf(c, qv.x, dot[4 * g4]);
-            dot[4 * g4 + 1] = fmaf(c, qv.y, dot[4 * g4 + 1]);
-            dot[4 * g4 + 2] = fmaf(c, qv.z, dot[4 * g4 + 2]);
-            dot[4 * g4 + 3] = fmaf(c, qv.w, dot[4 * g4 + 3]);
-        }
-    }
-}
-
-// the four codes of coordinates 4*lane .. 4*lane+3 of a staged row
-template <int LI>
-__device__ inline void lane_codes(const uint8_t *__restrict__ row, int lane, int (&code)[4]) {
-    if (LI == 0) {
-        uint32_t b = row[lane];
-#pragma unroll
-        for (int d = 0; d < 4; ++d) code[d] = (b >> (2 * d)) & 3;
-    } else if (LI == 1) {
-        uint32_t b = row[lane], h = row[32 + (lane >> 1)] >> ((lane & 1) * 4);
-#pragma unroll
-        for (int d = 0; d < 4; ++d) code[d] = ((b >> (2 * d)) & 3) | (((h >> d) & 1) << 2);
-    } else if (LI == 2) {
-        uint32_t b = *reinterpret_cast<const uint16_t *>(row + 2 * lane);
-#pragma unroll
-        for (int d = 0; d < 4; ++d) code[d] = (b >> (4 * d)) & 15;
-    } else {
-        uint32_t b = *reinterpret_cast<const uint32_t *>(row + 4 * lane);
-#pragma unroll
-        for (int d = 0; d < 4; ++d) code[d] = (b >> (8 * d)) & 255;
-    }
-}
-
-// one group of up to 32 slots of a quantised bank
-template <int LI, int GP>
-__device__ inline void process_codes(WarpState<GP> &st, const odmkv_chunk &ch, int s_begin, int s_end, const float *__restrict__ lut,
-                                     const float *__restrict__ qs, uint8_t *__restrict__ stage, float scale, int lane) {
-    constexpr int NB = LI == 0 ? 32 : LI == 1 ? 48 : LI == 2 ? 64 : 128;
-    constexpr int NW = NB / 4;
+// one group of up to 32 slots of a quantised bank; lane = token for the key dot products, lane = four
+// coordinates for the value accumulation.  Codes are read through the layout accessors, so this path
+// serves every level (it is the plain, slow reader; the tensor-core kernel is the fast one).
+template <int GP>
+__device__ inline void process_codes(WarpState<GP> &st, const odmkv_chunk &ch, int li, int s_begin, int s_end,
+                                     const float *__restrict__ lut, const float *__restrict__ qs, float scale, int lane) {
     const int s = s_begin + lane;
     const bool valid = s < s_end;
     float logit[GP], p[GP];
-    uint32_t w[NW];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) logit[g] = 0.f;
     if (valid) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(ch.k_codes[LI] + (size_t)s * NB);
+        const uint8_t *bank = ch.k_codes[li];
+        for (int i = 0; i < kD; ++i) {
+            const float c = lut[k_code(bank, li, s, i)];
 #pragma unroll
-        for (int v = 0; v < NW / 4; ++v) {
-            uint4 t = src[v];
-            w[4 * v] = t.x; w[4 * v + 1] = t.y; w[4 * v + 2] = t.z; w[4 * v + 3] = t.w;
+            for (int g4 = 0; g4 < GP / 4; ++g4) {
+                float4 qv = *reinterpret_cast<const float4 *>(qs + i * GP + 4 * g4);
+                logit[4 * g4] = fmaf(c, qv.x, logit[4 * g4]);
+                logit[4 * g4 + 1] = fmaf(c, qv.y, logit[4 * g4 + 1]);
+                logit[4 * g4 + 2] = fmaf(c, qv.z, logit[4 * g4 + 2]);
+                logit[4 * g4 + 3] = fmaf(c, qv.w, logit[4 * g4 + 3]);
+            }
         }
-        float dot[GP];
-        code_dot<LI, GP>(w, lut, qs, dot);
-        const float kn = ch.k_norm[LI][s] * scale;
+        const float kn = ch.k_norm[li][s] * scale;
 #pragma unroll
-        for (int g = 0; g < GP; ++g) logit[g] = dot[g] * kn;
-    } else {
-#pragma unroll
-        for (int g = 0; g < GP; ++g) logit[g] = 0.f;
+        for (int g = 0; g < GP; ++g) logit[g] *= kn;
     }
     softmax_step<GP>(st, logit, valid, p);
-    // stage this group's value codes, one row per lane
-    __syncwarp();
     if (valid) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(ch.v_codes[LI] + (size_t)s * NB);
-        uint4 *dst = reinterpret_cast<uint4 *>(stage + lane * NB);
-#pragma unroll
-        for (int v = 0; v < NW / 4; ++v) dst[v] = src[v];
-        const float vn = ch.v_norm[LI][s];
+        const float vn = ch.v_norm[li][s];
 #pragma unroll
         for (int g = 0; g < GP; ++g) p[g] *= vn;
     }
-    __syncwarp();
     const int cnt = min(32, s_end - s_begin);
+    const uint8_t *vbank = ch.v_codes[li];
     for (int j = 0; j < cnt; ++j) {
-        int code[4];
-        lane_codes<LI>(stage + j * NB, lane, code);
         float c[4];
 #pragma unroll
-        for (int d = 0; d < 4; ++d) c[d] = lut[code[d]];
+        for (int d = 0; d < 4; ++d) c[d] = lut[v_code(vbank, li, s_begin + j, 4 * lane + d)];
 #pragma unroll
         for (int g = 0; g < GP; ++g) {
             float pj = __shfl_sync(0xffffffffu, p[g], j);
@@ -226,11 +157,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
     __shared__ __align__(16) float qs[kD * GP];   // rotated queries, [i][g]
     __shared__ __align__(16) float qx[kD * GP];   // plain queries, [i][g]
     __shared__ float lut[4 * 256];
-    // the value-code staging rows and the end-of-kernel reduction buffer share storage
-    constexpr int kStageBytes = kDecWarps * 32 * 128, kRedBytes = kDecWarps * GP * 2 * kD * 4;
-    __shared__ __align__(16) uint8_t raw[kStageBytes > kRedBytes ? kStageBytes : kRedBytes];
-    uint8_t (*stage)[32 * 128] = reinterpret_cast<uint8_t (*)[32 * 128]>(raw);
-    float (*red_acc)[GP][2][kD] = reinterpret_cast<float (*)[GP][2][kD]>(raw);
+    __shared__ float red_acc[kDecWarps][GP][2][kD];
     __shared__ float red_m[kDecWarps][GP], red_l[kDecWarps][GP];
 
     const int bh = blockIdx.y, split = blockIdx.x;
@@ -255,6 +182,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
     for (int ci = 0; ci < chunks.n; ++ci) {
         const odmkv_chunk &ch = chunks.ch[ci];
         for (int c = 1; c <= 5; ++c) {
+            if (!((a.class_mask >> c) & 1)) continue;
             const int cnt = ch.seg_count[c * BH + bh];
             if (cnt == 0) continue;
             const int s0 = ch.seg_start[c * BH + bh];
@@ -262,15 +190,12 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
             const int g_lo = (int)((long long)ngroups * split / a.nsplit), g_hi = (int)((long long)ngroups * (split + 1) / a.nsplit);
             for (int gi = g_lo + warp; gi < g_hi; gi += kDecWarps) {
                 const int sb = s0 + gi * 32, se = min(s0 + cnt, sb + 32);
-                if (c == 1) process_codes<0, GP>(st, ch, sb, se, lut, qs, stage[warp], a.scale, lane);
-                else if (c == 2) process_codes<1, GP>(st, ch, sb, se, lut + 256, qs, stage[warp], a.scale, lane);
-                else if (c == 3) process_codes<2, GP>(st, ch, sb, se, lut + 512, qs, stage[warp], a.scale, lane);
-                else if (c == 4) process_codes<3, GP>(st, ch, sb, se, lut + 768, qs, stage[warp], a.scale, lane);
+                if (c <= 4) process_codes<GP>(st, ch, c - 1, sb, se, lut + (c - 1) * 256, qs, a.scale, lane);
                 else process_exact<CDT, GP>(st, ch.exact_k, ch.exact_v, (size_t)sb, (size_t)se, qx, a.scale, lane);
             }
         }
     }
-    if (a.tail_len > 0) {
+    if (a.tail_len > 0 && ((a.class_mask >> 6) & 1)) {
         const int ngroups = (a.tail_len + 31) / 32;
         const int g_lo = (int)((long long)ngroups * split / a.nsplit), g_hi = (int)((long long)ngroups * (split + 1) / a.nsplit);
         const size_t base = (size_t)bh * a.tail_cap;
@@ -304,7 +229,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
             v += (&red_acc[w][g][0][0])[rest] * f;
             l += red_l[w][g] * f;
         }
-        const size_t pi = ((size_t)bh * a.nsplit + split) * GP + g;
+        const size_t pi = ((size_t)bh * a.nslots + a.slot_base + split) * GP + g;
         a.part_acc[pi * 2 * kD + rest] = v;
         if (rest == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = l; }
     }
@@ -316,7 +241,7 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
                                                            const float *__restrict__ pi_v, int G, int GP, int nsplit,
                                                            void *__restrict__ out, float *__restrict__ lse) {
     __shared__ float ar[kD];
-    __shared__ float w[64];
+    __shared__ float w[kMaxSlots];
     __shared__ float sh_ml[2];
     const int r = blockIdx.x;          // bh * G + g
     const int bh = r / G, g = r % G, j = threadIdx.x;
@@ -352,22 +277,47 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
     if (lse && j == 0) lse[r] = l > 0.f ? sh_ml[0] + logf(l) : -INFINITY;
 }
 
-inline int round_gp(int G) { return G <= 4 ? 4 : 8; }
+void launch_rotate_q(const void *q, int q_dtype, const float *pi_k, const DecodeWs &ws, int R, cudaStream_t st) {
+    if (q_dtype == kF16) rotate_q_kernel<kF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    else if (q_dtype == kBF16) rotate_q_kernel<kBF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    else rotate_q_kernel<kF32><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+}
 
-struct DecodeWs {
-    float *qrot, *qf, *part_ml, *part_acc;
-};
-inline size_t decode_ws_layout(int B, int H, int G, int nsplit, DecodeWs *ws, unsigned char *base) {
-    const size_t BH = (size_t)B * H, GP = round_gp(G);
-    size_t off = 0;
-    auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
-    size_t o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nsplit * GP * 2 * 4),
-           o_acc = take(BH * nsplit * GP * 2 * kD * 4);
-    if (ws && base) {
-        ws->qrot = (float *)(base + o_qr); ws->qf = (float *)(base + o_qf);
-        ws->part_ml = (float *)(base + o_ml); ws->part_acc = (float *)(base + o_acc);
+void launch_decode_cuda_core(const DecodeChunks &dc, const DecodeArgs &a, int cache_dtype, cudaStream_t st) {
+    const int GP = round_gp(a.G);
+    dim3 grid(a.nsplit, a.B * a.H);
+#define ODMKV_DEC(CDT)                                                                           \
+    if (GP == 4) decode_main_kernel<CDT, 4><<<grid, kDecThreads, 0, st>>>(dc, a);                \
+    else decode_main_kernel<CDT, 8><<<grid, kDecThreads, 0, st>>>(dc, a);
+    if (cache_dtype == kF16) { ODMKV_DEC(kF16) } else if (cache_dtype == kBF16) { ODMKV_DEC(kBF16) } else { ODMKV_DEC(kF32) }
+#undef ODMKV_DEC
+}
+
+void launch_decode_merge(const DecodeWs &ws, const float *pi_v, int BH, int G, int nslots, void *out, int out_dtype, float *lse,
+                         cudaStream_t st) {
+    const int R = BH * G, GP = round_gp(G);
+    if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
+    else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
+    else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
+}
+
+int decode_check_args(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype, const void *tail_k,
+                      const void *tail_v, int tail_len, int tail_cap, const float *pi_k, const float *pi_v, const float *codebooks,
+                      int B, int H, int G, void *out, int out_dtype, int n_splits, void *workspace, DecodeChunks *dc) {
+    if (!q || !pi_k || !pi_v || !codebooks || !out || !workspace) return ODMKV_ERR_ARG;
+    if (n_chunks < 0 || n_chunks > kMaxChunks) return ODMKV_ERR_LIMIT;
+    if (n_chunks > 0 && !chunks) return ODMKV_ERR_ARG;
+    if (B <= 0 || H <= 0 || G <= 0 || G > 8 || (long long)B * H > 65535) return ODMKV_ERR_SHAPE;
+    if (q_dtype < 0 || q_dtype > 2 || out_dtype < 0 || out_dtype > 2 || cache_dtype < 0 || cache_dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    if (tail_len < 0 || tail_len > tail_cap || (tail_len > 0 && (!tail_k || !tail_v))) return ODMKV_ERR_ARG;
+    if (n_splits <= 0 || n_splits > 128) return ODMKV_ERR_ARG;
+    if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    dc->n = n_chunks;
+    for (int i = 0; i < n_chunks; ++i) {
+        if (chunks[i].B != B || chunks[i].H != H || !chunks[i].seg_start || !chunks[i].seg_count) return ODMKV_ERR_SHAPE;
+        dc->ch[i] = chunks[i];
     }
-    return off;
+    return ODMKV_OK;
 }
 
 }  // namespace odmkv
@@ -387,9 +337,10 @@ int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
     return (int)n;
 }
 
+// room for n_splits partial slots of the main kernel plus the slots of the exact / tail kernel
 size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits) {
     if (B <= 0 || H <= 0 || G <= 0 || n_splits <= 0) return 0;
-    return decode_ws_layout(B, H, G, n_splits, nullptr, nullptr) + 256;
+    return decode_ws_layout(B, H, G, n_splits + 8, nullptr, nullptr) + 256;
 }
 
 int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
@@ -397,42 +348,24 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
                       const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
                       int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                       void *stream) {
-    if (!q || !pi_k || !pi_v || !codebooks || !out || !workspace) return ODMKV_ERR_ARG;
-    if (n_chunks < 0 || n_chunks > kMaxChunks) return ODMKV_ERR_LIMIT;
-    if (n_chunks > 0 && !chunks) return ODMKV_ERR_ARG;
-    if (B <= 0 || H <= 0 || G <= 0 || G > 8 || (long long)B * H > 65535) return ODMKV_ERR_SHAPE;
-    if (q_dtype < 0 || q_dtype > 2 || out_dtype < 0 || out_dtype > 2 || cache_dtype < 0 || cache_dtype > 2) return ODMKV_ERR_UNSUPPORTED;
-    if (tail_len < 0 || tail_len > tail_cap || (tail_len > 0 && (!tail_k || !tail_v))) return ODMKV_ERR_ARG;
-    if (n_splits <= 0 || n_splits > 64) return ODMKV_ERR_ARG;
-    if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    DecodeChunks dc;
+    int rc = decode_check_args(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len, tail_cap, pi_k, pi_v, codebooks,
+                               B, H, G, out, out_dtype, n_splits, workspace, &dc);
+    if (rc) return rc;
+    if (n_splits > 64) return ODMKV_ERR_ARG;
     DecodeWs ws;
     if (workspace_bytes < decode_ws_layout(B, H, G, n_splits, &ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
-    DecodeChunks dc;
-    dc.n = n_chunks;
-    for (int i = 0; i < n_chunks; ++i) {
-        if (chunks[i].B != B || chunks[i].H != H || !chunks[i].seg_start || !chunks[i].seg_count) return ODMKV_ERR_SHAPE;
-        dc.ch[i] = chunks[i];
-    }
     cudaStream_t st = (cudaStream_t)stream;
-    const int BH = B * H, R = BH * G, GP = round_gp(G);
-    if (q_dtype == kF16) rotate_q_kernel<kF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
-    else if (q_dtype == kBF16) rotate_q_kernel<kBF16><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
-    else rotate_q_kernel<kF32><<<R, kD, 0, st>>>(q, pi_k, ws.qrot, ws.qf);
+    const int BH = B * H;
+    launch_rotate_q(q, q_dtype, pi_k, ws, BH * G, st);
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
-    a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.scale = scale;
-    dim3 grid(n_splits, BH);
+    a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.slot_base = 0; a.nslots = n_splits; a.class_mask = 0x7e; a.scale = scale;
     timing_begin("decode_main", st);
-#define ODMKV_DEC(CDT)                                                                           \
-    if (GP == 4) decode_main_kernel<CDT, 4><<<grid, kDecThreads, 0, st>>>(dc, a);                \
-    else decode_main_kernel<CDT, 8><<<grid, kDecThreads, 0, st>>>(dc, a);
-    if (cache_dtype == kF16) { ODMKV_DEC(kF16) } else if (cache_dtype == kBF16) { ODMKV_DEC(kBF16) } else { ODMKV_DEC(kF32) }
-#undef ODMKV_DEC
+    launch_decode_cuda_core(dc, a, cache_dtype, st);
     timing_end(st);
-    if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
-    else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
-    else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, n_splits, out, lse);
+    launch_decode_merge(ws, pi_v, BH, G, n_splits, out, out_dtype, lse, st);
     return launch_status();
 }
 

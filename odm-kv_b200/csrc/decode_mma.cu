@@ -1,0 +1,396 @@
+// Tensor-core decode attention over the 2/3/4-bit banks (sm_100a).
+//
+// Same contract as decode.cu (it replaces the q_len = 1 attention call behind the reference's wrapper,
+// kvquant/attention_patch.py:30-55, over the dequantised cache of kvquant/tq_adaptive_backend.py:205-242),
+// different machine mapping.  A warp consumes one bank tile of 16 tokens at a time:
+//   * the tile's key codes arrive as one 8*b-byte load per lane, already in m16n8k16 A-fragment order;
+//     a pair of codes (2*b bits) indexes a per-lane copy of a small table of half2 centroid pairs, so
+//     one shared-memory read yields one A register;
+//   * S = K_dec (16 x 128) . q'^T (128 x 8) runs as 8 HMMA steps; the 8 columns are the fp16 high and
+//     low limbs of the rotated queries of up to 4 heads (two column tiles for up to 8 heads), so the
+//     query enters with ~22 bits;
+//   * softmax weights use a lazily updated warp-wide running maximum of logit + log2(value norm), which
+//     bounds every weight by 2^6 and keeps the fp16 P operand in range whatever the norms are;
+//   * P is transposed in registers with movmatrix and O^T (128 x 8) += V_dec^T (128 x 16) . P (16 x 8)
+//     runs as 8 more HMMA steps with the value codes decoded through the same tables.
+// 8-bit tokens, the exact bank and the dense tail go through the CUDA-core kernel of decode.cu in a
+// second launch that writes its own partial slots; one merge kernel combines everything.
+#include "decode_shared.cuh"
+
+namespace odmkv {
+
+constexpr int kMmaThreads = 256;
+constexpr int kMmaWarps = kMmaThreads / 32;
+constexpr float kTau = 6.0f;   // lazy-maximum slack in log2 units: weights stay below 2^6
+
+struct MmaArgs {
+    const float *qrot;
+    const float *codebooks;
+    float *part_ml;
+    float *part_acc;
+    int B, H, G, nsplit, slot_base, nslots;
+    float scale_log2;      // softmax scale * log2(e)
+    float lut_scale[3];    // centroids are stored in the tables as fp16(c * lut_scale[li])
+};
+
+__device__ inline void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ inline uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+
+__device__ inline uint32_t pack_half2(__half lo, __half hi) {
+    return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+}
+
+// pair field f (2*B bits at bit 2*B*f) of a little-endian word array; f is a compile-time constant
+// at every call site, so the branch and the shifts fold away
+template <int B>
+__device__ inline uint32_t pair_field(const uint32_t *w, int f) {
+    const int off = 2 * B * f, wi = off >> 5, sh = off & 31;
+    uint32_t v;
+    if (sh + 2 * B <= 32) v = w[wi] >> sh;
+    else v = __funnelshift_r(w[wi], w[wi + 1], sh);
+    return v & ((1u << (2 * B)) - 1u);
+}
+
+// table lookup: 2- and 3-bit tables hold one copy per lane (index * 32 + lane) so that a warp's reads
+// never collide; the 4-bit table is a single copy
+template <int B>
+__device__ inline uint32_t lut_pair(const uint32_t *__restrict__ lut, uint32_t idx, int lane) {
+    if (B == 4) return lut[idx];
+    return lut[idx * 32 + lane];
+}
+
+template <int NT>
+struct MmaState {
+    float M[2], l[2];        // per head column of this lane (two heads per lane)
+    float O[NT][8][4];       // O^T fragments: [column tile][16-coordinate block][c0..c3]
+};
+
+template <int B, int NT>
+__device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B], const uint32_t (&vw)[2 * B], float kn0, float kn1,
+                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], const uint32_t *__restrict__ lut,
+                                    int lane, float kfac, float inv_lut_scale) {
+    const int g = lane >> 2, t = lane & 3;
+    // ---- S = K_dec . q'^T
+    float S[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) S[nt][i] = 0.f;
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+        uint32_t a[4];
+        a[0] = lut_pair<B>(lut, pair_field<B>(kw, 2 * s), lane);
+        a[1] = lut_pair<B>(lut, pair_field<B>(kw + B, 2 * s), lane);
+        a[2] = lut_pair<B>(lut, pair_field<B>(kw, 2 * s + 1), lane);
+        a[3] = lut_pair<B>(lut, pair_field<B>(kw + B, 2 * s + 1), lane);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
+    }
+    // ---- high + low query limbs
+    float sv[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        if (NT == 1) sv[i] = S[0][i] + __shfl_xor_sync(0xffffffffu, S[0][i], 2);
+        else sv[i] = S[0][i] + S[NT - 1][i];
+    }
+    // ---- weights relative to the lazily updated maximum of logit2 + log2(value norm)
+    const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+    const float vc0 = fmaxf(vn0, 1e-30f) * inv_lut_scale, vc1 = fmaxf(vn1, 1e-30f) * inv_lut_scale;
+    const float lv0 = __log2f(vc0), lv1 = __log2f(vc1);
+    const float rv0 = __fdividef(1.0f, vc0), rv1 = __fdividef(1.0f, vc1);
+    const float f0 = kn0 * kfac, f1 = kn1 * kfac;
+    float z[4];
+    z[0] = ok0 ? fmaf(sv[0], f0, lv0) : -INFINITY;
+    z[1] = ok0 ? fmaf(sv[1], f0, lv0) : -INFINITY;
+    z[2] = ok1 ? fmaf(sv[2], f1, lv1) : -INFINITY;
+    z[3] = ok1 ? fmaf(sv[3], f1, lv1) : -INFINITY;
+    float zm0 = fmaxf(z[0], z[2]), zm1 = fmaxf(z[1], z[3]);
+    const bool need = (zm0 > st.M[0] + kTau) || (zm1 > st.M[1] + kTau);
+    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            zm0 = fmaxf(zm0, __shfl_xor_sync(0xffffffffu, zm0, o));
+            zm1 = fmaxf(zm1, __shfl_xor_sync(0xffffffffu, zm1, o));
+        }
+        const float n0 = fmaxf(st.M[0], zm0), n1 = fmaxf(st.M[1], zm1);
+        const float c0 = st.M[0] == -INFINITY ? 0.f : exp2f(st.M[0] - n0);
+        const float c1 = st.M[1] == -INFINITY ? 0.f : exp2f(st.M[1] - n1);
+        st.M[0] = n0; st.M[1] = n1;
+        st.l[0] *= c0; st.l[1] *= c1;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                st.O[nt][m][0] *= c0; st.O[nt][m][1] *= c1; st.O[nt][m][2] *= c0; st.O[nt][m][3] *= c1;
+            }
+    }
+    float W[4];
+    W[0] = ok0 ? exp2f(z[0] - st.M[0]) : 0.f;
+    W[1] = ok0 ? exp2f(z[1] - st.M[1]) : 0.f;
+    W[2] = ok1 ? exp2f(z[2] - st.M[0]) : 0.f;
+    W[3] = ok1 ? exp2f(z[3] - st.M[1]) : 0.f;
+    st.l[0] += W[0] * rv0 + W[2] * rv1;
+    st.l[1] += W[1] * rv0 + W[3] * rv1;
+    // ---- P operand: fp16 high limb and low limb of every weight
+    __half hi[4], lo[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        hi[i] = __float2half_rn(W[i]);
+        lo[i] = __float2half_rn(W[i] - __half2float(hi[i]));
+    }
+    uint32_t pb[NT][2];
+    if (NT == 1) {
+        const bool low = (t & 2) != 0;   // columns 4..7 carry the low limbs
+        pb[0][0] = movmatrix_trans(low ? pack_half2(lo[0], lo[1]) : pack_half2(hi[0], hi[1]));
+        pb[0][1] = movmatrix_trans(low ? pack_half2(lo[2], lo[3]) : pack_half2(hi[2], hi[3]));
+    } else {
+        pb[0][0] = movmatrix_trans(pack_half2(hi[0], hi[1]));
+        pb[0][1] = movmatrix_trans(pack_half2(hi[2], hi[3]));
+        pb[NT - 1][0] = movmatrix_trans(pack_half2(lo[0], lo[1]));
+        pb[NT - 1][1] = movmatrix_trans(pack_half2(lo[2], lo[3]));
+    }
+    // ---- O^T += V_dec^T . P
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        uint32_t a[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = lut_pair<B>(lut, pair_field<B>(vw, 4 * m + r), lane);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[nt][0], pb[nt][1]);
+    }
+}
+
+template <int B>
+__device__ inline void load_words(const uint8_t *__restrict__ p, uint32_t (&w)[2 * B]) {
+    if (B == 2) {
+        uint4 v = *reinterpret_cast<const uint4 *>(p);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+    } else if (B == 3) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            uint2 v = reinterpret_cast<const uint2 *>(p)[i];
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint4 v = reinterpret_cast<const uint4 *>(p)[i];
+            w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+        }
+    }
+}
+
+template <int B, int NT>
+__device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
+                                       const uint32_t (&qB)[NT][8][2], const uint32_t *__restrict__ lut, float scale_log2, float lut_scale) {
+    constexpr int LI = B - 2;
+    const int ntiles = (cnt + 15) >> 4;
+    const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
+    const int g = lane >> 2;
+    const float kfac = scale_log2 / lut_scale, inv_ls = 1.0f / lut_scale;
+    const uint8_t *kb = ch.k_codes[LI], *vb = ch.v_codes[LI];
+    const float *kn = ch.k_norm[LI], *vn = ch.v_norm[LI];
+    for (int ti = t_lo + warp; ti < t_hi; ti += kMmaWarps) {
+        const int slot0 = s0 + ti * 16;
+        const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
+        uint32_t kw[2 * B], vw[2 * B];
+        load_words<B>(kb + off, kw);
+        load_words<B>(vb + off, vw);
+        const float kn0 = kn[slot0 + g], kn1 = kn[slot0 + g + 8], vn0 = vn[slot0 + g], vn1 = vn[slot0 + g + 8];
+        process_tile<B, NT>(st, kw, vw, kn0, kn1, vn0, vn1, min(16, cnt - ti * 16), qB, lut, lane, kfac, inv_ls);
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeChunks chunks, const MmaArgs a) {
+    __shared__ uint32_t lut2[16 * 32];
+    __shared__ uint32_t lut3[64 * 32];
+    __shared__ uint32_t lut4[256];
+    __shared__ float Osh[4 * NT][kD];
+    __shared__ float lsh[4 * NT], Msh[4 * NT];
+    __shared__ float warpM[kMmaWarps][4 * NT];
+
+    const int bh = blockIdx.y, split = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int BH = a.B * a.H, G = a.G;
+    constexpr int NH = 4 * NT;   // head slots of this kernel variant
+
+    // ---- tables of half2 centroid pairs
+    {
+        const float *c2 = a.codebooks, *c3 = a.codebooks + 256, *c4 = a.codebooks + 512;
+        for (int e = tid; e < 16 * 32; e += kMmaThreads) {
+            int idx = e >> 5;
+            lut2[e] = pack_half2(__float2half_rn(c2[idx & 3] * a.lut_scale[0]), __float2half_rn(c2[idx >> 2] * a.lut_scale[0]));
+        }
+        for (int e = tid; e < 64 * 32; e += kMmaThreads) {
+            int idx = e >> 5;
+            lut3[e] = pack_half2(__float2half_rn(c3[idx & 7] * a.lut_scale[1]), __float2half_rn(c3[idx >> 3] * a.lut_scale[1]));
+        }
+        for (int e = tid; e < 256; e += kMmaThreads)
+            lut4[e] = pack_half2(__float2half_rn(c4[e & 15] * a.lut_scale[2]), __float2half_rn(c4[e >> 4] * a.lut_scale[2]));
+        for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
+        if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = -INFINITY; }
+    }
+    // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
+    // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
+    uint32_t qB[NT][8][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        const int head = NT == 1 ? (g & 3) : g;
+        const bool low = NT == 1 ? (g >= 4) : (nt == 1);
+        const float *qr = a.qrot + ((size_t)bh * G + (head < G ? head : 0)) * kD + 32 * t;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+            __half h[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                float v = head < G ? qr[4 * s + e] : 0.f;
+                __half hv = __float2half_rn(v);
+                h[e] = low ? __float2half_rn(v - __half2float(hv)) : hv;
+            }
+            qB[nt][s][0] = pack_half2(h[0], h[1]);
+            qB[nt][s][1] = pack_half2(h[2], h[3]);
+        }
+    }
+    __syncthreads();
+
+    MmaState<NT> st;
+    st.M[0] = st.M[1] = -INFINITY;
+    st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st.O[nt][m][i] = 0.f;
+
+    for (int ci = 0; ci < chunks.n; ++ci) {
+        const odmkv_chunk &ch = chunks.ch[ci];
+        for (int c = 1; c <= 3; ++c) {
+            const int cnt = ch.seg_count[c * BH + bh];
+            if (cnt == 0) continue;
+            const int s0 = ch.seg_start[c * BH + bh];
+            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut2, a.scale_log2, a.lut_scale[0]);
+            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut3, a.scale_log2, a.lut_scale[1]);
+            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut4, a.scale_log2, a.lut_scale[2]);
+        }
+    }
+
+    // ---- per-warp totals: denominators summed over the 8 row groups; NT = 1: lanes t and t^2 hold copies
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+        st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
+        st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
+    }
+    // head slots of this lane's two columns
+    const int h0 = NT == 1 ? 2 * (t & 1) : 2 * t, h1 = h0 + 1;
+    const bool owner = NT == 1 ? (t < 2) : true;   // one lane per (g, head pair) publishes
+    if (NT == 1) {
+        // fold the low-limb columns (lanes t >= 2) into the high-limb lanes
+#pragma unroll
+        for (int m = 0; m < 8; ++m)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) st.O[0][m][i] += __shfl_xor_sync(0xffffffffu, st.O[0][m][i], 2);
+    }
+    if (g == 0 && owner) { warpM[warp][h0] = st.M[0]; warpM[warp][h1] = st.M[1]; }
+    __syncthreads();
+    if (tid < NH) {
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) m = fmaxf(m, warpM[w][tid]);
+        Msh[tid] = m;
+    }
+    __syncthreads();
+    const float c0 = st.M[0] == -INFINITY ? 0.f : exp2f(st.M[0] - Msh[h0]);
+    const float c1 = st.M[1] == -INFINITY ? 0.f : exp2f(st.M[1] - Msh[h1]);
+    for (int w = 0; w < kMmaWarps; ++w) {   // fixed order: the sum is reproducible
+        if (warp == w && owner) {
+#pragma unroll
+            for (int m = 0; m < 8; ++m) {
+                float v0 = st.O[0][m][0], v1 = st.O[0][m][1], v2 = st.O[0][m][2], v3 = st.O[0][m][3];
+                if (NT == 2) { v0 += st.O[NT - 1][m][0]; v1 += st.O[NT - 1][m][1]; v2 += st.O[NT - 1][m][2]; v3 += st.O[NT - 1][m][3]; }
+                Osh[h0][16 * m + g] += v0 * c0;
+                Osh[h1][16 * m + g] += v1 * c1;
+                Osh[h0][16 * m + g + 8] += v2 * c0;
+                Osh[h1][16 * m + g + 8] += v3 * c1;
+            }
+            if (g == 0) { lsh[h0] += st.l[0] * c0; lsh[h1] += st.l[1] * c1; }
+        }
+        __syncthreads();
+    }
+    // ---- write the partial (natural-log maximum, code-space accumulator; exact-space part is zero)
+    const int GP = round_gp(G);
+    for (int e = tid; e < GP * 2 * kD; e += kMmaThreads) {
+        const int gq = e / (2 * kD), rest = e % (2 * kD);
+        const size_t pi = ((size_t)bh * a.nslots + a.slot_base + split) * GP + gq;
+        float v = 0.f;
+        if (rest < kD && gq < NH) v = Osh[gq][rest];
+        a.part_acc[pi * 2 * kD + rest] = v;
+        if (rest == 0) {
+            a.part_ml[pi * 2] = gq < NH ? Msh[gq] * 0.6931471805599453f : -INFINITY;
+            a.part_ml[pi * 2 + 1] = gq < NH ? lsh[gq] : 0.f;
+        }
+    }
+}
+
+}  // namespace odmkv
+
+using namespace odmkv;
+
+extern "C" {
+
+// Same arguments as odmkv_decode_attn plus `lut_scales` (host float[3] or NULL for 1.0): per level a
+// factor s such that fp16(c * s) represents the centroids of the 2-, 3- and 4-bit codebooks with less
+// rounding error than fp16(c); the kernel divides it out again in fp32.
+int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                          const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                          const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                          int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                          const float *lut_scales, void *stream) {
+    DecodeChunks dc;
+    int rc = decode_check_args(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len, tail_cap, pi_k, pi_v, codebooks,
+                               B, H, G, out, out_dtype, n_splits, workspace, &dc);
+    if (rc) return rc;
+    // exact / 8-bit / tail tokens: a few CTAs of the CUDA-core kernel per (b, h)
+    long long side_tokens = tail_len;
+    for (int i = 0; i < n_chunks; ++i) side_tokens += ((long long)chunks[i].cap[4] + chunks[i].cap[5]) / ((long long)B * H) + 1;
+    int ns_side = (int)((side_tokens + 255) / 256);
+    if (ns_side < 1) ns_side = 1;
+    if (ns_side > 8) ns_side = 8;
+    const int nslots = n_splits + ns_side;
+    DecodeWs ws;
+    if (workspace_bytes < decode_ws_layout(B, H, G, nslots, &ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int BH = B * H;
+    launch_rotate_q(q, q_dtype, pi_k, ws, BH * G, st);
+    MmaArgs m;
+    m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc;
+    m.B = B; m.H = H; m.G = G; m.nsplit = n_splits; m.slot_base = 0; m.nslots = nslots;
+    m.scale_log2 = scale * 1.4426950408889634f;
+    for (int i = 0; i < 3; ++i) m.lut_scale[i] = lut_scales ? lut_scales[i] : 1.0f;
+    dim3 grid(n_splits, BH);
+    timing_begin("decode_main", st);
+    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, 0, st>>>(dc, m);
+    else decode_mma_kernel<2><<<grid, kMmaThreads, 0, st>>>(dc, m);
+    timing_end(st);
+    DecodeArgs a;
+    a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
+    a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
+    a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
+    a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
+    launch_decode_cuda_core(dc, a, cache_dtype, st);
+    launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st);
+    return launch_status();
+}
+
+}  // extern "C"

@@ -87,6 +87,7 @@ struct QuantArgs {
     const float *pi_v;
     const float *codebooks;
     const int32_t *tile_base;
+    uint8_t *v_scratch[3];   // linear-layout value codes of the 2/3/4-bit banks before re-tiling
     odmkv_chunk ch;
     int ntiles;
 };
@@ -121,26 +122,37 @@ __device__ inline void tile_product(const float *__restrict__ Xs, const float *_
     }
 }
 
-// pack the staged codes of one row and store them at its slot
-__device__ inline void store_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ dst, int lane) {
-    if (li == 0 || li == 1) {
-        uint32_t b = (row[4 * lane] & 3) | ((row[4 * lane + 1] & 3) << 2) | ((row[4 * lane + 2] & 3) << 4) |
-                     ((row[4 * lane + 3] & 3) << 6);
-        dst[lane] = (uint8_t)b;
-        if (li == 1 && lane < 16) {
-            uint32_t h = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) h |= ((row[8 * lane + i] >> 2) & 1u) << i;
-            dst[32 + lane] = (uint8_t)h;
+// Pack four staged codes per lane.  `j` is the lane's position inside the destination bit stream (each
+// lane contributes 4*b bits at bit offset 4*b*j); called by a full warp.
+__device__ inline void pack_lane_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ dst, int lane, int j) {
+    const uint32_t c0 = row[4 * lane], c1 = row[4 * lane + 1], c2 = row[4 * lane + 2], c3 = row[4 * lane + 3];
+    if (li == 0) {
+        dst[j] = (uint8_t)((c0 & 3) | ((c1 & 3) << 2) | ((c2 & 3) << 4) | ((c3 & 3) << 6));
+    } else if (li == 1) {
+        const uint32_t v = (c0 & 7) | ((c1 & 7) << 3) | ((c2 & 7) << 6) | ((c3 & 7) << 9);
+        const uint32_t nxt = __shfl_down_sync(0xffffffffu, v, 1);
+        if ((j & 1) == 0) {
+            const uint32_t w = v | (nxt << 12);
+            uint8_t *q = dst + 3 * (j >> 1);
+            q[0] = (uint8_t)w; q[1] = (uint8_t)(w >> 8); q[2] = (uint8_t)(w >> 16);
         }
     } else if (li == 2) {
-        uint32_t b0 = (row[4 * lane] & 15) | ((row[4 * lane + 1] & 15) << 4);
-        uint32_t b1 = (row[4 * lane + 2] & 15) | ((row[4 * lane + 3] & 15) << 4);
-        *reinterpret_cast<uint16_t *>(dst + 2 * lane) = (uint16_t)(b0 | (b1 << 8));
+        *reinterpret_cast<uint16_t *>(dst + 2 * j) = (uint16_t)((c0 & 15) | ((c1 & 15) << 4) | ((c2 & 15) << 8) | ((c3 & 15) << 12));
     } else {
-        uint32_t w = row[4 * lane] | (row[4 * lane + 1] << 8) | (row[4 * lane + 2] << 16) | (row[4 * lane + 3] << 24);
-        *reinterpret_cast<uint32_t *>(dst + 4 * lane) = w;
+        *reinterpret_cast<uint32_t *>(dst + 4 * j) = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
     }
+}
+
+// key codes of one slot: tile layout for 2/3/4 bits (lane covers coordinates 4*lane .. 4*lane+3, i.e.
+// two pair fields of row part lane / 8), token-major for 8 bits
+__device__ inline void store_key_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ bank, long long slot, int lane) {
+    if (li == 3) pack_lane_codes(row, 3, bank + (size_t)slot * 128, lane, lane);
+    else pack_lane_codes(row, li, bank + k_part_offset(qbits(li), slot, lane >> 3), lane, lane & 7);
+}
+
+// value codes of one slot in the linear layout (scratch for 2/3/4 bits, final for 8 bits)
+__device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ rows, long long slot, int lane) {
+    pack_lane_codes(row, li, rows + (size_t)slot * 16 * qbits(li), lane, lane);
 }
 
 template <int DT>
@@ -268,8 +280,8 @@ __global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
                 int t_abs = a.ch.t_offset + t0 + r;
                 if (cc >= 1 && cc <= 4) {
                     int li = cc - 1;
-                    uint8_t *dst = (side ? a.ch.v_codes[li] : a.ch.k_codes[li]) + (size_t)s * code_bytes(li);
-                    store_codes(C8 + r * kLdC, li, dst, lane);
+                    if (side == 0) store_key_codes(C8 + r * kLdC, li, a.ch.k_codes[li], s, lane);
+                    else store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.v_codes[3] : a.v_scratch[li], s, lane);
                     if (lane == 0) {
                         (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
                         if (side == 0) a.ch.pos[li][s] = t_abs;
@@ -294,7 +306,11 @@ __global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
 
 // zero the padding slots between a segment's last token and the next 16-slot boundary
 template <int DT>
-__global__ void fill_padding_kernel(const odmkv_chunk ch) {
+__global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *v_scratch0, uint8_t *v_scratch1, uint8_t *v_scratch2) {
+    uint8_t *v_scratch[3] = {v_scratch0, v_scratch1, v_scratch2};
+    __shared__ uint8_t zero_row[kD];
+    if (threadIdx.x < kD) zero_row[threadIdx.x] = 0;
+    __syncthreads();
     const int BH = ch.B * ch.H;
     const int bh = blockIdx.x, c = blockIdx.y;
     const int cnt = ch.seg_count[c * BH + bh];
@@ -314,17 +330,41 @@ __global__ void fill_padding_kernel(const odmkv_chunk ch) {
             }
             if (lane == 0) ch.exact_pos[s] = -1;
         } else {
-            const int li = c - 1, nb = code_bytes(li);
-            for (int i = lane; i < nb; i += 32) {
-                ch.k_codes[li][(size_t)s * nb + i] = 0;
-                ch.v_codes[li][(size_t)s * nb + i] = 0;
-            }
+            const int li = c - 1;
+            store_key_codes(zero_row, li, ch.k_codes[li], s, lane);
+            store_linear_codes(zero_row, li, li == 3 ? ch.v_codes[3] : v_scratch[li], s, lane);
             if (lane == 0) {
                 ch.k_norm[li][s] = 0.f;
                 ch.v_norm[li][s] = 0.f;
                 ch.pos[li][s] = -1;
             }
         }
+    }
+}
+
+// re-tile the value codes of one 2/3/4-bit bank: linear scratch rows -> tensor-core tile layout
+// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes)
+template <int B>
+__global__ void retile_values_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
+    constexpr int LI = B - 2;
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    for (int tile = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tile < ntiles; tile += gridDim.x * (blockDim.x >> 5)) {
+        uint32_t out[2 * B];
+#pragma unroll
+        for (int w = 0; w < 2 * B; ++w) out[w] = 0;
+#pragma unroll
+        for (int f = 0; f < 32; ++f) {
+            const int m = f >> 2, hi = (f >> 1) & 1, a = f & 1;
+            const int dim = 16 * m + g + 8 * a;
+            const long long slot = (long long)tile * 16 + 2 * t + 8 * hi;
+            const uint32_t field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot + 1, dim) << B);
+            const int off = f * 2 * B, w = off >> 5, sh = off & 31;
+            out[w] |= field << sh;
+            if (sh + 2 * B > 32) out[w + 1] |= field >> (32 - sh);
+        }
+        uint32_t *dst = reinterpret_cast<uint32_t *>(bank + (size_t)tile * 256 * B + (size_t)lane * 8 * B);
+#pragma unroll
+        for (int w = 0; w < 2 * B; ++w) dst[w] = out[w];
     }
 }
 
@@ -341,7 +381,7 @@ __global__ void encode_pack_kernel(const float *__restrict__ y, long long n, int
 #pragma unroll
         for (int q = 0; q < 4; ++q) stage[warp][lane + 32 * q] = (uint8_t)nearest_centroid(y[r * kD + lane + 32 * q], cb, k);
         __syncwarp();
-        store_codes(stage[warp], li, out + (size_t)r * code_bytes(li), lane);
+        store_linear_codes(stage[warp], li, out, r, lane);
         __syncwarp();
     }
 }
@@ -405,7 +445,6 @@ __global__ void __launch_bounds__(256, 1) dequant_kernel(const DequantArgs a) {
         const int s0 = (w - a.tiles_before[li]) * kTile;
         const int end = bank_end(a.ch, c);
         if (s0 >= end) continue;  // uniform across the block
-        const int nb = code_bytes(li);
         if (tid < kTile) {
             int s = s0 + tid;
             long long row = -1;
@@ -426,9 +465,12 @@ __global__ void __launch_bounds__(256, 1) dequant_kernel(const DequantArgs a) {
             {   // centroid gather: two threads per row
                 int r = tid >> 1, half = tid & 1, s = s0 + r;
                 bool ok = s < end;
-                const uint8_t *row = codes + (size_t)(ok ? s : 0) * nb;
                 const float *cbl = cb + li * 256;
-                for (int i = half * 64; i < half * 64 + 64; ++i) Xs[r * kLd + i] = ok ? cbl[extract_code(row, li, i)] : 0.f;
+                for (int i = half * 64; i < half * 64 + 64; ++i) {
+                    float v = 0.f;
+                    if (ok) v = cbl[side ? v_code(codes, li, s, i) : k_code(codes, li, s, i)];
+                    Xs[r * kLd + i] = v;
+                }
                 if (half == 0) nrm[r] = ok ? norms[s] : 0.f;
             }
             __syncthreads();
@@ -478,20 +520,23 @@ __global__ void export_bank_kernel(const odmkv_chunk ch, int c, const int32_t *_
                                    float *__restrict__ nv, int64_t *__restrict__ positions) {
     const int BH = ch.B * ch.H, bh = blockIdx.x, li = c - 1;
     const int cnt = ch.seg_count[c * BH + bh], s0 = ch.seg_start[c * BH + bh], r0 = row_start[bh];
-    const int nb = code_bytes(li), rb = ref_code_bytes(li);
+    const int rb = ref_code_bytes(li);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int k = warp; k < cnt; k += blockDim.x >> 5) {
         const size_t s = (size_t)s0 + k, r = (size_t)r0 + k;
         for (int side = 0; side < 2; ++side) {
-            const uint8_t *src = (side ? ch.v_codes[li] : ch.k_codes[li]) + s * nb;
+            const uint8_t *bank = side ? ch.v_codes[li] : ch.k_codes[li];
             uint8_t *dst = (side ? iv : ik) + r * rb;
-            if (li == 1) {
-                for (int j = lane; j < 64; j += 32) {
-                    int c0 = extract_code(src, 1, 2 * j), c1 = extract_code(src, 1, 2 * j + 1);
-                    dst[j] = (uint8_t)(c0 | (c1 << 4));
+            for (int j = lane; j < rb; j += 32) {
+                uint32_t out = 0;
+                if (li == 0) {
+                    for (int e = 0; e < 4; ++e) out |= (uint32_t)(side ? v_code(bank, li, s, 4 * j + e) : k_code(bank, li, s, 4 * j + e)) << (2 * e);
+                } else if (li == 3) {
+                    out = side ? v_code(bank, li, s, j) : k_code(bank, li, s, j);
+                } else {
+                    for (int e = 0; e < 2; ++e) out |= (uint32_t)(side ? v_code(bank, li, s, 2 * j + e) : k_code(bank, li, s, 2 * j + e)) << (4 * e);
                 }
-            } else {
-                for (int j = lane; j < nb; j += 32) dst[j] = src[j];
+                dst[j] = (uint8_t)out;
             }
         }
         if (lane == 0) {
@@ -570,12 +615,22 @@ static int check_chunk(const odmkv_chunk *ch) {
     return ODMKV_OK;
 }
 
+size_t odmkv_quantize_workspace_bytes(const int32_t *cap) {
+    if (!cap) return 0;
+    size_t n = 0;
+    for (int li = 0; li < 3; ++li) n += ((size_t)(cap[li + 1] > 0 ? cap[li + 1] : 0) * 16 * qbits(li) + 255) / 256 * 256;
+    return n + 256;
+}
+
 int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
                         const float *pi_v, const float *codebooks, const odmkv_chunk *chunk,
-                        const void *plan_workspace, void *stream) {
-    if (!K || !V || !bits || !pi_k || !pi_v || !codebooks || !plan_workspace) return ODMKV_ERR_ARG;
+                        const void *plan_workspace, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!K || !V || !bits || !pi_k || !pi_v || !codebooks || !plan_workspace || !workspace) return ODMKV_ERR_ARG;
     int rc = check_chunk(chunk);
     if (rc) return rc;
+    if (((uintptr_t)workspace & 255) != 0 || workspace_bytes < odmkv_quantize_workspace_bytes(chunk->cap)) return ODMKV_ERR_WORKSPACE;
+    for (int c = 1; c <= 3; ++c)
+        if (chunk->cap[c] % 16 != 0) return ODMKV_ERR_SHAPE;
     if (chunk->T <= 0) return ODMKV_ERR_SHAPE;
     if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
@@ -585,6 +640,13 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     const int BH = chunk->B * chunk->H;
     a.ntiles = (chunk->T + kTile - 1) / kTile;
     a.tile_base = (const int32_t *)plan_workspace + (size_t)BH * a.ntiles * kNumClasses;
+    {
+        size_t off = 0;
+        for (int li = 0; li < 3; ++li) {
+            a.v_scratch[li] = (uint8_t *)workspace + off;
+            off += ((size_t)chunk->cap[li + 1] * 16 * qbits(li) + 255) / 256 * 256;
+        }
+    }
     long long n_work = (long long)BH * a.ntiles;
     int grid = (int)(n_work < num_sms() ? n_work : num_sms());
     dim3 pad_grid(BH, kNumClasses);
@@ -592,12 +654,22 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
 #define ODMKV_LAUNCH_Q(DT)                                                                                   \
     e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantSmem); \
     if (e != cudaSuccess) return (int)e;                                                                     \
-    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk);                                               \
+    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
     timing_begin("quantize", st);                                                                            \
     quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);                                                   \
     timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q
+    // values of the 2/3/4-bit banks: linear scratch -> tile layout
+    for (int li = 0; li < 3; ++li) {
+        const int ntile = chunk->cap[li + 1] / 16;
+        if (ntile <= 0) continue;
+        int rg = (ntile + 7) / 8;
+        if (rg > 16 * num_sms()) rg = 16 * num_sms();
+        if (li == 0) retile_values_kernel<2><<<rg, 256, 0, st>>>(a.v_scratch[0], chunk->v_codes[0], ntile);
+        else if (li == 1) retile_values_kernel<3><<<rg, 256, 0, st>>>(a.v_scratch[1], chunk->v_codes[1], ntile);
+        else retile_values_kernel<4><<<rg, 256, 0, st>>>(a.v_scratch[2], chunk->v_codes[2], ntile);
+    }
     return launch_status();
 }
 

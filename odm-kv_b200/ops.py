@@ -264,8 +264,10 @@ def quantize_pack(K: torch.Tensor, V: torch.Tensor, bits: torch.Tensor, pi_k: to
     ch.exact_pos = torch.empty(n16, dtype=torch.int32, device=dev)
     ch.evicted_pos = torch.empty(max(totals[0], 1), dtype=torch.int32, device=dev)
     cs = ch.c_struct()
+    scratch = _ws(L.odmkv_quantize_workspace_bytes(cs.cap), dev)   # linear value codes before re-tiling
     check(L.odmkv_quantize_pack(ptr(K), ptr(V), dtype_code(K.dtype), ptr(bits), ptr(pi_k), ptr(pi_v),
-                                ptr(codebook_table(dev)), ctypes.byref(cs), ptr(plan), st), "odmkv_quantize_pack")
+                                ptr(codebook_table(dev)), ctypes.byref(cs), ptr(plan), ptr(scratch), scratch.numel(), st),
+          "odmkv_quantize_pack")
     return ch
 
 
@@ -339,6 +341,26 @@ def export_exact_rows(ch: PackedChunk) -> Tuple[torch.Tensor, torch.Tensor, torc
 # decode attention
 # ---------------------------------------------------------------------------------------------
 
+_LUT_SCALES = None
+
+
+def lut_scales():
+    """Per level (2, 3, 4 bits) a factor s in [1, 2) that minimises the worst relative error of
+    fp16(c * s) / s over the level's centroids; the tensor-core kernel stores fp16(c * s) in its tables."""
+    global _LUT_SCALES
+    if _LUT_SCALES is None:
+        cand = np.linspace(1.0, 2.0, 40001, dtype=np.float64)[:-1]
+        best = []
+        for b in QLEVEL_BITS[:3]:
+            c = codebook_f32(b).astype(np.float64)
+            prod = (c[None, :] * cand[:, None]).astype(np.float32)
+            back = prod.astype(np.float16).astype(np.float64) / cand[:, None]
+            err = np.abs(back - c[None, :]) / np.abs(c[None, :])
+            best.append(float(np.float32(cand[int(np.argmin(err.max(axis=1)))])))
+        _LUT_SCALES = (ctypes.c_float * 3)(*best)
+    return _LUT_SCALES
+
+
 def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tensor, pi_v: torch.Tensor,
                 tail_k: Optional[torch.Tensor] = None, tail_v: Optional[torch.Tensor] = None, tail_len: int = 0,
                 scale: Optional[float] = None, n_splits: int = 0, out_dtype: Optional[torch.dtype] = None,
@@ -369,6 +391,8 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
     if n_splits <= 0:
         per_head = sum(c.stored_tokens() for c in chunks) // max(B * H, 1) + tail_len
         n_splits = L.odmkv_decode_default_splits(B, H, per_head)
+    if impl in ("v1", "cuda_core"):
+        n_splits = min(n_splits, 64)
     out = torch.empty(B, Hq, HEAD_DIM, dtype=out_dtype or q.dtype, device=dev)
     lse = torch.empty(B, Hq, dtype=torch.float32, device=dev) if return_lse else None
     ws = _ws(L.odmkv_decode_workspace_bytes(B, H, G, n_splits), dev)
@@ -377,10 +401,13 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
         arr[i] = c.c_struct()
     cap = 0 if tail_k is None else tail_k.shape[2]
     scale = (1.0 / HEAD_DIM ** 0.5) if scale is None else float(scale)
-    fn = L.odmkv_decode_attn
-    if impl == "mma" or (impl == "auto" and hasattr(L, "odmkv_decode_attn_mma")):
-        fn = L.odmkv_decode_attn_mma
-    check(fn(ptr(q), dtype_code(q.dtype), arr, len(chunks), dtype_code(cdt), ptr(tail_k), ptr(tail_v), int(tail_len), int(cap),
-             ptr(pi_k), ptr(pi_v), ptr(codebook_table(dev)), B, H, G, scale, ptr(out), dtype_code(out.dtype), ptr(lse),
-             int(n_splits), ptr(ws), ws.numel(), stream_ptr(dev)), "odmkv_decode_attn")
+    common = (ptr(q), dtype_code(q.dtype), arr, len(chunks), dtype_code(cdt), ptr(tail_k), ptr(tail_v), int(tail_len), int(cap),
+              ptr(pi_k), ptr(pi_v), ptr(codebook_table(dev)), B, H, G, scale, ptr(out), dtype_code(out.dtype), ptr(lse),
+              int(n_splits), ptr(ws), ws.numel())
+    if impl in ("auto", "mma"):
+        check(L.odmkv_decode_attn_mma(*common, lut_scales(), stream_ptr(dev)), "odmkv_decode_attn_mma")
+    elif impl in ("v1", "cuda_core"):
+        check(L.odmkv_decode_attn(*common, stream_ptr(dev)), "odmkv_decode_attn")
+    else:
+        raise ValueError(f"unknown decode implementation {impl!r}")
     return (out, lse) if return_lse else out

@@ -24,20 +24,9 @@ def random_bits(rng, B, H, T, probs=(0.12, 0.5, 0.2, 0.08, 0.05, 0.05)):
 
 
 def unpack_slot_codes(packed, bits):
-    """This library's slot layout -> codes [n, 128]."""
-    packed = packed.astype(np.uint8)
-    if bits == 2:
-        sh = np.arange(4, dtype=np.uint8) * 2
-        return ((packed[:, :, None] >> sh) & 3).reshape(packed.shape[0], -1)
-    if bits == 3:
-        sh = np.arange(4, dtype=np.uint8) * 2
-        lo = ((packed[:, :32, None] >> sh) & 3).reshape(packed.shape[0], -1)
-        hi = ((packed[:, 32:, None] >> np.arange(8, dtype=np.uint8)) & 1).reshape(packed.shape[0], -1)
-        return lo | (hi << 2)
-    if bits == 4:
-        sh = np.arange(2, dtype=np.uint8) * 4
-        return ((packed[:, :, None] >> sh) & 15).reshape(packed.shape[0], -1)
-    return packed
+    """Little-endian bit stream of 128 codes per row -> codes [n, 128]."""
+    bitsarr = np.unpackbits(packed.astype(np.uint8), axis=1, bitorder="little").reshape(packed.shape[0], 128, bits)
+    return (bitsarr * (1 << np.arange(bits, dtype=np.uint8))).sum(axis=2).astype(np.uint8)
 
 
 @pytest.mark.parametrize("bits", QBITS)
