@@ -46,6 +46,21 @@ __device__ inline uint32_t movmatrix_trans(uint32_t x) {
     return y;
 }
 
+__device__ inline float fast_exp2(float x) {
+    float y;
+    asm volatile("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int N>
+__device__ inline void cp_async(void *smem, const void *gmem) {
+    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(s), "l"(gmem), "n"(N) : "memory");
+}
+__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ inline void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
 __device__ inline uint32_t pack_half2(__half lo, __half hi) {
     return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
 }
@@ -61,12 +76,56 @@ __device__ inline uint32_t pair_field(const uint32_t *w, int f) {
     return v & ((1u << (2 * B)) - 1u);
 }
 
-// table lookup: 2- and 3-bit tables hold one copy per lane (index * 32 + lane) so that a warp's reads
-// never collide; the 4-bit table is a single copy
+// Table lookups.  `tb` is this lane's view of the level's table in shared memory:
+//   2 bits: 256 entries of two half2 (one per nibble of a code byte), 16 interleaved copies -- a lane
+//           reads (byte * 16 + lane % 16) * 8 bytes, so the 16 lanes of a half-warp never collide;
+//   3 bits: 64 entries of one half2 (a pair field of 6 bits), 32 interleaved copies;
+//   4 bits: 256 entries of one half2 (a pair field = one byte), a single copy.
+// Each lookup is written as extract + scaled add + load so that it compiles to three instructions.
 template <int B>
-__device__ inline uint32_t lut_pair(const uint32_t *__restrict__ lut, uint32_t idx, int lane) {
-    if (B == 4) return lut[idx];
-    return lut[idx * 32 + lane];
+__device__ inline void decode_k(const uint8_t *__restrict__ tb, const uint32_t *kw, int s, uint32_t (&a)[4]) {
+    if (B == 2) {
+        // byte s of row part 0 = fields (2s, 2s+1) -> (a0, a2); byte s of row part 1 -> (a1, a3)
+        const uint32_t i0 = __byte_perm(kw[s >> 2], 0, 0x4440 | (s & 3));
+        const uint32_t i1 = __byte_perm(kw[2 + (s >> 2)], 0, 0x4440 | (s & 3));
+        const uint2 e0 = *reinterpret_cast<const uint2 *>(tb + i0 * 128);
+        const uint2 e1 = *reinterpret_cast<const uint2 *>(tb + i1 * 128);
+        a[0] = e0.x; a[2] = e0.y; a[1] = e1.x; a[3] = e1.y;
+    } else if (B == 3) {
+        a[0] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw, 2 * s) * 128);
+        a[1] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw + 3, 2 * s) * 128);
+        a[2] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw, 2 * s + 1) * 128);
+        a[3] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw + 3, 2 * s + 1) * 128);
+    } else {
+        // a pair field is one byte: row part 0 = words 0..3, row part 1 = words 4..7
+        const int f0 = 2 * s, f1 = 2 * s + 1;
+        a[0] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[f0 >> 2], 0, 0x4440 | (f0 & 3)) * 4);
+        a[1] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[4 + (f0 >> 2)], 0, 0x4440 | (f0 & 3)) * 4);
+        a[2] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[f1 >> 2], 0, 0x4440 | (f1 & 3)) * 4);
+        a[3] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[4 + (f1 >> 2)], 0, 0x4440 | (f1 & 3)) * 4);
+    }
+}
+
+template <int B>
+__device__ inline void decode_v(const uint8_t *__restrict__ tb, const uint32_t *vw, int m, uint32_t (&a)[4]) {
+    if (B == 2) {
+        // bytes 2m, 2m+1 = fields (4m, 4m+1), (4m+2, 4m+3)
+        const int b0 = 2 * m, b1 = 2 * m + 1;
+        const uint32_t i0 = __byte_perm(vw[b0 >> 2], 0, 0x4440 | (b0 & 3));
+        const uint32_t i1 = __byte_perm(vw[b1 >> 2], 0, 0x4440 | (b1 & 3));
+        const uint2 e0 = *reinterpret_cast<const uint2 *>(tb + i0 * 128);
+        const uint2 e1 = *reinterpret_cast<const uint2 *>(tb + i1 * 128);
+        a[0] = e0.x; a[1] = e0.y; a[2] = e1.x; a[3] = e1.y;
+    } else if (B == 3) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(vw, 4 * m + r) * 128);
+    } else {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+            const int f = 4 * m + r;
+            a[r] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(vw[f >> 2], 0, 0x4440 | (f & 3)) * 4);
+        }
+    }
 }
 
 template <int NT>
@@ -77,7 +136,7 @@ struct MmaState {
 
 template <int B, int NT>
 __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B], const uint32_t (&vw)[2 * B], float kn0, float kn1,
-                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], const uint32_t *__restrict__ lut,
+                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], const uint8_t *__restrict__ tb,
                                     int lane, float kfac, float inv_lut_scale) {
     const int g = lane >> 2, t = lane & 3;
     // ---- S = K_dec . q'^T
@@ -89,10 +148,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         uint32_t a[4];
-        a[0] = lut_pair<B>(lut, pair_field<B>(kw, 2 * s), lane);
-        a[1] = lut_pair<B>(lut, pair_field<B>(kw + B, 2 * s), lane);
-        a[2] = lut_pair<B>(lut, pair_field<B>(kw, 2 * s + 1), lane);
-        a[3] = lut_pair<B>(lut, pair_field<B>(kw + B, 2 * s + 1), lane);
+        decode_k<B>(tb, kw, s, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
     }
@@ -123,8 +179,8 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
             zm1 = fmaxf(zm1, __shfl_xor_sync(0xffffffffu, zm1, o));
         }
         const float n0 = fmaxf(st.M[0], zm0), n1 = fmaxf(st.M[1], zm1);
-        const float c0 = st.M[0] == -INFINITY ? 0.f : exp2f(st.M[0] - n0);
-        const float c1 = st.M[1] == -INFINITY ? 0.f : exp2f(st.M[1] - n1);
+        const float c0 = st.M[0] == -INFINITY ? 0.f : fast_exp2(st.M[0] - n0);
+        const float c1 = st.M[1] == -INFINITY ? 0.f : fast_exp2(st.M[1] - n1);
         st.M[0] = n0; st.M[1] = n1;
         st.l[0] *= c0; st.l[1] *= c1;
 #pragma unroll
@@ -135,10 +191,10 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
             }
     }
     float W[4];
-    W[0] = ok0 ? exp2f(z[0] - st.M[0]) : 0.f;
-    W[1] = ok0 ? exp2f(z[1] - st.M[1]) : 0.f;
-    W[2] = ok1 ? exp2f(z[2] - st.M[0]) : 0.f;
-    W[3] = ok1 ? exp2f(z[3] - st.M[1]) : 0.f;
+    W[0] = ok0 ? fast_exp2(z[0] - st.M[0]) : 0.f;
+    W[1] = ok0 ? fast_exp2(z[1] - st.M[1]) : 0.f;
+    W[2] = ok1 ? fast_exp2(z[2] - st.M[0]) : 0.f;
+    W[3] = ok1 ? fast_exp2(z[3] - st.M[1]) : 0.f;
     st.l[0] += W[0] * rv0 + W[2] * rv1;
     st.l[1] += W[1] * rv0 + W[3] * rv1;
     // ---- P operand: fp16 high limb and low limb of every weight
@@ -163,24 +219,60 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
         uint32_t a[4];
-#pragma unroll
-        for (int r = 0; r < 4; ++r) a[r] = lut_pair<B>(lut, pair_field<B>(vw, 4 * m + r), lane);
+        decode_v<B>(tb, vw, m, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[nt][0], pb[nt][1]);
     }
 }
 
+// Per-lane staging: every lane copies its own key chunk, value chunk and four norms of a tile into
+// its private 80-byte slot of a ring of kStages tiles with cp.async, and later reads back only what it
+// wrote itself, so completion needs cp.async.wait_group alone -- no barrier and no flag to spin on.
+constexpr int kStages = 3;
+constexpr int kLaneStage = 80;                       // 32 B keys + 32 B values + 16 B norms
+constexpr int kWarpStage = 32 * kLaneStage;          // one tile of one warp
+constexpr int kRingBytes = kMmaWarps * kStages * kWarpStage;
+constexpr int kLut2Bytes = 256 * 16 * 8;             // byte -> two half2, 16 copies
+constexpr int kLut3Bytes = 64 * 32 * 4;              // 6-bit pair -> half2, 32 copies
+constexpr int kLut4Bytes = 256 * 4;                  // byte pair -> half2, one copy
+constexpr int kStageBytes = kLut2Bytes + kLut3Bytes + kLut4Bytes + kRingBytes;
+
 template <int B>
-__device__ inline void load_words(const uint8_t *__restrict__ p, uint32_t (&w)[2 * B]) {
+__device__ inline void issue_tile(uint8_t *__restrict__ mine, const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb,
+                                  const float *__restrict__ kn, const float *__restrict__ vn, int slot0, int lane) {
+    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
+    const int g = lane >> 2;
+    if (B == 2) {
+        cp_async<16>(mine, kb + off);
+        cp_async<16>(mine + 32, vb + off);
+    } else if (B == 3) {
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            cp_async<8>(mine + 8 * i, kb + off + 8 * i);
+            cp_async<8>(mine + 32 + 8 * i, vb + off + 8 * i);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            cp_async<16>(mine + 16 * i, kb + off + 16 * i);
+            cp_async<16>(mine + 32 + 16 * i, vb + off + 16 * i);
+        }
+    }
+    cp_async<4>(mine + 64, kn + slot0 + g);
+    cp_async<4>(mine + 68, kn + slot0 + g + 8);
+    cp_async<4>(mine + 72, vn + slot0 + g);
+    cp_async<4>(mine + 76, vn + slot0 + g + 8);
+}
+
+template <int B>
+__device__ inline void read_words(const uint8_t *__restrict__ p, uint32_t (&w)[2 * B]) {
     if (B == 2) {
         uint4 v = *reinterpret_cast<const uint4 *>(p);
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else if (B == 3) {
-#pragma unroll
-        for (int i = 0; i < 3; ++i) {
-            uint2 v = reinterpret_cast<const uint2 *>(p)[i];
-            w[2 * i] = v.x; w[2 * i + 1] = v.y;
-        }
+        uint4 v = *reinterpret_cast<const uint4 *>(p);
+        uint2 u = *reinterpret_cast<const uint2 *>(p + 16);
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; w[4] = u.x; w[5] = u.y;
     } else {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
@@ -192,33 +284,48 @@ __device__ inline void load_words(const uint8_t *__restrict__ p, uint32_t (&w)[2
 
 template <int B, int NT>
 __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
-                                       const uint32_t (&qB)[NT][8][2], const uint32_t *__restrict__ lut, float scale_log2, float lut_scale) {
+                                       const uint32_t (&qB)[NT][8][2], const uint8_t *__restrict__ tb, float scale_log2, float lut_scale,
+                                       uint8_t *__restrict__ ring /* this lane's slot of stage 0 of this warp */) {
     constexpr int LI = B - 2;
     const int ntiles = (cnt + 15) >> 4;
     const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
-    const int g = lane >> 2;
     const float kfac = scale_log2 / lut_scale, inv_ls = 1.0f / lut_scale;
     const uint8_t *kb = ch.k_codes[LI], *vb = ch.v_codes[LI];
     const float *kn = ch.k_norm[LI], *vn = ch.v_norm[LI];
-    for (int ti = t_lo + warp; ti < t_hi; ti += kMmaWarps) {
-        const int slot0 = s0 + ti * 16;
-        const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
-        uint32_t kw[2 * B], vw[2 * B];
-        load_words<B>(kb + off, kw);
-        load_words<B>(vb + off, vw);
-        const float kn0 = kn[slot0 + g], kn1 = kn[slot0 + g + 8], vn0 = vn[slot0 + g], vn1 = vn[slot0 + g + 8];
-        process_tile<B, NT>(st, kw, vw, kn0, kn1, vn0, vn1, min(16, cnt - ti * 16), qB, lut, lane, kfac, inv_ls);
+    const int first = t_lo + warp;
+    // prologue: kStages - 1 tiles in flight
+#pragma unroll
+    for (int d = 0; d < kStages - 1; ++d) {
+        const int ti = first + d * kMmaWarps;
+        if (ti < t_hi) issue_tile<B>(ring + d * kWarpStage, kb, vb, kn, vn, s0 + ti * 16, lane);
+        cp_async_commit();
     }
+    int stage = 0;
+    for (int ti = first; ti < t_hi; ti += kMmaWarps) {
+        const int ahead = ti + (kStages - 1) * kMmaWarps;
+        int wstage = stage + kStages - 1;
+        if (wstage >= kStages) wstage -= kStages;
+        if (ahead < t_hi) issue_tile<B>(ring + wstage * kWarpStage, kb, vb, kn, vn, s0 + ahead * 16, lane);
+        cp_async_commit();
+        cp_async_wait<kStages - 1>();
+        const uint8_t *mine = ring + stage * kWarpStage;
+        uint32_t kw[2 * B], vw[2 * B];
+        read_words<B>(mine, kw);
+        read_words<B>(mine + 32, vw);
+        const float4 nr = *reinterpret_cast<const float4 *>(mine + 64);
+        process_tile<B, NT>(st, kw, vw, nr.x, nr.y, nr.z, nr.w, min(16, cnt - ti * 16), qB, tb, lane, kfac, inv_ls);
+        if (++stage == kStages) stage = 0;
+    }
+    cp_async_wait<0>();
 }
 
 template <int NT>
 __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeChunks chunks, const MmaArgs a) {
-    __shared__ uint32_t lut2[16 * 32];
-    __shared__ uint32_t lut3[64 * 32];
-    __shared__ uint32_t lut4[256];
     __shared__ float Osh[4 * NT][kD];
     __shared__ float lsh[4 * NT], Msh[4 * NT];
     __shared__ float warpM[kMmaWarps][4 * NT];
+    extern __shared__ __align__(128) uint8_t dyn[];
+    uint8_t *lut2 = dyn, *lut3 = dyn + kLut2Bytes, *lut4 = lut3 + kLut3Bytes, *stage_ring = lut4 + kLut4Bytes;
 
     const int bh = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
@@ -228,19 +335,24 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     // ---- tables of half2 centroid pairs
     {
         const float *c2 = a.codebooks, *c3 = a.codebooks + 256, *c4 = a.codebooks + 512;
-        for (int e = tid; e < 16 * 32; e += kMmaThreads) {
-            int idx = e >> 5;
-            lut2[e] = pack_half2(__float2half_rn(c2[idx & 3] * a.lut_scale[0]), __float2half_rn(c2[idx >> 2] * a.lut_scale[0]));
+        const float s2 = a.lut_scale[0], s3 = a.lut_scale[1], s4 = a.lut_scale[2];
+        for (int e = tid; e < 256 * 16; e += kMmaThreads) {
+            const int v = e >> 4;
+            uint2 ent;
+            ent.x = pack_half2(__float2half_rn(c2[v & 3] * s2), __float2half_rn(c2[(v >> 2) & 3] * s2));
+            ent.y = pack_half2(__float2half_rn(c2[(v >> 4) & 3] * s2), __float2half_rn(c2[(v >> 6) & 3] * s2));
+            reinterpret_cast<uint2 *>(lut2)[e] = ent;
         }
         for (int e = tid; e < 64 * 32; e += kMmaThreads) {
-            int idx = e >> 5;
-            lut3[e] = pack_half2(__float2half_rn(c3[idx & 7] * a.lut_scale[1]), __float2half_rn(c3[idx >> 3] * a.lut_scale[1]));
+            const int idx = e >> 5;
+            reinterpret_cast<uint32_t *>(lut3)[e] = pack_half2(__float2half_rn(c3[idx & 7] * s3), __float2half_rn(c3[idx >> 3] * s3));
         }
         for (int e = tid; e < 256; e += kMmaThreads)
-            lut4[e] = pack_half2(__float2half_rn(c4[e & 15] * a.lut_scale[2]), __float2half_rn(c4[e >> 4] * a.lut_scale[2]));
+            reinterpret_cast<uint32_t *>(lut4)[e] = pack_half2(__float2half_rn(c4[e & 15] * s4), __float2half_rn(c4[e >> 4] * s4));
         for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
         if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = -INFINITY; }
     }
+    const uint8_t *tb2 = lut2 + (lane & 15) * 8, *tb3 = lut3 + lane * 4, *tb4 = lut4;
     // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
     // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
     uint32_t qB[NT][8][2];
@@ -264,6 +376,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     }
     __syncthreads();
 
+    uint8_t *ring = stage_ring + (size_t)warp * kStages * kWarpStage + lane * kLaneStage;
     MmaState<NT> st;
     st.M[0] = st.M[1] = -INFINITY;
     st.l[0] = st.l[1] = 0.f;
@@ -280,9 +393,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
             const int cnt = ch.seg_count[c * BH + bh];
             if (cnt == 0) continue;
             const int s0 = ch.seg_start[c * BH + bh];
-            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut2, a.scale_log2, a.lut_scale[0]);
-            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut3, a.scale_log2, a.lut_scale[1]);
-            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, lut4, a.scale_log2, a.lut_scale[2]);
+            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb2, a.scale_log2, a.lut_scale[0], ring);
+            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb3, a.scale_log2, a.lut_scale[1], ring);
+            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb4, a.scale_log2, a.lut_scale[2], ring);
         }
     }
 
@@ -311,8 +424,8 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
         Msh[tid] = m;
     }
     __syncthreads();
-    const float c0 = st.M[0] == -INFINITY ? 0.f : exp2f(st.M[0] - Msh[h0]);
-    const float c1 = st.M[1] == -INFINITY ? 0.f : exp2f(st.M[1] - Msh[h1]);
+    const float c0 = st.M[0] == -INFINITY ? 0.f : fast_exp2(st.M[0] - Msh[h0]);
+    const float c1 = st.M[1] == -INFINITY ? 0.f : fast_exp2(st.M[1] - Msh[h1]);
     for (int w = 0; w < kMmaWarps; ++w) {   // fixed order: the sum is reproducible
         if (warp == w && owner) {
 #pragma unroll
@@ -379,9 +492,15 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     m.scale_log2 = scale * 1.4426950408889634f;
     for (int i = 0; i < 3; ++i) m.lut_scale[i] = lut_scales ? lut_scales[i] : 1.0f;
     dim3 grid(n_splits, BH);
+    {
+        cudaError_t e1 = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+        cudaError_t e2 = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+        if (e1 != cudaSuccess) return (int)e1;
+        if (e2 != cudaSuccess) return (int)e2;
+    }
     timing_begin("decode_main", st);
-    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, 0, st>>>(dc, m);
-    else decode_mma_kernel<2><<<grid, kMmaThreads, 0, st>>>(dc, m);
+    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
+    else decode_mma_kernel<2><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
     timing_end(st);
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;

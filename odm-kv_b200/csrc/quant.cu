@@ -449,11 +449,12 @@ __global__ void __launch_bounds__(256, 1) dequant_kernel(const DequantArgs a) {
             int s = s0 + tid;
             long long row = -1;
             if (s < end) {
-                int t = a.ch.pos[li][s];
-                if (t >= 0) {
-                    int bh = find_segment(a.ch.seg_start + c * BH, BH, s);
+                const int t = a.ch.pos[li][s];
+                const int bh = find_segment(a.ch.seg_start + c * BH, BH, s);
+                // a slot counts only while it lies inside its segment's current length (truncation shortens
+                // segments without touching the banks) and its position fits the dense tensor
+                if (t >= 0 && t < a.T_dense && s - a.ch.seg_start[c * BH + bh] < a.ch.seg_count[c * BH + bh])
                     row = (long long)bh * a.T_dense + t;
-                }
             }
             dst_row[tid] = row;
         }
@@ -504,8 +505,9 @@ __global__ void scatter_exact_kernel(const odmkv_chunk ch, void *K_out, void *V_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int s = blockIdx.x * (blockDim.x >> 5) + warp; s < end; s += gridDim.x * (blockDim.x >> 5)) {
         int t = ch.exact_pos[s];
-        if (t < 0) continue;
+        if (t < 0 || t >= T_dense) continue;
         int bh = find_segment(ch.seg_start + 5 * BH, BH, s);
+        if (s - ch.seg_start[5 * BH + bh] >= ch.seg_count[5 * BH + bh]) continue;
         size_t dst = ((size_t)bh * T_dense + t) * kD + 4 * lane;
         store4<ODT>(K_out, dst, load4<IDT>(ch.exact_k, (size_t)s * kD + 4 * lane));
         store4<ODT>(V_out, dst, load4<IDT>(ch.exact_v, (size_t)s * kD + 4 * lane));

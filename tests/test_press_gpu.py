@@ -1,0 +1,168 @@
+"""The press on a tiny random-init Llama: prefill compression through the hooks, decode through the
+attention override, decode-buffer flush.  Checked against the CPU oracle (bits, given the same scores) and
+against dense attention over the dequantised cache (what the reference's decode step computes)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+LEVELS = (0, 2, 3, 4, 8, 16)
+
+
+def tiny_llama(dev, dtype=torch.float16, layers=2):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=layers, num_attention_heads=8,
+                      num_key_value_heads=2, head_dim=128, max_position_embeddings=4096, rope_theta=10000.0,
+                      attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg)
+    for p in model.parameters():   # weights large enough for non-uniform attention
+        torch.nn.init.normal_(p, std=0.05)
+    return model.to(dev).to(dtype).eval()
+
+
+def make_press(pkg, **kw):
+    exp = {"mode": "backend_per_token", "bits": list(LEVELS), "target_avg_bits": 2.0, "eviction_cost": 0.5}
+    press = pkg.press_factory.make_press(exp, seed=42)
+    for k, v in kw.items():
+        setattr(press, k, v)
+    return press
+
+
+@torch.no_grad()
+def test_prefill_compression_and_packed_decode(pkg, orc, cuda):
+    from transformers import DynamicCache
+    # bf16: the reference's fake key (-1e5 * y / |y|^2) overflows fp16, so its dense decode path needs bf16
+    model = tiny_llama(cuda, dtype=torch.bfloat16)
+    press = make_press(pkg)
+    B, T = 2, 300
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 512, (B, T), generator=g).to(cuda)
+    cache = DynamicCache()
+    captured = {}
+
+    def grab(module, args, kwargs, output):
+        layer = cache.layers[module.layer_idx]
+        captured[module.layer_idx] = (layer.keys.clone(), layer.values.clone(), kwargs["hidden_states"].clone())
+
+    with press(model):
+        hooks = [l.self_attn.register_forward_hook(grab, with_kwargs=True, prepend=True) for l in model.model.layers]
+        model.model(input_ids=ids, past_key_values=cache)
+        for h in hooks:
+            h.remove()
+        assert press._prefill_hooks_fired == B * len(model.model.layers)
+        eps = press._epsilon
+        for li, layer in enumerate(model.model.layers):
+            state = cache.layers[li]._tq_backend_state
+            attn = layer.self_attn
+            assert state is attn._odmkv_state and state.seq_len == T and state.batch_size == B and state.num_heads == 2
+            K0, V0, h0 = captured[li]
+            # ---- bits: oracle Lagrangian on the kernel's own scores must give the same allocation
+            scores = press.scorer.score_prefill_batched(K0, V0, li, module=attn, hidden_states=h0).cpu().numpy()
+            # scores against the oracle, with the query statistics restated on the CPU in fp32
+            wq = attn.q_proj.weight.float().cpu().numpy()
+            pos = torch.arange(T, T + 512, device=cuda).unsqueeze(0)
+            cos, sin = model.model.rotary_emb(h0[:1].float(), pos)
+            cb, sb = orc.avg_rope_vectors(cos[0].float().cpu().numpy(), sin[0].float().cpu().numpy())
+            sink = np.zeros((2, T), bool)
+            sink[:, :4] = True
+            want_bits = []
+            for b in range(B):
+                mu = orc.apply_avg_rope(orc.mean_query(h0[b].float().cpu().numpy(), wq, None, 8, 128, 4), cb, sb)
+                want_s = orc.score_prefill(K0[b].float().cpu().numpy(), V0[b].float().cpu().numpy(), mu, 4, 1e-2)
+                rel = np.abs(scores[b] - want_s) / np.maximum(want_s, 1e-30)
+                assert rel.max() < 5e-3, rel.max()   # hidden states are bf16 here, so the mean query itself differs slightly
+                wb = orc.optimal_scores_to_bits(scores[b], LEVELS, 2.0, eps, sink, eviction_cost=0.5)
+                wb[:, -128:] = 16
+                want_bits.append(wb)
+            want_bits = np.stack(want_bits)
+            banks = state._quantized_banks
+            got_counts = {b: banks[b].size for b in (2, 3, 4, 8)}
+            assert got_counts == {b: int((want_bits == b).sum()) for b in (2, 3, 4, 8)}
+            assert state._masked_positions.shape[0] == int((want_bits == 0).sum())
+            assert state._exact_bank.size == int((want_bits == 16).sum())
+            mp = state._masked_positions.cpu().numpy()
+            assert (want_bits[mp[:, 0], mp[:, 1], mp[:, 2]] == 0).all()
+            for b in (2, 3):
+                p = banks[b].positions.cpu().numpy()
+                assert (want_bits[p[:, 0], p[:, 1], p[:, 2]] == b).all()
+            # ---- the dense HF cache holds the dequantised tokens (quantised positions only were rewritten)
+            Kd, Vd = state.materialize()
+            keep = state.keep_mask()
+            assert torch.equal(cache.layers[li].keys[keep], Kd[keep]) and torch.equal(cache.layers[li].values[keep], Vd[keep])
+            assert attn.masked_key_indices is not None or not (want_bits == 0).any()
+
+        # ---- decode steps: packed attention vs dense attention with fake keys over the dequantised cache
+        nxt = torch.randint(0, 512, (B, 1), generator=g).to(cuda)
+        import copy
+        for step in range(3):
+            cache_dense = copy.deepcopy(cache)
+            for l_packed, l_dense in zip(cache.layers, cache_dense.layers):
+                l_dense._tq_backend_state = l_packed._tq_backend_state
+            for layer in model.model.layers:
+                layer.self_attn._odmkv_decode = False
+            saved = {i: (s.seq_len, s.tail_len, s.tail_start) for i, s in press._states.items()}
+            bc, bs = dict(press._buffer_counts), dict(press._buffer_start_seqs)
+            ref_logits = model(input_ids=nxt, past_key_values=cache_dense).logits.float()
+            for i, s in press._states.items():   # undo the append the hook did during the dense pass
+                s.seq_len, s.tail_len, s.tail_start = saved[i]
+            press._buffer_counts, press._buffer_start_seqs = bc, bs
+            for layer in model.model.layers:
+                layer.self_attn._odmkv_decode = True
+            logits = model(input_ids=nxt, past_key_values=cache).logits.float()
+            err = (logits - ref_logits).abs().max() / ref_logits.abs().max()
+            assert err < 5e-2, err   # bf16 model: the dense path rounds the cache and the attention to bf16
+            for i, s in press._states.items():
+                assert s.seq_len == T + step + 1 and s.tail_len == step + 1
+            nxt = logits[:, -1].argmax(-1, keepdim=True)
+
+
+@torch.no_grad()
+def test_decode_buffer_flush_and_truncate(pkg, cuda):
+    from transformers import DynamicCache
+    model = tiny_llama(cuda, layers=1)
+    press = make_press(pkg, buffer_size=8)
+    B, T = 1, 200
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, 512, (B, T), generator=g).to(cuda)
+    cache = DynamicCache()
+    with press(model):
+        model.model(input_ids=ids, past_key_values=cache)
+        state = press._states[0]
+        attn = model.model.layers[0].self_attn
+        nxt = torch.randint(0, 512, (B, 1), generator=g).to(cuda)
+        for step in range(20):
+            logits = model(input_ids=nxt, past_key_values=cache).logits
+            nxt = logits[:, -1].argmax(-1, keepdim=True)
+            assert torch.isfinite(logits).all()
+        # 20 decode tokens with a buffer of 8: two flushes (after 8 and 16), 4 tokens still buffered
+        assert state.seq_len == T + 20 and len(state.chunks) == 3 and state.tail_len == 4
+        assert press._buffer_start_seqs[0] == T + 16 and press._buffer_counts[0] == 4
+        assert state.chunks[1].t_offset == T and state.chunks[2].t_offset == T + 8
+        # flushed tokens are never evicted (level 0 is excluded at decode)
+        assert int(state.chunks[1].seg_count_host()[0].sum()) == 0
+        # packed decode equals dense attention over the materialised cache at this point
+        Kf, Vf = state.materialize_fp32()
+        keep = state.keep_mask()
+        q = torch.randn(B, 8, 128, device=cuda, dtype=torch.float16)
+        out = state.decode_attention(q, out_dtype=torch.float32)
+        for hq in range(8):
+            h = hq // 4
+            lg = (Kf[0, h] @ q[0, hq].float()) / math.sqrt(128)
+            lg[~keep[0, h]] = float("-inf")
+            ref = torch.softmax(lg, 0) @ Vf[0, h]
+            assert (out[0, hq] - ref).abs().max() / ref.abs().max() < 1e-3
+        # rewind to the prompt, as the runner does between questions
+        n_masked = state._masked_positions.shape[0]
+        state.truncate(T)
+        assert state.seq_len == T and len(state.chunks) == 1 and state.tail_len == 0
+        assert state._masked_positions.shape[0] == n_masked
+        state.truncate(T - 50)
+        assert state.seq_len == T - 50
+        pos = state._exact_bank.positions
+        assert pos.numel() == 0 or int(pos[:, 2].max()) < T - 50
+        Kt, _ = state.materialize_fp32()
+        assert Kt.shape[2] == T - 50 and torch.equal(Kt, Kf[:, :, : T - 50] * state.keep_mask().unsqueeze(-1))
