@@ -222,6 +222,22 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
                           int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                           const float *lut_scales, void *stream);
 
+/* Decode attention without a caller-supplied workspace (no counterpart in the reference).  For hosts
+ * that cannot allocate device memory on the decode path -- a serving loop with a frozen memory pool, a
+ * thread that may not take the driver's allocation lock, a plug-in that only ever receives raw device
+ * pointers.  Same arguments and result as odmkv_decode_attn_mma, but the scratch is a device array inside
+ * the library: odmkv_decode_attn_noalloc_scratch_bytes() bytes (6 MiB) held by every GPU that loads the
+ * library until the process exits.  Sizes whose partials need more (roughly B*H*(n_splits+8)*8 KiB for
+ * G <= 4, twice that for G <= 8) return ODMKV_ERR_LIMIT and launch nothing.  The first call on a device
+ * resolves the array's address and should come before any stream capture.  All calls on a device share
+ * the array: calls that overlap on the GPU race, so keep them on one stream.  It calls no cudaMalloc,
+ * cudaFree or other allocating routine. */
+size_t odmkv_decode_attn_noalloc_scratch_bytes(void);
+int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                              const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                              const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                              int out_dtype, float *lse, int n_splits, const float *lut_scales, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Optional kernel timing (no counterpart in the reference).  When enabled, the launchers bracket
  * their dominant kernel with CUDA events on the launching stream under the names "score",
