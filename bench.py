@@ -279,6 +279,11 @@ def run_ours(args):
     total_ms = ev0.elapsed_time(ev1)
     tot, n = ctypes.c_double(), ctypes.c_longlong()
     L.odmkv_timing_read(b"decode_main", ctypes.byref(tot), ctypes.byref(n))
+    parts_ms = {}
+    for name in ("decode_rotate", "decode_side", "decode_merge"):
+        t2, n2 = ctypes.c_double(), ctypes.c_longlong()
+        L.odmkv_timing_read(name.encode(), ctypes.byref(t2), ctypes.byref(n2))
+        parts_ms[name] = t2.value / max(n2.value, 1)
     L.odmkv_timing_enable(0)
     main_ms = tot.value / max(n.value, 1)
     clocks = sampler.stop() if rank == 0 else None
@@ -347,7 +352,7 @@ def run_ours(args):
                    "multi_gpu": "each rank holds its own (sample, KV head) units; outputs all-gathered per step" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,
-                     "frac_of_8000": achieved / 8000.0},
+                     "frac_of_8000": achieved / 8000.0, "other_kernels_ms": parts_ms},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
                 "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": 3 * args.steps,

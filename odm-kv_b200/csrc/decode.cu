@@ -20,26 +20,38 @@ constexpr int kDecThreads = 128;
 constexpr int kDecWarps = kDecThreads / 32;
 constexpr int kMaxSlots = 160;   // partial slots per (b, h) the merge kernel accepts
 
-// rotate the queries once: qrot[r][i] = sum_j pi_k[i][j] q[r][j]; also keep q as fp32
+// rotate the queries once: qrot[r][i] = sum_j pi_k[i][j] q[r][j]; also keep q as fp32.
+// Warp w owns output rows w, w+4, ..., w+124: every lane loads its four columns of all 32 rows
+// (32 independent, coalesced 16-byte loads), then a reduce-scatter leaves row (w + 4*lane) in lane `lane`.
 template <int QDT>
-__global__ void rotate_q_kernel(const void *__restrict__ q, const float *__restrict__ pi_k, float *__restrict__ qrot,
-                                float *__restrict__ qf) {
-    __shared__ float qs[kD];
-    const int r = blockIdx.x, i = threadIdx.x;
-    qs[i] = Elem<QDT>::to_f32(reinterpret_cast<const typename Elem<QDT>::T *>(q)[(size_t)r * kD + i]);
+__global__ void __launch_bounds__(kD) rotate_q_kernel(const void *__restrict__ q, const float *__restrict__ pi_k, float *__restrict__ qrot,
+                                                       float *__restrict__ qf) {
+    __shared__ __align__(16) float qs[kD];
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    qs[tid] = Elem<QDT>::to_f32(reinterpret_cast<const typename Elem<QDT>::T *>(q)[(size_t)r * kD + tid]);
     __syncthreads();
-    float acc = 0.f;
-    const float4 *row = reinterpret_cast<const float4 *>(pi_k + (size_t)i * kD);
-#pragma unroll 8
-    for (int j4 = 0; j4 < kD / 4; ++j4) {
-        float4 p = row[j4];
-        acc = fmaf(p.x, qs[4 * j4], acc);
-        acc = fmaf(p.y, qs[4 * j4 + 1], acc);
-        acc = fmaf(p.z, qs[4 * j4 + 2], acc);
-        acc = fmaf(p.w, qs[4 * j4 + 3], acc);
+    qf[(size_t)r * kD + tid] = qs[tid];
+    const float4 qv = *reinterpret_cast<const float4 *>(qs + 4 * lane);
+    float v[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+        const float4 p = *reinterpret_cast<const float4 *>(pi_k + (size_t)(warp + 4 * k) * kD + 4 * lane);
+        float acc = p.x * qv.x;
+        acc = fmaf(p.y, qv.y, acc);
+        acc = fmaf(p.z, qv.z, acc);
+        v[k] = fmaf(p.w, qv.w, acc);
     }
-    qrot[(size_t)r * kD + i] = acc;
-    qf[(size_t)r * kD + i] = qs[i];
+#pragma unroll
+    for (int o = 16, n = 16; o >= 1; o >>= 1, n >>= 1) {
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int k = 0; k < n; ++k) {
+            const float send = upper ? v[k] : v[k + n];
+            const float keep = upper ? v[k + n] : v[k];
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+    }
+    qrot[(size_t)r * kD + warp + 4 * lane] = v[0];
 }
 
 // per-warp online-softmax state for GP query heads; each lane owns coordinates 4*lane .. 4*lane+3

@@ -52,9 +52,30 @@ __device__ inline float fast_exp2(float x) {
     return y;
 }
 
+// loads from a 32-bit shared-space address (no generic-pointer arithmetic on the lookup path)
+__device__ inline uint32_t lds32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ inline uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ inline uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ inline uint32_t cvt_f16x2(float lo, float hi) {   // one instruction: two floats -> half2
+    uint32_t v;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(v) : "f"(hi), "f"(lo));
+    return v;
+}
+
 template <int N>
-__device__ inline void cp_async(void *smem, const void *gmem) {
-    const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+__device__ inline void cp_async(uint32_t s, const void *gmem) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], %2;\n" ::"r"(s), "l"(gmem), "n"(N) : "memory");
 }
 __device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
@@ -76,54 +97,70 @@ __device__ inline uint32_t pair_field(const uint32_t *w, int f) {
     return v & ((1u << (2 * B)) - 1u);
 }
 
-// Table lookups.  `tb` is this lane's view of the level's table in shared memory:
-//   2 bits: 256 entries of two half2 (one per nibble of a code byte), 16 interleaved copies -- a lane
-//           reads (byte * 16 + lane % 16) * 8 bytes, so the 16 lanes of a half-warp never collide;
-//   3 bits: 64 entries of one half2 (a pair field of 6 bits), 32 interleaved copies;
-//   4 bits: 256 entries of one half2 (a pair field = one byte), a single copy.
-// Each lookup is written as extract + scaled add + load so that it compiles to three instructions.
+// Table lookups.  One shared-memory table serves the 2- and 3-bit levels; row r (256 bytes) holds
+//   bytes [0, 128):   for the code byte r (four 2-bit codes): two half2 (low nibble pair, high nibble pair),
+//                     16 copies of 8 bytes -- lane l reads copy l % 16, so a half-warp never collides;
+//   bytes [128, 256): for r < 64, the 6-bit pair field r of the 3-bit level: one half2, 32 copies.
+// With a 256-byte row the table offset of a 2-bit lookup is (code byte << 8) | lane offset, which a
+// single byte-permute builds from the data word and a lane constant; the table base is a link-time
+// constant folded into the load.  The 4-bit level (one byte per pair) uses a separate single-copy table.
+constexpr int kLutRow = 256;
+constexpr int kLutBytes = 256 * kLutRow;             // 64 KiB
+constexpr int kLut4Bytes = 256 * 4;
+constexpr int kStageBytes = kLutBytes + kLut4Bytes;
+
+extern __shared__ __align__(128) uint8_t g_dyn[];   // [kLutBytes combined table][kLut4Bytes]
+
+// 3-bit pair field f of a row part, already shifted to bits 8..13 and merged with the lane offset
+__device__ inline uint32_t field3_offset(const uint32_t *w, int f, uint32_t lane_off) {
+    const int off = 6 * f, wi = off >> 5, sh = off & 31;
+    uint32_t v;
+    if (sh < 8) v = w[wi] << (8 - sh);
+    else if (sh + 6 <= 32) v = w[wi] >> (sh - 8);
+    else v = __funnelshift_r(w[wi], w[wi + 1], sh - 8);
+    return (v & 0x3F00u) | lane_off;
+}
+
 template <int B>
-__device__ inline void decode_k(const uint8_t *__restrict__ tb, const uint32_t *kw, int s, uint32_t (&a)[4]) {
+__device__ inline void decode_k(uint32_t lane_off, const uint32_t *kw, int s, uint32_t (&a)[4]) {
     if (B == 2) {
         // byte s of row part 0 = fields (2s, 2s+1) -> (a0, a2); byte s of row part 1 -> (a1, a3)
-        const uint32_t i0 = __byte_perm(kw[s >> 2], 0, 0x4440 | (s & 3));
-        const uint32_t i1 = __byte_perm(kw[2 + (s >> 2)], 0, 0x4440 | (s & 3));
-        const uint2 e0 = *reinterpret_cast<const uint2 *>(tb + i0 * 128);
-        const uint2 e1 = *reinterpret_cast<const uint2 *>(tb + i1 * 128);
+        const uint2 e0 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(kw[s >> 2], lane_off, 0x5504 | ((s & 3) << 4)));
+        const uint2 e1 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(kw[2 + (s >> 2)], lane_off, 0x5504 | ((s & 3) << 4)));
         a[0] = e0.x; a[2] = e0.y; a[1] = e1.x; a[3] = e1.y;
     } else if (B == 3) {
-        a[0] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw, 2 * s) * 128);
-        a[1] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw + 3, 2 * s) * 128);
-        a[2] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw, 2 * s + 1) * 128);
-        a[3] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(kw + 3, 2 * s + 1) * 128);
+        a[0] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw, 2 * s, lane_off));
+        a[1] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw + 3, 2 * s, lane_off));
+        a[2] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw, 2 * s + 1, lane_off));
+        a[3] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw + 3, 2 * s + 1, lane_off));
     } else {
         // a pair field is one byte: row part 0 = words 0..3, row part 1 = words 4..7
         const int f0 = 2 * s, f1 = 2 * s + 1;
-        a[0] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[f0 >> 2], 0, 0x4440 | (f0 & 3)) * 4);
-        a[1] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[4 + (f0 >> 2)], 0, 0x4440 | (f0 & 3)) * 4);
-        a[2] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[f1 >> 2], 0, 0x4440 | (f1 & 3)) * 4);
-        a[3] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(kw[4 + (f1 >> 2)], 0, 0x4440 | (f1 & 3)) * 4);
+        const uint32_t *t4 = reinterpret_cast<const uint32_t *>(g_dyn + kLutBytes);
+        a[0] = t4[__byte_perm(kw[f0 >> 2], 0, 0x4440 | (f0 & 3))];
+        a[1] = t4[__byte_perm(kw[4 + (f0 >> 2)], 0, 0x4440 | (f0 & 3))];
+        a[2] = t4[__byte_perm(kw[f1 >> 2], 0, 0x4440 | (f1 & 3))];
+        a[3] = t4[__byte_perm(kw[4 + (f1 >> 2)], 0, 0x4440 | (f1 & 3))];
     }
 }
 
 template <int B>
-__device__ inline void decode_v(const uint8_t *__restrict__ tb, const uint32_t *vw, int m, uint32_t (&a)[4]) {
+__device__ inline void decode_v(uint32_t lane_off, const uint32_t *vw, int m, uint32_t (&a)[4]) {
     if (B == 2) {
         // bytes 2m, 2m+1 = fields (4m, 4m+1), (4m+2, 4m+3)
         const int b0 = 2 * m, b1 = 2 * m + 1;
-        const uint32_t i0 = __byte_perm(vw[b0 >> 2], 0, 0x4440 | (b0 & 3));
-        const uint32_t i1 = __byte_perm(vw[b1 >> 2], 0, 0x4440 | (b1 & 3));
-        const uint2 e0 = *reinterpret_cast<const uint2 *>(tb + i0 * 128);
-        const uint2 e1 = *reinterpret_cast<const uint2 *>(tb + i1 * 128);
+        const uint2 e0 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(vw[b0 >> 2], lane_off, 0x5504 | ((b0 & 3) << 4)));
+        const uint2 e1 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(vw[b1 >> 2], lane_off, 0x5504 | ((b1 & 3) << 4)));
         a[0] = e0.x; a[1] = e0.y; a[2] = e1.x; a[3] = e1.y;
     } else if (B == 3) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const uint32_t *>(tb + pair_field<3>(vw, 4 * m + r) * 128);
+        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(vw, 4 * m + r, lane_off));
     } else {
+        const uint32_t *t4 = reinterpret_cast<const uint32_t *>(g_dyn + kLutBytes);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
             const int f = 4 * m + r;
-            a[r] = *reinterpret_cast<const uint32_t *>(tb + __byte_perm(vw[f >> 2], 0, 0x4440 | (f & 3)) * 4);
+            a[r] = t4[__byte_perm(vw[f >> 2], 0, 0x4440 | (f & 3))];
         }
     }
 }
@@ -134,9 +171,9 @@ struct MmaState {
     float O[NT][8][4];       // O^T fragments: [column tile][16-coordinate block][c0..c3]
 };
 
-template <int B, int NT>
+template <int B, int NT, bool FULL>
 __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B], const uint32_t (&vw)[2 * B], float kn0, float kn1,
-                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], const uint8_t *__restrict__ tb,
+                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], uint32_t lane_off,
                                     int lane, float kfac, float inv_lut_scale) {
     const int g = lane >> 2, t = lane & 3;
     // ---- S = K_dec . q'^T
@@ -148,7 +185,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         uint32_t a[4];
-        decode_k<B>(tb, kw, s, a);
+        decode_k<B>(lane_off, kw, s, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
     }
@@ -160,16 +197,17 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
         else sv[i] = S[0][i] + S[NT - 1][i];
     }
     // ---- weights relative to the lazily updated maximum of logit2 + log2(value norm)
-    const bool ok0 = g < nvalid, ok1 = g + 8 < nvalid;
+    // rows past the segment's end get log2-weight -inf and reciprocal norm 0: they drop out branch-free
+    const bool ok0 = FULL || g < nvalid, ok1 = FULL || g + 8 < nvalid;
     const float vc0 = fmaxf(vn0, 1e-30f) * inv_lut_scale, vc1 = fmaxf(vn1, 1e-30f) * inv_lut_scale;
-    const float lv0 = __log2f(vc0), lv1 = __log2f(vc1);
-    const float rv0 = __fdividef(1.0f, vc0), rv1 = __fdividef(1.0f, vc1);
+    const float lv0 = ok0 ? __log2f(vc0) : -INFINITY, lv1 = ok1 ? __log2f(vc1) : -INFINITY;
+    const float rv0 = ok0 ? __fdividef(1.0f, vc0) : 0.f, rv1 = ok1 ? __fdividef(1.0f, vc1) : 0.f;
     const float f0 = kn0 * kfac, f1 = kn1 * kfac;
     float z[4];
-    z[0] = ok0 ? fmaf(sv[0], f0, lv0) : -INFINITY;
-    z[1] = ok0 ? fmaf(sv[1], f0, lv0) : -INFINITY;
-    z[2] = ok1 ? fmaf(sv[2], f1, lv1) : -INFINITY;
-    z[3] = ok1 ? fmaf(sv[3], f1, lv1) : -INFINITY;
+    z[0] = fmaf(sv[0], f0, lv0);
+    z[1] = fmaf(sv[1], f0, lv0);
+    z[2] = fmaf(sv[2], f1, lv1);
+    z[3] = fmaf(sv[3], f1, lv1);
     float zm0 = fmaxf(z[0], z[2]), zm1 = fmaxf(z[1], z[3]);
     const bool need = (zm0 > st.M[0] + kTau) || (zm1 > st.M[1] + kTau);
     if (__any_sync(0xffffffffu, need)) {
@@ -190,133 +228,149 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
                 st.O[nt][m][0] *= c0; st.O[nt][m][1] *= c1; st.O[nt][m][2] *= c0; st.O[nt][m][3] *= c1;
             }
     }
+    // while no row has been seen M is -inf and z is -inf too: keep the difference finite
+    const float m0 = st.M[0] == -INFINITY ? 0.f : st.M[0], m1 = st.M[1] == -INFINITY ? 0.f : st.M[1];
     float W[4];
-    W[0] = ok0 ? fast_exp2(z[0] - st.M[0]) : 0.f;
-    W[1] = ok0 ? fast_exp2(z[1] - st.M[1]) : 0.f;
-    W[2] = ok1 ? fast_exp2(z[2] - st.M[0]) : 0.f;
-    W[3] = ok1 ? fast_exp2(z[3] - st.M[1]) : 0.f;
-    st.l[0] += W[0] * rv0 + W[2] * rv1;
-    st.l[1] += W[1] * rv0 + W[3] * rv1;
-    // ---- P operand: fp16 high limb and low limb of every weight
-    __half hi[4], lo[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        hi[i] = __float2half_rn(W[i]);
-        lo[i] = __float2half_rn(W[i] - __half2float(hi[i]));
-    }
+    W[0] = fast_exp2(z[0] - m0);
+    W[1] = fast_exp2(z[1] - m1);
+    W[2] = fast_exp2(z[2] - m0);
+    W[3] = fast_exp2(z[3] - m1);
+    st.l[0] = fmaf(W[0], rv0, fmaf(W[2], rv1, st.l[0]));
+    st.l[1] = fmaf(W[1], rv0, fmaf(W[3], rv1, st.l[1]));
+    // ---- P operand: fp16 high limb and low limb of every weight, two weights per conversion
+    const uint32_t hi01 = cvt_f16x2(W[0], W[1]), hi23 = cvt_f16x2(W[2], W[3]);
+    const float2 b01 = __half22float2(*reinterpret_cast<const __half2 *>(&hi01));
+    const float2 b23 = __half22float2(*reinterpret_cast<const __half2 *>(&hi23));
+    const uint32_t lo01 = cvt_f16x2(W[0] - b01.x, W[1] - b01.y), lo23 = cvt_f16x2(W[2] - b23.x, W[3] - b23.y);
     uint32_t pb[NT][2];
     if (NT == 1) {
         const bool low = (t & 2) != 0;   // columns 4..7 carry the low limbs
-        pb[0][0] = movmatrix_trans(low ? pack_half2(lo[0], lo[1]) : pack_half2(hi[0], hi[1]));
-        pb[0][1] = movmatrix_trans(low ? pack_half2(lo[2], lo[3]) : pack_half2(hi[2], hi[3]));
+        pb[0][0] = movmatrix_trans(low ? lo01 : hi01);
+        pb[0][1] = movmatrix_trans(low ? lo23 : hi23);
     } else {
-        pb[0][0] = movmatrix_trans(pack_half2(hi[0], hi[1]));
-        pb[0][1] = movmatrix_trans(pack_half2(hi[2], hi[3]));
-        pb[NT - 1][0] = movmatrix_trans(pack_half2(lo[0], lo[1]));
-        pb[NT - 1][1] = movmatrix_trans(pack_half2(lo[2], lo[3]));
+        pb[0][0] = movmatrix_trans(hi01);
+        pb[0][1] = movmatrix_trans(hi23);
+        pb[NT - 1][0] = movmatrix_trans(lo01);
+        pb[NT - 1][1] = movmatrix_trans(lo23);
     }
     // ---- O^T += V_dec^T . P
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
         uint32_t a[4];
-        decode_v<B>(tb, vw, m, a);
+        decode_v<B>(lane_off, vw, m, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[nt][0], pb[nt][1]);
     }
 }
 
-// Per-lane staging: every lane copies its own key chunk, value chunk and four norms of a tile into
-// its private 80-byte slot of a ring of kStages tiles with cp.async, and later reads back only what it
-// wrote itself, so completion needs cp.async.wait_group alone -- no barrier and no flag to spin on.
-constexpr int kStages = 3;
-constexpr int kLaneStage = 80;                       // 32 B keys + 32 B values + 16 B norms
-constexpr int kWarpStage = 32 * kLaneStage;          // one tile of one warp
-constexpr int kRingBytes = kMmaWarps * kStages * kWarpStage;
-constexpr int kLut2Bytes = 256 * 16 * 8;             // byte -> two half2, 16 copies
-constexpr int kLut3Bytes = 64 * 32 * 4;              // 6-bit pair -> half2, 32 copies
-constexpr int kLut4Bytes = 256 * 4;                  // byte pair -> half2, one copy
-constexpr int kStageBytes = kLut2Bytes + kLut3Bytes + kLut4Bytes + kRingBytes;
-
+// Tile data goes straight from global memory to registers: every lane loads its own key chunk, value
+// chunk and four norms (its fragment rows g and g+8), one tile ahead of the tile being consumed, so the
+// loads of tile i+1 are in flight while tile i is decoded.  Nothing is staged in shared memory, which is
+// left to the lookup tables.
 template <int B>
-__device__ inline void issue_tile(uint8_t *__restrict__ mine, const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb,
-                                  const float *__restrict__ kn, const float *__restrict__ vn, int slot0, int lane) {
-    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
-    const int g = lane >> 2;
-    if (B == 2) {
-        cp_async<16>(mine, kb + off);
-        cp_async<16>(mine + 32, vb + off);
-    } else if (B == 3) {
-#pragma unroll
-        for (int i = 0; i < 3; ++i) {
-            cp_async<8>(mine + 8 * i, kb + off + 8 * i);
-            cp_async<8>(mine + 32 + 8 * i, vb + off + 8 * i);
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            cp_async<16>(mine + 16 * i, kb + off + 16 * i);
-            cp_async<16>(mine + 32 + 16 * i, vb + off + 16 * i);
-        }
-    }
-    cp_async<4>(mine + 64, kn + slot0 + g);
-    cp_async<4>(mine + 68, kn + slot0 + g + 8);
-    cp_async<4>(mine + 72, vn + slot0 + g);
-    cp_async<4>(mine + 76, vn + slot0 + g + 8);
+struct TileRegs {
+    uint32_t kw[2 * B], vw[2 * B];
+    float kn0, kn1, vn0, vn1;
+};
+
+__device__ inline uint4 ldg128(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ inline uint2 ldg64(const void *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
 }
 
 template <int B>
-__device__ inline void read_words(const uint8_t *__restrict__ p, uint32_t (&w)[2 * B]) {
+__device__ inline void load_words(const uint8_t *__restrict__ p, uint32_t (&w)[2 * B]) {
     if (B == 2) {
-        uint4 v = *reinterpret_cast<const uint4 *>(p);
+        const uint4 v = ldg128(p);
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
     } else if (B == 3) {
-        uint4 v = *reinterpret_cast<const uint4 *>(p);
-        uint2 u = *reinterpret_cast<const uint2 *>(p + 16);
-        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; w[4] = u.x; w[5] = u.y;
+#pragma unroll
+        for (int i = 0; i < 3; ++i) {
+            const uint2 v = ldg64(p + 8 * i);
+            w[2 * i] = v.x; w[2 * i + 1] = v.y;
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            uint4 v = reinterpret_cast<const uint4 *>(p)[i];
+            const uint4 v = ldg128(p + 16 * i);
             w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
         }
     }
 }
 
+// ask L2 for the lines of a tile a few iterations before its register loads are issued: with one tile
+// of register prefetch per warp the loads alone keep too few bytes in flight to cover HBM latency
+constexpr int kL2Ahead = 4;   // tiles of this warp
+template <int B>
+__device__ inline void prefetch_tile(const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb, const float *__restrict__ kn,
+                                     const float *__restrict__ vn, int slot0, int lane) {
+    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(kb + off));
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vb + off));
+    if (lane == 0) {
+        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(kn + slot0));
+        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vn + slot0));
+    }
+}
+
+template <int B>
+__device__ inline void load_tile(TileRegs<B> &r, const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb,
+                                 const float *__restrict__ kn, const float *__restrict__ vn, int slot0, int lane) {
+    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
+    const int g = lane >> 2;
+    load_words<B>(kb + off, r.kw);
+    load_words<B>(vb + off, r.vw);
+    // volatile so that these stay with the tile's other loads, one iteration ahead of their use
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.kn0) : "l"(kn + slot0 + g));
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.kn1) : "l"(kn + slot0 + g + 8));
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.vn0) : "l"(vn + slot0 + g));
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.vn1) : "l"(vn + slot0 + g + 8));
+}
+
+template <int B, int NT>
+__device__ inline void consume(MmaState<NT> &st, const TileRegs<B> &r, int nvalid, const uint32_t (&qB)[NT][8][2], uint32_t lane_off,
+                               int lane, float kfac, float inv_ls) {
+    if (nvalid >= 16) process_tile<B, NT, true>(st, r.kw, r.vw, r.kn0, r.kn1, r.vn0, r.vn1, 16, qB, lane_off, lane, kfac, inv_ls);
+    else process_tile<B, NT, false>(st, r.kw, r.vw, r.kn0, r.kn1, r.vn0, r.vn1, nvalid, qB, lane_off, lane, kfac, inv_ls);
+}
+
 template <int B, int NT>
 __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
-                                       const uint32_t (&qB)[NT][8][2], const uint8_t *__restrict__ tb, float scale_log2, float lut_scale,
-                                       uint8_t *__restrict__ ring /* this lane's slot of stage 0 of this warp */) {
+                                       const uint32_t (&qB)[NT][8][2], uint32_t lane_off, float scale_log2, float lut_scale) {
     constexpr int LI = B - 2;
     const int ntiles = (cnt + 15) >> 4;
     const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
     const float kfac = scale_log2 / lut_scale, inv_ls = 1.0f / lut_scale;
     const uint8_t *kb = ch.k_codes[LI], *vb = ch.v_codes[LI];
     const float *kn = ch.k_norm[LI], *vn = ch.v_norm[LI];
-    const int first = t_lo + warp;
-    // prologue: kStages - 1 tiles in flight
+    int ti = t_lo + warp;
+    if (ti >= t_hi) return;
+    // two register buffers used alternately: the next tile's loads are in flight while this one is decoded
+    TileRegs<B> ra, rb;
 #pragma unroll
-    for (int d = 0; d < kStages - 1; ++d) {
-        const int ti = first + d * kMmaWarps;
-        if (ti < t_hi) issue_tile<B>(ring + d * kWarpStage, kb, vb, kn, vn, s0 + ti * 16, lane);
-        cp_async_commit();
+    for (int d = 1; d < kL2Ahead; ++d)
+        if (ti + d * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + d * kMmaWarps) * 16, lane);
+    load_tile<B>(ra, kb, vb, kn, vn, s0 + ti * 16, lane);
+    while (true) {
+        int tn = ti + kMmaWarps < t_hi ? ti + kMmaWarps : ti;   // the last tile re-loads itself: no branch around the prefetch
+        if (ti + kL2Ahead * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + kL2Ahead * kMmaWarps) * 16, lane);
+        load_tile<B>(rb, kb, vb, kn, vn, s0 + tn * 16, lane);
+        consume<B, NT>(st, ra, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
+        ti += kMmaWarps;
+        if (ti >= t_hi) break;
+        tn = ti + kMmaWarps < t_hi ? ti + kMmaWarps : ti;
+        if (ti + kL2Ahead * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + kL2Ahead * kMmaWarps) * 16, lane);
+        load_tile<B>(ra, kb, vb, kn, vn, s0 + tn * 16, lane);
+        consume<B, NT>(st, rb, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
+        ti += kMmaWarps;
+        if (ti >= t_hi) break;
     }
-    int stage = 0;
-    for (int ti = first; ti < t_hi; ti += kMmaWarps) {
-        const int ahead = ti + (kStages - 1) * kMmaWarps;
-        int wstage = stage + kStages - 1;
-        if (wstage >= kStages) wstage -= kStages;
-        if (ahead < t_hi) issue_tile<B>(ring + wstage * kWarpStage, kb, vb, kn, vn, s0 + ahead * 16, lane);
-        cp_async_commit();
-        cp_async_wait<kStages - 1>();
-        const uint8_t *mine = ring + stage * kWarpStage;
-        uint32_t kw[2 * B], vw[2 * B];
-        read_words<B>(mine, kw);
-        read_words<B>(mine + 32, vw);
-        const float4 nr = *reinterpret_cast<const float4 *>(mine + 64);
-        process_tile<B, NT>(st, kw, vw, nr.x, nr.y, nr.z, nr.w, min(16, cnt - ti * 16), qB, tb, lane, kfac, inv_ls);
-        if (++stage == kStages) stage = 0;
-    }
-    cp_async_wait<0>();
 }
 
 template <int NT>
@@ -324,9 +378,6 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     __shared__ float Osh[4 * NT][kD];
     __shared__ float lsh[4 * NT], Msh[4 * NT];
     __shared__ float warpM[kMmaWarps][4 * NT];
-    extern __shared__ __align__(128) uint8_t dyn[];
-    uint8_t *lut2 = dyn, *lut3 = dyn + kLut2Bytes, *lut4 = lut3 + kLut3Bytes, *stage_ring = lut4 + kLut4Bytes;
-
     const int bh = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int BH = a.B * a.H, G = a.G;
@@ -337,22 +388,24 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
         const float *c2 = a.codebooks, *c3 = a.codebooks + 256, *c4 = a.codebooks + 512;
         const float s2 = a.lut_scale[0], s3 = a.lut_scale[1], s4 = a.lut_scale[2];
         for (int e = tid; e < 256 * 16; e += kMmaThreads) {
-            const int v = e >> 4;
+            const int v = e >> 4, c = e & 15;
             uint2 ent;
             ent.x = pack_half2(__float2half_rn(c2[v & 3] * s2), __float2half_rn(c2[(v >> 2) & 3] * s2));
             ent.y = pack_half2(__float2half_rn(c2[(v >> 4) & 3] * s2), __float2half_rn(c2[(v >> 6) & 3] * s2));
-            reinterpret_cast<uint2 *>(lut2)[e] = ent;
+            *reinterpret_cast<uint2 *>(g_dyn + v * kLutRow + c * 8) = ent;
         }
         for (int e = tid; e < 64 * 32; e += kMmaThreads) {
-            const int idx = e >> 5;
-            reinterpret_cast<uint32_t *>(lut3)[e] = pack_half2(__float2half_rn(c3[idx & 7] * s3), __float2half_rn(c3[idx >> 3] * s3));
+            const int idx = e >> 5, c = e & 31;
+            *reinterpret_cast<uint32_t *>(g_dyn + idx * kLutRow + 128 + c * 4) =
+                pack_half2(__float2half_rn(c3[idx & 7] * s3), __float2half_rn(c3[idx >> 3] * s3));
         }
         for (int e = tid; e < 256; e += kMmaThreads)
-            reinterpret_cast<uint32_t *>(lut4)[e] = pack_half2(__float2half_rn(c4[e & 15] * s4), __float2half_rn(c4[e >> 4] * s4));
+            reinterpret_cast<uint32_t *>(g_dyn + kLutBytes)[e] = pack_half2(__float2half_rn(c4[e & 15] * s4), __float2half_rn(c4[e >> 4] * s4));
         for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
         if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = -INFINITY; }
     }
-    const uint8_t *tb2 = lut2 + (lane & 15) * 8, *tb3 = lut3 + lane * 4, *tb4 = lut4;
+    // lane constants merged into every table offset: copy (lane % 16) of the 2-bit entries, copy `lane` of the 3-bit ones
+    const uint32_t off2 = (lane & 15) * 8, off3 = 128 + lane * 4;
     // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
     // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
     uint32_t qB[NT][8][2];
@@ -376,7 +429,6 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     }
     __syncthreads();
 
-    uint8_t *ring = stage_ring + (size_t)warp * kStages * kWarpStage + lane * kLaneStage;
     MmaState<NT> st;
     st.M[0] = st.M[1] = -INFINITY;
     st.l[0] = st.l[1] = 0.f;
@@ -393,9 +445,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
             const int cnt = ch.seg_count[c * BH + bh];
             if (cnt == 0) continue;
             const int s0 = ch.seg_start[c * BH + bh];
-            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb2, a.scale_log2, a.lut_scale[0], ring);
-            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb3, a.scale_log2, a.lut_scale[1], ring);
-            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, tb4, a.scale_log2, a.lut_scale[2], ring);
+            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off2, a.scale_log2, a.lut_scale[0]);
+            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off3, a.scale_log2, a.lut_scale[1]);
+            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, 0u, a.scale_log2, a.lut_scale[2]);
         }
     }
 
@@ -477,7 +529,7 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     // exact / 8-bit / tail tokens: a few CTAs of the CUDA-core kernel per (b, h)
     long long side_tokens = tail_len;
     for (int i = 0; i < n_chunks; ++i) side_tokens += ((long long)chunks[i].cap[4] + chunks[i].cap[5]) / ((long long)B * H) + 1;
-    int ns_side = (int)((side_tokens + 255) / 256);
+    int ns_side = (int)((side_tokens + 127) / 128);   // one 32-token group per warp of the CUDA-core kernel
     if (ns_side < 1) ns_side = 1;
     if (ns_side > 8) ns_side = 8;
     const int nslots = n_splits + ns_side;
@@ -485,7 +537,9 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     if (workspace_bytes < decode_ws_layout(B, H, G, nslots, &ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     const int BH = B * H;
+    timing_begin("decode_rotate", st);
     launch_rotate_q(q, q_dtype, pi_k, ws, BH * G, st);
+    timing_end(st);
     MmaArgs m;
     m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc;
     m.B = B; m.H = H; m.G = G; m.nsplit = n_splits; m.slot_base = 0; m.nslots = nslots;
@@ -493,10 +547,16 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     for (int i = 0; i < 3; ++i) m.lut_scale[i] = lut_scales ? lut_scales[i] : 1.0f;
     dim3 grid(n_splits, BH);
     {
-        cudaError_t e1 = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
-        cudaError_t e2 = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
-        if (e1 != cudaSuccess) return (int)e1;
-        if (e2 != cudaSuccess) return (int)e2;
+        static bool attr_set[64] = {};   // per device: the opt-in only has to happen once
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+            cudaError_t e1 = cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+            cudaError_t e2 = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
+            if (e1 != cudaSuccess) return (int)e1;
+            if (e2 != cudaSuccess) return (int)e2;
+            if (dev >= 0 && dev < 64) attr_set[dev] = true;
+        }
     }
     timing_begin("decode_main", st);
     if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
@@ -507,8 +567,12 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
     a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
     a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
+    timing_begin("decode_side", st);
     launch_decode_cuda_core(dc, a, cache_dtype, st);
+    timing_end(st);
+    timing_begin("decode_merge", st);
     launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st);
+    timing_end(st);
     return launch_status();
 }
 
