@@ -138,9 +138,9 @@ int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start
  * The 8-bit bank is token-major (byte d of a slot = code of coordinate d).  The 2/3/4-bit banks are
  * stored in tiles of 16 slots arranged for the tensor-core fragments of the decode kernel: lane
  * (g, t) = (lane / 4, lane % 4) of a warp owns the 8*b bytes at tile + lane*8*b as 32 little-endian
- * pair fields of 2*b bits; keys: bytes [0,4b) = slot g of the tile, [4b,8b) = slot g+8, field f =
- * coordinates (32t+2f, 32t+2f+1); values: field 4m+2hi+a = coordinate 16m+g+8a of slots (2t+8hi,
- * 2t+8hi+1).  odmkv_export_bank converts any bank to the reference's byte layout. */
+ * pair fields of 2*b bits; keys: field 4s+2odd+hi = coordinates (32t+4s+2odd, +1) of slot g+8hi;
+ * values: field 4m+2hi+a = coordinate 16m+g+8a of slots (2t+8hi, 2t+8hi+1) -- in both cases four consecutive
+ * fields are the A registers of one HMMA step.  odmkv_export_bank converts any bank to the reference's byte layout. */
 typedef struct odmkv_chunk {
     uint8_t *k_codes[ODMKV_NUM_QLEVELS];
     uint8_t *v_codes[ODMKV_NUM_QLEVELS];

@@ -123,9 +123,10 @@ __device__ inline int nearest_centroid(float y, const float *c, int k) {
 // A tile is laid out for the m16n8k16 tensor-core fragments of the decode kernel: lane (g, t) of a warp
 // (g = lane / 4, t = lane % 4) owns the 8*b bytes at tile + lane * 8 * b, as 32 "pair fields" of 2*b bits
 // (low code in the low bits), packed little-endian in ascending field order.
-//   keys:   bytes [0, 4b) hold row g of the tile, bytes [4b, 8b) row g + 8; field f of a row part holds
-//           coordinates (32 t + 2 f, 32 t + 2 f + 1).
-//   values: field 4 m + 2 hi + a holds coordinate 16 m + g + 8 a of tokens (2 t + 8 hi, 2 t + 8 hi + 1).
+//   keys:   field 4 s + 2 odd + hi holds coordinates (32 t + 4 s + 2 odd, + 1) of slot g + 8 hi, i.e. the
+//           four fields of step s are the A registers a0..a3 of that HMMA step, in order;
+//   values: field 4 m + 2 hi + a holds coordinate 16 m + g + 8 a of tokens (2 t + 8 hi, 2 t + 8 hi + 1),
+//           again a0..a3 of step m.
 // The "linear" layout (scratch and odmkv_encode_pack output) is the plain little-endian bit stream of the
 // 128 codes of one slot, 16*b bytes per slot.
 __host__ __device__ inline int qbits(int li) { return li == 0 ? 2 : li == 1 ? 3 : li == 2 ? 4 : 8; }
@@ -137,17 +138,13 @@ __device__ inline uint32_t read_bits(const uint8_t *p, int bitoff, int nbits) {
     return v & ((1u << nbits) - 1u);
 }
 
-// byte offset of the key row part of `slot` that holds coordinates [32 t, 32 t + 32)
-__host__ __device__ inline size_t k_part_offset(int b, long long slot, int t) {
-    const long long tile = slot >> 4;
-    const int r = (int)(slot & 15), g = r & 7, hi = r >> 3;
-    return (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b + (size_t)hi * 4 * b;
-}
-
 __device__ inline int k_code(const uint8_t *bank, int li, long long slot, int d) {
     if (li == 3) return bank[(size_t)slot * 128 + d];
     const int b = qbits(li);
-    return (int)read_bits(bank + k_part_offset(b, slot, d >> 5), ((d & 31) >> 1) * 2 * b + (d & 1) * b, b);
+    const long long tile = slot >> 4;
+    const int r = (int)(slot & 15), g = r & 7, hi = r >> 3, t = d >> 5, f = (d & 31) >> 1;
+    const int field = 4 * (f >> 1) + 2 * (f & 1) + hi;
+    return (int)read_bits(bank + (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b, field * 2 * b + (d & 1) * b, b);
 }
 
 __device__ inline int v_code(const uint8_t *bank, int li, long long slot, int d) {

@@ -17,11 +17,14 @@
 // second launch that writes its own partial slots; one merge kernel combines everything.
 #include "decode_shared.cuh"
 
+#include <cstdlib>
+
 namespace odmkv {
 
 constexpr int kMmaThreads = 256;
 constexpr int kMmaWarps = kMmaThreads / 32;
 constexpr float kTau = 6.0f;   // lazy-maximum slack in log2 units: weights stay below 2^6
+constexpr float kNegBig = -1.0e30f;   // stands for -inf where a finite value keeps the arithmetic free of special cases
 
 struct MmaArgs {
     const float *qrot;
@@ -31,6 +34,7 @@ struct MmaArgs {
     int B, H, G, nsplit, slot_base, nslots;
     float scale_log2;      // softmax scale * log2(e)
     float lut_scale[3];    // centroids are stored in the tables as fp16(c * lut_scale[li])
+    int tile_mask;         // ~0 normally; a measurement aid can set 0 so that every load hits the segment's first tile
 };
 
 __device__ inline void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -121,46 +125,25 @@ __device__ inline uint32_t field3_offset(const uint32_t *w, int f, uint32_t lane
     return (v & 0x3F00u) | lane_off;
 }
 
+// Both banks store, for HMMA step j (a key step s or a value block m), the four A registers a0..a3 as
+// fields 4j..4j+3, so one routine decodes either.
 template <int B>
-__device__ inline void decode_k(uint32_t lane_off, const uint32_t *kw, int s, uint32_t (&a)[4]) {
+__device__ inline void decode_step(uint32_t lane_off, const uint32_t *w, int j, uint32_t (&a)[4]) {
     if (B == 2) {
-        // byte s of row part 0 = fields (2s, 2s+1) -> (a0, a2); byte s of row part 1 -> (a1, a3)
-        const uint2 e0 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(kw[s >> 2], lane_off, 0x5504 | ((s & 3) << 4)));
-        const uint2 e1 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(kw[2 + (s >> 2)], lane_off, 0x5504 | ((s & 3) << 4)));
-        a[0] = e0.x; a[2] = e0.y; a[1] = e1.x; a[3] = e1.y;
-    } else if (B == 3) {
-        a[0] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw, 2 * s, lane_off));
-        a[1] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw + 3, 2 * s, lane_off));
-        a[2] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw, 2 * s + 1, lane_off));
-        a[3] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(kw + 3, 2 * s + 1, lane_off));
-    } else {
-        // a pair field is one byte: row part 0 = words 0..3, row part 1 = words 4..7
-        const int f0 = 2 * s, f1 = 2 * s + 1;
-        const uint32_t *t4 = reinterpret_cast<const uint32_t *>(g_dyn + kLutBytes);
-        a[0] = t4[__byte_perm(kw[f0 >> 2], 0, 0x4440 | (f0 & 3))];
-        a[1] = t4[__byte_perm(kw[4 + (f0 >> 2)], 0, 0x4440 | (f0 & 3))];
-        a[2] = t4[__byte_perm(kw[f1 >> 2], 0, 0x4440 | (f1 & 3))];
-        a[3] = t4[__byte_perm(kw[4 + (f1 >> 2)], 0, 0x4440 | (f1 & 3))];
-    }
-}
-
-template <int B>
-__device__ inline void decode_v(uint32_t lane_off, const uint32_t *vw, int m, uint32_t (&a)[4]) {
-    if (B == 2) {
-        // bytes 2m, 2m+1 = fields (4m, 4m+1), (4m+2, 4m+3)
-        const int b0 = 2 * m, b1 = 2 * m + 1;
-        const uint2 e0 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(vw[b0 >> 2], lane_off, 0x5504 | ((b0 & 3) << 4)));
-        const uint2 e1 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(vw[b1 >> 2], lane_off, 0x5504 | ((b1 & 3) << 4)));
+        // bytes 2j, 2j+1 = fields (4j, 4j+1), (4j+2, 4j+3): each 64-bit table entry is an aligned register pair
+        const int b0 = 2 * j, b1 = 2 * j + 1;
+        const uint2 e0 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(w[b0 >> 2], lane_off, 0x5504 | ((b0 & 3) << 4)));
+        const uint2 e1 = *reinterpret_cast<const uint2 *>(g_dyn + __byte_perm(w[b1 >> 2], lane_off, 0x5504 | ((b1 & 3) << 4)));
         a[0] = e0.x; a[1] = e0.y; a[2] = e1.x; a[3] = e1.y;
     } else if (B == 3) {
 #pragma unroll
-        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(vw, 4 * m + r, lane_off));
+        for (int r = 0; r < 4; ++r) a[r] = *reinterpret_cast<const uint32_t *>(g_dyn + field3_offset(w, 4 * j + r, lane_off));
     } else {
         const uint32_t *t4 = reinterpret_cast<const uint32_t *>(g_dyn + kLutBytes);
 #pragma unroll
         for (int r = 0; r < 4; ++r) {
-            const int f = 4 * m + r;
-            a[r] = t4[__byte_perm(vw[f >> 2], 0, 0x4440 | (f & 3))];
+            const int f = 4 * j + r;
+            a[r] = t4[__byte_perm(w[f >> 2], 0, 0x4440 | (f & 3))];
         }
     }
 }
@@ -177,18 +160,26 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
                                     int lane, float kfac, float inv_lut_scale) {
     const int g = lane >> 2, t = lane & 3;
     // ---- S = K_dec . q'^T
-    float S[NT][4];
+    // two accumulators per column tile (even / odd steps) halve the chain of dependent HMMAs
+    float S[NT][4], S2[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) S[nt][i] = 0.f;
+        for (int i = 0; i < 4; ++i) { S[nt][i] = 0.f; S2[nt][i] = 0.f; }
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
         uint32_t a[4];
-        decode_k<B>(lane_off, kw, s, a);
+        decode_step<B>(lane_off, kw, s, a);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
+        for (int nt = 0; nt < NT; ++nt) {
+            if (s & 1) mma16816(S2[nt], a, qB[nt][s][0], qB[nt][s][1]);
+            else mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
+        }
     }
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) S[nt][i] += S2[nt][i];
     // ---- high + low query limbs
     float sv[4];
 #pragma unroll
@@ -200,7 +191,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
     // rows past the segment's end get log2-weight -inf and reciprocal norm 0: they drop out branch-free
     const bool ok0 = FULL || g < nvalid, ok1 = FULL || g + 8 < nvalid;
     const float vc0 = fmaxf(vn0, 1e-30f) * inv_lut_scale, vc1 = fmaxf(vn1, 1e-30f) * inv_lut_scale;
-    const float lv0 = ok0 ? __log2f(vc0) : -INFINITY, lv1 = ok1 ? __log2f(vc1) : -INFINITY;
+    const float lv0 = ok0 ? __log2f(vc0) : kNegBig, lv1 = ok1 ? __log2f(vc1) : kNegBig;
     const float rv0 = ok0 ? __fdividef(1.0f, vc0) : 0.f, rv1 = ok1 ? __fdividef(1.0f, vc1) : 0.f;
     const float f0 = kn0 * kfac, f1 = kn1 * kfac;
     float z[4];
@@ -217,8 +208,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
             zm1 = fmaxf(zm1, __shfl_xor_sync(0xffffffffu, zm1, o));
         }
         const float n0 = fmaxf(st.M[0], zm0), n1 = fmaxf(st.M[1], zm1);
-        const float c0 = st.M[0] == -INFINITY ? 0.f : fast_exp2(st.M[0] - n0);
-        const float c1 = st.M[1] == -INFINITY ? 0.f : fast_exp2(st.M[1] - n1);
+        const float c0 = fast_exp2(st.M[0] - n0), c1 = fast_exp2(st.M[1] - n1);   // 2^(-1e30 - n) = 0 for the first tile
         st.M[0] = n0; st.M[1] = n1;
         st.l[0] *= c0; st.l[1] *= c1;
 #pragma unroll
@@ -228,8 +218,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
                 st.O[nt][m][0] *= c0; st.O[nt][m][1] *= c1; st.O[nt][m][2] *= c0; st.O[nt][m][3] *= c1;
             }
     }
-    // while no row has been seen M is -inf and z is -inf too: keep the difference finite
-    const float m0 = st.M[0] == -INFINITY ? 0.f : st.M[0], m1 = st.M[1] == -INFINITY ? 0.f : st.M[1];
+    const float m0 = st.M[0], m1 = st.M[1];
     float W[4];
     W[0] = fast_exp2(z[0] - m0);
     W[1] = fast_exp2(z[1] - m1);
@@ -257,7 +246,7 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
         uint32_t a[4];
-        decode_v<B>(lane_off, vw, m, a);
+        decode_step<B>(lane_off, vw, m, a);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[nt][0], pb[nt][1]);
     }
@@ -304,33 +293,25 @@ __device__ inline void load_words(const uint8_t *__restrict__ p, uint32_t (&w)[2
     }
 }
 
-// ask L2 for the lines of a tile a few iterations before its register loads are issued: with one tile
-// of register prefetch per warp the loads alone keep too few bytes in flight to cover HBM latency
-constexpr int kL2Ahead = 4;   // tiles of this warp
 template <int B>
-__device__ inline void prefetch_tile(const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb, const float *__restrict__ kn,
-                                     const float *__restrict__ vn, int slot0, int lane) {
-    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
-    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(kb + off));
-    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vb + off));
-    if (lane == 0) {
-        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(kn + slot0));
-        asm volatile("prefetch.global.L2 [%0];\n" ::"l"(vn + slot0));
+struct TilePtrs {   // this lane's addresses inside the current tile of the four arrays
+    const uint8_t *k, *v;
+    const float *kn, *vn;
+    __device__ void advance(int tiles) {
+        k += (size_t)tiles * 256 * B; v += (size_t)tiles * 256 * B;
+        kn += tiles * 16; vn += tiles * 16;
     }
-}
+};
 
 template <int B>
-__device__ inline void load_tile(TileRegs<B> &r, const uint8_t *__restrict__ kb, const uint8_t *__restrict__ vb,
-                                 const float *__restrict__ kn, const float *__restrict__ vn, int slot0, int lane) {
-    const size_t off = ((size_t)(slot0 >> 4) * 32 + lane) * 8 * B;
-    const int g = lane >> 2;
-    load_words<B>(kb + off, r.kw);
-    load_words<B>(vb + off, r.vw);
+__device__ inline void load_tile(TileRegs<B> &r, const TilePtrs<B> &p) {
+    load_words<B>(p.k, r.kw);
+    load_words<B>(p.v, r.vw);
     // volatile so that these stay with the tile's other loads, one iteration ahead of their use
-    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.kn0) : "l"(kn + slot0 + g));
-    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.kn1) : "l"(kn + slot0 + g + 8));
-    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.vn0) : "l"(vn + slot0 + g));
-    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.vn1) : "l"(vn + slot0 + g + 8));
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.kn0) : "l"(p.kn));
+    asm volatile("ld.global.nc.f32 %0, [%1+32];\n" : "=f"(r.kn1) : "l"(p.kn));
+    asm volatile("ld.global.nc.f32 %0, [%1];\n" : "=f"(r.vn0) : "l"(p.vn));
+    asm volatile("ld.global.nc.f32 %0, [%1+32];\n" : "=f"(r.vn1) : "l"(p.vn));
 }
 
 template <int B, int NT>
@@ -342,31 +323,33 @@ __device__ inline void consume(MmaState<NT> &st, const TileRegs<B> &r, int nvali
 
 template <int B, int NT>
 __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
-                                       const uint32_t (&qB)[NT][8][2], uint32_t lane_off, float scale_log2, float lut_scale) {
+                                       const uint32_t (&qB)[NT][8][2], uint32_t lane_off, float scale_log2, float lut_scale, int tile_mask) {
     constexpr int LI = B - 2;
     const int ntiles = (cnt + 15) >> 4;
     const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
     const float kfac = scale_log2 / lut_scale, inv_ls = 1.0f / lut_scale;
-    const uint8_t *kb = ch.k_codes[LI], *vb = ch.v_codes[LI];
-    const float *kn = ch.k_norm[LI], *vn = ch.v_norm[LI];
     int ti = t_lo + warp;
     if (ti >= t_hi) return;
+    const int stride = tile_mask ? kMmaWarps : 0;   // tile_mask = 0: measurement aid, every load hits the first tile
+    TilePtrs<B> p;
+    {
+        const size_t tile0 = (size_t)(s0 >> 4) + ti;
+        p.k = ch.k_codes[LI] + (tile0 * 32 + lane) * 8 * B;
+        p.v = ch.v_codes[LI] + (tile0 * 32 + lane) * 8 * B;
+        p.kn = ch.k_norm[LI] + tile0 * 16 + (lane >> 2);
+        p.vn = ch.v_norm[LI] + tile0 * 16 + (lane >> 2);
+    }
     // two register buffers used alternately: the next tile's loads are in flight while this one is decoded
     TileRegs<B> ra, rb;
-#pragma unroll
-    for (int d = 1; d < kL2Ahead; ++d)
-        if (ti + d * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + d * kMmaWarps) * 16, lane);
-    load_tile<B>(ra, kb, vb, kn, vn, s0 + ti * 16, lane);
+    load_tile<B>(ra, p);
     while (true) {
-        int tn = ti + kMmaWarps < t_hi ? ti + kMmaWarps : ti;   // the last tile re-loads itself: no branch around the prefetch
-        if (ti + kL2Ahead * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + kL2Ahead * kMmaWarps) * 16, lane);
-        load_tile<B>(rb, kb, vb, kn, vn, s0 + tn * 16, lane);
+        if (ti + kMmaWarps < t_hi) p.advance(stride);     // the last tile re-loads itself: no branch around the prefetch
+        load_tile<B>(rb, p);
         consume<B, NT>(st, ra, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
         ti += kMmaWarps;
         if (ti >= t_hi) break;
-        tn = ti + kMmaWarps < t_hi ? ti + kMmaWarps : ti;
-        if (ti + kL2Ahead * kMmaWarps < t_hi) prefetch_tile<B>(kb, vb, kn, vn, s0 + (ti + kL2Ahead * kMmaWarps) * 16, lane);
-        load_tile<B>(ra, kb, vb, kn, vn, s0 + tn * 16, lane);
+        if (ti + kMmaWarps < t_hi) p.advance(stride);
+        load_tile<B>(ra, p);
         consume<B, NT>(st, rb, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
         ti += kMmaWarps;
         if (ti >= t_hi) break;
@@ -402,7 +385,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
         for (int e = tid; e < 256; e += kMmaThreads)
             reinterpret_cast<uint32_t *>(g_dyn + kLutBytes)[e] = pack_half2(__float2half_rn(c4[e & 15] * s4), __float2half_rn(c4[e >> 4] * s4));
         for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
-        if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = -INFINITY; }
+        if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = kNegBig; }
     }
     // lane constants merged into every table offset: copy (lane % 16) of the 2-bit entries, copy `lane` of the 3-bit ones
     const uint32_t off2 = (lane & 15) * 8, off3 = 128 + lane * 4;
@@ -430,7 +413,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     __syncthreads();
 
     MmaState<NT> st;
-    st.M[0] = st.M[1] = -INFINITY;
+    st.M[0] = st.M[1] = kNegBig;
     st.l[0] = st.l[1] = 0.f;
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -445,9 +428,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
             const int cnt = ch.seg_count[c * BH + bh];
             if (cnt == 0) continue;
             const int s0 = ch.seg_start[c * BH + bh];
-            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off2, a.scale_log2, a.lut_scale[0]);
-            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off3, a.scale_log2, a.lut_scale[1]);
-            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, 0u, a.scale_log2, a.lut_scale[2]);
+            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off2, a.scale_log2, a.lut_scale[0], a.tile_mask);
+            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off3, a.scale_log2, a.lut_scale[1], a.tile_mask);
+            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, 0u, a.scale_log2, a.lut_scale[2], a.tile_mask);
         }
     }
 
@@ -470,14 +453,14 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     if (g == 0 && owner) { warpM[warp][h0] = st.M[0]; warpM[warp][h1] = st.M[1]; }
     __syncthreads();
     if (tid < NH) {
-        float m = -INFINITY;
+        float m = kNegBig;
 #pragma unroll
         for (int w = 0; w < kMmaWarps; ++w) m = fmaxf(m, warpM[w][tid]);
         Msh[tid] = m;
     }
     __syncthreads();
-    const float c0 = st.M[0] == -INFINITY ? 0.f : fast_exp2(st.M[0] - Msh[h0]);
-    const float c1 = st.M[1] == -INFINITY ? 0.f : fast_exp2(st.M[1] - Msh[h1]);
+    const float c0 = st.M[0] <= kNegBig ? 0.f : fast_exp2(st.M[0] - Msh[h0]);
+    const float c1 = st.M[1] <= kNegBig ? 0.f : fast_exp2(st.M[1] - Msh[h1]);
     for (int w = 0; w < kMmaWarps; ++w) {   // fixed order: the sum is reproducible
         if (warp == w && owner) {
 #pragma unroll
@@ -502,7 +485,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
         if (rest < kD && gq < NH) v = Osh[gq][rest];
         a.part_acc[pi * 2 * kD + rest] = v;
         if (rest == 0) {
-            a.part_ml[pi * 2] = gq < NH ? Msh[gq] * 0.6931471805599453f : -INFINITY;
+            a.part_ml[pi * 2] = (gq < NH && Msh[gq] > kNegBig) ? Msh[gq] * 0.6931471805599453f : -INFINITY;
             a.part_ml[pi * 2 + 1] = gq < NH ? lsh[gq] : 0.f;
         }
     }
@@ -545,6 +528,7 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     m.B = B; m.H = H; m.G = G; m.nsplit = n_splits; m.slot_base = 0; m.nslots = nslots;
     m.scale_log2 = scale * 1.4426950408889634f;
     for (int i = 0; i < 3; ++i) m.lut_scale[i] = lut_scales ? lut_scales[i] : 1.0f;
+    m.tile_mask = getenv("ODMKV_MEASURE_NO_DRAM") ? 0 : ~0;   // measurement aid only: results are meaningless when set
     dim3 grid(n_splits, BH);
     {
         static bool attr_set[64] = {};   // per device: the opt-in only has to happen once

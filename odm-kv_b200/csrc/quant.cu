@@ -87,7 +87,8 @@ struct QuantArgs {
     const float *pi_v;
     const float *codebooks;
     const int32_t *tile_base;
-    uint8_t *v_scratch[3];   // linear-layout value codes of the 2/3/4-bit banks before re-tiling
+    uint8_t *k_scratch[3];   // linear-layout codes of the 2/3/4-bit banks before re-tiling
+    uint8_t *v_scratch[3];
     odmkv_chunk ch;
     int ntiles;
 };
@@ -143,14 +144,7 @@ __device__ inline void pack_lane_codes(const uint8_t *__restrict__ row, int li, 
     }
 }
 
-// key codes of one slot: tile layout for 2/3/4 bits (lane covers coordinates 4*lane .. 4*lane+3, i.e.
-// two pair fields of row part lane / 8), token-major for 8 bits
-__device__ inline void store_key_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ bank, long long slot, int lane) {
-    if (li == 3) pack_lane_codes(row, 3, bank + (size_t)slot * 128, lane, lane);
-    else pack_lane_codes(row, li, bank + k_part_offset(qbits(li), slot, lane >> 3), lane, lane & 7);
-}
-
-// value codes of one slot in the linear layout (scratch for 2/3/4 bits, final for 8 bits)
+// codes of one slot in the linear layout (scratch for 2/3/4 bits, final for 8 bits)
 __device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int li, uint8_t *__restrict__ rows, long long slot, int lane) {
     pack_lane_codes(row, li, rows + (size_t)slot * 16 * qbits(li), lane, lane);
 }
@@ -280,7 +274,7 @@ __global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
                 int t_abs = a.ch.t_offset + t0 + r;
                 if (cc >= 1 && cc <= 4) {
                     int li = cc - 1;
-                    if (side == 0) store_key_codes(C8 + r * kLdC, li, a.ch.k_codes[li], s, lane);
+                    if (side == 0) store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.k_codes[3] : a.k_scratch[li], s, lane);
                     else store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.v_codes[3] : a.v_scratch[li], s, lane);
                     if (lane == 0) {
                         (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
@@ -306,7 +300,9 @@ __global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
 
 // zero the padding slots between a segment's last token and the next 16-slot boundary
 template <int DT>
-__global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *v_scratch0, uint8_t *v_scratch1, uint8_t *v_scratch2) {
+__global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *k_scratch0, uint8_t *k_scratch1, uint8_t *k_scratch2,
+                                    uint8_t *v_scratch0, uint8_t *v_scratch1, uint8_t *v_scratch2) {
+    uint8_t *k_scratch[3] = {k_scratch0, k_scratch1, k_scratch2};
     uint8_t *v_scratch[3] = {v_scratch0, v_scratch1, v_scratch2};
     __shared__ uint8_t zero_row[kD];
     if (threadIdx.x < kD) zero_row[threadIdx.x] = 0;
@@ -331,7 +327,7 @@ __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *v_scratch0, u
             if (lane == 0) ch.exact_pos[s] = -1;
         } else {
             const int li = c - 1;
-            store_key_codes(zero_row, li, ch.k_codes[li], s, lane);
+            store_linear_codes(zero_row, li, li == 3 ? ch.k_codes[3] : k_scratch[li], s, lane);
             store_linear_codes(zero_row, li, li == 3 ? ch.v_codes[3] : v_scratch[li], s, lane);
             if (lane == 0) {
                 ch.k_norm[li][s] = 0.f;
@@ -342,10 +338,10 @@ __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *v_scratch0, u
     }
 }
 
-// re-tile the value codes of one 2/3/4-bit bank: linear scratch rows -> tensor-core tile layout
-// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes)
-template <int B>
-__global__ void retile_values_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
+// re-tile the codes of one 2/3/4-bit bank: linear scratch rows -> tensor-core tile layout
+// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes; KEYS selects the field map)
+template <int B, bool KEYS>
+__global__ void retile_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
     constexpr int LI = B - 2;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     for (int tile = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tile < ntiles; tile += gridDim.x * (blockDim.x >> 5)) {
@@ -354,10 +350,18 @@ __global__ void retile_values_kernel(const uint8_t *__restrict__ rows, uint8_t *
         for (int w = 0; w < 2 * B; ++w) out[w] = 0;
 #pragma unroll
         for (int f = 0; f < 32; ++f) {
-            const int m = f >> 2, hi = (f >> 1) & 1, a = f & 1;
-            const int dim = 16 * m + g + 8 * a;
-            const long long slot = (long long)tile * 16 + 2 * t + 8 * hi;
-            const uint32_t field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot + 1, dim) << B);
+            uint32_t field;
+            if (KEYS) {
+                const int s = f >> 2, odd = (f >> 1) & 1, hi = f & 1;
+                const long long slot = (long long)tile * 16 + g + 8 * hi;
+                const int dim = 32 * t + 4 * s + 2 * odd;
+                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot, dim + 1) << B);
+            } else {
+                const int m = f >> 2, hi = (f >> 1) & 1, a = f & 1;
+                const int dim = 16 * m + g + 8 * a;
+                const long long slot = (long long)tile * 16 + 2 * t + 8 * hi;
+                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot + 1, dim) << B);
+            }
             const int off = f * 2 * B, w = off >> 5, sh = off & 31;
             out[w] |= field << sh;
             if (sh + 2 * B > 32) out[w + 1] |= field >> (32 - sh);
@@ -620,7 +624,7 @@ static int check_chunk(const odmkv_chunk *ch) {
 size_t odmkv_quantize_workspace_bytes(const int32_t *cap) {
     if (!cap) return 0;
     size_t n = 0;
-    for (int li = 0; li < 3; ++li) n += ((size_t)(cap[li + 1] > 0 ? cap[li + 1] : 0) * 16 * qbits(li) + 255) / 256 * 256;
+    for (int li = 0; li < 3; ++li) n += 2 * (((size_t)(cap[li + 1] > 0 ? cap[li + 1] : 0) * 16 * qbits(li) + 255) / 256 * 256);
     return n + 256;
 }
 
@@ -645,8 +649,10 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     {
         size_t off = 0;
         for (int li = 0; li < 3; ++li) {
-            a.v_scratch[li] = (uint8_t *)workspace + off;
-            off += ((size_t)chunk->cap[li + 1] * 16 * qbits(li) + 255) / 256 * 256;
+            const size_t bytes = ((size_t)chunk->cap[li + 1] * 16 * qbits(li) + 255) / 256 * 256;
+            a.k_scratch[li] = (uint8_t *)workspace + off;
+            a.v_scratch[li] = (uint8_t *)workspace + off + bytes;
+            off += 2 * bytes;
         }
     }
     long long n_work = (long long)BH * a.ntiles;
@@ -656,21 +662,28 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
 #define ODMKV_LAUNCH_Q(DT)                                                                                   \
     e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantSmem); \
     if (e != cudaSuccess) return (int)e;                                                                     \
-    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
+    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.k_scratch[0], a.k_scratch[1], a.k_scratch[2], a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
     timing_begin("quantize", st);                                                                            \
     quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);                                                   \
     timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q
-    // values of the 2/3/4-bit banks: linear scratch -> tile layout
+    // 2/3/4-bit banks: linear scratch -> tile layout
     for (int li = 0; li < 3; ++li) {
         const int ntile = chunk->cap[li + 1] / 16;
         if (ntile <= 0) continue;
         int rg = (ntile + 7) / 8;
         if (rg > 16 * num_sms()) rg = 16 * num_sms();
-        if (li == 0) retile_values_kernel<2><<<rg, 256, 0, st>>>(a.v_scratch[0], chunk->v_codes[0], ntile);
-        else if (li == 1) retile_values_kernel<3><<<rg, 256, 0, st>>>(a.v_scratch[1], chunk->v_codes[1], ntile);
-        else retile_values_kernel<4><<<rg, 256, 0, st>>>(a.v_scratch[2], chunk->v_codes[2], ntile);
+        if (li == 0) {
+            retile_kernel<2, true><<<rg, 256, 0, st>>>(a.k_scratch[0], chunk->k_codes[0], ntile);
+            retile_kernel<2, false><<<rg, 256, 0, st>>>(a.v_scratch[0], chunk->v_codes[0], ntile);
+        } else if (li == 1) {
+            retile_kernel<3, true><<<rg, 256, 0, st>>>(a.k_scratch[1], chunk->k_codes[1], ntile);
+            retile_kernel<3, false><<<rg, 256, 0, st>>>(a.v_scratch[1], chunk->v_codes[1], ntile);
+        } else {
+            retile_kernel<4, true><<<rg, 256, 0, st>>>(a.k_scratch[2], chunk->k_codes[2], ntile);
+            retile_kernel<4, false><<<rg, 256, 0, st>>>(a.v_scratch[2], chunk->v_codes[2], ntile);
+        }
     }
     return launch_status();
 }
