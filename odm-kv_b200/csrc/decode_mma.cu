@@ -154,52 +154,65 @@ struct MmaState {
     float O[NT][8][4];       // O^T fragments: [column tile][16-coordinate block][c0..c3]
 };
 
-template <int B, int NT, bool FULL>
-__device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B], const uint32_t (&vw)[2 * B], float kn0, float kn1,
-                                    float vn0, float vn1, int nvalid, const uint32_t (&qB)[NT][8][2], uint32_t lane_off,
-                                    int lane, float kfac, float inv_lut_scale) {
+template <int B>
+struct TileRegs {
+    uint32_t kw[2 * B], vw[2 * B];
+    float kn0, kn1, vn0, vn1;
+};
+
+// Consume U (1 or 2) tiles at once.  With two tiles the two dependency chains (table load -> HMMA ->
+// softmax -> HMMA) interleave, which is what keeps the schedulers fed at 4 warps each.  qBs holds the
+// query B fragments in shared memory as [column tile][step][lane] register pairs.
+template <int B, int NT, int U, bool FULL>
+__device__ inline void process_tiles(MmaState<NT> &st, const TileRegs<B> (&tr)[U], const int (&nvalid)[U], const uint2 *__restrict__ qBs,
+                                     uint32_t lane_off, int lane, float kfac, float inv_lut_scale) {
     const int g = lane >> 2, t = lane & 3;
     // ---- S = K_dec . q'^T
-    // two accumulators per column tile (even / odd steps) halve the chain of dependent HMMAs
-    float S[NT][4], S2[NT][4];
+    float S[U][NT][4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int u = 0; u < U; ++u)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { S[nt][i] = 0.f; S2[nt][i] = 0.f; }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) S[u][nt][i] = 0.f;
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
-        uint32_t a[4];
-        decode_step<B>(lane_off, kw, s, a);
+        uint2 qb[NT];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            if (s & 1) mma16816(S2[nt], a, qB[nt][s][0], qB[nt][s][1]);
-            else mma16816(S[nt], a, qB[nt][s][0], qB[nt][s][1]);
+        for (int nt = 0; nt < NT; ++nt) qb[nt] = qBs[(nt * 8 + s) * 32 + lane];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            uint32_t a[4];
+            decode_step<B>(lane_off, tr[u].kw, s, a);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816(S[u][nt], a, qb[nt].x, qb[nt].y);
         }
     }
+    // ---- logits in the log2 domain plus log2(value norm); rows past the segment's end drop out branch-free
+    float z[U][4], rv[U][2];
+    float zm0 = kNegBig, zm1 = kNegBig;
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
+    for (int u = 0; u < U; ++u) {
+        float sv[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) S[nt][i] += S2[nt][i];
-    // ---- high + low query limbs
-    float sv[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if (NT == 1) sv[i] = S[0][i] + __shfl_xor_sync(0xffffffffu, S[0][i], 2);
-        else sv[i] = S[0][i] + S[NT - 1][i];
+        for (int i = 0; i < 4; ++i) {
+            if (NT == 1) sv[i] = S[u][0][i] + __shfl_xor_sync(0xffffffffu, S[u][0][i], 2);   // high + low query limbs
+            else sv[i] = S[u][0][i] + S[u][NT - 1][i];
+        }
+        const bool ok0 = FULL || g < nvalid[u], ok1 = FULL || g + 8 < nvalid[u];
+        const float vc0 = fmaxf(tr[u].vn0, 1e-30f) * inv_lut_scale, vc1 = fmaxf(tr[u].vn1, 1e-30f) * inv_lut_scale;
+        const float lv0 = ok0 ? __log2f(vc0) : kNegBig, lv1 = ok1 ? __log2f(vc1) : kNegBig;
+        rv[u][0] = ok0 ? __fdividef(1.0f, vc0) : 0.f;
+        rv[u][1] = ok1 ? __fdividef(1.0f, vc1) : 0.f;
+        const float f0 = tr[u].kn0 * kfac, f1 = tr[u].kn1 * kfac;
+        z[u][0] = fmaf(sv[0], f0, lv0);
+        z[u][1] = fmaf(sv[1], f0, lv0);
+        z[u][2] = fmaf(sv[2], f1, lv1);
+        z[u][3] = fmaf(sv[3], f1, lv1);
+        zm0 = fmaxf(zm0, fmaxf(z[u][0], z[u][2]));
+        zm1 = fmaxf(zm1, fmaxf(z[u][1], z[u][3]));
     }
-    // ---- weights relative to the lazily updated maximum of logit2 + log2(value norm)
-    // rows past the segment's end get log2-weight -inf and reciprocal norm 0: they drop out branch-free
-    const bool ok0 = FULL || g < nvalid, ok1 = FULL || g + 8 < nvalid;
-    const float vc0 = fmaxf(vn0, 1e-30f) * inv_lut_scale, vc1 = fmaxf(vn1, 1e-30f) * inv_lut_scale;
-    const float lv0 = ok0 ? __log2f(vc0) : kNegBig, lv1 = ok1 ? __log2f(vc1) : kNegBig;
-    const float rv0 = ok0 ? __fdividef(1.0f, vc0) : 0.f, rv1 = ok1 ? __fdividef(1.0f, vc1) : 0.f;
-    const float f0 = kn0 * kfac, f1 = kn1 * kfac;
-    float z[4];
-    z[0] = fmaf(sv[0], f0, lv0);
-    z[1] = fmaf(sv[1], f0, lv0);
-    z[2] = fmaf(sv[2], f1, lv1);
-    z[3] = fmaf(sv[3], f1, lv1);
-    float zm0 = fmaxf(z[0], z[2]), zm1 = fmaxf(z[1], z[3]);
+    // ---- lazily updated running maximum (one vote per group of tiles)
     const bool need = (zm0 > st.M[0] + kTau) || (zm1 > st.M[1] + kTau);
     if (__any_sync(0xffffffffu, need)) {
 #pragma unroll
@@ -218,37 +231,39 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
                 st.O[nt][m][0] *= c0; st.O[nt][m][1] *= c1; st.O[nt][m][2] *= c0; st.O[nt][m][3] *= c1;
             }
     }
+    // ---- weights and the P operand (fp16 high and low limb of every weight, two weights per conversion)
     const float m0 = st.M[0], m1 = st.M[1];
-    float W[4];
-    W[0] = fast_exp2(z[0] - m0);
-    W[1] = fast_exp2(z[1] - m1);
-    W[2] = fast_exp2(z[2] - m0);
-    W[3] = fast_exp2(z[3] - m1);
-    st.l[0] = fmaf(W[0], rv0, fmaf(W[2], rv1, st.l[0]));
-    st.l[1] = fmaf(W[1], rv0, fmaf(W[3], rv1, st.l[1]));
-    // ---- P operand: fp16 high limb and low limb of every weight, two weights per conversion
-    const uint32_t hi01 = cvt_f16x2(W[0], W[1]), hi23 = cvt_f16x2(W[2], W[3]);
-    const float2 b01 = __half22float2(*reinterpret_cast<const __half2 *>(&hi01));
-    const float2 b23 = __half22float2(*reinterpret_cast<const __half2 *>(&hi23));
-    const uint32_t lo01 = cvt_f16x2(W[0] - b01.x, W[1] - b01.y), lo23 = cvt_f16x2(W[2] - b23.x, W[3] - b23.y);
-    uint32_t pb[NT][2];
-    if (NT == 1) {
-        const bool low = (t & 2) != 0;   // columns 4..7 carry the low limbs
-        pb[0][0] = movmatrix_trans(low ? lo01 : hi01);
-        pb[0][1] = movmatrix_trans(low ? lo23 : hi23);
-    } else {
-        pb[0][0] = movmatrix_trans(hi01);
-        pb[0][1] = movmatrix_trans(hi23);
-        pb[NT - 1][0] = movmatrix_trans(lo01);
-        pb[NT - 1][1] = movmatrix_trans(lo23);
+    uint32_t pb[U][NT][2];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const float W0 = fast_exp2(z[u][0] - m0), W1 = fast_exp2(z[u][1] - m1), W2 = fast_exp2(z[u][2] - m0), W3 = fast_exp2(z[u][3] - m1);
+        st.l[0] = fmaf(W0, rv[u][0], fmaf(W2, rv[u][1], st.l[0]));
+        st.l[1] = fmaf(W1, rv[u][0], fmaf(W3, rv[u][1], st.l[1]));
+        const uint32_t hi01 = cvt_f16x2(W0, W1), hi23 = cvt_f16x2(W2, W3);
+        const float2 b01 = __half22float2(*reinterpret_cast<const __half2 *>(&hi01));
+        const float2 b23 = __half22float2(*reinterpret_cast<const __half2 *>(&hi23));
+        const uint32_t lo01 = cvt_f16x2(W0 - b01.x, W1 - b01.y), lo23 = cvt_f16x2(W2 - b23.x, W3 - b23.y);
+        if (NT == 1) {
+            const bool low = (t & 2) != 0;   // columns 4..7 carry the low limbs
+            pb[u][0][0] = movmatrix_trans(low ? lo01 : hi01);
+            pb[u][0][1] = movmatrix_trans(low ? lo23 : hi23);
+        } else {
+            pb[u][0][0] = movmatrix_trans(hi01);
+            pb[u][0][1] = movmatrix_trans(hi23);
+            pb[u][NT - 1][0] = movmatrix_trans(lo01);
+            pb[u][NT - 1][1] = movmatrix_trans(lo23);
+        }
     }
     // ---- O^T += V_dec^T . P
 #pragma unroll
     for (int m = 0; m < 8; ++m) {
-        uint32_t a[4];
-        decode_step<B>(lane_off, vw, m, a);
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[nt][0], pb[nt][1]);
+        for (int u = 0; u < U; ++u) {
+            uint32_t a[4];
+            decode_step<B>(lane_off, tr[u].vw, m, a);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[u][nt][0], pb[u][nt][1]);
+        }
     }
 }
 
@@ -256,12 +271,6 @@ __device__ inline void process_tile(MmaState<NT> &st, const uint32_t (&kw)[2 * B
 // chunk and four norms (its fragment rows g and g+8), one tile ahead of the tile being consumed, so the
 // loads of tile i+1 are in flight while tile i is decoded.  Nothing is staged in shared memory, which is
 // left to the lookup tables.
-template <int B>
-struct TileRegs {
-    uint32_t kw[2 * B], vw[2 * B];
-    float kn0, kn1, vn0, vn1;
-};
-
 __device__ inline uint4 ldg128(const void *p) {
     uint4 v;
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
@@ -315,15 +324,8 @@ __device__ inline void load_tile(TileRegs<B> &r, const TilePtrs<B> &p) {
 }
 
 template <int B, int NT>
-__device__ inline void consume(MmaState<NT> &st, const TileRegs<B> &r, int nvalid, const uint32_t (&qB)[NT][8][2], uint32_t lane_off,
-                               int lane, float kfac, float inv_ls) {
-    if (nvalid >= 16) process_tile<B, NT, true>(st, r.kw, r.vw, r.kn0, r.kn1, r.vn0, r.vn1, 16, qB, lane_off, lane, kfac, inv_ls);
-    else process_tile<B, NT, false>(st, r.kw, r.vw, r.kn0, r.kn1, r.vn0, r.vn1, nvalid, qB, lane_off, lane, kfac, inv_ls);
-}
-
-template <int B, int NT>
 __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
-                                       const uint32_t (&qB)[NT][8][2], uint32_t lane_off, float scale_log2, float lut_scale, int tile_mask) {
+                                       const uint2 *__restrict__ qBs, uint32_t lane_off, float scale_log2, float lut_scale, int tile_mask) {
     constexpr int LI = B - 2;
     const int ntiles = (cnt + 15) >> 4;
     const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
@@ -339,20 +341,22 @@ __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, 
         p.kn = ch.k_norm[LI] + tile0 * 16 + (lane >> 2);
         p.vn = ch.v_norm[LI] + tile0 * 16 + (lane >> 2);
     }
-    // two register buffers used alternately: the next tile's loads are in flight while this one is decoded
-    TileRegs<B> ra, rb;
-    load_tile<B>(ra, p);
-    while (true) {
-        if (ti + kMmaWarps < t_hi) p.advance(stride);     // the last tile re-loads itself: no branch around the prefetch
-        load_tile<B>(rb, p);
-        consume<B, NT>(st, ra, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
-        ti += kMmaWarps;
-        if (ti >= t_hi) break;
-        if (ti + kMmaWarps < t_hi) p.advance(stride);
-        load_tile<B>(ra, p);
-        consume<B, NT>(st, rb, cnt - ti * 16, qB, lane_off, lane, kfac, inv_ls);
-        ti += kMmaWarps;
-        if (ti >= t_hi) break;
+    // this warp's tiles two at a time (ti and ti + 8); a last odd tile goes alone
+    for (; ti + kMmaWarps < t_hi; ti += 2 * kMmaWarps) {
+        TileRegs<B> tr[2];
+        load_tile<B>(tr[0], p);
+        p.advance(stride);
+        load_tile<B>(tr[1], p);
+        p.advance(stride);
+        const int nv[2] = {cnt - ti * 16, cnt - (ti + kMmaWarps) * 16};
+        if (nv[1] >= 16) process_tiles<B, NT, 2, true>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
+        else process_tiles<B, NT, 2, false>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
+    }
+    if (ti < t_hi) {
+        TileRegs<B> tr[1];
+        load_tile<B>(tr[0], p);
+        const int nv[1] = {cnt - ti * 16};
+        process_tiles<B, NT, 1, false>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
     }
 }
 
@@ -361,6 +365,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     __shared__ float Osh[4 * NT][kD];
     __shared__ float lsh[4 * NT], Msh[4 * NT];
     __shared__ float warpM[kMmaWarps][4 * NT];
+    __shared__ uint2 qBs[NT * 8 * 32];   // query B fragments: [column tile][step][lane]
     const int bh = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int BH = a.B * a.H, G = a.G;
@@ -391,23 +396,23 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     const uint32_t off2 = (lane & 15) * 8, off3 = 128 + lane * 4;
     // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
     // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
-    uint32_t qB[NT][8][2];
+    if (warp == 0) {
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        const int head = NT == 1 ? (g & 3) : g;
-        const bool low = NT == 1 ? (g >= 4) : (nt == 1);
-        const float *qr = a.qrot + ((size_t)bh * G + (head < G ? head : 0)) * kD + 32 * t;
+        for (int nt = 0; nt < NT; ++nt) {
+            const int head = NT == 1 ? (g & 3) : g;
+            const bool low = NT == 1 ? (g >= 4) : (nt == 1);
+            const float *qr = a.qrot + ((size_t)bh * G + (head < G ? head : 0)) * kD + 32 * t;
 #pragma unroll
-        for (int s = 0; s < 8; ++s) {
-            __half h[4];
+            for (int s = 0; s < 8; ++s) {
+                __half h[4];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                float v = head < G ? qr[4 * s + e] : 0.f;
-                __half hv = __float2half_rn(v);
-                h[e] = low ? __float2half_rn(v - __half2float(hv)) : hv;
+                for (int e = 0; e < 4; ++e) {
+                    float v = head < G ? qr[4 * s + e] : 0.f;
+                    __half hv = __float2half_rn(v);
+                    h[e] = low ? __float2half_rn(v - __half2float(hv)) : hv;
+                }
+                qBs[(nt * 8 + s) * 32 + lane] = make_uint2(pack_half2(h[0], h[1]), pack_half2(h[2], h[3]));
             }
-            qB[nt][s][0] = pack_half2(h[0], h[1]);
-            qB[nt][s][1] = pack_half2(h[2], h[3]);
         }
     }
     __syncthreads();
@@ -428,9 +433,9 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
             const int cnt = ch.seg_count[c * BH + bh];
             if (cnt == 0) continue;
             const int s0 = ch.seg_start[c * BH + bh];
-            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off2, a.scale_log2, a.lut_scale[0], a.tile_mask);
-            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, off3, a.scale_log2, a.lut_scale[1], a.tile_mask);
-            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qB, 0u, a.scale_log2, a.lut_scale[2], a.tile_mask);
+            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, off2, a.scale_log2, a.lut_scale[0], a.tile_mask);
+            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, off3, a.scale_log2, a.lut_scale[1], a.tile_mask);
+            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, 0u, a.scale_log2, a.lut_scale[2], a.tile_mask);
         }
     }
 
