@@ -273,6 +273,7 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
     }
     __syncthreads();
     float accr = 0.f, acce = 0.f;
+#pragma unroll 8
     for (int s = 0; s < nsplit; ++s) {
         const float *p = part_acc + (((size_t)bh * nsplit + s) * GP + g) * 2 * kD;
         accr = fmaf(p[j], w[s], accr);
@@ -341,11 +342,11 @@ extern "C" {
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
     if (B <= 0 || H <= 0) return 1;
     long long BH = (long long)B * H;
-    long long want = (4 * 148 + BH - 1) / BH;
-    long long by_len = (max_tokens_per_head + 255) / 256;
+    long long want = (7 * 148 + BH - 1) / BH;   // about 3.5 waves of two CTAs per SM
+    long long by_len = (max_tokens_per_head + 511) / 512;
     long long n = want < by_len ? want : by_len;
     if (n < 1) n = 1;
-    if (n > 64) n = 64;
+    if (n > 128) n = 128;
     return (int)n;
 }
 

@@ -23,6 +23,9 @@ namespace odmkv {
 
 constexpr int kMmaThreads = 256;
 constexpr int kMmaWarps = kMmaThreads / 32;
+#ifndef ODMKV_TILES_PER_ITER
+#define ODMKV_TILES_PER_ITER 3
+#endif
 constexpr float kTau = 6.0f;   // lazy-maximum slack in log2 units: weights stay below 2^6
 constexpr float kNegBig = -1.0e30f;   // stands for -inf where a finite value keeps the arithmetic free of special cases
 
@@ -341,20 +344,24 @@ __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, 
         p.kn = ch.k_norm[LI] + tile0 * 16 + (lane >> 2);
         p.vn = ch.v_norm[LI] + tile0 * 16 + (lane >> 2);
     }
-    // this warp's tiles two at a time (ti and ti + 8); a last odd tile goes alone
-    for (; ti + kMmaWarps < t_hi; ti += 2 * kMmaWarps) {
-        TileRegs<B> tr[2];
-        load_tile<B>(tr[0], p);
-        p.advance(stride);
-        load_tile<B>(tr[1], p);
-        p.advance(stride);
-        const int nv[2] = {cnt - ti * 16, cnt - (ti + kMmaWarps) * 16};
-        if (nv[1] >= 16) process_tiles<B, NT, 2, true>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
-        else process_tiles<B, NT, 2, false>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
+    // this warp's tiles kU at a time (ti, ti + 8, ...); the remainder goes one by one
+    constexpr int kU = (B == 2 && NT == 1) ? ODMKV_TILES_PER_ITER : 2;
+    for (; ti + (kU - 1) * kMmaWarps < t_hi; ti += kU * kMmaWarps) {
+        TileRegs<B> tr[kU];
+        int nv[kU];
+#pragma unroll
+        for (int u = 0; u < kU; ++u) {
+            load_tile<B>(tr[u], p);
+            p.advance(stride);
+            nv[u] = cnt - (ti + u * kMmaWarps) * 16;
+        }
+        if (nv[kU - 1] >= 16) process_tiles<B, NT, kU, true>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
+        else process_tiles<B, NT, kU, false>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
     }
-    if (ti < t_hi) {
+    for (; ti < t_hi; ti += kMmaWarps) {
         TileRegs<B> tr[1];
         load_tile<B>(tr[0], p);
+        p.advance(stride);
         const int nv[1] = {cnt - ti * 16};
         process_tiles<B, NT, 1, false>(st, tr, nv, qBs, lane_off, lane, kfac, inv_ls);
     }
@@ -496,6 +503,23 @@ __global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const Decode
     }
 }
 
+// one helper stream and two events per device, created on first use (host objects, no device memory)
+struct SideStream { cudaStream_t stream; cudaEvent_t fork, join; bool ok; };
+static SideStream *side_stream() {
+    static SideStream table[64] = {};
+    static bool tried[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!tried[dev]) {
+        tried[dev] = true;
+        SideStream &s = table[dev];
+        s.ok = cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking) == cudaSuccess &&
+               cudaEventCreateWithFlags(&s.fork, cudaEventDisableTiming) == cudaSuccess &&
+               cudaEventCreateWithFlags(&s.join, cudaEventDisableTiming) == cudaSuccess;
+    }
+    return table[dev].ok ? &table[dev] : nullptr;
+}
+
 }  // namespace odmkv
 
 using namespace odmkv;
@@ -528,6 +552,10 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     timing_begin("decode_rotate", st);
     launch_rotate_q(q, q_dtype, pi_k, ws, BH * G, st);
     timing_end(st);
+    {
+        SideStream *fk = side_stream();
+        if (fk) cudaEventRecord(fk->fork, st);
+    }
     MmaArgs m;
     m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc;
     m.B = B; m.H = H; m.G = G; m.nsplit = n_splits; m.slot_base = 0; m.nslots = nslots;
@@ -556,9 +584,21 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
     a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
     a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
-    timing_begin("decode_side", st);
-    launch_decode_cuda_core(dc, a, cache_dtype, st);
-    timing_end(st);
+    // the exact / tail kernel only needs the rotated queries, so it runs beside the tensor-core kernel on a
+    // second stream (fork after the rotation, join before the merge)
+    SideStream *ss = side_stream();
+    if (ss) {
+        cudaStreamWaitEvent(ss->stream, ss->fork, 0);
+        timing_begin("decode_side", ss->stream);
+        launch_decode_cuda_core(dc, a, cache_dtype, ss->stream);
+        timing_end(ss->stream);
+        cudaEventRecord(ss->join, ss->stream);
+        cudaStreamWaitEvent(st, ss->join, 0);
+    } else {
+        timing_begin("decode_side", st);
+        launch_decode_cuda_core(dc, a, cache_dtype, st);
+        timing_end(st);
+    }
     timing_begin("decode_merge", st);
     launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st);
     timing_end(st);
