@@ -268,7 +268,9 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
     uint8_t *chosen = ws.chosen + (size_t)p * n;
     if (tid < kAccHead) sh_cnt[tid] = 0ull;
     __syncthreads();
-    const long long base = (long long)blockIdx.x * (kAllocThreads * kPerThread);
+    // a block walks over chunks of kAllocThreads * kPerThread scores with the grid's stride
+    constexpr long long kChunk = (long long)kAllocThreads * kPerThread;
+    const long long base0 = (long long)blockIdx.x * kChunk, stride = (long long)gridDim.x * kChunk;
 
     if (phase <= 2) {
         const float lam32 = (float)pr.lam;
@@ -279,6 +281,7 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
 #pragma unroll
         for (int k = 0; k < kMaxL; ++k) cnt[k] = 0;
         unsigned ties = 0;
+        for (long long base = base0; base < n; base += stride)
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
@@ -322,6 +325,7 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
     } else if (phase == 3) {
         const bool inv = pr.dir < 0;
         const int shift_digit = 48 - 16 * pr.sel_pass;
+        for (long long base = base0; base < n; base += stride)
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
@@ -336,6 +340,7 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
         const unsigned long long cut = pr.sel_prefix;
         const unsigned cut_score = (unsigned)((inv ? ~cut : cut) >> 32);
         unsigned same_sel = 0, same_unsel = 0;
+        for (long long base = base0; base < n; base += stride)
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
@@ -368,6 +373,14 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
             update_problem(prp, acc, cfg);
         }
     }
+}
+
+// blocks per problem of a pass: enough to fill the GPU a few times over, never more than one chunk each
+static int pass_blocks(int n, int P) {
+    const int chunks = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
+    int want = (6 * 148 + P - 1) / P;
+    if (want < 1) want = 1;
+    return chunks < want ? chunks : want;
 }
 
 // stepwise path: copy the accumulator out / consume the rank-summed accumulator
@@ -472,7 +485,7 @@ int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, in
     AllocWs ws;
     rc = alloc_begin_impl(scores, sink_mask, P, n, cfg, &ws, workspace, workspace_bytes, st);
     if (rc) return rc;
-    const int nblk = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
+    const int nblk = pass_blocks(n, P);
     const int rounds = (K > 1 ? kEvalRounds : 1) + closure_rounds(K);
     timing_begin("allocate", st);
     for (int r = 0; r < rounds; ++r)
@@ -535,7 +548,7 @@ int odmkv_alloc_eval(void *workspace, long long *exchange, void *stream) {
     if (!exchange) return ODMKV_ERR_ARG;
     cudaStream_t st = (cudaStream_t)stream;
     const int n = ctx.hdr.n, P = ctx.hdr.P;
-    const int nblk = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
+    const int nblk = pass_blocks(n, P);
     alloc_pass_kernel<false><<<dim3(nblk, P), kAllocThreads, 0, st>>>(ctx.hdr.scores, ctx.hdr.sink_mask, n, ctx.hdr.idx_base, ws, ctx.cfg);
     alloc_export_acc_kernel<<<dim3((kAccLen + 255) / 256, P), 256, 0, st>>>(ws.acc, exchange, kAccLen);
     return launch_status();

@@ -149,152 +149,274 @@ __device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int l
     pack_lane_codes(row, li, rows + (size_t)slot * 16 * qbits(li), lane, lane);
 }
 
+// 64x128x128 product: acc[a][b] = sum_i X[ty+16a][i] * P[tx+16b][i], ascending i, one FMA chain each
+__device__ inline void half_tile_product(const float *__restrict__ Xs, const float *__restrict__ Ps, int ty, int tx,
+                                         float (&acc)[4][8]) {
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+    const float *xrow = Xs + ty * kLd;
+    const float *prow = Ps + tx * kLd;
+#pragma unroll 2
+    for (int i4 = 0; i4 < kD / 4; ++i4) {
+        float4 xa[4], pb[8];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) xa[a] = *reinterpret_cast<const float4 *>(xrow + a * 16 * kLd + 4 * i4);
+#pragma unroll
+        for (int b = 0; b < 8; ++b) pb[b] = *reinterpret_cast<const float4 *>(prow + b * 16 * kLd + 4 * i4);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                float v = acc[a][b];
+                v = fmaf(xa[a].x, pb[b].x, v);
+                v = fmaf(xa[a].y, pb[b].y, v);
+                v = fmaf(xa[a].z, pb[b].z, v);
+                v = fmaf(xa[a].w, pb[b].w, v);
+                acc[a][b] = v;
+            }
+    }
+}
+
+constexpr int kQRows = 64;  // tokens per work item of quantize_kernel: one half of a plan tile
+
+// searchsorted(left) by counting the centroids below y (K <= 8 centroids held in registers), then the
+// nearer neighbour, lower index on ties: the same result as nearest_centroid()
+template <int K>
+__device__ __forceinline__ int nearest_counted(float y, const float (&c)[8], const float *__restrict__ cbl) {
+    int idx = 0;
+#pragma unroll
+    for (int j = 0; j < K; ++j) idx += (c[j] < y) ? 1 : 0;
+    const int a = idx - 1 < 0 ? 0 : idx - 1;
+    const int b = idx > K - 1 ? K - 1 : idx;
+    const float da = fabsf(__fsub_rn(y, cbl[a]));
+    const float db = fabsf(__fsub_rn(y, cbl[b]));
+    return (da <= db) ? a : b;
+}
+
+// the 16-byte pieces of a half tile that one thread moves (64 rows of 128 elements, 256 threads)
 template <int DT>
-__global__ void __launch_bounds__(256, 1) quantize_kernel(const QuantArgs a) {
+struct RawPieces {
+    static constexpr int kN = (DT == kF32) ? 8 : 4;
+    uint4 v[kN];
+};
+
+template <int DT>
+__device__ __forceinline__ void load_pieces(const void *__restrict__ src, size_t row0, int rows_left, int tid, RawPieces<DT> &r) {
+    constexpr int kPerRow = (DT == kF32) ? 32 : 16;   // pieces per row
+    const uint4 *base = reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(src) +
+                                                        row0 * sizeof(typename Elem<DT>::T));
+#pragma unroll
+    for (int u = 0; u < RawPieces<DT>::kN; ++u) {
+        const int g = tid + 256 * u, row = g / kPerRow;
+        r.v[u] = row < rows_left ? __ldg(base + g) : make_uint4(0u, 0u, 0u, 0u);
+    }
+}
+
+template <int DT>
+__device__ __forceinline__ void store_pieces_f32(const RawPieces<DT> &r, int tid, float *__restrict__ Xs) {
+    constexpr int kPerRow = (DT == kF32) ? 32 : 16;
+#pragma unroll
+    for (int u = 0; u < RawPieces<DT>::kN; ++u) {
+        const int g = tid + 256 * u, row = g / kPerRow, pc = g % kPerRow;
+        const uint32_t w[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
+        if constexpr (DT == kF32) {
+            *reinterpret_cast<float4 *>(Xs + row * kLd + 4 * pc) =
+                make_float4(__uint_as_float(w[0]), __uint_as_float(w[1]), __uint_as_float(w[2]), __uint_as_float(w[3]));
+        } else {
+            float f[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float2 t2;
+                if constexpr (DT == kF16) t2 = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                else t2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[k]));
+                f[2 * k] = t2.x; f[2 * k + 1] = t2.y;
+            }
+            *reinterpret_cast<float4 *>(Xs + row * kLd + 8 * pc) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4 *>(Xs + row * kLd + 8 * pc + 4) = make_float4(f[4], f[5], f[6], f[7]);
+        }
+    }
+}
+
+// One CTA serves one side (even blocks: keys, odd blocks: values), keeps that side's rotation in
+// shared memory and walks over half tiles of 64 tokens; two CTAs share an SM, so the norm chain,
+// divisions and packing of one overlap the product of the other.  The next item's rows, bit widths
+// and slot bases are fetched into registers right after the product, under the centroid search and
+// the packing of the current item.
+template <int DT>
+__global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *PiK = reinterpret_cast<float *>(smem_raw);
-    float *PiV = PiK + kD * kLd;
-    float *Xs = PiV + kD * kLd;
-    float *cb = Xs + kD * kLd;        // [4][256]
-    float *nrm = cb + 4 * 256;        // [128]
-    int *cls = reinterpret_cast<int *>(nrm + kTile);  // [128]
-    int *slot = cls + kTile;          // [128]
-    int *wcnt = slot + kTile;         // [4][6]
-    int *flags = wcnt + 4 * kNumClasses;  // [1]
+    float *Ps = reinterpret_cast<float *>(smem_raw);   // [128][kLd]
+    float *Xs = Ps + kD * kLd;                          // [64][kLd]
+    float *cb = Xs + kQRows * kLd;                      // [4][256]
+    float *nrm = cb + 4 * 256;                          // [64]
+    int *cls = reinterpret_cast<int *>(nrm + kQRows);   // [128]
+    int *slot = cls + kTile;                            // [128]
+    int *wcnt = slot + kTile;                           // [4][6]
+    int *tbase = wcnt + 4 * kNumClasses;                // [6] slot base of this plan tile per class
+    int *flags = tbase + 8;                             // [1]
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int ty = tid >> 4, tx = tid & 15;
     const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
-
-    for (int g = tid; g < kD * kD / 4; g += 256) {
-        int j = g >> 5, i4 = g & 31;
-        *reinterpret_cast<float4 *>(PiK + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(a.pi_k + j * kD + 4 * i4);
-        *reinterpret_cast<float4 *>(PiV + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(a.pi_v + j * kD + 4 * i4);
+    const int side = blockIdx.x & 1;
+    const void *src = side ? a.V : a.K;
+    {
+        const float *pi = side ? a.pi_v : a.pi_k;
+        for (int g = tid; g < kD * kD / 4; g += 256) {
+            int j = g >> 5, i4 = g & 31;
+            *reinterpret_cast<float4 *>(Ps + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(pi + j * kD + 4 * i4);
+        }
     }
     for (int g = tid; g < 4 * 256; g += 256) cb[g] = a.codebooks[g];
+
+    const long long n_work = (long long)BH * a.ntiles * 2;
+    const long long w_step = gridDim.x >> 1;
+    // fetched ahead: rows, this thread's bit width (threads < 128) and slot base (threads < 6)
+    RawPieces<DT> raw;
+    int pf_bits = 0, pf_base = 0;
+    auto prefetch = [&](long long w) {
+        if (w >= n_work) return;
+        const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
+        const int tile = rem >> 1, half = rem & 1;
+        const int t0 = tile * kTile, h0 = half * kQRows;
+        if (t0 + h0 >= T) return;
+        load_pieces<DT>(src, ((size_t)bh * T + t0 + h0) * kD, T - t0 - h0, tid, raw);
+        if (tid < kTile) pf_bits = (t0 + tid < T) ? a.bits[(size_t)bh * T + t0 + tid] : -1;
+        if (tid < kNumClasses)
+            pf_base = a.ch.seg_start[tid * BH + bh] + a.tile_base[((size_t)bh * a.ntiles + tile) * kNumClasses + tid];
+    };
+    prefetch(blockIdx.x >> 1);
     __syncthreads();
 
-    const long long n_work = (long long)BH * a.ntiles;
-    for (long long w = blockIdx.x; w < n_work; w += gridDim.x) {
-        const int bh = (int)(w / a.ntiles), tile = (int)(w % a.ntiles);
-        const int t0 = tile * kTile;
+    for (long long w = blockIdx.x >> 1; w < n_work; w += w_step) {
+        const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
+        const int tile = rem >> 1, half = rem & 1;
+        const int t0 = tile * kTile, h0 = half * kQRows;
+        if (t0 + h0 >= T) { prefetch(w + w_step); continue; }
         if (tid == 0) flags[0] = 0;
-        // ---- classes and slots
+        // ---- classes and slots of the whole plan tile (the slot of a token counts the tokens before it)
         int c = -1, rank = 0;
         if (tid < kTile) {
-            int t = t0 + tid;
-            if (t < T) c = class_of_bits(a.bits[(size_t)bh * T + t]);
+            if (t0 + tid < T) c = class_of_bits(pf_bits);
 #pragma unroll
             for (int cc = 0; cc < kNumClasses; ++cc) {
                 unsigned m = __ballot_sync(0xffffffffu, c == cc);
                 if (c == cc) rank = __popc(m & ((1u << lane) - 1u));
                 if (lane == 0) wcnt[warp * kNumClasses + cc] = __popc(m);
             }
+            if (tid < kNumClasses) tbase[tid] = pf_base;
         }
+        store_pieces_f32<DT>(raw, tid, Xs);
         __syncthreads();
         if (tid < kTile) {
             int s = -1;
             if (c >= 0) {
-                s = a.ch.seg_start[c * BH + bh] + a.tile_base[((size_t)bh * a.ntiles + tile) * kNumClasses + c] + rank;
+                s = tbase[c] + rank;
                 for (int ww = 0; ww < warp; ++ww) s += wcnt[ww * kNumClasses + c];
-                if (c >= 1 && c <= 4) flags[0] = 1;
+                if (c >= 1 && c <= 4 && (tid >> 6) == half) flags[0] = 1;
             }
             cls[tid] = c;
             slot[tid] = s;
         }
+        // ---- fp32 norm: one ascending FMA chain of squares, IEEE square root
+        if (tid >= 192) {
+            const int r = tid - 192;
+            float acc = 0.0f;
+            const float *xr = Xs + r * kLd;
+#pragma unroll 8
+            for (int i4 = 0; i4 < kD / 4; ++i4) {
+                float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i4);
+                acc = fmaf(v.x, v.x, acc);
+                acc = fmaf(v.y, v.y, acc);
+                acc = fmaf(v.z, v.z, acc);
+                acc = fmaf(v.w, v.w, acc);
+            }
+            nrm[r] = __fsqrt_rn(acc);
+        }
         __syncthreads();
         const bool any_q = flags[0] != 0;
-
-        for (int side = 0; side < 2; ++side) {
-            const void *src = side ? a.V : a.K;
-            const float *Ps = side ? PiV : PiK;
-            const size_t row0 = ((size_t)bh * T + t0) * kD;
-            if (any_q) {
-                // ---- load the tile as fp32
-                for (int g = tid; g < kTile * kD / 4; g += 256) {
-                    int r = g >> 5, i4 = g & 31;
-                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (t0 + r < T) v = load4<DT>(src, row0 + (size_t)r * kD + 4 * i4);
-                    *reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4) = v;
-                }
-                __syncthreads();
-                // ---- fp32 norm: one ascending FMA chain of squares, IEEE square root
-                if (tid < kTile) {
-                    float acc = 0.0f;
-                    const float *xr = Xs + tid * kLd;
-#pragma unroll 4
-                    for (int i4 = 0; i4 < kD / 4; ++i4) {
-                        float4 v = *reinterpret_cast<const float4 *>(xr + 4 * i4);
-                        acc = fmaf(v.x, v.x, acc);
-                        acc = fmaf(v.y, v.y, acc);
-                        acc = fmaf(v.z, v.z, acc);
-                        acc = fmaf(v.w, v.w, acc);
-                    }
-                    nrm[tid] = __fsqrt_rn(acc);
-                }
-                __syncthreads();
-                // ---- x / (norm + 1e-10), IEEE division
-                for (int g = tid; g < kTile * kD / 4; g += 256) {
-                    int r = g >> 5, i4 = g & 31;
-                    float den = __fadd_rn(nrm[r], 1e-10f);
-                    float4 *p = reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4);
-                    float4 v = *p;
-                    v.x = __fdiv_rn(v.x, den);
-                    v.y = __fdiv_rn(v.y, den);
-                    v.z = __fdiv_rn(v.z, den);
-                    v.w = __fdiv_rn(v.w, den);
-                    *p = v;
-                }
-                __syncthreads();
-                float acc[8][8];
-                tile_product(Xs, Ps, ty, tx, acc);
-                __syncthreads();
-                // ---- nearest centroid, staged as bytes over the tile buffer
-                uint8_t *C8 = reinterpret_cast<uint8_t *>(Xs);
+        const size_t row0 = ((size_t)bh * T + t0 + h0) * kD;
+        if (any_q) {
+            // ---- x / (norm + 1e-10), IEEE division
 #pragma unroll
-                for (int aa = 0; aa < 8; ++aa) {
-                    int r = ty + 16 * aa;
-                    int cc = cls[r];
-                    if (cc >= 1 && cc <= 4) {
-                        int li = cc - 1;
-                        const float *cbl = cb + li * 256;
-                        int k = 1 << bits_of_qlevel(li);
-#pragma unroll
-                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_centroid(acc[aa][bb], cbl, k);
-                    }
-                }
-                __syncthreads();
+            for (int u = 0; u < kQRows * kD / 4 / 256; ++u) {
+                const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
+                float den = __fadd_rn(nrm[r], 1e-10f);
+                float4 *p = reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4);
+                float4 v = *p;
+                v.x = __fdiv_rn(v.x, den);
+                v.y = __fdiv_rn(v.y, den);
+                v.z = __fdiv_rn(v.z, den);
+                v.w = __fdiv_rn(v.w, den);
+                *p = v;
             }
-            // ---- pack and store: one warp per row
-            const uint8_t *C8 = reinterpret_cast<const uint8_t *>(Xs);
-            for (int r = warp; r < kTile; r += 8) {
-                int cc = cls[r];
-                int s = slot[r];
-                if (cc < 0) continue;
-                int t_abs = a.ch.t_offset + t0 + r;
-                if (cc >= 1 && cc <= 4) {
-                    int li = cc - 1;
-                    if (side == 0) store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.k_codes[3] : a.k_scratch[li], s, lane);
-                    else store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.v_codes[3] : a.v_scratch[li], s, lane);
-                    if (lane == 0) {
-                        (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
-                        if (side == 0) a.ch.pos[li][s] = t_abs;
-                    }
-                } else if (cc == 5) {
-                    const unsigned char *srow = reinterpret_cast<const unsigned char *>(src) + (row0 + (size_t)r * kD) * sizeof(typename Elem<DT>::T);
-                    unsigned char *drow = reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + (size_t)s * kD * sizeof(typename Elem<DT>::T);
-                    if constexpr (DT == kF32) {
-                        reinterpret_cast<uint4 *>(drow)[lane] = reinterpret_cast<const uint4 *>(srow)[lane];
+            __syncthreads();
+            float acc[4][8];
+            half_tile_product(Xs, Ps, ty, tx, acc);
+            __syncthreads();
+            prefetch(w + w_step);
+            // ---- nearest centroid, staged as bytes over the tile buffer
+            uint8_t *C8 = reinterpret_cast<uint8_t *>(Xs);
+#pragma unroll
+            for (int aa = 0; aa < 4; ++aa) {
+                const int r = ty + 16 * aa;
+                const int cc = cls[h0 + r];
+                if (cc == 1 || cc == 2) {
+                    const float *cbl = cb + (cc - 1) * 256;
+                    float cr[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) cr[j] = cbl[j];
+                    if (cc == 1) {
+#pragma unroll
+                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_counted<4>(acc[aa][bb], cr, cbl);
                     } else {
-                        reinterpret_cast<uint2 *>(drow)[lane] = reinterpret_cast<const uint2 *>(srow)[lane];
+#pragma unroll
+                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_counted<8>(acc[aa][bb], cr, cbl);
                     }
-                    if (lane == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
-                } else if (cc == 0 && side == 0 && lane == 0) {
-                    a.ch.evicted_pos[s] = t_abs;
+                } else if (cc == 3 || cc == 4) {
+                    const int li = cc - 1;
+                    const float *cbl = cb + li * 256;
+                    const int k = 1 << bits_of_qlevel(li);
+#pragma unroll
+                    for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_centroid(acc[aa][bb], cbl, k);
                 }
             }
             __syncthreads();
+        } else {
+            prefetch(w + w_step);
         }
+        // ---- pack and store: one warp per row
+        const uint8_t *C8 = reinterpret_cast<const uint8_t *>(Xs);
+#pragma unroll 2
+        for (int r = warp; r < kQRows; r += 8) {
+            int cc = cls[h0 + r];
+            int s = slot[h0 + r];
+            if (cc < 0) continue;
+            int t_abs = a.ch.t_offset + t0 + h0 + r;
+            if (cc >= 1 && cc <= 4) {
+                int li = cc - 1;
+                if (side == 0) store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.k_codes[3] : a.k_scratch[li], s, lane);
+                else store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.v_codes[3] : a.v_scratch[li], s, lane);
+                if (lane == 0) {
+                    (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
+                    if (side == 0) a.ch.pos[li][s] = t_abs;
+                }
+            } else if (cc == 5) {
+                const unsigned char *srow = reinterpret_cast<const unsigned char *>(src) + (row0 + (size_t)r * kD) * sizeof(typename Elem<DT>::T);
+                unsigned char *drow = reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + (size_t)s * kD * sizeof(typename Elem<DT>::T);
+                if constexpr (DT == kF32) {
+                    reinterpret_cast<uint4 *>(drow)[lane] = reinterpret_cast<const uint4 *>(srow)[lane];
+                } else {
+                    reinterpret_cast<uint2 *>(drow)[lane] = reinterpret_cast<const uint2 *>(srow)[lane];
+                }
+                if (lane == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
+            } else if (cc == 0 && side == 0 && lane == 0) {
+                a.ch.evicted_pos[s] = t_abs;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -579,7 +701,7 @@ static int num_sms() {
     return n;
 }
 
-constexpr size_t kQuantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + (2 * kTile + 4 * kNumClasses + 4) * sizeof(int);
+constexpr size_t kQuantKernelSmem = (size_t)(kD * kLd + kQRows * kLd + 4 * 256 + kQRows) * sizeof(float) + (2 * kTile + 4 * kNumClasses + 16) * sizeof(int);
 constexpr size_t kDequantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + kTile * sizeof(long long);
 
 }  // namespace odmkv
@@ -655,16 +777,16 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
             off += 2 * bytes;
         }
     }
-    long long n_work = (long long)BH * a.ntiles;
-    int grid = (int)(n_work < num_sms() ? n_work : num_sms());
+    long long n_work = (long long)BH * a.ntiles * 2;   // half tiles; each is visited by a key CTA and a value CTA
+    int grid = 2 * (int)(n_work < 2 * num_sms() ? n_work : 2 * num_sms());
     dim3 pad_grid(BH, kNumClasses);
     cudaError_t e;
 #define ODMKV_LAUNCH_Q(DT)                                                                                   \
-    e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantSmem); \
+    e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantKernelSmem); \
     if (e != cudaSuccess) return (int)e;                                                                     \
     fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.k_scratch[0], a.k_scratch[1], a.k_scratch[2], a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
     timing_begin("quantize", st);                                                                            \
-    quantize_kernel<DT><<<grid, 256, kQuantSmem, st>>>(a);                                                   \
+    quantize_kernel<DT><<<grid, 256, kQuantKernelSmem, st>>>(a);                                                   \
     timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q

@@ -6,8 +6,9 @@
 //   1. K only:  logits of the G mean queries, |k|^2, per-split softmax statistics;
 //   2. V:       p = mean_g softmax_g, |v|^2, partial sums of p v (for o) and of p;
 //   3. V again: |v - o|^2 and the score; per-sample maximum for the sink slots.
-// A quad of lanes owns one token (32 coordinates per lane), so every 16-byte load of a row is
-// fully used and each reduction takes two shuffles.
+// A quad of lanes owns one token (32 coordinates per lane, interleaved in 16-byte pieces so that a
+// quad reads 64 contiguous bytes per instruction); each reduction takes two shuffles.  The next row
+// of a lane is in flight while the current one is processed.
 #include "common.cuh"
 
 namespace odmkv {
@@ -53,14 +54,64 @@ inline size_t score_ws_layout(int B, int H, int G, int T, int n_sink, ScoreWs *w
     return off;
 }
 
-// load this lane's 32 coordinates of one row (quad lane q covers [32q, 32q+32))
+// A quad of lanes owns one row.  Lane q of the quad holds the 16-byte pieces q, q + 4, q + 8, ... of
+// the row, so the four lanes of a quad read 64 contiguous bytes with one instruction.  x[i] of lane q is
+// coordinate coord_of<DT>(q, i).
 template <int DT>
-__device__ inline void load_row32(const void *base, size_t row, int q, float (&x)[32]) {
+struct RawRow {
+    static constexpr int kVec = (DT == kF32) ? 8 : 4;
+    uint4 v[kVec];
+};
+
+template <int DT>
+__device__ __forceinline__ int coord_of(int q, int i) {
+    if constexpr (DT == kF32) return 16 * (i >> 2) + 4 * q + (i & 3);
+    else return 32 * (i >> 3) + 8 * q + (i & 7);
+}
+
+template <int DT>
+__device__ __forceinline__ void load_raw(const void *base, size_t row, int q, RawRow<DT> &r) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(base) +
+                                                     row * kD * sizeof(typename Elem<DT>::T));
 #pragma unroll
-    for (int v = 0; v < 8; ++v) {
-        float4 f = load4<DT>(base, row * kD + 32 * q + 4 * v);
-        x[4 * v] = f.x; x[4 * v + 1] = f.y; x[4 * v + 2] = f.z; x[4 * v + 3] = f.w;
+    for (int v = 0; v < RawRow<DT>::kVec; ++v) r.v[v] = __ldg(p + 4 * v + q);
+}
+
+template <int DT>
+__device__ __forceinline__ void unpack_row(const RawRow<DT> &r, bool live, float (&x)[32]) {
+    if (!live) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[i] = 0.f;
+        return;
     }
+#pragma unroll
+    for (int v = 0; v < RawRow<DT>::kVec; ++v) {
+        const uint32_t w[4] = {r.v[v].x, r.v[v].y, r.v[v].z, r.v[v].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            if constexpr (DT == kF32) {
+                x[4 * v + k] = __uint_as_float(w[k]);
+            } else if constexpr (DT == kF16) {
+                float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                x[8 * v + 2 * k] = f.x; x[8 * v + 2 * k + 1] = f.y;
+            } else {
+                float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[k]));
+                x[8 * v + 2 * k] = f.x; x[8 * v + 2 * k + 1] = f.y;
+            }
+        }
+    }
+}
+
+// this lane's 32 entries of a 128-vector in shared memory, in the lane's coordinate order
+template <int DT>
+__device__ __forceinline__ void gather_lane_vec(const float *__restrict__ vec, int q, float (&o)[32]) {
+    constexpr int kRun = (DT == kF32) ? 4 : 8;
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+        float4 f = *reinterpret_cast<const float4 *>(vec + coord_of<DT>(q, i));
+        o[i] = f.x; o[i + 1] = f.y; o[i + 2] = f.z; o[i + 3] = f.w;
+    }
+    (void)kRun;
 }
 
 __device__ inline float quad_sum(float v) {
@@ -70,76 +121,84 @@ __device__ inline float quad_sum(float v) {
 }
 
 // ---- sweep 1 ---------------------------------------------------------------------------------
-template <int DT>
-__global__ void __launch_bounds__(kScoreThreads) score_logits_kernel(const void *__restrict__ K, const float *__restrict__ mu,
-                                                                      int H, int G, int T, int n_sink, int nsplit, ScoreWs ws) {
-    __shared__ __align__(16) float mus[kMaxG * kD];
-    __shared__ float red_m[kTokPerIter], red_l[kTokPerIter];
+// GM: compile-time bound on the group size (4, 8 or 16).  Lane q of a quad keeps the running softmax
+// statistics of the query heads g with g % 4 == q.
+template <int DT, int GM>
+__global__ void __launch_bounds__(kScoreThreads, 2) score_logits_kernel(const void *__restrict__ K, const float *__restrict__ mu,
+                                                                         int H, int G, int T, int n_sink, int nsplit, ScoreWs ws) {
+    __shared__ __align__(16) float mus[GM * kD];
+    __shared__ float red_m[GM][kTokPerIter], red_l[GM][kTokPerIter];
     const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
     const int Tc = T - n_sink;
-    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2, warp = tid >> 5, lane = tid & 31;
     const float inv_sqrt_d = 1.0f / sqrtf((float)kD);
-    for (int i = tid; i < G * kD; i += kScoreThreads) mus[i] = mu[((size_t)b * H * G + (size_t)(bh % H) * G) * kD + i];
+    for (int i = tid; i < GM * kD; i += kScoreThreads)
+        mus[i] = i < G * kD ? mu[((size_t)b * H * G + (size_t)(bh % H) * G) * kD + i] : 0.f;
     __syncthreads();
     const int per = (Tc + nsplit - 1) / nsplit;
     const int j0 = split * per, j1 = min(Tc, j0 + per);
-    float m_run[kMaxG], l_run[kMaxG];
+    float m_run[GM / 4], l_run[GM / 4];
 #pragma unroll
-    for (int g = 0; g < kMaxG; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; }
+    for (int k = 0; k < GM / 4; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
+    const size_t row_base = (size_t)bh * T + n_sink;
+    RawRow<DT> nxt;
+    if (j0 + quad < j1) load_raw<DT>(K, row_base + j0 + quad, q, nxt);
     // every lane of a warp runs the same number of iterations: the quad reductions below are
     // full-warp shuffles and must not be reached by a partial warp
     for (int jb = j0; jb < j1; jb += kTokPerIter) {
         const int j = jb + quad;
         const bool live = j < j1;
         float x[32];
-        if (live) load_row32<DT>(K, (size_t)bh * T + n_sink + j, q, x);
-        else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
-        }
+        unpack_row<DT>(nxt, live, x);
+        if (j + kTokPerIter < j1) load_raw<DT>(K, row_base + j + kTokPerIter, q, nxt);
         float kk = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) kk = fmaf(x[i], x[i], kk);
         kk = quad_sum(kk);
         if (q == 0 && live) ws.kn2[(size_t)bh * Tc + j] = kk;
 #pragma unroll
-        for (int g = 0; g < kMaxG; ++g) {
+        for (int g = 0; g < GM; ++g) {
             if (g < G) {
-                const float4 *mg = reinterpret_cast<const float4 *>(mus + g * kD + 32 * q);
                 float acc = 0.f;
 #pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    float4 m4 = mg[v];
-                    acc = fmaf(x[4 * v], m4.x, acc);
-                    acc = fmaf(x[4 * v + 1], m4.y, acc);
-                    acc = fmaf(x[4 * v + 2], m4.z, acc);
-                    acc = fmaf(x[4 * v + 3], m4.w, acc);
+                for (int i = 0; i < 32; i += 4) {
+                    float4 m4 = *reinterpret_cast<const float4 *>(mus + g * kD + coord_of<DT>(q, i));
+                    acc = fmaf(x[i], m4.x, acc);
+                    acc = fmaf(x[i + 1], m4.y, acc);
+                    acc = fmaf(x[i + 2], m4.z, acc);
+                    acc = fmaf(x[i + 3], m4.w, acc);
                 }
                 acc = quad_sum(acc) * inv_sqrt_d;
-                if (q == 0 && live) {
+                if ((g & 3) == q && live) {
                     ws.logits[((size_t)bh * G + g) * Tc + j] = acc;
-                    float mn = fmaxf(m_run[g], acc);
-                    l_run[g] = l_run[g] * expf(m_run[g] - mn) + expf(acc - mn);
-                    m_run[g] = mn;
+                    const float mo = m_run[g >> 2];
+                    const float mn = fmaxf(mo, acc);
+                    const float e = expf(fminf(mo, acc) - mn);
+                    l_run[g >> 2] = acc > mo ? fmaf(l_run[g >> 2], e, 1.0f) : l_run[g >> 2] + e;
+                    m_run[g >> 2] = mn;
                 }
             }
         }
     }
-    // block merge of the per-quad (m, l) pairs, one head at a time
-    for (int g = 0; g < G; ++g) {
-        __syncthreads();
-        if (q == 0) { red_m[quad] = m_run[g]; red_l[quad] = l_run[g]; }
-        __syncthreads();
-        if (tid < 32) {
-            float m = fmaxf(red_m[tid], red_m[tid + 32]);
-            float mm = warp_max(m);
-            float l = 0.f;
-            if (mm > -INFINITY) l = red_l[tid] * expf(red_m[tid] - mm) + red_l[tid + 32] * expf(red_m[tid + 32] - mm);
-            l = warp_sum(l);
-            if (tid == 0) {
-                float *dst = ws.part_ml + (((size_t)bh * nsplit + split) * G + g) * 2;
-                dst[0] = mm; dst[1] = l;
-            }
+    // block merge of the per-quad (m, l) pairs: warp w reduces the heads w, w + 8
+#pragma unroll
+    for (int k = 0; k < GM / 4; ++k) {
+        red_m[4 * k + q][quad] = m_run[k];
+        red_l[4 * k + q][quad] = l_run[k];
+    }
+    __syncthreads();
+    for (int g = warp; g < G; g += kScoreThreads / 32) {
+        const float ma = red_m[g][lane], mb = red_m[g][lane + 32];
+        const float mm = warp_max(fmaxf(ma, mb));
+        float l = 0.f;
+        if (mm > -INFINITY) {
+            if (red_l[g][lane] > 0.f) l += red_l[g][lane] * expf(ma - mm);
+            if (red_l[g][lane + 32] > 0.f) l += red_l[g][lane + 32] * expf(mb - mm);
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            float *dst = ws.part_ml + (((size_t)bh * nsplit + split) * G + g) * 2;
+            dst[0] = mm; dst[1] = l;
         }
     }
 }
@@ -160,8 +219,8 @@ __device__ inline void merge_ml(const float *__restrict__ part_ml, int bh, int n
 
 // ---- sweep 2 ---------------------------------------------------------------------------------
 template <int DT>
-__global__ void __launch_bounds__(kScoreThreads) score_pv_kernel(const void *__restrict__ V, int H, int G, int T, int n_sink,
-                                                                  int nsplit, ScoreWs ws) {
+__global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *__restrict__ V, int H, int G, int T, int n_sink,
+                                                                     int nsplit, ScoreWs ws) {
     __shared__ float M[kMaxG], L[kMaxG];
     __shared__ float osum[kTokPerIter / 8][kD];  // one row per warp
     __shared__ float psum[kTokPerIter / 8];
@@ -177,19 +236,20 @@ __global__ void __launch_bounds__(kScoreThreads) score_pv_kernel(const void *__r
     for (int i = 0; i < 32; ++i) o[i] = 0.f;
     float ps = 0.f;
     const float inv_g = 1.0f / (float)G;
+    const size_t row_base = (size_t)bh * T + n_sink;
+    RawRow<DT> nxt;
+    if (j0 + quad < j1) load_raw<DT>(V, row_base + j0 + quad, q, nxt);
     for (int jb = j0; jb < j1; jb += kTokPerIter) {
         const int j = jb + quad;
         const bool live = j < j1;
         float x[32];
+        unpack_row<DT>(nxt, live, x);
+        if (j + kTokPerIter < j1) load_raw<DT>(V, row_base + j + kTokPerIter, q, nxt);
+        // lane q adds the softmax terms of the heads g = q, q + 4, ...; the quad sum is their total
         float p = 0.f;
-        if (live) {
-            load_row32<DT>(V, (size_t)bh * T + n_sink + j, q, x);
-            for (int g = 0; g < G; ++g) p += expf(ws.logits[((size_t)bh * G + g) * Tc + j] - M[g]) / L[g];
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
-        }
-        p *= inv_g;
+        if (live)
+            for (int g = q; g < G; g += 4) p += expf(ws.logits[((size_t)bh * G + g) * Tc + j] - M[g]) / L[g];
+        p = quad_sum(p) * inv_g;
         float vv = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) { vv = fmaf(x[i], x[i], vv); o[i] = fmaf(p, x[i], o[i]); }
@@ -214,7 +274,7 @@ __global__ void __launch_bounds__(kScoreThreads) score_pv_kernel(const void *__r
     ps += __shfl_xor_sync(0xffffffffu, ps, 16);
     if (lane < 4) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) osum[warp][32 * lane + i] = o[i];
+        for (int i = 0; i < 32; ++i) osum[warp][coord_of<DT>(lane, i)] = o[i];
         if (lane == 0) psum[warp] = ps;
     }
     __syncthreads();
@@ -233,8 +293,8 @@ __global__ void __launch_bounds__(kScoreThreads) score_pv_kernel(const void *__r
 
 // ---- sweep 3 ---------------------------------------------------------------------------------
 template <int DT>
-__global__ void __launch_bounds__(kScoreThreads) score_final_kernel(const void *__restrict__ V, int H, int T, int n_sink,
-                                                                     int nsplit, float eps, ScoreWs ws, float *__restrict__ scores) {
+__global__ void __launch_bounds__(kScoreThreads, 2) score_final_kernel(const void *__restrict__ V, int H, int T, int n_sink,
+                                                                        int nsplit, float eps, ScoreWs ws, float *__restrict__ scores) {
     __shared__ __align__(16) float ob[kD];
     __shared__ float wmax[kScoreThreads / 32];
     const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
@@ -250,20 +310,19 @@ __global__ void __launch_bounds__(kScoreThreads) score_final_kernel(const void *
     }
     __syncthreads();
     float oq[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) oq[i] = ob[32 * q + i];
+    gather_lane_vec<DT>(ob, q, oq);
     const int per = (Tc + nsplit - 1) / nsplit;
     const int j0 = split * per, j1 = min(Tc, j0 + per);
     float best = 0.f;
+    const size_t row_base = (size_t)bh * T + n_sink;
+    RawRow<DT> nxt;
+    if (j0 + quad < j1) load_raw<DT>(V, row_base + j0 + quad, q, nxt);
     for (int jb = j0; jb < j1; jb += kTokPerIter) {
         const int j = jb + quad;
         const bool live = j < j1;
         float x[32];
-        if (live) load_row32<DT>(V, (size_t)bh * T + n_sink + j, q, x);
-        else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] = 0.f;
-        }
+        unpack_row<DT>(nxt, live, x);
+        if (j + kTokPerIter < j1) load_raw<DT>(V, row_base + j + kTokPerIter, q, nxt);
         float ir = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) { float dlt = x[i] - oq[i]; ir = fmaf(dlt, dlt, ir); }
@@ -312,7 +371,9 @@ __global__ void __launch_bounds__(kScoreThreads) score_with_attn_kernel(const vo
     float ps = 0.f;
     for (int j = quad; j < T; j += kTokPerIter) {
         float x[32];
-        load_row32<DT>(V, (size_t)row * T + j, q, x);
+        RawRow<DT> rv;
+        load_raw<DT>(V, (size_t)row * T + j, q, rv);
+        unpack_row<DT>(rv, true, x);
         float pj = p[(size_t)row * T + j];
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] = fmaf(pj, x[i], o[i]);
@@ -331,7 +392,7 @@ __global__ void __launch_bounds__(kScoreThreads) score_with_attn_kernel(const vo
     ps += __shfl_xor_sync(0xffffffffu, ps, 16);
     if (lane < 4) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) osum[warp][32 * lane + i] = o[i];
+        for (int i = 0; i < 32; ++i) osum[warp][coord_of<DT>(lane, i)] = o[i];
         if (lane == 0) psum[warp] = ps;
     }
     __syncthreads();
@@ -342,19 +403,18 @@ __global__ void __launch_bounds__(kScoreThreads) score_with_attn_kernel(const vo
     }
     __syncthreads();
     float oq[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) oq[i] = ob[32 * q + i];
+    gather_lane_vec<DT>(ob, q, oq);
     for (int jb = 0; jb < T; jb += kTokPerIter) {
         const int j = jb + quad;
         const bool live = j < T;
         float x[32], y[32];
+        RawRow<DT> rv, rk;
         if (live) {
-            load_row32<DT>(V, (size_t)row * T + j, q, x);
-            load_row32<DT>(K, (size_t)row * T + j, q, y);
-        } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) { x[i] = 0.f; y[i] = 0.f; }
+            load_raw<DT>(V, (size_t)row * T + j, q, rv);
+            load_raw<DT>(K, (size_t)row * T + j, q, rk);
         }
+        unpack_row<DT>(rv, live, x);
+        unpack_row<DT>(rk, live, y);
         float ir = 0.f, vv = 0.f, kk = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -404,7 +464,9 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     dim3 grid(ns, BH);
     timing_begin("score", st);
 #define ODMKV_SCORE(DT)                                                                                    \
-    score_logits_kernel<DT><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);                 \
+    if (G <= 4) score_logits_kernel<DT, 4><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);   \
+    else if (G <= 8) score_logits_kernel<DT, 8><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws); \
+    else score_logits_kernel<DT, 16><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);         \
     score_pv_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, G, T, n_sink, ns, ws);                          \
     score_final_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, T, n_sink, ns, eps, ws, scores);
     if (dtype == kF16) { ODMKV_SCORE(kF16) } else if (dtype == kBF16) { ODMKV_SCORE(kBF16) } else { ODMKV_SCORE(kF32) }
