@@ -572,6 +572,9 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
             cudaError_t e2 = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
             if (e1 != cudaSuccess) return (int)e1;
             if (e2 != cudaSuccess) return (int)e2;
+            // two CTAs per SM need the large shared-memory carveout
+            cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+            cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
             if (dev >= 0 && dev < 64) attr_set[dev] = true;
         }
     }

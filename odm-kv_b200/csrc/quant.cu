@@ -149,50 +149,58 @@ __device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int l
     pack_lane_codes(row, li, rows + (size_t)slot * 16 * qbits(li), lane, lane);
 }
 
-// 64x128x128 product: acc[a][b] = sum_i X[ty+16a][i] * P[tx+16b][i], ascending i, one FMA chain each
-__device__ inline void half_tile_product(const float *__restrict__ Xs, const float *__restrict__ Ps, int ty, int tx,
-                                         float (&acc)[4][8]) {
+constexpr int kQRows = 64;   // tokens per work item of quantize_kernel: one half of a plan tile
+constexpr int kLdH = 136;    // padded fp16 row stride (272 bytes: conflict-free ldmatrix rows)
+
+// Decision margin of the tensor-core pass.  The rotation is first evaluated with fp16 operands on the
+// tensor cores; with |x_unit| <= 1 and |row of Pi| = 1 the result differs from the fp32 FMA chain by at
+// most  (2^-10 + 2^-22) * sum|x_i p_i|  (operand rounding, sum|x_i p_i| <= 1 by Cauchy-Schwarz)
+//     + 2^-25 * (sum|x_i| + sum|p_i|)   (fp16 subnormal operands, <= 6.8e-7)
+//     + 128 * 2^-21                     (accumulation, generous) + 128 * 2^-24 (the chain's own error)
+//     <= 1.05e-3.
+// The decision itself runs in fp16 against fp16 midpoints of adjacent centroids: both roundings cost at
+// most 2^-14 each for |y| < 0.25 (every midpoint of the 2/3/4-bit codebooks is below 0.22).  A coordinate
+// closer than kTcMarginBits (1.2503e-3 >= 1.05e-3 + 2 * 6.1e-5) to a midpoint is recomputed with the exact
+// chain and the exact rule, so every emitted code equals the code of the chain.
+constexpr uint32_t kTcMarginBits = 0x151f151fu;   // half2 {1.2503e-3, 1.2503e-3}
+
+// per-level constants of the fp16 decision: positive midpoints (padded with +inf) and the code offset
+struct LevelConst {
+    uint32_t mid[7];   // half2 broadcast
+    uint32_t base;     // half2 broadcast of 512 + K/2 - 0.5
+};
+
+__device__ __forceinline__ __half2 u2h(uint32_t u) { return *reinterpret_cast<__half2 *>(&u); }
+__device__ __forceinline__ uint32_t h2u(__half2 h) { return *reinterpret_cast<uint32_t *>(&h); }
+
+// Two coordinates at once.  Returns the fp16 pair 512 + code (so code = (bits >> 1) & 15 per half); `ok`
+// holds 1.0 per half whose distance to every midpoint (and to zero) is at least the margin.
+template <int NM>
+__device__ __forceinline__ uint32_t decide_pair(uint32_t y2, const uint32_t (&mid)[7], uint32_t base, uint32_t &ok) {
+    const __half2 ay = __habs2(u2h(y2));
+    __half2 cnt = __hgt2(ay, u2h(mid[0]));
+    __half2 d = __hmin2(ay, __habs2(__hsub2(ay, u2h(mid[0]))));
 #pragma unroll
-    for (int a = 0; a < 4; ++a)
-#pragma unroll
-        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
-    const float *xrow = Xs + ty * kLd;
-    const float *prow = Ps + tx * kLd;
-#pragma unroll 2
-    for (int i4 = 0; i4 < kD / 4; ++i4) {
-        float4 xa[4], pb[8];
-#pragma unroll
-        for (int a = 0; a < 4; ++a) xa[a] = *reinterpret_cast<const float4 *>(xrow + a * 16 * kLd + 4 * i4);
-#pragma unroll
-        for (int b = 0; b < 8; ++b) pb[b] = *reinterpret_cast<const float4 *>(prow + b * 16 * kLd + 4 * i4);
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int b = 0; b < 8; ++b) {
-                float v = acc[a][b];
-                v = fmaf(xa[a].x, pb[b].x, v);
-                v = fmaf(xa[a].y, pb[b].y, v);
-                v = fmaf(xa[a].z, pb[b].z, v);
-                v = fmaf(xa[a].w, pb[b].w, v);
-                acc[a][b] = v;
-            }
+    for (int j = 1; j < NM; ++j) {
+        cnt = __hadd2(cnt, __hgt2(ay, u2h(mid[j])));
+        d = __hmin2(d, __habs2(__hsub2(ay, u2h(mid[j]))));
     }
+    const uint32_t sgn = (y2 & 0x80008000u) | 0x3c003c00u;   // +-1.0
+    const __half2 cf = __hfma2(u2h(sgn), __hadd2(cnt, u2h(0x38003800u)), u2h(base));
+    ok = h2u(__hge2(d, u2h(kTcMarginBits)));                  // NaN compares false
+    return h2u(cf);
 }
 
-constexpr int kQRows = 64;  // tokens per work item of quantize_kernel: one half of a plan tile
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *smem_ptr) {
+    const uint32_t addr = (uint32_t)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
 
-// searchsorted(left) by counting the centroids below y (K <= 8 centroids held in registers), then the
-// nearer neighbour, lower index on ties: the same result as nearest_centroid()
-template <int K>
-__device__ __forceinline__ int nearest_counted(float y, const float (&c)[8], const float *__restrict__ cbl) {
-    int idx = 0;
-#pragma unroll
-    for (int j = 0; j < K; ++j) idx += (c[j] < y) ? 1 : 0;
-    const int a = idx - 1 < 0 ? 0 : idx - 1;
-    const int b = idx > K - 1 ? K - 1 : idx;
-    const float da = fabsf(__fsub_rn(y, cbl[a]));
-    const float db = fabsf(__fsub_rn(y, cbl[b]));
-    return (da <= db) ? a : b;
+__device__ __forceinline__ void hmma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
 // the 16-byte pieces of a half tile that one thread moves (64 rows of 128 elements, 256 threads)
@@ -239,37 +247,72 @@ __device__ __forceinline__ void store_pieces_f32(const RawPieces<DT> &r, int tid
     }
 }
 
-// One CTA serves one side (even blocks: keys, odd blocks: values), keeps that side's rotation in
-// shared memory and walks over half tiles of 64 tokens; two CTAs share an SM, so the norm chain,
-// divisions and packing of one overlap the product of the other.  The next item's rows, bit widths
-// and slot bases are fetched into registers right after the product, under the centroid search and
-// the packing of the current item.
+// overwrite the b-bit code of coordinate `col` in a packed row held in shared memory
+__device__ __forceinline__ void patch_code(uint32_t *__restrict__ row_words, int b, int col, uint32_t code) {
+    const int bit = b * col, wi = bit >> 5, sh = bit & 31;
+    const uint32_t mask = (1u << b) - 1u;
+    atomicAnd(row_words + wi, ~(mask << sh));
+    atomicOr(row_words + wi, code << sh);
+    if (sh + b > 32) {
+        atomicAnd(row_words + wi + 1, ~(mask >> (32 - sh)));
+        atomicOr(row_words + wi + 1, code >> (32 - sh));
+    }
+}
+
+// One CTA serves one side (even blocks: keys, odd blocks: values) and walks over half tiles of 64
+// tokens; two CTAs share an SM.  Per item: rows -> fp32 shared tile; norm (one ascending FMA chain per
+// row, IEEE square root); IEEE division; the 64x128x128 rotation on the tensor cores with fp16 operands;
+// an fp16 decision per coordinate, packed straight into the row's bit stream in shared memory (a thread
+// owns eight consecutive coordinates of a row); every coordinate closer to a decision boundary than the
+// tensor-core error bound is queued and recomputed with the exact fp32 chain (ascending contraction
+// index, one FMA per term) and the exact nearest-centroid rule, then patched into the packed row -- so
+// the codes are those of the chain, bit for bit; copy-out.  The next item's rows, bit widths and slot
+// bases are fetched into registers under the decision step of the current one.
 template <int DT>
 __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *Ps = reinterpret_cast<float *>(smem_raw);   // [128][kLd]
-    float *Xs = Ps + kD * kLd;                          // [64][kLd]
-    float *cb = Xs + kQRows * kLd;                      // [4][256]
-    float *nrm = cb + 4 * 256;                          // [64]
-    int *cls = reinterpret_cast<int *>(nrm + kQRows);   // [128]
-    int *slot = cls + kTile;                            // [128]
-    int *wcnt = slot + kTile;                           // [4][6]
-    int *tbase = wcnt + 4 * kNumClasses;                // [6] slot base of this plan tile per class
-    int *flags = tbase + 8;                             // [1]
+    float *Xs = reinterpret_cast<float *>(smem_raw);                 // [64][kLd] fp32 rows, normalised in place
+    __half *Ph = reinterpret_cast<__half *>(Xs + kQRows * kLd);      // [128][kLdH] fp16 rotation, rows permuted
+    __half *Xh = Ph + kD * kLdH;                                     // [64][kLdH] fp16 normalised rows
+    float *cb = reinterpret_cast<float *>(Xh + kQRows * kLdH);       // [4][256]
+    float *nrm = cb + 4 * 256;                                       // [64]
+    int *cls = reinterpret_cast<int *>(nrm + kQRows);                // [128]
+    int *slot = cls + kTile;                                         // [128]
+    int *wcnt = slot + kTile;                                        // [4][6]
+    int *tbase = wcnt + 4 * kNumClasses;                             // [8] slot base of this plan tile per class
+    int *flags = tbase + 8;                                          // [0] any quantised row, [1] queue length
+    LevelConst *lc = reinterpret_cast<LevelConst *>(flags + 8);      // [3] 2, 3, 4 bits
+    uint16_t *queue = reinterpret_cast<uint16_t *>(lc + 3);          // [64*128] coordinates to recompute
+    unsigned char *PK = reinterpret_cast<unsigned char *>(Xh);       // [64][kLdC] packed rows (after the product)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int ty = tid >> 4, tx = tid & 15;
     const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
     const int side = blockIdx.x & 1;
     const void *src = side ? a.V : a.K;
-    {
-        const float *pi = side ? a.pi_v : a.pi_k;
-        for (int g = tid; g < kD * kD / 4; g += 256) {
-            int j = g >> 5, i4 = g & 31;
-            *reinterpret_cast<float4 *>(Ps + j * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(pi + j * kD + 4 * i4);
-        }
+    const float *pi = side ? a.pi_v : a.pi_k;
+    // shared row q of the fp16 rotation holds row j(q) of Pi, chosen so that the eight tensor-core columns
+    // a thread owns per 32-column window are eight consecutive coordinates:
+    //   q = 32 wn + 8 nb + n  ->  j = 32 wn + 8 (n >> 1) + 2 nb + (n & 1)
+    for (int g = tid; g < kD * kD / 4; g += 256) {
+        const int q = g >> 5, i4 = g & 31;
+        const int j = (q & ~31) + 8 * ((q & 7) >> 1) + 2 * ((q >> 3) & 3) + (q & 1);
+        const float4 f = *reinterpret_cast<const float4 *>(pi + j * kD + 4 * i4);
+        __half2 *dst = reinterpret_cast<__half2 *>(Ph + q * kLdH + 4 * i4);
+        dst[0] = __floats2half2_rn(f.x, f.y);
+        dst[1] = __floats2half2_rn(f.z, f.w);
     }
     for (int g = tid; g < 4 * 256; g += 256) cb[g] = a.codebooks[g];
+    if (tid < 3 * 8) {
+        const int li = tid >> 3, j = tid & 7, half_k = 1 << (li + 1);   // K/2 for 2, 3, 4 bits
+        const float *cbl = a.codebooks + li * 256;
+        if (j < 7) {
+            __half m = __ushort_as_half((unsigned short)0x7c00);        // +inf: never exceeded, never near
+            if (j + 1 < half_k) m = __float2half_rn(0.5f * (cbl[half_k + j] + cbl[half_k + j + 1]));
+            lc[li].mid[j] = h2u(__half2half2(m));
+        } else {
+            lc[li].base = h2u(__half2half2(__float2half_rn(512.0f + (float)half_k - 0.5f)));
+        }
+    }
 
     const long long n_work = (long long)BH * a.ntiles * 2;
     const long long w_step = gridDim.x >> 1;
@@ -290,12 +333,15 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
     prefetch(blockIdx.x >> 1);
     __syncthreads();
 
+    // tensor-core tiling: warp (wm, wn) owns rows [32 wm, +32) and columns [32 wn, +32)
+    const int wm = warp & 1, wn = warp >> 1, g8 = lane >> 2, t4 = lane & 3;
+
     for (long long w = blockIdx.x >> 1; w < n_work; w += w_step) {
         const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
         const int tile = rem >> 1, half = rem & 1;
         const int t0 = tile * kTile, h0 = half * kQRows;
         if (t0 + h0 >= T) { prefetch(w + w_step); continue; }
-        if (tid == 0) flags[0] = 0;
+        if (tid == 0) { flags[0] = 0; flags[1] = 0; }
         // ---- classes and slots of the whole plan tile (the slot of a token counts the tokens before it)
         int c = -1, rank = 0;
         if (tid < kTile) {
@@ -339,7 +385,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
         const bool any_q = flags[0] != 0;
         const size_t row0 = ((size_t)bh * T + t0 + h0) * kD;
         if (any_q) {
-            // ---- x / (norm + 1e-10), IEEE division
+            // ---- x / (norm + 1e-10), IEEE division; fp32 result in place, fp16 copy for the tensor cores
 #pragma unroll
             for (int u = 0; u < kQRows * kD / 4 / 256; ++u) {
                 const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
@@ -351,68 +397,135 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                 v.z = __fdiv_rn(v.z, den);
                 v.w = __fdiv_rn(v.w, den);
                 *p = v;
+                __half2 *hd = reinterpret_cast<__half2 *>(Xh + r * kLdH + 4 * i4);
+                hd[0] = __floats2half2_rn(v.x, v.y);
+                hd[1] = __floats2half2_rn(v.z, v.w);
             }
             __syncthreads();
-            float acc[4][8];
-            half_tile_product(Xs, Ps, ty, tx, acc);
-            __syncthreads();
+            // ---- approximate rotation on the tensor cores: acc[mb][nb] = 16x8 block of X Pi^T
+            float acc[2][4][4];
+#pragma unroll
+            for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+                for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) acc[mb][nb][e] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < kD / 16; ++ks) {
+                uint32_t af[2][4], bf[2][4];
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb)
+                    ldmatrix_x4(af[mb], Xh + (32 * wm + 16 * mb + (lane & 15)) * kLdH + 16 * ks + 8 * (lane >> 4));
+#pragma unroll
+                for (int np = 0; np < 2; ++np)
+                    ldmatrix_x4(bf[np], Ph + (32 * wn + 16 * np + 8 * (lane >> 4) + (lane & 7)) * kLdH + 16 * ks + 8 * ((lane >> 3) & 1));
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb)
+#pragma unroll
+                    for (int nb = 0; nb < 4; ++nb)
+                        hmma_16816(acc[mb][nb], af[mb], bf[nb >> 1][2 * (nb & 1)], bf[nb >> 1][2 * (nb & 1) + 1]);
+            }
+            __syncthreads();   // every warp is done with Xh: the packed rows reuse its space
             prefetch(w + w_step);
-            // ---- nearest centroid, staged as bytes over the tile buffer
-            uint8_t *C8 = reinterpret_cast<uint8_t *>(Xs);
+            // ---- fp16 decision and packing; this thread's coordinates of a row are 32 wn + 8 t4 + [0, 8),
+            //      element (nb, e) of the accumulator being coordinate 2 nb + e of those
 #pragma unroll
-            for (int aa = 0; aa < 4; ++aa) {
-                const int r = ty + 16 * aa;
-                const int cc = cls[h0 + r];
-                if (cc == 1 || cc == 2) {
-                    const float *cbl = cb + (cc - 1) * 256;
-                    float cr[8];
+            for (int mb = 0; mb < 2; ++mb)
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) cr[j] = cbl[j];
-                    if (cc == 1) {
+                for (int hi = 0; hi < 2; ++hi) {
+                    const int r = 32 * wm + 16 * mb + g8 + 8 * hi;
+                    const int cc = cls[h0 + r];
+                    if (cc < 1 || cc > 4) continue;
+                    const int col0 = 32 * wn + 8 * t4;
+                    if (cc == 4) {   // 8 bits: the centroid spacing is within the margin, every coordinate is exact work
 #pragma unroll
-                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_counted<4>(acc[aa][bb], cr, cbl);
-                    } else {
-#pragma unroll
-                        for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_counted<8>(acc[aa][bb], cr, cbl);
+                        for (int k = 0; k < 8; ++k) queue[atomicAdd(&flags[1], 1)] = (uint16_t)((r << 7) | (col0 + k));
+                        continue;
                     }
-                } else if (cc == 3 || cc == 4) {
-                    const int li = cc - 1;
-                    const float *cbl = cb + li * 256;
-                    const int k = 1 << bits_of_qlevel(li);
+                    const int b = cc + 1;
+                    const LevelConst &L = lc[cc - 1];
+                    uint32_t mid[7];
 #pragma unroll
-                    for (int bb = 0; bb < 8; ++bb) C8[r * kLdC + tx + 16 * bb] = (uint8_t)nearest_centroid(acc[aa][bb], cbl, k);
+                    for (int j = 0; j < 7; ++j) mid[j] = L.mid[j];
+                    const uint32_t base = L.base;
+                    uint32_t word = 0, bad = 0;
+#pragma unroll
+                    for (int nb = 0; nb < 4; ++nb) {
+                        const uint32_t y2 = h2u(__floats2half2_rn(acc[mb][nb][2 * hi], acc[mb][nb][2 * hi + 1]));
+                        uint32_t ok, cf;
+                        if (cc == 3) cf = decide_pair<7>(y2, mid, base, ok);
+                        else cf = decide_pair<3>(y2, mid, base, ok);
+                        const uint32_t field = ((cf >> 1) & 15u) | (((cf >> 17) & 15u) << b);
+                        word |= field << (2 * b * nb);
+                        if ((ok & 0xffffu) != 0x3c00u) bad |= 1u << (2 * nb);
+                        if ((ok >> 16) != 0x3c00u) bad |= 2u << (2 * nb);
+                    }
+                    unsigned char *dst = PK + r * kLdC + b * (4 * wn + t4);
+                    if (b == 2) *reinterpret_cast<uint16_t *>(dst) = (uint16_t)word;
+                    else if (b == 4) *reinterpret_cast<uint32_t *>(dst) = word;
+                    else { dst[0] = (unsigned char)word; dst[1] = (unsigned char)(word >> 8); dst[2] = (unsigned char)(word >> 16); }
+                    while (bad) {
+                        const int k = __ffs(bad) - 1;
+                        bad &= bad - 1;
+                        queue[atomicAdd(&flags[1], 1)] = (uint16_t)((r << 7) | (col0 + k));
+                    }
                 }
+            __syncthreads();
+            // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain, exact rule
+            const int qn = flags[1];
+            for (int e = tid; e < qn; e += 256) {
+                const int r = queue[e] >> 7, col = queue[e] & 127;
+                const float4 *xr = reinterpret_cast<const float4 *>(Xs + r * kLd);
+                const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);
+                float y = 0.0f;
+#pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    float4 pv[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) pv[i] = __ldg(pr + 16 * hb + i);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float4 xv = xr[16 * hb + i];
+                        y = fmaf(xv.x, pv[i].x, y);
+                        y = fmaf(xv.y, pv[i].y, y);
+                        y = fmaf(xv.z, pv[i].z, y);
+                        y = fmaf(xv.w, pv[i].w, y);
+                    }
+                }
+                const int li = cls[h0 + r] - 1;
+                const int code = nearest_centroid(y, cb + li * 256, 1 << bits_of_qlevel(li));
+                patch_code(reinterpret_cast<uint32_t *>(PK + r * kLdC), qbits(li), col, (uint32_t)code);
             }
             __syncthreads();
         } else {
             prefetch(w + w_step);
         }
-        // ---- pack and store: one warp per row
-        const uint8_t *C8 = reinterpret_cast<const uint8_t *>(Xs);
-#pragma unroll 2
-        for (int r = warp; r < kQRows; r += 8) {
-            int cc = cls[h0 + r];
-            int s = slot[h0 + r];
-            if (cc < 0) continue;
-            int t_abs = a.ch.t_offset + t0 + h0 + r;
+        // ---- copy-out: four threads per row, each moves a quarter of the row
+        {
+            const int r = tid >> 2, qt = tid & 3;
+            const int cc = cls[h0 + r];
+            const int s = slot[h0 + r];
+            const int t_abs = a.ch.t_offset + t0 + h0 + r;
             if (cc >= 1 && cc <= 4) {
-                int li = cc - 1;
-                if (side == 0) store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.k_codes[3] : a.k_scratch[li], s, lane);
-                else store_linear_codes(C8 + r * kLdC, li, li == 3 ? a.ch.v_codes[3] : a.v_scratch[li], s, lane);
-                if (lane == 0) {
+                const int li = cc - 1, nw = qbits(li);   // words per quarter row
+                uint8_t *rows = side ? (li == 3 ? a.ch.v_codes[3] : a.v_scratch[li]) : (li == 3 ? a.ch.k_codes[3] : a.k_scratch[li]);
+                uint32_t *dst = reinterpret_cast<uint32_t *>(rows + (size_t)s * 16 * nw) + qt * nw;
+                const uint32_t *srcw = reinterpret_cast<const uint32_t *>(PK + r * kLdC) + qt * nw;
+                for (int k = 0; k < nw; ++k) dst[k] = srcw[k];
+                if (qt == 0) {
                     (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[r];
                     if (side == 0) a.ch.pos[li][s] = t_abs;
                 }
             } else if (cc == 5) {
-                const unsigned char *srow = reinterpret_cast<const unsigned char *>(src) + (row0 + (size_t)r * kD) * sizeof(typename Elem<DT>::T);
-                unsigned char *drow = reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + (size_t)s * kD * sizeof(typename Elem<DT>::T);
-                if constexpr (DT == kF32) {
-                    reinterpret_cast<uint4 *>(drow)[lane] = reinterpret_cast<const uint4 *>(srow)[lane];
-                } else {
-                    reinterpret_cast<uint2 *>(drow)[lane] = reinterpret_cast<const uint2 *>(srow)[lane];
-                }
-                if (lane == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
-            } else if (cc == 0 && side == 0 && lane == 0) {
+                constexpr int kVec = (int)(kD * sizeof(typename Elem<DT>::T) / 64);   // 16-byte pieces per quarter row
+                const uint4 *srow = reinterpret_cast<const uint4 *>(reinterpret_cast<const unsigned char *>(src) +
+                                                                    (row0 + (size_t)r * kD) * sizeof(typename Elem<DT>::T)) + qt * kVec;
+                uint4 *drow = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) +
+                                                        (size_t)s * kD * sizeof(typename Elem<DT>::T)) + qt * kVec;
+#pragma unroll
+                for (int k = 0; k < kVec; ++k) drow[k] = srow[k];
+                if (qt == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
+            } else if (cc == 0 && side == 0 && qt == 0) {
                 a.ch.evicted_pos[s] = t_abs;
             }
         }
@@ -701,7 +814,8 @@ static int num_sms() {
     return n;
 }
 
-constexpr size_t kQuantKernelSmem = (size_t)(kD * kLd + kQRows * kLd + 4 * 256 + kQRows) * sizeof(float) + (2 * kTile + 4 * kNumClasses + 16) * sizeof(int);
+constexpr size_t kQuantKernelSmem = (size_t)(kQRows * kLd + 4 * 256 + kQRows) * sizeof(float) + (size_t)(kD + kQRows) * kLdH * 2 +
+                                    (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + 3 * sizeof(LevelConst) + (size_t)kQRows * kD * 2;
 constexpr size_t kDequantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + kTile * sizeof(long long);
 
 }  // namespace odmkv
@@ -783,6 +897,8 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     cudaError_t e;
 #define ODMKV_LAUNCH_Q(DT)                                                                                   \
     e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kQuantKernelSmem); \
+    if (e != cudaSuccess) return (int)e;                                                                     \
+    e = cudaFuncSetAttribute(quantize_kernel<DT>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared); \
     if (e != cudaSuccess) return (int)e;                                                                     \
     fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.k_scratch[0], a.k_scratch[1], a.k_scratch[2], a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
     timing_begin("quantize", st);                                                                            \
