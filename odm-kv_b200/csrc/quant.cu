@@ -259,33 +259,49 @@ __device__ __forceinline__ void patch_code(uint32_t *__restrict__ row_words, int
     }
 }
 
-// One CTA serves one side (even blocks: keys, odd blocks: values) and walks over half tiles of 64
-// tokens; two CTAs share an SM.  Per item: rows -> fp32 shared tile; norm (one ascending FMA chain per
-// row, IEEE square root); IEEE division; the 64x128x128 rotation on the tensor cores with fp16 operands;
-// an fp16 decision per coordinate, packed straight into the row's bit stream in shared memory (a thread
-// owns eight consecutive coordinates of a row); every coordinate closer to a decision boundary than the
-// tensor-core error bound is queued and recomputed with the exact fp32 chain (ascending contraction
-// index, one FMA per term) and the exact nearest-centroid rule, then patched into the packed row -- so
-// the codes are those of the chain, bit for bit; copy-out.  The next item's rows, bit widths and slot
-// bases are fetched into registers under the decision step of the current one.
+// One CTA serves one side (even blocks: keys, odd blocks: values) with two independent groups of 256
+// threads; each group walks over half tiles of 64 tokens with its own buffers and its own named barrier,
+// so the latency-bound steps of one group run under the arithmetic of the other.  The fp32 rotation of
+// the side (for the exact chains) and its fp16 copy (for the tensor cores) are shared by both groups.
+// Per item: rows -> fp32 shared tile; norm (one ascending FMA chain per row, IEEE square root); IEEE
+// division; the 64x128x128 rotation on the tensor cores with fp16 operands; an fp16 decision per
+// coordinate, packed straight into the row's bit stream in shared memory (a thread owns eight consecutive
+// coordinates of a row); every coordinate closer to a decision boundary than the tensor-core error bound
+// is queued and recomputed with the exact fp32 chain (ascending contraction index, one FMA per term) and
+// the exact nearest-centroid rule, then patched into the packed row -- so the codes are those of the
+// chain, bit for bit; copy-out.  The next item's rows, bit widths and slot bases are fetched into
+// registers under the decision step of the current one.
+constexpr int kQueueCap = 2048;   // queued coordinates per item; beyond that the whole item is redone exactly
+constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + (size_t)kQRows * kLdH * 2 +
+                                   (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + (size_t)kQueueCap * 2;
+constexpr size_t kQuantKernelSmem = (size_t)(kD * kLd + 4 * 256) * sizeof(float) + (size_t)kD * kLdH * 2 + 3 * sizeof(LevelConst) +
+                                    2 * kQuantGroupSmem;
+
+__device__ __forceinline__ void group_sync(int gid) {
+    asm volatile("bar.sync %0, 256;\n" ::"r"(gid + 1) : "memory");
+}
+
 template <int DT>
-__global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
+__global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *Xs = reinterpret_cast<float *>(smem_raw);                 // [64][kLd] fp32 rows, normalised in place
-    __half *Ph = reinterpret_cast<__half *>(Xs + kQRows * kLd);      // [128][kLdH] fp16 rotation, rows permuted
-    __half *Xh = Ph + kD * kLdH;                                     // [64][kLdH] fp16 normalised rows
-    float *cb = reinterpret_cast<float *>(Xh + kQRows * kLdH);       // [4][256]
-    float *nrm = cb + 4 * 256;                                       // [64]
-    int *cls = reinterpret_cast<int *>(nrm + kQRows);                // [128]
+    float *Pf = reinterpret_cast<float *>(smem_raw);                 // [128][kLd] fp32 rotation (exact chains)
+    float *cb = Pf + kD * kLd;                                       // [4][256]
+    __half *Ph = reinterpret_cast<__half *>(cb + 4 * 256);           // [128][kLdH] fp16 rotation, rows permuted
+    LevelConst *lc = reinterpret_cast<LevelConst *>(Ph + kD * kLdH); // [3] 2, 3, 4 bits
+    const int gid = threadIdx.x >> 8, tid = threadIdx.x & 255;       // group, thread within the group
+    unsigned char *gbase = reinterpret_cast<unsigned char *>(lc + 3) + (size_t)gid * kQuantGroupSmem;
+    float *Xs = reinterpret_cast<float *>(gbase);                    // [64][kLd] fp32 rows, normalised in place
+    float *nrm = Xs + kQRows * kLd;                                  // [64]
+    __half *Xh = reinterpret_cast<__half *>(nrm + kQRows);           // [64][kLdH] fp16 normalised rows
+    int *cls = reinterpret_cast<int *>(Xh + kQRows * kLdH);          // [128]
     int *slot = cls + kTile;                                         // [128]
     int *wcnt = slot + kTile;                                        // [4][6]
     int *tbase = wcnt + 4 * kNumClasses;                             // [8] slot base of this plan tile per class
     int *flags = tbase + 8;                                          // [0] any quantised row, [1] queue length
-    LevelConst *lc = reinterpret_cast<LevelConst *>(flags + 8);      // [3] 2, 3, 4 bits
-    uint16_t *queue = reinterpret_cast<uint16_t *>(lc + 3);          // [64*128] coordinates to recompute
+    uint16_t *queue = reinterpret_cast<uint16_t *>(flags + 8);       // [kQueueCap] coordinates to recompute
     unsigned char *PK = reinterpret_cast<unsigned char *>(Xh);       // [64][kLdC] packed rows (after the product)
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lane = tid & 31, warp = tid >> 5;
     const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
     const int side = blockIdx.x & 1;
     const void *src = side ? a.V : a.K;
@@ -293,17 +309,18 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
     // shared row q of the fp16 rotation holds row j(q) of Pi, chosen so that the eight tensor-core columns
     // a thread owns per 32-column window are eight consecutive coordinates:
     //   q = 32 wn + 8 nb + n  ->  j = 32 wn + 8 (n >> 1) + 2 nb + (n & 1)
-    for (int g = tid; g < kD * kD / 4; g += 256) {
+    for (int g = threadIdx.x; g < kD * kD / 4; g += 512) {
         const int q = g >> 5, i4 = g & 31;
         const int j = (q & ~31) + 8 * ((q & 7) >> 1) + 2 * ((q >> 3) & 3) + (q & 1);
         const float4 f = *reinterpret_cast<const float4 *>(pi + j * kD + 4 * i4);
         __half2 *dst = reinterpret_cast<__half2 *>(Ph + q * kLdH + 4 * i4);
         dst[0] = __floats2half2_rn(f.x, f.y);
         dst[1] = __floats2half2_rn(f.z, f.w);
+        *reinterpret_cast<float4 *>(Pf + q * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(pi + q * kD + 4 * i4);
     }
-    for (int g = tid; g < 4 * 256; g += 256) cb[g] = a.codebooks[g];
-    if (tid < 3 * 8) {
-        const int li = tid >> 3, j = tid & 7, half_k = 1 << (li + 1);   // K/2 for 2, 3, 4 bits
+    for (int g = threadIdx.x; g < 4 * 256; g += 512) cb[g] = a.codebooks[g];
+    if (threadIdx.x < 3 * 8) {
+        const int li = threadIdx.x >> 3, j = threadIdx.x & 7, half_k = 1 << (li + 1);   // K/2 for 2, 3, 4 bits
         const float *cbl = a.codebooks + li * 256;
         if (j < 7) {
             __half m = __ushort_as_half((unsigned short)0x7c00);        // +inf: never exceeded, never near
@@ -315,7 +332,8 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
     }
 
     const long long n_work = (long long)BH * a.ntiles * 2;
-    const long long w_step = gridDim.x >> 1;
+    const long long w_step = (long long)(gridDim.x >> 1) * 2;   // two groups per CTA, half of the CTAs per side
+    const long long w_first = (long long)(blockIdx.x >> 1) * 2 + gid;
     // fetched ahead: rows, this thread's bit width (threads < 128) and slot base (threads < 6)
     RawPieces<DT> raw;
     int pf_bits = 0, pf_base = 0;
@@ -330,13 +348,13 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
         if (tid < kNumClasses)
             pf_base = a.ch.seg_start[tid * BH + bh] + a.tile_base[((size_t)bh * a.ntiles + tile) * kNumClasses + tid];
     };
-    prefetch(blockIdx.x >> 1);
+    prefetch(w_first);
     __syncthreads();
 
     // tensor-core tiling: warp (wm, wn) owns rows [32 wm, +32) and columns [32 wn, +32)
     const int wm = warp & 1, wn = warp >> 1, g8 = lane >> 2, t4 = lane & 3;
 
-    for (long long w = blockIdx.x >> 1; w < n_work; w += w_step) {
+    for (long long w = w_first; w < n_work; w += w_step) {
         const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
         const int tile = rem >> 1, half = rem & 1;
         const int t0 = tile * kTile, h0 = half * kQRows;
@@ -355,7 +373,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
             if (tid < kNumClasses) tbase[tid] = pf_base;
         }
         store_pieces_f32<DT>(raw, tid, Xs);
-        __syncthreads();
+        group_sync(gid);
         if (tid < kTile) {
             int s = -1;
             if (c >= 0) {
@@ -381,7 +399,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
             }
             nrm[r] = __fsqrt_rn(acc);
         }
-        __syncthreads();
+        group_sync(gid);
         const bool any_q = flags[0] != 0;
         const size_t row0 = ((size_t)bh * T + t0 + h0) * kD;
         if (any_q) {
@@ -401,7 +419,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                 hd[0] = __floats2half2_rn(v.x, v.y);
                 hd[1] = __floats2half2_rn(v.z, v.w);
             }
-            __syncthreads();
+            group_sync(gid);
             // ---- approximate rotation on the tensor cores: acc[mb][nb] = 16x8 block of X Pi^T
             float acc[2][4][4];
 #pragma unroll
@@ -425,7 +443,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                     for (int nb = 0; nb < 4; ++nb)
                         hmma_16816(acc[mb][nb], af[mb], bf[nb >> 1][2 * (nb & 1)], bf[nb >> 1][2 * (nb & 1) + 1]);
             }
-            __syncthreads();   // every warp is done with Xh: the packed rows reuse its space
+            group_sync(gid);   // every warp is done with Xh: the packed rows reuse its space
             prefetch(w + w_step);
             // ---- fp16 decision and packing; this thread's coordinates of a row are 32 wn + 8 t4 + [0, 8),
             //      element (nb, e) of the accumulator being coordinate 2 nb + e of those
@@ -439,7 +457,10 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                     const int col0 = 32 * wn + 8 * t4;
                     if (cc == 4) {   // 8 bits: the centroid spacing is within the margin, every coordinate is exact work
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) queue[atomicAdd(&flags[1], 1)] = (uint16_t)((r << 7) | (col0 + k));
+                        for (int k = 0; k < 8; ++k) {
+                            const int qi = atomicAdd(&flags[1], 1);
+                            if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + k));
+                        }
                         continue;
                     }
                     const int b = cc + 1;
@@ -467,36 +488,34 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                     while (bad) {
                         const int k = __ffs(bad) - 1;
                         bad &= bad - 1;
-                        queue[atomicAdd(&flags[1], 1)] = (uint16_t)((r << 7) | (col0 + k));
+                        const int qi = atomicAdd(&flags[1], 1);
+                        if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + k));
                     }
                 }
-            __syncthreads();
+            group_sync(gid);
             // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain, exact rule
             const int qn = flags[1];
-            for (int e = tid; e < qn; e += 256) {
-                const int r = queue[e] >> 7, col = queue[e] & 127;
-                const float4 *xr = reinterpret_cast<const float4 *>(Xs + r * kLd);
-                const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);
-                float y = 0.0f;
-#pragma unroll
-                for (int hb = 0; hb < 2; ++hb) {
-                    float4 pv[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) pv[i] = __ldg(pr + 16 * hb + i);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const float4 xv = xr[16 * hb + i];
-                        y = fmaf(xv.x, pv[i].x, y);
-                        y = fmaf(xv.y, pv[i].y, y);
-                        y = fmaf(xv.z, pv[i].z, y);
-                        y = fmaf(xv.w, pv[i].w, y);
-                    }
-                }
+            const bool redo_all = qn > kQueueCap;   // queue overflow: every coordinate of the item is exact work
+            const int n_fix = redo_all ? kQRows * kD : qn;
+            for (int e = tid; e < n_fix; e += 256) {
+                const int r = redo_all ? (e >> 7) : (queue[e] >> 7), col = redo_all ? (e & 127) : (queue[e] & 127);
                 const int li = cls[h0 + r] - 1;
+                if (li < 0 || li > 3) continue;
+                const float4 *xr = reinterpret_cast<const float4 *>(Xs + r * kLd);
+                const float4 *pr = reinterpret_cast<const float4 *>(Pf + col * kLd);
+                float y = 0.0f;
+#pragma unroll 8
+                for (int i = 0; i < kD / 4; ++i) {
+                    const float4 xv = xr[i], pv = pr[i];
+                    y = fmaf(xv.x, pv.x, y);
+                    y = fmaf(xv.y, pv.y, y);
+                    y = fmaf(xv.z, pv.z, y);
+                    y = fmaf(xv.w, pv.w, y);
+                }
                 const int code = nearest_centroid(y, cb + li * 256, 1 << bits_of_qlevel(li));
                 patch_code(reinterpret_cast<uint32_t *>(PK + r * kLdC), qbits(li), col, (uint32_t)code);
             }
-            __syncthreads();
+            group_sync(gid);
         } else {
             prefetch(w + w_step);
         }
@@ -529,7 +548,7 @@ __global__ void __launch_bounds__(256, 2) quantize_kernel(const QuantArgs a) {
                 a.ch.evicted_pos[s] = t_abs;
             }
         }
-        __syncthreads();
+        group_sync(gid);
     }
 }
 
@@ -814,8 +833,6 @@ static int num_sms() {
     return n;
 }
 
-constexpr size_t kQuantKernelSmem = (size_t)(kQRows * kLd + 4 * 256 + kQRows) * sizeof(float) + (size_t)(kD + kQRows) * kLdH * 2 +
-                                    (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + 3 * sizeof(LevelConst) + (size_t)kQRows * kD * 2;
 constexpr size_t kDequantSmem = (size_t)(3 * kD * kLd + 4 * 256 + kTile) * sizeof(float) + kTile * sizeof(long long);
 
 }  // namespace odmkv
@@ -891,8 +908,8 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
             off += 2 * bytes;
         }
     }
-    long long n_work = (long long)BH * a.ntiles * 2;   // half tiles; each is visited by a key CTA and a value CTA
-    int grid = 2 * (int)(n_work < 2 * num_sms() ? n_work : 2 * num_sms());
+    long long n_work = (long long)BH * a.ntiles * 2;   // half tiles; each is visited by a key group and a value group
+    int grid = 2 * (int)((n_work + 1) / 2 < num_sms() / 2 ? (n_work + 1) / 2 : num_sms() / 2);
     dim3 pad_grid(BH, kNumClasses);
     cudaError_t e;
 #define ODMKV_LAUNCH_Q(DT)                                                                                   \
@@ -902,7 +919,7 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     if (e != cudaSuccess) return (int)e;                                                                     \
     fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.k_scratch[0], a.k_scratch[1], a.k_scratch[2], a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
     timing_begin("quantize", st);                                                                            \
-    quantize_kernel<DT><<<grid, 256, kQuantKernelSmem, st>>>(a);                                                   \
+    quantize_kernel<DT><<<grid, 512, kQuantKernelSmem, st>>>(a);                                                   \
     timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q
