@@ -49,6 +49,7 @@ def parse():
     ap.add_argument("--decode-impl", default="auto")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
     return ap.parse_args()
 
 
@@ -111,6 +112,11 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def workload_name(ctx, batch, kv_heads, group, target_bits) -> str:
+    return (f"decode attention over packed cache: ctx {ctx}, batch {batch}, GQA {kv_heads * group}/{kv_heads}, d 128, target "
+            f"{target_bits} bits over {list(LEVELS)}, fp16 cache")
+
+
 def algorithmic_bytes_per_token_head(target_bits: float) -> float:
     """Expected bytes per stored token-head for the synthetic distribution (documentation only)."""
     return 71.0 if target_bits <= 2.0 else 104.0
@@ -162,8 +168,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"decode attention, ctx {args.ctx}, batch {args.batch}, GQA {args.kv_heads * args.group}/{args.kv_heads}, "
-                               f"d 128, target {args.target_bits} bits", "timing": "host wall clock, bounded sample scaled per (sample, KV head) unit"},
+        "config": {"workload": workload_name(args.ctx, args.batch, args.kv_heads, args.group, args.target_bits),
+                   "timing": "host wall clock; each step is a bounded sample (one batch element, all KV heads) scaled per (sample, KV head) unit",
+                   "reference_path": "dense fp32 softmax(q K^T) V over the dequantised cache with evicted keys masked, as the reference's decode step does on CPU"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -174,6 +181,20 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------
 # our arm
 # ------------------------------------------------------------------------------------------------
+
+def compress_rooflines(stage_ms, token_heads, packed_bytes, peak):
+    """Algorithmic HBM bytes of each compress stage over its measured time.  score: K and V once in 16 bit plus
+    one fp32 score (516 B per token-head); allocate: score in, bit width out (8 B); quantize: K, V and the bit
+    width in (516 B), packed banks out."""
+    alg = {"score": 516.0 * token_heads, "allocate": 8.0 * token_heads, "quantize": 516.0 * token_heads + packed_bytes}
+    out = {}
+    for k, b in alg.items():
+        ms = stage_ms.get(k)
+        if ms:
+            gbs = b / (ms * 1e-3) / 1e9
+            out[k] = {"algorithmic_bytes": b, "achieved_gbs": gbs, "frac_of_hbm_peak": gbs / peak}
+    return out
+
 
 def synth_kv(torch, B, H, T, G, dev, seed):
     """Config-0 style synthetic cache on the device: N(0,1) fp16, key channels 0-3 x10, four sink tokens."""
@@ -225,13 +246,14 @@ def run_ours(args):
         return ops.quantize_pack(K, V, bits, pi_k, pi_v), rep
 
     L.odmkv_timing_enable(0)
-    chunk, rep = compress()           # warm-up + the cache the decode steps read
+    warm, _ = compress()              # warm-up; freed so that the timed run reuses its device blocks
     torch.cuda.synchronize()
+    del warm
     stage_ms = {}
     L.odmkv_timing_enable(1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    chunk2, _ = compress()
+    chunk, rep = compress()           # timed; also the cache the decode steps read
     e1.record()
     torch.cuda.synchronize()
     compress_ms = e0.elapsed_time(e1)
@@ -240,7 +262,7 @@ def run_ours(args):
         tot, n = ctypes.c_double(), ctypes.c_longlong()
         L.odmkv_timing_read(name.encode(), ctypes.byref(tot), ctypes.byref(n))
         stage_ms[name] = tot.value
-    del chunk2
+    L.odmkv_timing_enable(0)
     reports = ops.read_reports(rep)
     cnt = chunk.seg_count_host().sum(axis=1)
     stored = int(cnt[1:].sum())
@@ -263,22 +285,58 @@ def run_ours(args):
     for i in range(max(args.warmup, 3)):
         out = step(i)
     torch.cuda.synchronize()
+
+    # The timed step is one CUDA graph of the four launches of a decode call (rotate, tensor-core kernel,
+    # exact/tail kernel on a forked stream, merge), replayed once per step: no host work inside the region.
+    step_mode = "cuda graph replay of one decode call"
+    graph = None
+    graph_err = None
+    if not args.eager:
+        try:
+            gq = qd.clone()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                g_out = ops.decode_attn(gq, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+            for _ in range(3):
+                graph.replay()
+            torch.cuda.synchronize()
+            graph_err = float((g_out.float() - out.float()).abs().max())
+        except Exception as exc:
+            graph, graph_err = None, repr(exc)[:200]
+    if graph is None:
+        step_mode = "eager launches through the C ABI"
+
+    def timed_step(i):
+        if graph is not None:
+            graph.replay()
+            return g_out
+        return step(i)
+
     if world > 1:
         dist.barrier()
-    L.odmkv_timing_enable(1)
     gathered = [torch.empty_like(out) for _ in range(world)] if world > 1 else None
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for i in range(args.steps):
-        out = step(i)
+        o = timed_step(i)
         if world > 1:
-            dist.all_gather(gathered, out)   # the per-head output gather of a KV-head / layer sharded run
+            dist.all_gather(gathered, o)   # the per-head output gather of a KV-head / layer sharded run
     ev1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     total_ms = ev0.elapsed_time(ev1)
+
+    # per-kernel durations: the same steps launched eagerly with an event pair around each kernel
+    L.odmkv_timing_enable(1)
+    ee0, ee1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ee0.record()
+    for i in range(args.steps):
+        out = step(i)
+    ee1.record()
+    torch.cuda.synchronize()
+    eager_ms = ee0.elapsed_time(ee1) / args.steps
     tot, n = ctypes.c_double(), ctypes.c_longlong()
     L.odmkv_timing_read(b"decode_main", ctypes.byref(tot), ctypes.byref(n))
     parts_ms = {}
@@ -350,10 +408,9 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "us_per_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 codes -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": f"decode attention over packed cache: ctx {T}, batch {B}, GQA {H * G}/{H}, d 128, target "
-                               f"{args.target_bits} bits over {list(LEVELS)}, fp16 cache",
+        "config": {"workload": workload_name(T, B, H, G, args.target_bits),
                    "l2": "packed cache per rank %.0f MB > 126 MB L2, re-read every step" % (bytes_per_step / 1e6),
-                   "timing": "CUDA events on the launching stream, max over ranks",
+                   "timing": "CUDA events on the launching stream, max over ranks; per-kernel times from a second, eager pass of the same steps",
                    "level_counts": {str(b): int(c) for b, c in zip(LEVELS, cnt)},
                    "stored_token_heads": stored, "bytes_per_step_per_rank": bytes_per_step,
                    "decode_impl": args.decode_impl, "n_splits": n_splits,
@@ -364,8 +421,11 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
                 "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": 4 * args.steps,
+        "step_mode": {"timed_step": step_mode, "graph_vs_eager_max_abs_diff": graph_err,
+                      "eager_ms_per_step_with_kernel_events": eager_ms},
         "clocks": clocks,
         "compress": {"mtok_per_s": B * T / (compress_ms * 1e-3) / 1e6, "ms_per_layer": compress_ms, "stage_ms": stage_ms,
+                     "stage_roofline": compress_rooflines(stage_ms, B * H * T, bytes_per_step, peak),
                      "tokens": B * T, "alloc_evaluations": reports[0]["evaluations"], "alloc_moved": reports[0]["moved"],
                      "ties_lambda": sum(r["ties_lambda"] for r in reports), "ties_cut": sum(r["ties_cut"] for r in reports)},
     }

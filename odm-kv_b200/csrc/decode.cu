@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
     }
     __syncthreads();
     float accr = 0.f, acce = 0.f;
-#pragma unroll 8
+#pragma unroll 16
     for (int s = 0; s < nsplit; ++s) {
         const float *p = part_acc + (((size_t)bh * nsplit + s) * GP + g) * 2 * kD;
         accr = fmaf(p[j], w[s], accr);
@@ -281,9 +281,17 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
     }
     ar[j] = accr;
     __syncthreads();
-    float o = 0.f;
-#pragma unroll 8
-    for (int i = 0; i < kD; ++i) o = fmaf(ar[i], pi_v[(size_t)i * kD + j], o);
+    // four interleaved partial sums keep 32 loads of the rotation in flight per thread
+    float o4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i0 = 0; i0 < kD; i0 += 32) {
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) pv[i] = __ldg(pi_v + (size_t)(i0 + i) * kD + j);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o4[i & 3] = fmaf(ar[i0 + i], pv[i], o4[i & 3]);
+    }
+    float o = (o4[0] + o4[1]) + (o4[2] + o4[3]);
     const float l = sh_ml[1];
     o = l > 0.f ? (o + acce) / l : 0.f;
     reinterpret_cast<typename Elem<ODT>::T *>(out)[(size_t)r * kD + j] = Elem<ODT>::from_f32(o);

@@ -23,6 +23,9 @@ namespace odmkv {
 
 constexpr int kMmaThreads = 256;
 constexpr int kMmaWarps = kMmaThreads / 32;
+#ifndef ODMKV_MMA_CTAS
+#define ODMKV_MMA_CTAS 2
+#endif
 #ifndef ODMKV_TILES_PER_ITER
 #define ODMKV_TILES_PER_ITER 3
 #endif
@@ -368,7 +371,7 @@ __device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, 
 }
 
 template <int NT>
-__global__ void __launch_bounds__(kMmaThreads, 2) decode_mma_kernel(const DecodeChunks chunks, const MmaArgs a) {
+__global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel(const DecodeChunks chunks, const MmaArgs a) {
     __shared__ float Osh[4 * NT][kD];
     __shared__ float lsh[4 * NT], Msh[4 * NT];
     __shared__ float warpM[kMmaWarps][4 * NT];
@@ -572,9 +575,6 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
             cudaError_t e2 = cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStageBytes);
             if (e1 != cudaSuccess) return (int)e1;
             if (e2 != cudaSuccess) return (int)e2;
-            // two CTAs per SM need the large shared-memory carveout
-            cudaFuncSetAttribute(decode_mma_kernel<1>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
-            cudaFuncSetAttribute(decode_mma_kernel<2>, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
             if (dev >= 0 && dev < 64) attr_set[dev] = true;
         }
     }

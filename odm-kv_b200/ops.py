@@ -182,8 +182,12 @@ class PackedChunk:
     exact_pos: Optional[torch.Tensor] = None
     evicted_pos: Optional[torch.Tensor] = None
     _seg_count_host: Optional[np.ndarray] = None
+    _c_struct: Optional[Chunk] = None     # chunks are immutable once built: the C view and the totals are cached
+    _stored: Optional[int] = None
 
     def c_struct(self) -> Chunk:
+        if self._c_struct is not None:
+            return self._c_struct
         c = Chunk()
         for li in range(NUM_QLEVELS):
             c.k_codes[li] = self.k_codes[li].data_ptr()
@@ -200,6 +204,7 @@ class PackedChunk:
         for k in range(NUM_CLASSES):
             c.cap[k] = int(self.totals[k])
         c.B, c.H, c.T, c.t_offset = self.B, self.H, self.T, self.t_offset
+        self._c_struct = c
         return c
 
     def seg_count_host(self) -> np.ndarray:
@@ -217,7 +222,9 @@ class PackedChunk:
         return total
 
     def stored_tokens(self) -> int:
-        return int(self.seg_count_host()[1:].sum())
+        if self._stored is None:
+            self._stored = int(self.seg_count_host()[1:].sum())
+        return self._stored
 
 
 def quantize_pack(K: torch.Tensor, V: torch.Tensor, bits: torch.Tensor, pi_k: torch.Tensor, pi_v: torch.Tensor,
