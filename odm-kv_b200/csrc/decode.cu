@@ -251,21 +251,35 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
 template <int ODT>
 __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restrict__ part_ml, const float *__restrict__ part_acc,
                                                            const float *__restrict__ pi_v, int G, int GP, int nsplit,
-                                                           void *__restrict__ out, float *__restrict__ lse) {
+                                                           void *__restrict__ out, float *__restrict__ lse, int n_main, int n_cta, int BH) {
     __shared__ float ar[kD];
     __shared__ float w[kMaxSlots];
     __shared__ float sh_ml[2];
     const int r = blockIdx.x;          // bh * G + g
     const int bh = r / G, g = r % G, j = threadIdx.x;
+    // Slots in use: all of them, or (n_cta > 0) the first `cnt` main slots -- one per CTA of the persistent
+    // tensor-core kernel that overlaps this unit -- followed by the slots from n_main on.
+    int cnt = nsplit, skip = 0;
+    if (n_cta > 0) {
+        const int first = (int)(((long long)bh * n_cta) / BH);
+        const int last = (int)((((long long)bh + 1) * n_cta + BH - 1) / BH) - 1;
+        cnt = last - first + 1;
+        skip = n_main - cnt;
+    }
+    const int n_used = nsplit - skip;
     if (j < 32) {
         float m = -INFINITY;
-        for (int s = j; s < nsplit; s += 32) m = fmaxf(m, part_ml[(((size_t)bh * nsplit + s) * GP + g) * 2]);
+        for (int u = j; u < n_used; u += 32) {
+            const int s = u < cnt ? u : u + skip;
+            m = fmaxf(m, part_ml[(((size_t)bh * nsplit + s) * GP + g) * 2]);
+        }
         m = warp_max(m);
         float l = 0.f;
-        for (int s = j; s < nsplit; s += 32) {
+        for (int u = j; u < n_used; u += 32) {
+            const int s = u < cnt ? u : u + skip;
             const float *p = part_ml + (((size_t)bh * nsplit + s) * GP + g) * 2;
             float f = p[0] == -INFINITY ? 0.f : __expf(p[0] - m);
-            w[s] = f;
+            w[u] = f;
             l += p[1] * f;
         }
         l = warp_sum(l);
@@ -274,10 +288,11 @@ __global__ void __launch_bounds__(kD) decode_merge_kernel(const float *__restric
     __syncthreads();
     float accr = 0.f, acce = 0.f;
 #pragma unroll 16
-    for (int s = 0; s < nsplit; ++s) {
+    for (int u = 0; u < n_used; ++u) {
+        const int s = u < cnt ? u : u + skip;
         const float *p = part_acc + (((size_t)bh * nsplit + s) * GP + g) * 2 * kD;
-        accr = fmaf(p[j], w[s], accr);
-        acce = fmaf(p[kD + j], w[s], acce);
+        accr = fmaf(p[j], w[u], accr);
+        acce = fmaf(p[kD + j], w[u], acce);
     }
     ar[j] = accr;
     __syncthreads();
@@ -315,11 +330,11 @@ void launch_decode_cuda_core(const DecodeChunks &dc, const DecodeArgs &a, int ca
 }
 
 void launch_decode_merge(const DecodeWs &ws, const float *pi_v, int BH, int G, int nslots, void *out, int out_dtype, float *lse,
-                         cudaStream_t st) {
+                         cudaStream_t st, int n_main, int n_cta) {
     const int R = BH * G, GP = round_gp(G);
-    if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
-    else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
-    else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse);
+    if (out_dtype == kF16) decode_merge_kernel<kF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse, n_main, n_cta, BH);
+    else if (out_dtype == kBF16) decode_merge_kernel<kBF16><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse, n_main, n_cta, BH);
+    else decode_merge_kernel<kF32><<<R, kD, 0, st>>>(ws.part_ml, ws.part_acc, pi_v, G, GP, nslots, out, lse, n_main, n_cta, BH);
 }
 
 int decode_check_args(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype, const void *tail_k,
@@ -348,12 +363,15 @@ using namespace odmkv;
 extern "C" {
 
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
+    // Partial slots per (sample, KV head) that let the tensor-core kernel run one CTA pair per SM of a
+    // 148-SM device: the CTAs that can overlap one unit, plus one.  The plain kernel uses the same number of
+    // equal splits (at most 64), shortened for short contexts.
     if (B <= 0 || H <= 0) return 1;
-    long long BH = (long long)B * H;
-    long long want = (7 * 148 + BH - 1) / BH;   // about 3.5 waves of two CTAs per SM
-    long long by_len = (max_tokens_per_head + 511) / 512;
-    long long n = want < by_len ? want : by_len;
-    if (n < 1) n = 1;
+    const long long BH = (long long)B * H;
+    long long n = (2 * 148 + BH - 1) / BH + 1;
+    const long long by_len = (max_tokens_per_head + 255) / 256 + 1;
+    if (n > by_len) n = by_len;
+    if (n < 2) n = 2;
     if (n > 128) n = 128;
     return (int)n;
 }

@@ -37,7 +37,7 @@ struct MmaArgs {
     const float *codebooks;
     float *part_ml;
     float *part_acc;
-    int B, H, G, nsplit, slot_base, nslots;
+    int B, H, G, n_cta, slot_base, nslots;   // n_cta CTAs share the B*H units evenly; nslots = partial slots per unit
     float scale_log2;      // softmax scale * log2(e)
     float lut_scale[3];    // centroids are stored in the tables as fp16(c * lut_scale[li])
     int tile_mask;         // ~0 normally; a measurement aid can set 0 so that every load hits the segment's first tile
@@ -330,11 +330,11 @@ __device__ inline void load_tile(TileRegs<B> &r, const TilePtrs<B> &p) {
 }
 
 template <int B, int NT>
-__device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int split, int nsplit, int warp, int lane,
+__device__ inline void process_segment(MmaState<NT> &st, const odmkv_chunk &ch, int s0, int cnt, int r0, int r1, int rn, int warp, int lane,
                                        const uint2 *__restrict__ qBs, uint32_t lane_off, float scale_log2, float lut_scale, int tile_mask) {
     constexpr int LI = B - 2;
     const int ntiles = (cnt + 15) >> 4;
-    const int t_lo = (int)((long long)ntiles * split / nsplit), t_hi = (int)((long long)ntiles * (split + 1) / nsplit);
+    const int t_lo = (int)((long long)ntiles * r0 / rn), t_hi = (int)((long long)ntiles * r1 / rn);   // this CTA's share of the tiles
     const float kfac = scale_log2 / lut_scale, inv_ls = 1.0f / lut_scale;
     int ti = t_lo + warp;
     if (ti >= t_hi) return;
@@ -376,12 +376,11 @@ __global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel
     __shared__ float lsh[4 * NT], Msh[4 * NT];
     __shared__ float warpM[kMmaWarps][4 * NT];
     __shared__ uint2 qBs[NT * 8 * 32];   // query B fragments: [column tile][step][lane]
-    const int bh = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int BH = a.B * a.H, G = a.G;
     constexpr int NH = 4 * NT;   // head slots of this kernel variant
 
-    // ---- tables of half2 centroid pairs
+    // ---- tables of half2 centroid pairs (once per CTA)
     {
         const float *c2 = a.codebooks, *c3 = a.codebooks + 256, *c4 = a.codebooks + 512;
         const float s2 = a.lut_scale[0], s3 = a.lut_scale[1], s4 = a.lut_scale[2];
@@ -399,111 +398,137 @@ __global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel
         }
         for (int e = tid; e < 256; e += kMmaThreads)
             reinterpret_cast<uint32_t *>(g_dyn + kLutBytes)[e] = pack_half2(__float2half_rn(c4[e & 15] * s4), __float2half_rn(c4[e >> 4] * s4));
-        for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
-        if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = kNegBig; }
     }
     // lane constants merged into every table offset: copy (lane % 16) of the 2-bit entries, copy `lane` of the 3-bit ones
     const uint32_t off2 = (lane & 15) * 8, off3 = 128 + lane * 4;
-    // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
-    // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
-    if (warp == 0) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int head = NT == 1 ? (g & 3) : g;
-            const bool low = NT == 1 ? (g >= 4) : (nt == 1);
-            const float *qr = a.qrot + ((size_t)bh * G + (head < G ? head : 0)) * kD + 32 * t;
-#pragma unroll
-            for (int s = 0; s < 8; ++s) {
-                __half h[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float v = head < G ? qr[4 * s + e] : 0.f;
-                    __half hv = __float2half_rn(v);
-                    h[e] = low ? __float2half_rn(v - __half2float(hv)) : hv;
-                }
-                qBs[(nt * 8 + s) * 32 + lane] = make_uint2(pack_half2(h[0], h[1]), pack_half2(h[2], h[3]));
-            }
-        }
-    }
-    __syncthreads();
-
-    MmaState<NT> st;
-    st.M[0] = st.M[1] = kNegBig;
-    st.l[0] = st.l[1] = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int m = 0; m < 8; ++m)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) st.O[nt][m][i] = 0.f;
-
-    for (int ci = 0; ci < chunks.n; ++ci) {
-        const odmkv_chunk &ch = chunks.ch[ci];
-        for (int c = 1; c <= 3; ++c) {
-            const int cnt = ch.seg_count[c * BH + bh];
-            if (cnt == 0) continue;
-            const int s0 = ch.seg_start[c * BH + bh];
-            if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, off2, a.scale_log2, a.lut_scale[0], a.tile_mask);
-            else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, off3, a.scale_log2, a.lut_scale[1], a.tile_mask);
-            else process_segment<4, NT>(st, ch, s0, cnt, split, a.nsplit, warp, lane, qBs, 0u, a.scale_log2, a.lut_scale[2], a.tile_mask);
-        }
-    }
-
-    // ---- per-warp totals: denominators summed over the 8 row groups; NT = 1: lanes t and t^2 hold copies
-#pragma unroll
-    for (int o = 4; o < 32; o <<= 1) {
-        st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
-        st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
-    }
     // head slots of this lane's two columns
     const int h0 = NT == 1 ? 2 * (t & 1) : 2 * t, h1 = h0 + 1;
     const bool owner = NT == 1 ? (t < 2) : true;   // one lane per (g, head pair) publishes
-    if (NT == 1) {
-        // fold the low-limb columns (lanes t >= 2) into the high-limb lanes
+
+    // The (sample, KV head) units are laid end to end, each n_cta long; CTA c owns [c * BH, (c + 1) * BH) of
+    // that line, i.e. the same fraction r0/n_cta .. r1/n_cta of every segment of each unit it overlaps.
+    const int n = a.n_cta;
+    long long pos = (long long)blockIdx.x * BH;
+    const long long end = pos + BH;
+    while (pos < end) {
+        const int bh = (int)(pos / n), r0 = (int)(pos % n);
+        const int r1 = (int)((long long)r0 + (end - pos) < (long long)n ? (long long)r0 + (end - pos) : (long long)n);
+        pos += r1 - r0;
+        const int slot = blockIdx.x - (int)(((long long)bh * n) / BH);   // index among the CTAs that overlap this unit
+
+        // ---- query B fragments: column g of tile nt; NT = 1: columns 0..3 high limbs, 4..7 low limbs of
+        // heads 0..3; NT = 2: tile 0 high limbs, tile 1 low limbs of heads 0..7
+        for (int e = tid; e < NH * kD; e += kMmaThreads) (&Osh[0][0])[e] = 0.f;
+        if (tid < NH) { lsh[tid] = 0.f; Msh[tid] = kNegBig; }
+        if (warp == 0) {
 #pragma unroll
-        for (int m = 0; m < 8; ++m)
+            for (int nt = 0; nt < NT; ++nt) {
+                const int head = NT == 1 ? (g & 3) : g;
+                const bool low = NT == 1 ? (g >= 4) : (nt == 1);
+                const float *qr = a.qrot + ((size_t)bh * G + (head < G ? head : 0)) * kD + 32 * t;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) st.O[0][m][i] += __shfl_xor_sync(0xffffffffu, st.O[0][m][i], 2);
-    }
-    if (g == 0 && owner) { warpM[warp][h0] = st.M[0]; warpM[warp][h1] = st.M[1]; }
-    __syncthreads();
-    if (tid < NH) {
-        float m = kNegBig;
+                for (int s = 0; s < 8; ++s) {
+                    __half h[4];
 #pragma unroll
-        for (int w = 0; w < kMmaWarps; ++w) m = fmaxf(m, warpM[w][tid]);
-        Msh[tid] = m;
-    }
-    __syncthreads();
-    const float c0 = st.M[0] <= kNegBig ? 0.f : fast_exp2(st.M[0] - Msh[h0]);
-    const float c1 = st.M[1] <= kNegBig ? 0.f : fast_exp2(st.M[1] - Msh[h1]);
-    for (int w = 0; w < kMmaWarps; ++w) {   // fixed order: the sum is reproducible
-        if (warp == w && owner) {
-#pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                float v0 = st.O[0][m][0], v1 = st.O[0][m][1], v2 = st.O[0][m][2], v3 = st.O[0][m][3];
-                if (NT == 2) { v0 += st.O[NT - 1][m][0]; v1 += st.O[NT - 1][m][1]; v2 += st.O[NT - 1][m][2]; v3 += st.O[NT - 1][m][3]; }
-                Osh[h0][16 * m + g] += v0 * c0;
-                Osh[h1][16 * m + g] += v1 * c1;
-                Osh[h0][16 * m + g + 8] += v2 * c0;
-                Osh[h1][16 * m + g + 8] += v3 * c1;
+                    for (int e = 0; e < 4; ++e) {
+                        float v = head < G ? qr[4 * s + e] : 0.f;
+                        __half hv = __float2half_rn(v);
+                        h[e] = low ? __float2half_rn(v - __half2float(hv)) : hv;
+                    }
+                    qBs[(nt * 8 + s) * 32 + lane] = make_uint2(pack_half2(h[0], h[1]), pack_half2(h[2], h[3]));
+                }
             }
-            if (g == 0) { lsh[h0] += st.l[0] * c0; lsh[h1] += st.l[1] * c1; }
         }
         __syncthreads();
-    }
-    // ---- write the partial (natural-log maximum, code-space accumulator; exact-space part is zero)
-    const int GP = round_gp(G);
-    for (int e = tid; e < GP * 2 * kD; e += kMmaThreads) {
-        const int gq = e / (2 * kD), rest = e % (2 * kD);
-        const size_t pi = ((size_t)bh * a.nslots + a.slot_base + split) * GP + gq;
-        float v = 0.f;
-        if (rest < kD && gq < NH) v = Osh[gq][rest];
-        a.part_acc[pi * 2 * kD + rest] = v;
-        if (rest == 0) {
-            a.part_ml[pi * 2] = (gq < NH && Msh[gq] > kNegBig) ? Msh[gq] * 0.6931471805599453f : -INFINITY;
-            a.part_ml[pi * 2 + 1] = gq < NH ? lsh[gq] : 0.f;
+
+        MmaState<NT> st;
+        st.M[0] = st.M[1] = kNegBig;
+        st.l[0] = st.l[1] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int m = 0; m < 8; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) st.O[nt][m][i] = 0.f;
+
+        for (int ci = 0; ci < chunks.n; ++ci) {
+            const odmkv_chunk &ch = chunks.ch[ci];
+            for (int c = 1; c <= 3; ++c) {
+                const int cnt = ch.seg_count[c * BH + bh];
+                if (cnt == 0) continue;
+                const int s0 = ch.seg_start[c * BH + bh];
+                if (c == 1) process_segment<2, NT>(st, ch, s0, cnt, r0, r1, n, warp, lane, qBs, off2, a.scale_log2, a.lut_scale[0], a.tile_mask);
+                else if (c == 2) process_segment<3, NT>(st, ch, s0, cnt, r0, r1, n, warp, lane, qBs, off3, a.scale_log2, a.lut_scale[1], a.tile_mask);
+                else process_segment<4, NT>(st, ch, s0, cnt, r0, r1, n, warp, lane, qBs, 0u, a.scale_log2, a.lut_scale[2], a.tile_mask);
+            }
         }
+
+        // ---- per-warp totals: denominators summed over the 8 row groups; NT = 1: lanes t and t^2 hold copies
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], o);
+            st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], o);
+        }
+        if (NT == 1) {
+            // fold the low-limb columns (lanes t >= 2) into the high-limb lanes
+#pragma unroll
+            for (int m = 0; m < 8; ++m)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) st.O[0][m][i] += __shfl_xor_sync(0xffffffffu, st.O[0][m][i], 2);
+        }
+        if (g == 0 && owner) { warpM[warp][h0] = st.M[0]; warpM[warp][h1] = st.M[1]; }
+        __syncthreads();
+        if (tid < NH) {
+            float m = kNegBig;
+#pragma unroll
+            for (int w = 0; w < kMmaWarps; ++w) m = fmaxf(m, warpM[w][tid]);
+            Msh[tid] = m;
+        }
+        __syncthreads();
+        const float c0 = st.M[0] <= kNegBig ? 0.f : fast_exp2(st.M[0] - Msh[h0]);
+        const float c1 = st.M[1] <= kNegBig ? 0.f : fast_exp2(st.M[1] - Msh[h1]);
+        for (int w = 0; w < kMmaWarps; ++w) {   // fixed order: the sum is reproducible
+            if (warp == w && owner) {
+#pragma unroll
+                for (int m = 0; m < 8; ++m) {
+                    float v0 = st.O[0][m][0], v1 = st.O[0][m][1], v2 = st.O[0][m][2], v3 = st.O[0][m][3];
+                    if (NT == 2) { v0 += st.O[NT - 1][m][0]; v1 += st.O[NT - 1][m][1]; v2 += st.O[NT - 1][m][2]; v3 += st.O[NT - 1][m][3]; }
+                    Osh[h0][16 * m + g] += v0 * c0;
+                    Osh[h1][16 * m + g] += v1 * c1;
+                    Osh[h0][16 * m + g + 8] += v2 * c0;
+                    Osh[h1][16 * m + g + 8] += v3 * c1;
+                }
+                if (g == 0) { lsh[h0] += st.l[0] * c0; lsh[h1] += st.l[1] * c1; }
+            }
+            __syncthreads();
+        }
+        // ---- write the partial (natural-log maximum, code-space accumulator; exact-space part is zero)
+        const int GP = round_gp(G);
+        for (int e = tid; e < GP * 2 * kD; e += kMmaThreads) {
+            const int gq = e / (2 * kD), rest = e % (2 * kD);
+            const size_t pi = ((size_t)bh * a.nslots + a.slot_base + slot) * GP + gq;
+            float v = 0.f;
+            if (rest < kD && gq < NH) v = Osh[gq][rest];
+            a.part_acc[pi * 2 * kD + rest] = v;
+            if (rest == 0) {
+                a.part_ml[pi * 2] = (gq < NH && Msh[gq] > kNegBig) ? Msh[gq] * 0.6931471805599453f : -INFINITY;
+                a.part_ml[pi * 2 + 1] = gq < NH ? lsh[gq] : 0.f;
+            }
+        }
+        __syncthreads();   // the shared accumulators are reset for the next unit
     }
+}
+
+static int num_sms_cached() {
+    static int table[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (table[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        table[dev] = n;
+    }
+    return table[dev];
 }
 
 // one helper stream and two events per device, created on first use (host objects, no device memory)
@@ -561,11 +586,24 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     }
     MmaArgs m;
     m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc;
-    m.B = B; m.H = H; m.G = G; m.nsplit = n_splits; m.slot_base = 0; m.nslots = nslots;
+    // grid: one CTA pair per SM, fewer when the cache is short (at least ~32 tiles per CTA) or when the caller's
+    // slot count bounds the CTAs that may overlap one unit
+    long long total_tiles = 0;
+    for (int i = 0; i < n_chunks; ++i) total_tiles += ((long long)chunks[i].cap[1] + chunks[i].cap[2] + chunks[i].cap[3]) / 16;
+    long long n_cta = 2ll * num_sms_cached();
+    if (n_cta > total_tiles / 32) n_cta = total_tiles / 32;
+    if (n_splits >= 2) {
+        if (n_cta > (long long)(n_splits - 1) * BH) n_cta = (long long)(n_splits - 1) * BH;
+    } else {
+        if (n_cta > BH) n_cta = BH;
+        while (n_cta > 1 && BH % n_cta != 0) --n_cta;   // one slot: every unit belongs to exactly one CTA
+    }
+    if (n_cta < 1) n_cta = 1;
+    m.B = B; m.H = H; m.G = G; m.n_cta = (int)n_cta; m.slot_base = 0; m.nslots = nslots;
     m.scale_log2 = scale * 1.4426950408889634f;
     for (int i = 0; i < 3; ++i) m.lut_scale[i] = lut_scales ? lut_scales[i] : 1.0f;
     m.tile_mask = getenv("ODMKV_MEASURE_NO_DRAM") ? 0 : ~0;   // measurement aid only: results are meaningless when set
-    dim3 grid(n_splits, BH);
+    dim3 grid((unsigned)n_cta);
     {
         static bool attr_set[64] = {};   // per device: the opt-in only has to happen once
         int dev = 0;
@@ -603,7 +641,7 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
         timing_end(st);
     }
     timing_begin("decode_merge", st);
-    launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st);
+    launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st, n_splits, (int)n_cta);
     timing_end(st);
     return launch_status();
 }

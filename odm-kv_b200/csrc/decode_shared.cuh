@@ -54,8 +54,10 @@ inline size_t decode_ws_layout(int B, int H, int G, int nslots, DecodeWs *ws, un
 // implemented in decode.cu
 void launch_rotate_q(const void *q, int q_dtype, const float *pi_k, const DecodeWs &ws, int R, cudaStream_t st);
 void launch_decode_cuda_core(const DecodeChunks &dc, const DecodeArgs &a, int cache_dtype, cudaStream_t st);
+// n_cta > 0: the first n_main slots of a unit belong to the persistent tensor-core kernel and only those of
+// its CTAs that overlap the unit were written
 void launch_decode_merge(const DecodeWs &ws, const float *pi_v, int BH, int G, int nslots, void *out, int out_dtype, float *lse,
-                         cudaStream_t st);
+                         cudaStream_t st, int n_main = 0, int n_cta = 0);
 int decode_check_args(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype, const void *tail_k,
                       const void *tail_v, int tail_len, int tail_cap, const float *pi_k, const float *pi_v, const float *codebooks,
                       int B, int H, int G, void *out, int out_dtype, int n_splits, void *workspace, DecodeChunks *dc);

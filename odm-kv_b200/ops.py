@@ -185,6 +185,15 @@ class PackedChunk:
     _c_struct: Optional[Chunk] = None     # chunks are immutable once built: the C view and the totals are cached
     _stored: Optional[int] = None
 
+    def __deepcopy__(self, memo):
+        # the cached C view holds raw pointers into this chunk's tensors: a copy gets its own on first use
+        import copy
+        new = self.__class__.__new__(self.__class__)
+        memo[id(self)] = new
+        for k, v in self.__dict__.items():
+            setattr(new, k, None if k == "_c_struct" else copy.deepcopy(v, memo))
+        return new
+
     def c_struct(self) -> Chunk:
         if self._c_struct is not None:
             return self._c_struct
