@@ -34,6 +34,72 @@ struct AllocCfg {
     double target;
 };
 
+// Breakpoints of the lower envelope of the K cost lines  s -> eps32[k] * s + lamb[k]  over s >= 0 (exact real
+// arithmetic on the fp32 constants, evaluated in fp64).  Between two breakpoints the level of the envelope
+// is also the fp32 argmin of the reference's three-operation cost, as long as s stays outside a relative band
+// around each breakpoint: the fp32 costs differ from the lines by at most 2^-23 of their value, two lines that
+// cross at tau separate by |eps_i - eps_j| * |s - tau|, so a band of 64 * 2^-23 * cost(tau) / |lamb_j - lamb_i|
+// (at least 1e-5) is more than enough.  Scores inside a band, and every score when a level that is not on
+// the envelope comes within 1e-4 (relative) of it at a breakpoint, are evaluated with the full cost formula.
+struct Envelope {
+    float lo[kMaxL], hi[kMaxL];   // band [lo, hi] around breakpoint v (v < nh - 1)
+    int level[kMaxL];             // level of the envelope between breakpoints v - 1 and v
+    int nh;                       // number of envelope pieces; 0 = use the full formula for every score
+};
+
+__device__ inline void build_envelope(const AllocCfg &cfg, const float *lamb, Envelope &env) {
+    const int K = cfg.K;
+    double a[kMaxL], c[kMaxL];
+    for (int k = 0; k < K; ++k) { a[k] = (double)cfg.eps32[k]; c[k] = (double)lamb[k]; }
+    bool on[kMaxL];
+    for (int k = 0; k < K; ++k) on[k] = false;
+    int cur = 0;
+    for (int k = 1; k < K; ++k)
+        if (c[k] < c[cur] || (c[k] == c[cur] && a[k] < a[cur])) cur = k;
+    double tau[kMaxL];
+    int nh = 0;
+    double s_cur = 0.0;
+    bool ok = true;
+    while (true) {
+        env.level[nh] = cur;
+        on[cur] = true;
+        int nxt = -1;
+        double best = 0.0;
+        for (int k = 0; k < K; ++k) {
+            if (k == cur || !(a[k] < a[cur])) continue;
+            const double sx = (c[k] - c[cur]) / (a[cur] - a[k]);
+            if (sx < s_cur) continue;
+            if (nxt < 0 || sx < best || (sx == best && a[k] < a[nxt])) { nxt = k; best = sx; }
+        }
+        if (nxt < 0) { ++nh; break; }
+        const double f = a[cur] * best + c[cur];
+        const double dc = fabs(c[nxt] - c[cur]);
+        double band = dc > 0.0 ? 64.0 * 1.1920928955078125e-07 * fabs(f) / dc : 1.0;
+        if (band < 1e-5) band = 1e-5;
+        if (!(band <= 1e-2) || !(best > 0.0) || !(best < 1e37)) ok = false;
+        tau[nh] = best;
+        env.lo[nh] = (float)(best * (1.0 - band) * (1.0 - 1e-7));
+        env.hi[nh] = (float)(best * (1.0 + band) * (1.0 + 1e-7));
+        ++nh;
+        s_cur = best;
+        cur = nxt;
+        if (nh >= kMaxL) { ok = false; break; }
+    }
+    // levels off the envelope must stay clear of it at every breakpoint (their gap is smallest there or at s = 0)
+    for (int k = 0; k < K && ok; ++k) {
+        if (on[k]) continue;
+        for (int v = 0; v + 1 < nh; ++v) {
+            const double h = a[env.level[v]] * tau[v] + c[env.level[v]];
+            const double h_next = v + 2 < nh ? a[env.level[v + 1]] * tau[v + 1] + c[env.level[v + 1]] : h;
+            const double gk = a[k] * tau[v] + c[k];
+            if (!(gk - h > 1e-4 * fmax(fabs(h), fabs(h_next)))) ok = false;   // 1e-4 >> 2^-22: holds along the whole piece
+        }
+        const double h0 = c[env.level[0]];
+        if (!(c[k] - h0 > 1e-4 * fabs(h0)) && !(c[k] > h0 && h0 == 0.0)) ok = false;
+    }
+    env.nh = ok ? nh : 0;
+}
+
 struct AllocProblem {
     double lo, hi, lam, gap, gap_before;
     long long level_counts[kMaxL];
@@ -47,6 +113,7 @@ struct AllocProblem {
     unsigned ticket;
     unsigned max_finite_bits;
     int any_nonfinite, any_finite;
+    Envelope env;    // envelope of the cost lines at `lam` (counting passes)
 };
 
 struct AllocWs {
@@ -88,13 +155,21 @@ __device__ inline float sanitize(float s, const AllocProblem &pr) {
     return s;
 }
 
-__global__ void alloc_init_kernel(AllocProblem *prob, unsigned long long *acc, int P, int K) {
+__device__ inline void refresh_envelope(AllocProblem &pr, const AllocCfg &cfg) {
+    const float lam32 = (float)pr.lam;
+    float lamb[kMaxL];
+    for (int k = 0; k < kMaxL; ++k) lamb[k] = k < cfg.K ? __fmul_rn(lam32, cfg.bits32[k]) : 0.f;
+    build_envelope(cfg, lamb, pr.env);
+}
+
+__global__ void alloc_init_kernel(AllocProblem *prob, unsigned long long *acc, int P, int K, const AllocCfg cfg) {
     const int p = blockIdx.x;
     if (threadIdx.x == 0) {
         AllocProblem z = {};
         z.lo = 0.0; z.hi = 1.0; z.lam = 1.0;
         z.phase = K == 1 ? 2 : 0;
         z.sel_level = -1;
+        if (z.phase == 0) refresh_envelope(z, cfg);
         prob[p] = z;
     }
     for (int i = threadIdx.x; i < kAccLen; i += blockDim.x) acc[(size_t)p * kAccLen + i] = 0ull;
@@ -176,7 +251,9 @@ __device__ void update_problem(AllocProblem *prp, unsigned long long *acc, const
                 pr.iter += 1;
                 pr.lam = (pr.lo + pr.hi) * 0.5;
                 if (pr.iter == 64) pr.phase = 2;
-            } else {
+            }
+            if (phase <= 1 && pr.phase <= 1) refresh_envelope(pr, cfg);   // the next pass counts at the new lambda
+            if (phase == 2) {
                 pr.n_active = (int)nact;
                 for (int k = 0; k < cfg.K; ++k) pr.level_counts[k] = counts[k];
                 pr.ties_lambda = (int)acc[8];
@@ -253,11 +330,12 @@ __device__ inline unsigned long long make_key(float s, long long gidx, bool inve
 
 // One pass over the scores of every problem.  FUSED: the last block of a problem updates its state.
 template <bool FUSED>
-__global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *__restrict__ scores,
+__global__ void __launch_bounds__(kAllocThreads, 3) alloc_pass_kernel(const float *__restrict__ scores,
                                                                    const uint8_t *__restrict__ sink_mask, int n,
                                                                    long long idx_base, AllocWs ws, const AllocCfg cfg) {
     __shared__ unsigned long long sh_cnt[kAccHead];
     __shared__ int sh_last;
+    __shared__ Envelope sh_env;
     const int p = blockIdx.y, tid = threadIdx.x, lane = tid & 31;
     AllocProblem *prp = ws.prob + p;
     unsigned long long *acc = ws.acc + (size_t)p * kAccLen;
@@ -281,13 +359,97 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
 #pragma unroll
         for (int k = 0; k < kMaxL; ++k) cnt[k] = 0;
         unsigned ties = 0;
-        for (long long base = base0; base < n; base += stride)
+        if (phase <= 1) {
+            // counting passes: level by envelope breakpoints, full formula only inside the bands
+            if (tid == 0) sh_env = prp->env;
+            __syncthreads();
+            const int nh = sh_env.nh;
+            float blo[kMaxL], bhi[kMaxL];
+#pragma unroll
+            for (int v = 0; v < kMaxL; ++v) {
+                blo[v] = v + 1 < nh ? sh_env.lo[v] : INFINITY;
+                bhi[v] = v + 1 < nh ? sh_env.hi[v] : INFINITY;
+            }
+            unsigned long long packed = 0ull;   // eight 8-bit counters, one per envelope piece or level
+            int since_flush = 0;
+            // software pipeline: the loads of the next chunk are in flight while this one is counted
+            float sv_n[kPerThread];
+            int mk_n[kPerThread];
+            auto load_chunk = [&](long long base) {
+#pragma unroll
+                for (int u = 0; u < kPerThread; ++u) {
+                    const long long i = base + u * kAllocThreads + tid;
+                    const bool in = i < n;
+                    sv_n[u] = in ? __ldg(sc + i) : 0.f;
+                    mk_n[u] = in ? (sink_mask ? (int)__ldg(sink_mask + i) : 0) : -1;
+                }
+            };
+            if (base0 < n) load_chunk(base0);
+            for (long long base = base0; base < n; base += stride) {
+                float sv[kPerThread];
+                int mk[kPerThread];
+#pragma unroll
+                for (int u = 0; u < kPerThread; ++u) { sv[u] = sv_n[u]; mk[u] = mk_n[u]; }
+                if (base + stride < n) load_chunk(base + stride);
+                // branch-free for the eight scores; the few that sit inside a band are redone below
+                unsigned redo = 0;
+#pragma unroll
+                for (int u = 0; u < kPerThread; ++u) {
+                    const float s = sanitize(sv[u], pr);
+                    sv[u] = s;
+                    int above = 0, reached = 0;
+#pragma unroll
+                    for (int v = 0; v < kMaxL - 1; ++v) { above += (s > bhi[v]) ? 1 : 0; reached += (s >= blo[v]) ? 1 : 0; }
+                    const bool live = mk[u] == 0;
+                    const bool sure = nh > 0 && above == reached;
+                    const int arg = sh_env.level[above];
+                    packed += (live && sure) ? (1ull << (8 * arg)) : 0ull;
+                    redo |= (live && !sure) ? (1u << u) : 0u;
+                }
+                while (redo) {
+                    const int u = __ffs(redo) - 1;
+                    redo &= redo - 1;
+                    float s = 0.f;
+#pragma unroll
+                    for (int uu = 0; uu < kPerThread; ++uu) s = uu == u ? sv[uu] : s;
+                    float best = __fadd_rn(__fmul_rn(s, cfg.eps32[0]), lamb[0]);
+                    int arg = 0;
+#pragma unroll
+                    for (int k = 1; k < kMaxL; ++k) {
+                        if (k < cfg.K) {
+                            float c = __fadd_rn(__fmul_rn(s, cfg.eps32[k]), lamb[k]);
+                            if (c < best) { best = c; arg = k; }
+                        }
+                    }
+                    packed += 1ull << (8 * arg);
+                }
+                if (++since_flush == 31) {
+#pragma unroll
+                    for (int k = 0; k < kMaxL; ++k) cnt[k] += (unsigned)((packed >> (8 * k)) & 0xffull);
+                    packed = 0ull;
+                    since_flush = 0;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < kMaxL; ++k) cnt[k] += (unsigned)((packed >> (8 * k)) & 0xffull);
+        } else
+        for (long long base = base0; base < n; base += stride) {
+            // all loads of the iteration are issued before the first one is used
+            float sv[kPerThread];
+            int mk[kPerThread];
+#pragma unroll
+            for (int u = 0; u < kPerThread; ++u) {
+                const long long i = base + u * kAllocThreads + tid;
+                const bool in = i < n;
+                sv[u] = in ? sc[i] : 0.f;
+                mk[u] = in ? (sink_mask ? (int)sink_mask[i] : 0) : -1;
+            }
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
-            if (i >= n) continue;
-            if (sink_mask && sink_mask[i]) { if (phase == 2) chosen[i] = 255; continue; }
-            const float s = sanitize(sc[i], pr);
+            if (mk[u] < 0) continue;
+            if (mk[u]) { if (phase == 2) chosen[i] = 255; continue; }
+            const float s = sanitize(sv[u], pr);
             float best = __fadd_rn(__fmul_rn(s, cfg.eps32[0]), lamb[0]);
             float cost[kMaxL];
             cost[0] = best;
@@ -313,6 +475,7 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
                 }
             }
         }
+        }
 #pragma unroll
         for (int k = 0; k < kMaxL; ++k) {
             unsigned v = __reduce_add_sync(0xffffffffu, cnt[k]);
@@ -325,32 +488,50 @@ __global__ void __launch_bounds__(kAllocThreads) alloc_pass_kernel(const float *
     } else if (phase == 3) {
         const bool inv = pr.dir < 0;
         const int shift_digit = 48 - 16 * pr.sel_pass;
-        for (long long base = base0; base < n; base += stride)
+        for (long long base = base0; base < n; base += stride) {
+            float sv[kPerThread];
+            int ch[kPerThread];
+#pragma unroll
+            for (int u = 0; u < kPerThread; ++u) {
+                const long long i = base + u * kAllocThreads + tid;
+                const bool in = i < n;
+                sv[u] = in ? sc[i] : 0.f;
+                ch[u] = in ? (int)chosen[i] : -1;
+            }
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
-            if (i >= n) continue;
-            if (chosen[i] != (uint8_t)pr.sel_level) continue;
-            unsigned long long key = make_key(sanitize(sc[i], pr), idx_base + i, inv);
+            if (ch[u] != (int)(uint8_t)pr.sel_level) continue;
+            unsigned long long key = make_key(sanitize(sv[u], pr), idx_base + i, inv);
             if (pr.sel_pass > 0 && (key >> (shift_digit + 16)) != pr.sel_prefix) continue;
             atomicAdd(&acc[kAccHead + ((key >> shift_digit) & 0xffffull)], 1ull);
+        }
         }
     } else {  // phase 4: move every candidate whose key is <= the selected key
         const bool inv = pr.dir < 0;
         const unsigned long long cut = pr.sel_prefix;
         const unsigned cut_score = (unsigned)((inv ? ~cut : cut) >> 32);
         unsigned same_sel = 0, same_unsel = 0;
-        for (long long base = base0; base < n; base += stride)
+        for (long long base = base0; base < n; base += stride) {
+            float sv[kPerThread];
+            int ch[kPerThread];
+#pragma unroll
+            for (int u = 0; u < kPerThread; ++u) {
+                const long long i = base + u * kAllocThreads + tid;
+                const bool in = i < n;
+                sv[u] = in ? sc[i] : 0.f;
+                ch[u] = in ? (int)chosen[i] : -1;
+            }
 #pragma unroll
         for (int u = 0; u < kPerThread; ++u) {
             long long i = base + u * kAllocThreads + tid;
-            if (i >= n) continue;
-            if (chosen[i] != (uint8_t)pr.sel_level) continue;
-            const float s = sanitize(sc[i], pr);
+            if (ch[u] != (int)(uint8_t)pr.sel_level) continue;
+            const float s = sanitize(sv[u], pr);
             unsigned long long key = make_key(s, idx_base + i, inv);
             const bool sel = key <= cut;
             if (sel) chosen[i] = (uint8_t)pr.sel_to;
             if (__float_as_uint(s) == cut_score) { if (sel) same_sel++; else same_unsel++; }
+        }
         }
         unsigned a = __reduce_add_sync(0xffffffffu, same_sel), b = __reduce_add_sync(0xffffffffu, same_unsel);
         if (lane == 0) {
@@ -467,7 +648,7 @@ static int alloc_begin_impl(const float *scores, const uint8_t *sink_mask, int P
     if (P <= 0 || n <= 0 || P > 65535) return ODMKV_ERR_SHAPE;
     if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
     if (workspace_bytes < alloc_ws_layout(P, n, ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
-    alloc_init_kernel<<<P, 256, 0, st>>>(ws->prob, ws->acc, P, cfg.K);
+    alloc_init_kernel<<<P, 256, 0, st>>>(ws->prob, ws->acc, P, cfg.K, cfg);
     int blocks = (n + 256 * 8 - 1) / (256 * 8);
     if (blocks > 1024) blocks = 1024;
     alloc_stats_kernel<<<dim3(blocks, P), 256, 0, st>>>(scores, sink_mask, n, ws->prob);

@@ -272,7 +272,7 @@ __device__ __forceinline__ void patch_code(uint32_t *__restrict__ row_words, int
 // chain, bit for bit; copy-out.  The next item's rows, bit widths and slot bases are fetched into
 // registers under the decision step of the current one.
 constexpr int kQueueCap = 2048;   // queued coordinates per item; beyond that the whole item is redone exactly
-constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + (size_t)kQRows * kLdH * 2 +
+constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + kQRows * sizeof(double) + (size_t)kQRows * kLdH * 2 +
                                    (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + (size_t)kQueueCap * 2;
 constexpr size_t kQuantKernelSmem = (size_t)(kD * kLd + 4 * 256) * sizeof(float) + (size_t)kD * kLdH * 2 + 3 * sizeof(LevelConst) +
                                     2 * kQuantGroupSmem;
@@ -292,7 +292,8 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     unsigned char *gbase = reinterpret_cast<unsigned char *>(lc + 3) + (size_t)gid * kQuantGroupSmem;
     float *Xs = reinterpret_cast<float *>(gbase);                    // [64][kLd] fp32 rows, normalised in place
     float *nrm = Xs + kQRows * kLd;                                  // [64]
-    __half *Xh = reinterpret_cast<__half *>(nrm + kQRows);           // [64][kLdH] fp16 normalised rows
+    double *rinv = reinterpret_cast<double *>(nrm + kQRows);         // [64] 1 / (norm + 1e-10) in fp64
+    __half *Xh = reinterpret_cast<__half *>(rinv + kQRows);          // [64][kLdH] fp16 normalised rows
     int *cls = reinterpret_cast<int *>(Xh + kQRows * kLdH);          // [128]
     int *slot = cls + kTile;                                         // [128]
     int *wcnt = slot + kTile;                                        // [4][6]
@@ -397,23 +398,28 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
                 acc = fmaf(v.z, v.z, acc);
                 acc = fmaf(v.w, v.w, acc);
             }
-            nrm[r] = __fsqrt_rn(acc);
+            const float nr = __fsqrt_rn(acc);
+            nrm[r] = nr;
+            rinv[r] = 1.0 / (double)__fadd_rn(nr, 1e-10f);
         }
         group_sync(gid);
         const bool any_q = flags[0] != 0;
         const size_t row0 = ((size_t)bh * T + t0 + h0) * kD;
         if (any_q) {
-            // ---- x / (norm + 1e-10), IEEE division; fp32 result in place, fp16 copy for the tensor cores
+            // ---- x / (norm + 1e-10) as the IEEE fp32 quotient, computed as fp32(fp64(x) * fp64(1 / den)): the fp64
+            //      product is within 2^-52 of the quotient, while a quotient of two fp32 numbers is never closer
+            //      than 2^-49 (relative) to a rounding boundary of fp32 and never on one, so the final rounding
+            //      lands where the division's would.  fp32 result in place, fp16 copy for the tensor cores.
 #pragma unroll
             for (int u = 0; u < kQRows * kD / 4 / 256; ++u) {
                 const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
-                float den = __fadd_rn(nrm[r], 1e-10f);
+                const double ri = rinv[r];
                 float4 *p = reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4);
                 float4 v = *p;
-                v.x = __fdiv_rn(v.x, den);
-                v.y = __fdiv_rn(v.y, den);
-                v.z = __fdiv_rn(v.z, den);
-                v.w = __fdiv_rn(v.w, den);
+                v.x = __double2float_rn(__dmul_rn((double)v.x, ri));
+                v.y = __double2float_rn(__dmul_rn((double)v.y, ri));
+                v.z = __double2float_rn(__dmul_rn((double)v.z, ri));
+                v.w = __double2float_rn(__dmul_rn((double)v.w, ri));
                 *p = v;
                 __half2 *hd = reinterpret_cast<__half2 *>(Xh + r * kLdH + 4 * i4);
                 hd[0] = __floats2half2_rn(v.x, v.y);
@@ -446,52 +452,92 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
             group_sync(gid);   // every warp is done with Xh: the packed rows reuse its space
             prefetch(w + w_step);
             // ---- fp16 decision and packing; this thread's coordinates of a row are 32 wn + 8 t4 + [0, 8),
-            //      element (nb, e) of the accumulator being coordinate 2 nb + e of those
+            //      element (nb, e) of the accumulator being coordinate 2 nb + e of those.  The four rows of a
+            //      thread go through one branch-free path for 2 and 3 bits (a 2-bit row pads its midpoints with
+            //      +inf); 4- and 8-bit rows are redone afterwards.
+            {
+                const int col0 = 32 * wn + 8 * t4;
+                int ccs[4];
+                uint32_t words[4], bads[4];
 #pragma unroll
-            for (int mb = 0; mb < 2; ++mb)
+                for (int k = 0; k < 4; ++k) ccs[k] = cls[h0 + 32 * wm + 16 * (k >> 1) + g8 + 8 * (k & 1)];
 #pragma unroll
-                for (int hi = 0; hi < 2; ++hi) {
-                    const int r = 32 * wm + 16 * mb + g8 + 8 * hi;
-                    const int cc = cls[h0 + r];
-                    if (cc < 1 || cc > 4) continue;
-                    const int col0 = 32 * wn + 8 * t4;
-                    if (cc == 4) {   // 8 bits: the centroid spacing is within the margin, every coordinate is exact work
-#pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const int qi = atomicAdd(&flags[1], 1);
-                            if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + k));
-                        }
-                        continue;
-                    }
-                    const int b = cc + 1;
-                    const LevelConst &L = lc[cc - 1];
+                for (int k = 0; k < 4; ++k) {
+                    const int mb = k >> 1, hi = k & 1;
+                    const LevelConst &L = lc[ccs[k] == 2 ? 1 : 0];
                     uint32_t mid[7];
 #pragma unroll
-                    for (int j = 0; j < 7; ++j) mid[j] = L.mid[j];
+                    for (int j = 0; j < 3; ++j) mid[j] = L.mid[j];
                     const uint32_t base = L.base;
+                    const int b = ccs[k] == 2 ? 3 : 2;
                     uint32_t word = 0, bad = 0;
 #pragma unroll
                     for (int nb = 0; nb < 4; ++nb) {
                         const uint32_t y2 = h2u(__floats2half2_rn(acc[mb][nb][2 * hi], acc[mb][nb][2 * hi + 1]));
-                        uint32_t ok, cf;
-                        if (cc == 3) cf = decide_pair<7>(y2, mid, base, ok);
-                        else cf = decide_pair<3>(y2, mid, base, ok);
+                        uint32_t ok;
+                        const uint32_t cf = decide_pair<3>(y2, mid, base, ok);
                         const uint32_t field = ((cf >> 1) & 15u) | (((cf >> 17) & 15u) << b);
                         word |= field << (2 * b * nb);
                         if ((ok & 0xffffu) != 0x3c00u) bad |= 1u << (2 * nb);
                         if ((ok >> 16) != 0x3c00u) bad |= 2u << (2 * nb);
                     }
-                    unsigned char *dst = PK + r * kLdC + b * (4 * wn + t4);
-                    if (b == 2) *reinterpret_cast<uint16_t *>(dst) = (uint16_t)word;
-                    else if (b == 4) *reinterpret_cast<uint32_t *>(dst) = word;
-                    else { dst[0] = (unsigned char)word; dst[1] = (unsigned char)(word >> 8); dst[2] = (unsigned char)(word >> 16); }
-                    while (bad) {
-                        const int k = __ffs(bad) - 1;
-                        bad &= bad - 1;
-                        const int qi = atomicAdd(&flags[1], 1);
-                        if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + k));
+                    words[k] = word;
+                    bads[k] = bad;
+                }
+                bool rare = false;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int r = 32 * wm + 16 * (k >> 1) + g8 + 8 * (k & 1);
+                    unsigned char *dst = PK + r * kLdC + (ccs[k] + 1) * (4 * wn + t4);
+                    if (ccs[k] == 1) *reinterpret_cast<uint16_t *>(dst) = (uint16_t)words[k];
+                    else if (ccs[k] == 2) { dst[0] = (unsigned char)words[k]; dst[1] = (unsigned char)(words[k] >> 8); dst[2] = (unsigned char)(words[k] >> 16); }
+                    else if (ccs[k] == 3 || ccs[k] == 4) rare = true;
+                    if (ccs[k] == 1 || ccs[k] == 2) {
+                        uint32_t bad = bads[k];
+                        while (bad) {
+                            const int c8 = __ffs(bad) - 1;
+                            bad &= bad - 1;
+                            const int qi = atomicAdd(&flags[1], 1);
+                            if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + c8));
+                        }
                     }
                 }
+                if (rare) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int mb = k >> 1, hi = k & 1;
+                        const int r = 32 * wm + 16 * mb + g8 + 8 * hi;
+                        if (ccs[k] == 4) {   // 8 bits: the centroid spacing is within the margin, every coordinate is exact work
+                            for (int c8 = 0; c8 < 8; ++c8) {
+                                const int qi = atomicAdd(&flags[1], 1);
+                                if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + c8));
+                            }
+                        } else if (ccs[k] == 3) {
+                            const LevelConst &L = lc[2];
+                            uint32_t mid[7];
+#pragma unroll
+                            for (int j = 0; j < 7; ++j) mid[j] = L.mid[j];
+                            uint32_t word = 0, bad = 0;
+#pragma unroll
+                            for (int nb = 0; nb < 4; ++nb) {
+                                const uint32_t y2 = h2u(__floats2half2_rn(acc[mb][nb][2 * hi], acc[mb][nb][2 * hi + 1]));
+                                uint32_t ok;
+                                const uint32_t cf = decide_pair<7>(y2, mid, L.base, ok);
+                                word |= (((cf >> 1) & 15u) | (((cf >> 17) & 15u) << 4)) << (8 * nb);
+                                if ((ok & 0xffffu) != 0x3c00u) bad |= 1u << (2 * nb);
+                                if ((ok >> 16) != 0x3c00u) bad |= 2u << (2 * nb);
+                            }
+                            *reinterpret_cast<uint32_t *>(PK + r * kLdC + 4 * (4 * wn + t4)) = word;
+                            while (bad) {
+                                const int c8 = __ffs(bad) - 1;
+                                bad &= bad - 1;
+                                const int qi = atomicAdd(&flags[1], 1);
+                                if (qi < kQueueCap) queue[qi] = (uint16_t)((r << 7) | (col0 + c8));
+                            }
+                        }
+                    }
+                }
+            }
             group_sync(gid);
             // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain, exact rule
             const int qn = flags[1];
