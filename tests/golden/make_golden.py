@@ -252,7 +252,7 @@ def kats(outdir):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds kvquant/)")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"))
     args = ap.parse_args()
     torch.set_num_threads(os.cpu_count() or 1)
