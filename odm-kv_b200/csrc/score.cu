@@ -26,12 +26,13 @@ struct ScoreWs {
     float *part_o;    // [BH, nsplit, 128]
     float *part_ps;   // [BH, nsplit]
     unsigned *smax;   // [B]
+    unsigned *status; // [1] set to 1 when a bounded wait of a sweep expired
 };
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline int score_splits(int BH, int Tc) {
-    int want = (4 * 148 + BH - 1) / BH;
+    int want = (6 * 148 + BH - 1) / BH;   // two waves of three CTAs per SM
     int by_len = (Tc + 511) / 512;
     int n = want < by_len ? want : by_len;
     if (n < 1) n = 1;
@@ -45,11 +46,11 @@ inline size_t score_ws_layout(int B, int H, int G, int T, int n_sink, ScoreWs *w
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
     size_t o_logits = take(BH * G * Tc * 4), o_pbar = take(BH * Tc * 4), o_kn2 = take(BH * Tc * 4), o_vn2 = take(BH * Tc * 4);
-    size_t o_ml = take(BH * ns * G * 2 * 4), o_po = take(BH * ns * kD * 4), o_ps = take(BH * ns * 4), o_sm = take((size_t)B * 4);
+    size_t o_ml = take(BH * ns * G * 2 * 4), o_po = take(BH * ns * kD * 4), o_ps = take(BH * ns * 4), o_sm = take((size_t)B * 4 + 4);
     if (ws && base) {
         ws->logits = (float *)(base + o_logits); ws->pbar = (float *)(base + o_pbar); ws->kn2 = (float *)(base + o_kn2);
         ws->vn2 = (float *)(base + o_vn2); ws->part_ml = (float *)(base + o_ml); ws->part_o = (float *)(base + o_po);
-        ws->part_ps = (float *)(base + o_ps); ws->smax = (unsigned *)(base + o_sm);
+        ws->part_ps = (float *)(base + o_ps); ws->smax = (unsigned *)(base + o_sm); ws->status = ws->smax + B;
     }
     return off;
 }
@@ -114,6 +115,94 @@ __device__ __forceinline__ void gather_lane_vec(const float *__restrict__ vec, i
     (void)kRun;
 }
 
+// ---- row stream: bulk asynchronous copies (TMA, one-dimensional) of 64-row tiles into a ring of shared-memory
+// stages.  Thread 0 issues `cp.async.bulk` for a tile and arms the stage's mbarrier with the byte count; every
+// thread waits on the barrier's phase before reading the stage.  A stage is refilled right after the CTA-wide
+// barrier that ends its consumption, so kRingStages - 1 tiles (48 KB) are always in flight per CTA, independent
+// of what the compiler does with the consuming code.  Waits are bounded: when one expires the CTA records it in
+// the status word, waits (bounded again) for its outstanding copies and leaves.
+constexpr int kRingStages = 4;
+constexpr int kRingStageBytes = 16384;
+constexpr unsigned kWaitPolls = 1u << 16;   // each poll blocks for up to the hardware's try_wait window
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned it = 0; it < kWaitPolls; ++it) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+template <int DT>
+struct RowStream {
+    static constexpr int kRowBytes = kD * (int)sizeof(typename Elem<DT>::T);
+    static constexpr int kTileRows = kTokPerIter;                      // one row per quad and tile
+    static constexpr int kTileBytes = kTileRows * kRowBytes;           // 16 KB (16-bit) or 32 KB (fp32)
+    static constexpr int kStages = kRingStages * kRingStageBytes / kTileBytes;
+    unsigned char *ring;
+    uint64_t *bars;
+    const unsigned char *src;   // first row of this CTA
+    int nrows, ntiles;
+
+    __device__ void issue(int tile) {   // thread 0 only
+        const int s = tile % kStages;
+        const int rows = min(kTileRows, nrows - tile * kTileRows);
+        const uint32_t bytes = (uint32_t)rows * kRowBytes;
+        const uint32_t bar = smem_u32(bars + s), dst = smem_u32(ring + (size_t)s * kTileBytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                     ::"r"(dst), "l"(src + (size_t)tile * kTileBytes), "r"(bytes), "r"(bar) : "memory");
+    }
+    __device__ void start(unsigned char *ring_, uint64_t *bars_, const void *base, size_t first_row, int nrows_) {
+        ring = ring_; bars = bars_; nrows = nrows_;
+        src = reinterpret_cast<const unsigned char *>(base) + first_row * kRowBytes;
+        ntiles = (nrows + kTileRows - 1) / kTileRows;
+        if (threadIdx.x == 0) {
+            for (int s = 0; s < kStages; ++s)
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(bars + s)) : "memory");
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int t = 0; t < kStages && t < ntiles; ++t) issue(t);
+    }
+    // all threads; false when the wait expired (uniform over the CTA)
+    __device__ bool acquire(int tile, unsigned *status) {
+        const bool ok = mbar_wait(bars + tile % kStages, (unsigned)(tile / kStages) & 1u);
+        if (__syncthreads_or(!ok)) {
+            if (threadIdx.x == 0) {
+                atomicExch(status, 1u);
+                // outstanding copies target this CTA's shared memory: give them a bounded chance to land
+                for (int t = tile; t < ntiles && t < tile + kStages; ++t) mbar_wait(bars + t % kStages, (unsigned)(t / kStages) & 1u);
+            }
+            __syncthreads();
+            return false;
+        }
+        return true;
+    }
+    __device__ const unsigned char *row_ptr(int tile, int row_in_tile) const {
+        return ring + (size_t)(tile % kStages) * kTileBytes + (size_t)row_in_tile * kRowBytes;
+    }
+    // after the consumers are done with `tile` (call from all threads)
+    __device__ void release(int tile) {
+        __syncthreads();
+        if (threadIdx.x == 0 && tile + kStages < ntiles) issue(tile + kStages);
+    }
+};
+
+// load this lane's pieces of a row that sits in shared memory
+template <int DT>
+__device__ __forceinline__ void load_raw_smem(const unsigned char *row, int q, RawRow<DT> &r) {
+    const uint4 *p = reinterpret_cast<const uint4 *>(row);
+#pragma unroll
+    for (int v = 0; v < RawRow<DT>::kVec; ++v) r.v[v] = p[4 * v + q];
+}
+
 __device__ inline float quad_sum(float v) {
     v += __shfl_xor_sync(0xffffffffu, v, 1);
     v += __shfl_xor_sync(0xffffffffu, v, 2);
@@ -124,8 +213,10 @@ __device__ inline float quad_sum(float v) {
 // GM: compile-time bound on the group size (4, 8 or 16).  Lane q of a quad keeps the running softmax
 // statistics of the query heads g with g % 4 == q.
 template <int DT, int GM>
-__global__ void __launch_bounds__(kScoreThreads, 2) score_logits_kernel(const void *__restrict__ K, const float *__restrict__ mu,
+__global__ void __launch_bounds__(kScoreThreads, 3) score_logits_kernel(const void *__restrict__ K, const float *__restrict__ mu,
                                                                          int H, int G, int T, int n_sink, int nsplit, ScoreWs ws) {
+    extern __shared__ __align__(128) unsigned char score_ring[];
+    __shared__ __align__(8) uint64_t bars[kRingStages];
     __shared__ __align__(16) float mus[GM * kD];
     __shared__ float red_m[GM][kTokPerIter], red_l[GM][kTokPerIter];
     const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
@@ -141,16 +232,21 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_logits_kernel(const vo
 #pragma unroll
     for (int k = 0; k < GM / 4; ++k) { m_run[k] = -INFINITY; l_run[k] = 0.f; }
     const size_t row_base = (size_t)bh * T + n_sink;
-    RawRow<DT> nxt;
-    if (j0 + quad < j1) load_raw<DT>(K, row_base + j0 + quad, q, nxt);
+    RowStream<DT> rs;
+    rs.start(score_ring, bars, K, row_base + j0, max(j1 - j0, 0));
     // every lane of a warp runs the same number of iterations: the quad reductions below are
     // full-warp shuffles and must not be reached by a partial warp
-    for (int jb = j0; jb < j1; jb += kTokPerIter) {
-        const int j = jb + quad;
+    for (int tile = 0; tile < rs.ntiles; ++tile) {
+        if (!rs.acquire(tile, ws.status)) return;
+        const int j = j0 + tile * kTokPerIter + quad;
         const bool live = j < j1;
         float x[32];
-        unpack_row<DT>(nxt, live, x);
-        if (j + kTokPerIter < j1) load_raw<DT>(K, row_base + j + kTokPerIter, q, nxt);
+        {
+            RawRow<DT> raw;
+            if (live) load_raw_smem<DT>(rs.row_ptr(tile, quad), q, raw);
+            unpack_row<DT>(raw, live, x);
+        }
+        rs.release(tile);
         float kk = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) kk = fmaf(x[i], x[i], kk);
@@ -203,6 +299,137 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_logits_kernel(const vo
     }
 }
 
+// ---- sweep 1 on the tensor cores (16-bit caches, G <= 8) ----------------------------------------
+// logits^T = mu . K^T as m16n8k16 products: the sixteen A rows are the fp16 (bf16) high limbs of the G mean
+// queries (rows 0..7) and their low limbs (rows 8..15), so the product carries about 22 (16) bits of mu; the
+// eight B columns are the eight rows a warp holds, one per quad.  Contraction index p of k-block kb stands for
+// coordinate 8 (4 (kb / 2) + t) + 4 (kb % 2) + {0, 1 | 2, 3} of lane t's pieces, which makes the B registers
+// the lane's raw 32-bit words, unconverted.  |k|^2 stays an fp32 FMA sum.
+template <int DT>
+__device__ __forceinline__ void mma_16816_f32(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    if constexpr (DT == kF16)
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+    else
+        asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                     : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int DT>
+__device__ __forceinline__ void split_pair(float v0, float v1, uint32_t &hi, uint32_t &lo) {
+    if constexpr (DT == kF16) {
+        const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+        const __half l0 = __float2half_rn(v0 - __half2float(h0)), l1 = __float2half_rn(v1 - __half2float(h1));
+        hi = (uint32_t)__half_as_ushort(h0) | ((uint32_t)__half_as_ushort(h1) << 16);
+        lo = (uint32_t)__half_as_ushort(l0) | ((uint32_t)__half_as_ushort(l1) << 16);
+    } else {
+        const __nv_bfloat16 h0 = __float2bfloat16_rn(v0), h1 = __float2bfloat16_rn(v1);
+        const __nv_bfloat16 l0 = __float2bfloat16_rn(v0 - __bfloat162float(h0)), l1 = __float2bfloat16_rn(v1 - __bfloat162float(h1));
+        hi = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+        lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+    }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kScoreThreads, 3) score_logits_mma_kernel(const void *__restrict__ K, const float *__restrict__ mu,
+                                                                             int H, int G, int T, int n_sink, int nsplit, ScoreWs ws) {
+    static_assert(DT != kF32, "16-bit caches only");
+    extern __shared__ __align__(128) unsigned char score_ring[];
+    __shared__ __align__(8) uint64_t bars[kRingStages];
+    __shared__ float red_m[8][kScoreThreads / 32], red_l[8][kScoreThreads / 32];
+    const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
+    const int Tc = T - n_sink;
+    const int tid = threadIdx.x, q = tid & 3, quad = tid >> 2, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2;
+    const float inv_sqrt_d = 1.0f / sqrtf((float)kD);
+    // A fragments of this lane: head g8, high limbs in a0 / a2, low limbs in a1 / a3
+    uint32_t afr[8][4];
+    {
+        const float *mrow = mu + ((size_t)b * H * G + (size_t)(bh % H) * G + (g8 < G ? g8 : 0)) * kD;
+#pragma unroll
+        for (int kb = 0; kb < 8; ++kb) {
+            const int d0 = 8 * (4 * (kb >> 1) + q) + 4 * (kb & 1);
+            float4 m4 = *reinterpret_cast<const float4 *>(mrow + d0);
+            if (g8 >= G) m4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            split_pair<DT>(m4.x, m4.y, afr[kb][0], afr[kb][1]);
+            split_pair<DT>(m4.z, m4.w, afr[kb][2], afr[kb][3]);
+        }
+    }
+    const int per = (Tc + nsplit - 1) / nsplit;
+    const int j0 = split * per, j1 = min(Tc, j0 + per);
+    float m_run = -INFINITY, l_run = 0.f;   // head g8, rows 2q and 2q + 1 of every group of eight
+    const size_t row_base = (size_t)bh * T + n_sink;
+    RowStream<DT> rs;
+    rs.start(score_ring, bars, K, row_base + j0, max(j1 - j0, 0));
+    for (int tile = 0; tile < rs.ntiles; ++tile) {
+        if (!rs.acquire(tile, ws.status)) return;
+        const int j = j0 + tile * kTokPerIter + quad;
+        const bool live = j < j1;
+        RawRow<DT> raw;
+        if (live) load_raw_smem<DT>(rs.row_ptr(tile, quad), q, raw);
+        else {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) raw.v[v] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        rs.release(tile);
+        float d[4] = {0.f, 0.f, 0.f, 0.f};
+        float kk = 0.f;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint32_t w[4] = {raw.v[v].x, raw.v[v].y, raw.v[v].z, raw.v[v].w};
+            mma_16816_f32<DT>(d, afr[2 * v], w[0], w[1]);
+            mma_16816_f32<DT>(d, afr[2 * v + 1], w[2], w[3]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float2 f;
+                if constexpr (DT == kF16) f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+                else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[k]));
+                kk = fmaf(f.x, f.x, kk);
+                kk = fmaf(f.y, f.y, kk);
+            }
+        }
+        kk = quad_sum(kk);
+        if (q == 0 && live) ws.kn2[(size_t)bh * Tc + j] = kk;
+        // this lane's two logits: head g8, rows 2q and 2q + 1 of the warp's eight rows
+        const int jr = j0 + tile * kTokPerIter + warp * 8 + 2 * q;
+        if (g8 < G) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                if (jr + e < j1) {
+                    const float acc = (d[e] + d[2 + e]) * inv_sqrt_d;
+                    ws.logits[((size_t)bh * G + g8) * Tc + jr + e] = acc;
+                    const float mn = fmaxf(m_run, acc);
+                    const float ex = expf(fminf(m_run, acc) - mn);
+                    l_run = acc > m_run ? fmaf(l_run, ex, 1.0f) : l_run + ex;
+                    m_run = mn;
+                }
+            }
+        }
+    }
+    // merge over the four lanes of a head, then over the warps
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        const float mo = __shfl_xor_sync(0xffffffffu, m_run, o), lo = __shfl_xor_sync(0xffffffffu, l_run, o);
+        const float mn = fmaxf(m_run, mo);
+        float l = 0.f;
+        if (l_run > 0.f) l += l_run * expf(m_run - mn);
+        if (lo > 0.f) l += lo * expf(mo - mn);
+        m_run = mn; l_run = l;
+    }
+    if (q == 0) { red_m[g8][warp] = m_run; red_l[g8][warp] = l_run; }
+    __syncthreads();
+    if (tid < G) {
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kScoreThreads / 32; ++w) mm = fmaxf(mm, red_m[tid][w]);
+        float l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kScoreThreads / 32; ++w)
+            if (red_l[tid][w] > 0.f) l += red_l[tid][w] * expf(red_m[tid][w] - mm);
+        float *dst = ws.part_ml + (((size_t)bh * nsplit + split) * G + tid) * 2;
+        dst[0] = mm; dst[1] = l;
+    }
+}
+
 // merge the split statistics of one (b, h): final max and denominator per query head
 __device__ inline void merge_ml(const float *__restrict__ part_ml, int bh, int nsplit, int G, float *M, float *L) {
     // called by threads g < G
@@ -221,6 +448,8 @@ __device__ inline void merge_ml(const float *__restrict__ part_ml, int bh, int n
 template <int DT>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *__restrict__ V, int H, int G, int T, int n_sink,
                                                                      int nsplit, ScoreWs ws) {
+    extern __shared__ __align__(128) unsigned char score_ring[];
+    __shared__ __align__(8) uint64_t bars[kRingStages];
     __shared__ float M[kMaxG], L[kMaxG];
     __shared__ float osum[kTokPerIter / 8][kD];  // one row per warp
     __shared__ float psum[kTokPerIter / 8];
@@ -237,18 +466,41 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *
     float ps = 0.f;
     const float inv_g = 1.0f / (float)G;
     const size_t row_base = (size_t)bh * T + n_sink;
-    RawRow<DT> nxt;
-    if (j0 + quad < j1) load_raw<DT>(V, row_base + j0 + quad, q, nxt);
-    for (int jb = j0; jb < j1; jb += kTokPerIter) {
-        const int j = jb + quad;
+    RowStream<DT> rs;
+    rs.start(score_ring, bars, V, row_base + j0, max(j1 - j0, 0));
+    // lane q adds the softmax terms of the heads g = q, q + 4, ...; their logits are fetched one tile ahead
+    float lg_n[kMaxG / 4];
+    auto fetch_logits = [&](int j) {
+#pragma unroll
+        for (int k = 0; k < kMaxG / 4; ++k) {
+            const int g = q + 4 * k;
+            lg_n[k] = (j < j1 && g < G) ? __ldg(ws.logits + ((size_t)bh * G + g) * Tc + j) : 0.f;
+        }
+    };
+    fetch_logits(j0 + quad);
+    for (int tile = 0; tile < rs.ntiles; ++tile) {
+        if (!rs.acquire(tile, ws.status)) return;
+        const int j = j0 + tile * kTokPerIter + quad;
         const bool live = j < j1;
         float x[32];
-        unpack_row<DT>(nxt, live, x);
-        if (j + kTokPerIter < j1) load_raw<DT>(V, row_base + j + kTokPerIter, q, nxt);
-        // lane q adds the softmax terms of the heads g = q, q + 4, ...; the quad sum is their total
+        {
+            RawRow<DT> raw;
+            if (live) load_raw_smem<DT>(rs.row_ptr(tile, quad), q, raw);
+            unpack_row<DT>(raw, live, x);
+        }
+        rs.release(tile);
+        float lg[kMaxG / 4];
+#pragma unroll
+        for (int k = 0; k < kMaxG / 4; ++k) lg[k] = lg_n[k];
+        fetch_logits(j + kTokPerIter);
         float p = 0.f;
-        if (live)
-            for (int g = q; g < G; g += 4) p += expf(ws.logits[((size_t)bh * G + g) * Tc + j] - M[g]) / L[g];
+        if (live) {
+#pragma unroll
+            for (int k = 0; k < kMaxG / 4; ++k) {
+                const int g = q + 4 * k;
+                if (g < G) p += expf(lg[k] - M[g]) / L[g];
+            }
+        }
         p = quad_sum(p) * inv_g;
         float vv = 0.f;
 #pragma unroll
@@ -295,6 +547,8 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *
 template <int DT>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_final_kernel(const void *__restrict__ V, int H, int T, int n_sink,
                                                                         int nsplit, float eps, ScoreWs ws, float *__restrict__ scores) {
+    extern __shared__ __align__(128) unsigned char score_ring[];
+    __shared__ __align__(8) uint64_t bars[kRingStages];
     __shared__ __align__(16) float ob[kD];
     __shared__ float wmax[kScoreThreads / 32];
     const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
@@ -315,22 +569,37 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_final_kernel(const voi
     const int j0 = split * per, j1 = min(Tc, j0 + per);
     float best = 0.f;
     const size_t row_base = (size_t)bh * T + n_sink;
-    RawRow<DT> nxt;
-    if (j0 + quad < j1) load_raw<DT>(V, row_base + j0 + quad, q, nxt);
-    for (int jb = j0; jb < j1; jb += kTokPerIter) {
-        const int j = jb + quad;
+    RowStream<DT> rs;
+    rs.start(score_ring, bars, V, row_base + j0, max(j1 - j0, 0));
+    // the three per-row scalars of the next tile are fetched one tile ahead by the lane that uses them
+    float pb_n = 0.f, vn_n = 0.f, kn_n = 0.f;
+    auto fetch_scalars = [&](int j) {
+        if (q == 0 && j < j1) {
+            const size_t e = (size_t)bh * Tc + j;
+            pb_n = __ldg(ws.pbar + e); vn_n = __ldg(ws.vn2 + e); kn_n = __ldg(ws.kn2 + e);
+        }
+    };
+    fetch_scalars(j0 + quad);
+    for (int tile = 0; tile < rs.ntiles; ++tile) {
+        if (!rs.acquire(tile, ws.status)) return;
+        const int j = j0 + tile * kTokPerIter + quad;
         const bool live = j < j1;
         float x[32];
-        unpack_row<DT>(nxt, live, x);
-        if (j + kTokPerIter < j1) load_raw<DT>(V, row_base + j + kTokPerIter, q, nxt);
+        {
+            RawRow<DT> raw;
+            if (live) load_raw_smem<DT>(rs.row_ptr(tile, quad), q, raw);
+            unpack_row<DT>(raw, live, x);
+        }
+        rs.release(tile);
+        const float pb = pb_n, vn = vn_n, kn = kn_n;
+        fetch_scalars(j + kTokPerIter);
         float ir = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) { float dlt = x[i] - oq[i]; ir = fmaf(dlt, dlt, ir); }
         ir = quad_sum(ir);
         if (q == 0 && live) {
-            size_t e = (size_t)bh * Tc + j;
-            float p = ws.pbar[e] + eps;
-            float s = p * p * (ws.vn2[e] + (ws.kn2[e] / (float)kD) * ir);
+            float p = pb + eps;
+            float s = p * p * (vn + (kn / (float)kD) * ir);
             scores[(size_t)bh * T + n_sink + j] = s;
             best = fmaxf(best, s);  // NaN-free inputs assumed; scores are non-negative
         }
@@ -460,17 +729,43 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     size_t need = score_ws_layout(B, H, G, T, n_sink, &ws, (unsigned char *)workspace);
     if (workspace_bytes < need) return ODMKV_ERR_WORKSPACE;
     const int BH = B * H, Tc = T - n_sink, ns = score_splits(BH, Tc);
-    cudaMemsetAsync(ws.smax, 0, (size_t)B * 4, st);
+    cudaMemsetAsync(ws.smax, 0, (size_t)B * 4 + 4, st);   // per-sample maxima and the status word
     dim3 grid(ns, BH);
+    constexpr int kRing = kRingStages * kRingStageBytes;
     timing_begin("score", st);
-#define ODMKV_SCORE(DT)                                                                                    \
-    if (G <= 4) score_logits_kernel<DT, 4><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);   \
-    else if (G <= 8) score_logits_kernel<DT, 8><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws); \
-    else score_logits_kernel<DT, 16><<<grid, kScoreThreads, 0, st>>>(K, mu, H, G, T, n_sink, ns, ws);         \
-    score_pv_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, G, T, n_sink, ns, ws);                          \
-    score_final_kernel<DT><<<grid, kScoreThreads, 0, st>>>(V, H, T, n_sink, ns, eps, ws, scores);
-    if (dtype == kF16) { ODMKV_SCORE(kF16) } else if (dtype == kBF16) { ODMKV_SCORE(kBF16) } else { ODMKV_SCORE(kF32) }
+#define ODMKV_SCORE_L(DT, GM)                                                                                         \
+    {                                                                                                                 \
+        cudaError_t e = cudaFuncSetAttribute(score_logits_kernel<DT, GM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
+        if (e != cudaSuccess) return (int)e;                                                                          \
+        score_logits_kernel<DT, GM><<<grid, kScoreThreads, kRing, st>>>(K, mu, H, G, T, n_sink, ns, ws);              \
+    }
+#define ODMKV_SCORE_M(DT)                                                                                             \
+    {                                                                                                                 \
+        cudaError_t e = cudaFuncSetAttribute(score_logits_mma_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
+        if (e != cudaSuccess) return (int)e;                                                                          \
+        score_logits_mma_kernel<DT><<<grid, kScoreThreads, kRing, st>>>(K, mu, H, G, T, n_sink, ns, ws);              \
+    }
+#define ODMKV_SCORE(DT)                                                                                               \
+    if (G <= 4) ODMKV_SCORE_L(DT, 4) else if (G <= 8) ODMKV_SCORE_L(DT, 8) else ODMKV_SCORE_L(DT, 16)                 \
+    ODMKV_SCORE_REST(DT)
+#define ODMKV_SCORE16(DT)                                                                                             \
+    if (G <= 8) ODMKV_SCORE_M(DT) else ODMKV_SCORE_L(DT, 16)                                                          \
+    ODMKV_SCORE_REST(DT)
+#define ODMKV_SCORE_REST(DT)                                                                                          \
+    {                                                                                                                 \
+        cudaError_t e = cudaFuncSetAttribute(score_pv_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
+        if (e != cudaSuccess) return (int)e;                                                                          \
+        e = cudaFuncSetAttribute(score_final_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);         \
+        if (e != cudaSuccess) return (int)e;                                                                          \
+        score_pv_kernel<DT><<<grid, kScoreThreads, kRing, st>>>(V, H, G, T, n_sink, ns, ws);                          \
+        score_final_kernel<DT><<<grid, kScoreThreads, kRing, st>>>(V, H, T, n_sink, ns, eps, ws, scores);             \
+    }
+    if (dtype == kF16) { ODMKV_SCORE16(kF16) } else if (dtype == kBF16) { ODMKV_SCORE16(kBF16) } else { ODMKV_SCORE(kF32) }
 #undef ODMKV_SCORE
+#undef ODMKV_SCORE16
+#undef ODMKV_SCORE_REST
+#undef ODMKV_SCORE_M
+#undef ODMKV_SCORE_L
     timing_end(st);
     if (n_sink > 0) score_sinks_kernel<<<BH, 32, 0, st>>>(scores, ws.smax, H, T, n_sink);
     return launch_status();
