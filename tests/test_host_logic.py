@@ -142,3 +142,30 @@ def test_collectives_on_two_gloo_ranks():
         ret = mgr.dict()
         mp.spawn(_gloo_worker, args=(world, port, ret), nprocs=world, join=True)
         assert all(ret.get(r) for r in range(world)), dict(ret)
+
+
+def test_packed_chunk_deepcopy_rebuilds_c_view():
+    """A deep copy of a packed chunk (the runner copies caches between questions) must not share or pickle
+    the cached ctypes view, and its view must point at the copy's own tensors."""
+    import copy
+    import importlib
+
+    import torch
+
+    ops = importlib.import_module("odm-kv_b200").ops
+    z = lambda *s, dt=torch.uint8: torch.zeros(*s, dtype=dt)
+    ch = ops.PackedChunk(B=1, H=1, T=16, t_offset=0, dtype=torch.float16, device=torch.device("cpu"),
+                         seg_start=z(6, 1, dt=torch.int32), seg_count=z(6, 1, dt=torch.int32), totals=[0, 16, 0, 0, 0, 0],
+                         k_codes=[z(512), z(0), z(0), z(0)], v_codes=[z(512), z(0), z(0), z(0)],
+                         k_norm=[z(16, dt=torch.float32)] + [z(0, dt=torch.float32)] * 3,
+                         v_norm=[z(16, dt=torch.float32)] + [z(0, dt=torch.float32)] * 3,
+                         pos=[z(16, dt=torch.int32)] + [z(0, dt=torch.int32)] * 3,
+                         exact_k=z(0, 128, dt=torch.float16), exact_v=z(0, 128, dt=torch.float16),
+                         exact_pos=z(0, dt=torch.int32), evicted_pos=z(0, dt=torch.int32))
+    first = ch.c_struct()
+    assert ch.c_struct() is first                       # cached
+    dup = copy.deepcopy(ch)
+    assert dup._c_struct is None
+    view = dup.c_struct()
+    assert view.k_codes[0] == dup.k_codes[0].data_ptr() != ch.k_codes[0].data_ptr()
+    assert view.cap[1] == 16 and view.T == 16
