@@ -121,7 +121,8 @@ __device__ __forceinline__ void gather_lane_vec(const float *__restrict__ vec, i
 // barrier that ends its consumption, so kRingStages - 1 tiles (48 KB) are always in flight per CTA, independent
 // of what the compiler does with the consuming code.  Waits are bounded: when one expires the CTA records it in
 // the status word, waits (bounded again) for its outstanding copies and leaves.
-constexpr int kRingStages = 4;
+constexpr int kRingStages = 4;    // K sweep: three CTAs per SM
+constexpr int kRingStagesV = 6;   // V sweeps: two CTAs per SM, so more stages each keep the same bytes in flight
 constexpr int kRingStageBytes = 16384;
 constexpr unsigned kWaitPolls = 1u << 16;   // each poll blocks for up to the hardware's try_wait window
 
@@ -138,12 +139,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     return false;
 }
 
-template <int DT>
+template <int DT, int RING = kRingStages>
 struct RowStream {
     static constexpr int kRowBytes = kD * (int)sizeof(typename Elem<DT>::T);
     static constexpr int kTileRows = kTokPerIter;                      // one row per quad and tile
     static constexpr int kTileBytes = kTileRows * kRowBytes;           // 16 KB (16-bit) or 32 KB (fp32)
-    static constexpr int kStages = kRingStages * kRingStageBytes / kTileBytes;
+    static constexpr int kStages = RING * kRingStageBytes / kTileBytes;
     unsigned char *ring;
     uint64_t *bars;
     const unsigned char *src;   // first row of this CTA
@@ -449,7 +450,7 @@ template <int DT>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *__restrict__ V, int H, int G, int T, int n_sink,
                                                                      int nsplit, ScoreWs ws) {
     extern __shared__ __align__(128) unsigned char score_ring[];
-    __shared__ __align__(8) uint64_t bars[kRingStages];
+    __shared__ __align__(8) uint64_t bars[kRingStagesV];
     __shared__ float M[kMaxG], L[kMaxG];
     __shared__ float osum[kTokPerIter / 8][kD];  // one row per warp
     __shared__ float psum[kTokPerIter / 8];
@@ -466,7 +467,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_pv_kernel(const void *
     float ps = 0.f;
     const float inv_g = 1.0f / (float)G;
     const size_t row_base = (size_t)bh * T + n_sink;
-    RowStream<DT> rs;
+    RowStream<DT, kRingStagesV> rs;
     rs.start(score_ring, bars, V, row_base + j0, max(j1 - j0, 0));
     // lane q adds the softmax terms of the heads g = q, q + 4, ...; their logits are fetched one tile ahead
     float lg_n[kMaxG / 4];
@@ -548,7 +549,7 @@ template <int DT>
 __global__ void __launch_bounds__(kScoreThreads, 2) score_final_kernel(const void *__restrict__ V, int H, int T, int n_sink,
                                                                         int nsplit, float eps, ScoreWs ws, float *__restrict__ scores) {
     extern __shared__ __align__(128) unsigned char score_ring[];
-    __shared__ __align__(8) uint64_t bars[kRingStages];
+    __shared__ __align__(8) uint64_t bars[kRingStagesV];
     __shared__ __align__(16) float ob[kD];
     __shared__ float wmax[kScoreThreads / 32];
     const int bh = blockIdx.y, split = blockIdx.x, b = bh / H;
@@ -569,7 +570,7 @@ __global__ void __launch_bounds__(kScoreThreads, 2) score_final_kernel(const voi
     const int j0 = split * per, j1 = min(Tc, j0 + per);
     float best = 0.f;
     const size_t row_base = (size_t)bh * T + n_sink;
-    RowStream<DT> rs;
+    RowStream<DT, kRingStagesV> rs;
     rs.start(score_ring, bars, V, row_base + j0, max(j1 - j0, 0));
     // the three per-row scalars of the next tile are fetched one tile ahead by the lane that uses them
     float pb_n = 0.f, vn_n = 0.f, kn_n = 0.f;
@@ -731,7 +732,7 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     const int BH = B * H, Tc = T - n_sink, ns = score_splits(BH, Tc);
     cudaMemsetAsync(ws.smax, 0, (size_t)B * 4 + 4, st);   // per-sample maxima and the status word
     dim3 grid(ns, BH);
-    constexpr int kRing = kRingStages * kRingStageBytes;
+    constexpr int kRing = kRingStages * kRingStageBytes, kRingV = kRingStagesV * kRingStageBytes;
     timing_begin("score", st);
 #define ODMKV_SCORE_L(DT, GM)                                                                                         \
     {                                                                                                                 \
@@ -753,12 +754,12 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     ODMKV_SCORE_REST(DT)
 #define ODMKV_SCORE_REST(DT)                                                                                          \
     {                                                                                                                 \
-        cudaError_t e = cudaFuncSetAttribute(score_pv_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing); \
+        cudaError_t e = cudaFuncSetAttribute(score_pv_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingV); \
         if (e != cudaSuccess) return (int)e;                                                                          \
-        e = cudaFuncSetAttribute(score_final_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRing);         \
+        e = cudaFuncSetAttribute(score_final_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingV);        \
         if (e != cudaSuccess) return (int)e;                                                                          \
-        score_pv_kernel<DT><<<grid, kScoreThreads, kRing, st>>>(V, H, G, T, n_sink, ns, ws);                          \
-        score_final_kernel<DT><<<grid, kScoreThreads, kRing, st>>>(V, H, T, n_sink, ns, eps, ws, scores);             \
+        score_pv_kernel<DT><<<grid, kScoreThreads, kRingV, st>>>(V, H, G, T, n_sink, ns, ws);                         \
+        score_final_kernel<DT><<<grid, kScoreThreads, kRingV, st>>>(V, H, T, n_sink, ns, eps, ws, scores);            \
     }
     if (dtype == kF16) { ODMKV_SCORE16(kF16) } else if (dtype == kBF16) { ODMKV_SCORE16(kBF16) } else { ODMKV_SCORE(kF32) }
 #undef ODMKV_SCORE
