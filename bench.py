@@ -295,7 +295,8 @@ def run_ours(args):
         try:
             gq = qd.clone()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            # thread-local capture mode: other threads (the NCCL watchdog under torchrun) may keep making CUDA calls
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
                 g_out = ops.decode_attn(gq, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
             for _ in range(3):
                 graph.replay()
