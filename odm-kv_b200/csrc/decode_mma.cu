@@ -157,7 +157,8 @@ __device__ inline void decode_step(uint32_t lane_off, const uint32_t *w, int j, 
 template <int NT>
 struct MmaState {
     float M[2], l[2];        // per head column of this lane (two heads per lane)
-    float O[NT][8][4];       // O^T fragments: [column tile][16-coordinate block][c0..c3]
+    float O[8][4];           // O^T fragments: [16-coordinate block][c0..c3]; NT = 1: columns 4..7 take the low limbs of the weights,
+                             // NT = 2: eight heads, weights enter as fp16 (the denominators use the same rounded weights)
 };
 
 template <int B>
@@ -231,33 +232,32 @@ __device__ inline void process_tiles(MmaState<NT> &st, const TileRegs<B> (&tr)[U
         st.M[0] = n0; st.M[1] = n1;
         st.l[0] *= c0; st.l[1] *= c1;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int m = 0; m < 8; ++m) {
-                st.O[nt][m][0] *= c0; st.O[nt][m][1] *= c1; st.O[nt][m][2] *= c0; st.O[nt][m][3] *= c1;
-            }
+        for (int m = 0; m < 8; ++m) {
+            st.O[m][0] *= c0; st.O[m][1] *= c1; st.O[m][2] *= c0; st.O[m][3] *= c1;
+        }
     }
     // ---- weights and the P operand (fp16 high and low limb of every weight, two weights per conversion)
     const float m0 = st.M[0], m1 = st.M[1];
-    uint32_t pb[U][NT][2];
+    uint32_t pb[U][2];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
         const float W0 = fast_exp2(z[u][0] - m0), W1 = fast_exp2(z[u][1] - m1), W2 = fast_exp2(z[u][2] - m0), W3 = fast_exp2(z[u][3] - m1);
-        st.l[0] = fmaf(W0, rv[u][0], fmaf(W2, rv[u][1], st.l[0]));
-        st.l[1] = fmaf(W1, rv[u][0], fmaf(W3, rv[u][1], st.l[1]));
         const uint32_t hi01 = cvt_f16x2(W0, W1), hi23 = cvt_f16x2(W2, W3);
         const float2 b01 = __half22float2(*reinterpret_cast<const __half2 *>(&hi01));
         const float2 b23 = __half22float2(*reinterpret_cast<const __half2 *>(&hi23));
-        const uint32_t lo01 = cvt_f16x2(W0 - b01.x, W1 - b01.y), lo23 = cvt_f16x2(W2 - b23.x, W3 - b23.y);
         if (NT == 1) {
+            st.l[0] = fmaf(W0, rv[u][0], fmaf(W2, rv[u][1], st.l[0]));
+            st.l[1] = fmaf(W1, rv[u][0], fmaf(W3, rv[u][1], st.l[1]));
+            const uint32_t lo01 = cvt_f16x2(W0 - b01.x, W1 - b01.y), lo23 = cvt_f16x2(W2 - b23.x, W3 - b23.y);
             const bool low = (t & 2) != 0;   // columns 4..7 carry the low limbs
-            pb[u][0][0] = movmatrix_trans(low ? lo01 : hi01);
-            pb[u][0][1] = movmatrix_trans(low ? lo23 : hi23);
+            pb[u][0] = movmatrix_trans(low ? lo01 : hi01);
+            pb[u][1] = movmatrix_trans(low ? lo23 : hi23);
         } else {
-            pb[u][0][0] = movmatrix_trans(hi01);
-            pb[u][0][1] = movmatrix_trans(hi23);
-            pb[u][NT - 1][0] = movmatrix_trans(lo01);
-            pb[u][NT - 1][1] = movmatrix_trans(lo23);
+            // numerator and denominator see the same fp16-rounded weights
+            st.l[0] = fmaf(b01.x, rv[u][0], fmaf(b23.x, rv[u][1], st.l[0]));
+            st.l[1] = fmaf(b01.y, rv[u][0], fmaf(b23.y, rv[u][1], st.l[1]));
+            pb[u][0] = movmatrix_trans(hi01);
+            pb[u][1] = movmatrix_trans(hi23);
         }
     }
     // ---- O^T += V_dec^T . P
@@ -268,7 +268,7 @@ __device__ inline void process_tiles(MmaState<NT> &st, const TileRegs<B> (&tr)[U
             uint32_t a[4];
             decode_step<B>(lane_off, tr[u].vw, m, a);
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) mma16816(st.O[nt][m], a, pb[u][nt][0], pb[u][nt][1]);
+            mma16816(st.O[m], a, pb[u][0], pb[u][1]);
         }
     }
 }
@@ -445,11 +445,9 @@ __global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel
         st.M[0] = st.M[1] = kNegBig;
         st.l[0] = st.l[1] = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+        for (int m = 0; m < 8; ++m)
 #pragma unroll
-            for (int m = 0; m < 8; ++m)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) st.O[nt][m][i] = 0.f;
+            for (int i = 0; i < 4; ++i) st.O[m][i] = 0.f;
 
         for (int ci = 0; ci < chunks.n; ++ci) {
             const odmkv_chunk &ch = chunks.ch[ci];
@@ -474,7 +472,7 @@ __global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel
 #pragma unroll
             for (int m = 0; m < 8; ++m)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) st.O[0][m][i] += __shfl_xor_sync(0xffffffffu, st.O[0][m][i], 2);
+                for (int i = 0; i < 4; ++i) st.O[m][i] += __shfl_xor_sync(0xffffffffu, st.O[m][i], 2);
         }
         if (g == 0 && owner) { warpM[warp][h0] = st.M[0]; warpM[warp][h1] = st.M[1]; }
         __syncthreads();
@@ -491,8 +489,7 @@ __global__ void __launch_bounds__(kMmaThreads, ODMKV_MMA_CTAS) decode_mma_kernel
             if (warp == w && owner) {
 #pragma unroll
                 for (int m = 0; m < 8; ++m) {
-                    float v0 = st.O[0][m][0], v1 = st.O[0][m][1], v2 = st.O[0][m][2], v3 = st.O[0][m][3];
-                    if (NT == 2) { v0 += st.O[NT - 1][m][0]; v1 += st.O[NT - 1][m][1]; v2 += st.O[NT - 1][m][2]; v3 += st.O[NT - 1][m][3]; }
+                    const float v0 = st.O[m][0], v1 = st.O[m][1], v2 = st.O[m][2], v3 = st.O[m][3];
                     Osh[h0][16 * m + g] += v0 * c0;
                     Osh[h1][16 * m + g] += v1 * c1;
                     Osh[h0][16 * m + g + 8] += v2 * c0;
