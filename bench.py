@@ -314,21 +314,33 @@ def run_ours(args):
             return g_out
         return step(i)
 
-    if world > 1:
-        dist.barrier()
-    gathered = [torch.empty_like(out) for _ in range(world)] if world > 1 else None
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        o = timed_step(i)
+    # Multi-GPU schedules.  Headline: every rank owns whole (layer, sample, KV head) units, so a decode step needs
+    # no exchange and the outputs are gathered once after the K steps (inside the timed region).  Also measured:
+    # the KV-head-sharded schedule of one layer, which all-gathers the outputs after every step.
+    def timed_loop(gather_every_step):
         if world > 1:
-            dist.all_gather(gathered, o)   # the per-head output gather of a KV-head / layer sharded run
-    ev1.record()
-    torch.cuda.synchronize()
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        o = None
+        for i in range(args.steps):
+            o = timed_step(i)
+            if world > 1 and gather_every_step:
+                dist.all_gather(gathered, o)
+        if world > 1 and not gather_every_step:
+            dist.all_gather(gathered, o)
+        b.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        return a.elapsed_time(b)
+
+    gathered = [torch.empty_like(out) for _ in range(world)] if world > 1 else None
     if world > 1:
-        dist.barrier()
-    total_ms = ev0.elapsed_time(ev1)
+        dist.all_gather(gathered, out)   # NCCL warm-up outside the timed region
+    total_ms = timed_loop(gather_every_step=False)
+    tp_ms = timed_loop(gather_every_step=True) if world > 1 else None
 
     # per-kernel durations: the same steps launched eagerly with an event pair around each kernel
     L.odmkv_timing_enable(1)
@@ -378,13 +390,13 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- max over ranks, totals over ranks
-    stats = torch.tensor([total_ms, e2e_ms, float(bytes_per_step), main_ms, compress_ms], dtype=torch.float64, device=dev)
+    stats = torch.tensor([total_ms, e2e_ms, float(bytes_per_step), main_ms, compress_ms, tp_ms or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, e2e_ms, main_ms, compress_ms = mx[0].item(), mx[1].item(), mx[3].item(), mx[4].item()
+        total_ms, e2e_ms, main_ms, compress_ms, tp_ms = mx[0].item(), mx[1].item(), mx[3].item(), mx[4].item(), mx[5].item()
         bytes_all = sm[2].item()
     else:
         bytes_all = float(bytes_per_step)
@@ -416,13 +428,16 @@ def run_ours(args):
                    "level_counts": {str(b): int(c) for b, c in zip(LEVELS, cnt)},
                    "stored_token_heads": stored, "bytes_per_step_per_rank": bytes_per_step,
                    "decode_impl": args.decode_impl, "n_splits": n_splits,
-                   "multi_gpu": "each rank holds its own (sample, KV head) units; outputs all-gathered per step" if world > 1 else "single GPU"},
+                   "multi_gpu": "each rank holds its own (layer, sample, KV head) units: no exchange inside a step, outputs all-gathered once after the timed steps" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,
                      "frac_of_8000": achieved / 8000.0, "other_kernels_ms": parts_ms},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
                 "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps},
         "gpu_launches": 4 * args.steps,
+        "gather_per_step": None if tp_ms is None else {
+            "schedule": "KV heads of one layer sharded over the ranks: outputs all-gathered (NCCL) after every step",
+            "ms_per_step": tp_ms / args.steps, "value": bytes_all / (tp_ms / args.steps * 1e-3) / 1e9},
         "step_mode": {"timed_step": step_mode, "graph_vs_eager_max_abs_diff": graph_err,
                       "eager_ms_per_step_with_kernel_events": eager_ms},
         "clocks": clocks,
