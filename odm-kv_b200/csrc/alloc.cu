@@ -15,6 +15,8 @@
 // over ranks the caller sums the accumulator over ranks between `eval` and `update`.
 #include "common.cuh"
 
+#include <cub/device/device_radix_sort.cuh>
+
 namespace odmkv {
 
 constexpr int kMaxL = ODMKV_MAX_LEVELS;
@@ -114,6 +116,7 @@ struct AllocProblem {
     unsigned max_finite_bits;
     int any_nonfinite, any_finite;
     Envelope env;    // envelope of the cost lines at `lam` (counting passes)
+    int n_sorted;    // live (non-sink) scores of the problem, i.e. the length of its sorted key array
 };
 
 struct AllocWs {
@@ -121,6 +124,9 @@ struct AllocWs {
     unsigned long long *acc;     // [P][kAccLen]
     uint8_t *chosen;             // [P][n]
     AllocCfg *cfg;               // device copy (for the stepwise entry points)
+    unsigned *keys_in, *keys_out;   // [P][n] sanitised scores as ordered keys (sinks = 0xffffffff), unsorted / ascending
+    void *sort_temp;             // scratch of the radix sort
+    size_t sort_temp_bytes;
     // host-side header kept at the start of the workspace is mirrored in AllocHeader
 };
 
@@ -136,8 +142,13 @@ inline size_t alloc_ws_layout(int P, int n, AllocWs *ws, unsigned char *base) {
     auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
     size_t o_hdr = take(sizeof(AllocHeader)), o_cfg = take(sizeof(AllocCfg)), o_prob = take(sizeof(AllocProblem) * (size_t)P);
     size_t o_acc = take(sizeof(unsigned long long) * (size_t)P * kAccLen), o_ch = take((size_t)P * n);
+    size_t sort_bytes = 0;
+    cub::DeviceRadixSort::SortKeys(nullptr, sort_bytes, (const unsigned *)nullptr, (unsigned *)nullptr, n);
+    size_t o_ki = take((size_t)P * n * 4), o_ko = take((size_t)P * n * 4), o_st = take(sort_bytes);
     (void)o_hdr;
     if (ws && base) {
+        ws->keys_in = (unsigned *)(base + o_ki); ws->keys_out = (unsigned *)(base + o_ko);
+        ws->sort_temp = base + o_st; ws->sort_temp_bytes = sort_bytes;
         ws->cfg = (AllocCfg *)(base + o_cfg);
         ws->prob = (AllocProblem *)(base + o_prob);
         ws->acc = (unsigned long long *)(base + o_acc);
@@ -556,6 +567,109 @@ __global__ void __launch_bounds__(kAllocThreads, 3) alloc_pass_kernel(const floa
     }
 }
 
+// ---- sorted-score solver for the counting passes (single-device path) -----------------------------------
+// The scores of a problem are sorted once (keys = bit patterns of the sanitised, non-negative scores; sinks sort
+// to the end).  A counting pass at a given lambda then needs, per breakpoint band of the envelope, two binary
+// searches and the exact evaluation of the few scores inside the band; everything between two bands belongs to
+// one envelope piece.  One CTA per problem runs all widening and bisection steps back to back.
+__global__ void alloc_keys_kernel(const float *__restrict__ scores, const uint8_t *__restrict__ sink_mask, int n, AllocWs ws) {
+    const int p = blockIdx.y;
+    const AllocProblem pr = ws.prob[p];
+    unsigned live = 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const bool sink = sink_mask && sink_mask[i];
+        ws.keys_in[(size_t)p * n + i] = sink ? 0xffffffffu : __float_as_uint(sanitize(scores[(size_t)p * n + i], pr));
+        live += sink ? 0u : 1u;
+    }
+    live = __reduce_add_sync(0xffffffffu, live);
+    if ((threadIdx.x & 31) == 0 && live) atomicAdd(&ws.prob[p].n_sorted, (int)live);
+}
+
+constexpr int kSolveThreads = 1024;
+constexpr int kCoarse = 4096;
+
+__global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, int n, const AllocCfg cfg) {
+    __shared__ float coarse[kCoarse];
+    __shared__ unsigned sh_counts[kMaxL];
+    __shared__ int sh_edge[2 * kMaxL];      // per band: first index >= lo, first index > hi
+    __shared__ int sh_rng[2 * kMaxL + 2];   // exact ranges [start, end)
+    __shared__ int sh_nr, sh_phase;
+    const int p = blockIdx.x, tid = threadIdx.x;
+    AllocProblem *prp = ws.prob + p;
+    unsigned long long *acc = ws.acc + (size_t)p * kAccLen;
+    const unsigned *keys = ws.keys_out + (size_t)p * n;
+    const int na = prp->n_sorted;
+    const int stride = na > kCoarse ? (na + kCoarse - 1) / kCoarse : 1;
+    const int nc = na > 0 ? (na + stride - 1) / stride : 0;
+    for (int i = tid; i < nc; i += kSolveThreads) coarse[i] = __uint_as_float(keys[(size_t)i * stride]);
+    if (tid == 0) sh_phase = prp->phase;
+    __syncthreads();
+    for (int guard = 0; guard < kEvalRounds + 2 && sh_phase <= 1; ++guard) {
+        const float lam32 = (float)prp->lam;
+        float lamb[kMaxL];
+#pragma unroll
+        for (int k = 0; k < kMaxL; ++k) lamb[k] = k < cfg.K ? __fmul_rn(lam32, cfg.bits32[k]) : 0.f;
+        const int nh = prp->env.nh;
+        if (tid < kMaxL) sh_counts[tid] = 0;
+        // ---- band edges by binary search (coarse index in shared memory, then the stride around it)
+        if (nh > 1 && tid < 2 * (nh - 1)) {
+            const int v = tid >> 1;
+            const bool upper = tid & 1;
+            const float x = upper ? prp->env.hi[v] : prp->env.lo[v];
+            int lo = 0, hi = nc;   // first coarse entry that is >= x (lower) or > x (upper)
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                const bool go = upper ? (coarse[mid] <= x) : (coarse[mid] < x);
+                if (go) lo = mid + 1; else hi = mid;
+            }
+            int a = lo > 0 ? (lo - 1) * stride : 0, b = lo < nc ? lo * stride : na;
+            if (b > na) b = na;
+            while (a < b) {
+                const int mid = (a + b) >> 1;
+                const float kv = __uint_as_float(keys[mid]);
+                const bool go = upper ? (kv <= x) : (kv < x);
+                if (go) a = mid + 1; else b = mid;
+            }
+            sh_edge[tid] = a;
+        }
+        __syncthreads();
+        // ---- pieces between the bands and the exact ranges inside them
+        if (tid == 0) {
+            int nr = 0, cursor = 0;
+            if (nh == 0) { sh_rng[0] = 0; sh_rng[1] = na; nr = 1; cursor = na; }
+            for (int v = 0; v + 1 < nh; ++v) {
+                const int i_lo = sh_edge[2 * v], i_hi = sh_edge[2 * v + 1];
+                if (i_lo > cursor) { sh_counts[prp->env.level[v]] += (unsigned)(i_lo - cursor); cursor = i_lo; }
+                if (i_hi > cursor) { sh_rng[2 * nr] = cursor; sh_rng[2 * nr + 1] = i_hi; ++nr; cursor = i_hi; }
+            }
+            if (nh > 0 && na > cursor) sh_counts[prp->env.level[nh - 1]] += (unsigned)(na - cursor);
+            sh_nr = nr;
+        }
+        __syncthreads();
+        for (int r = 0; r < sh_nr; ++r) {
+            for (int i = sh_rng[2 * r] + tid; i < sh_rng[2 * r + 1]; i += kSolveThreads) {
+                const float sc = __uint_as_float(keys[i]);
+                float best = __fadd_rn(__fmul_rn(sc, cfg.eps32[0]), lamb[0]);
+                int arg = 0;
+#pragma unroll
+                for (int k = 1; k < kMaxL; ++k) {
+                    if (k < cfg.K) {
+                        const float c = __fadd_rn(__fmul_rn(sc, cfg.eps32[k]), lamb[k]);
+                        if (c < best) { best = c; arg = k; }
+                    }
+                }
+                atomicAdd(&sh_counts[arg], 1u);
+            }
+        }
+        __syncthreads();
+        if (tid < kMaxL) acc[tid] = (unsigned long long)sh_counts[tid];
+        __syncthreads();
+        update_problem(prp, acc, cfg);   // advances lo / hi / lambda and the envelope exactly as a fused pass does
+        if (tid == 0) sh_phase = prp->phase;
+        __syncthreads();
+    }
+}
+
 // blocks per problem of a pass: enough to fill the GPU a few times over, never more than one chunk each
 static int pass_blocks(int n, int P) {
     const int chunks = (n + kAllocThreads * kPerThread - 1) / (kAllocThreads * kPerThread);
@@ -667,8 +781,19 @@ int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, in
     rc = alloc_begin_impl(scores, sink_mask, P, n, cfg, &ws, workspace, workspace_bytes, st);
     if (rc) return rc;
     const int nblk = pass_blocks(n, P);
-    const int rounds = (K > 1 ? kEvalRounds : 1) + closure_rounds(K);
+    const int rounds = 1 + closure_rounds(K);   // the final assignment pass and the gap closure
     timing_begin("allocate", st);
+    if (K > 1) {
+        int kb = (n + 256 * 8 - 1) / (256 * 8);
+        if (kb > 1024) kb = 1024;
+        alloc_keys_kernel<<<dim3(kb, P), 256, 0, st>>>(scores, sink_mask, n, ws);
+        for (int p = 0; p < P; ++p) {
+            size_t tb = ws.sort_temp_bytes;
+            cudaError_t e = cub::DeviceRadixSort::SortKeys(ws.sort_temp, tb, ws.keys_in + (size_t)p * n, ws.keys_out + (size_t)p * n, n, 0, 32, st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        alloc_solve_kernel<<<P, kSolveThreads, 0, st>>>(ws, n, cfg);
+    }
     for (int r = 0; r < rounds; ++r)
         alloc_pass_kernel<true><<<dim3(nblk, P), kAllocThreads, 0, st>>>(scores, sink_mask, n, 0ll, ws, cfg);
     timing_end(st);
