@@ -152,17 +152,20 @@ __device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int l
 constexpr int kQRows = 64;   // tokens per work item of quantize_kernel: one half of a plan tile
 constexpr int kLdH = 136;    // padded fp16 row stride (272 bytes: conflict-free ldmatrix rows)
 
-// Decision margin of the tensor-core pass.  The rotation is first evaluated with fp16 operands on the
-// tensor cores; with |x_unit| <= 1 and |row of Pi| = 1 the result differs from the fp32 FMA chain by at
-// most  (2^-10 + 2^-22) * sum|x_i p_i|  (operand rounding, sum|x_i p_i| <= 1 by Cauchy-Schwarz)
-//     + 2^-25 * (sum|x_i| + sum|p_i|)   (fp16 subnormal operands, <= 6.8e-7)
-//     + 128 * 2^-21                     (accumulation, generous) + 128 * 2^-24 (the chain's own error)
-//     <= 1.05e-3.
-// The decision itself runs in fp16 against fp16 midpoints of adjacent centroids: both roundings cost at
-// most 2^-14 each for |y| < 0.25 (every midpoint of the 2/3/4-bit codebooks is below 0.22).  A coordinate
-// closer than kTcMarginBits (1.2503e-3 >= 1.05e-3 + 2 * 6.1e-5) to a midpoint is recomputed with the exact
-// chain and the exact rule, so every emitted code equals the code of the chain.
-constexpr uint32_t kTcMarginBits = 0x151f151fu;   // half2 {1.2503e-3, 1.2503e-3}
+// Decision margin of the tensor-core pass.  The rotation is first evaluated on the tensor cores with every
+// operand split into an fp16 high and low limb (x = xh + xl, p = ph + pl) and the three products xh ph + xh pl +
+// xl ph accumulated in fp32.  With |x_unit| <= 1 and |row of Pi| = 1 (so sum|x_i p_i| <= 1 by Cauchy-Schwarz) the
+// result differs from the fp32 FMA chain by at most
+//     2^-22 sum|x p|                       (the dropped xl pl term)
+//   + 2 * 2^-21.5 sum|x p| + 7e-7          (what the low limbs miss: 11 bits each, 2^-25 absolute when subnormal)
+//   + 24 * 2^-22 + 8 * 16 * 2^-23          (fp32 accumulation of 24 HMMA steps, generous)
+//   + 128 * 2^-24                          (the chain's own error)
+//   < 3e-5.
+// The decision itself runs in fp16 against fp16 midpoints of adjacent centroids: both roundings cost at most
+// 2^-14 each for |y| < 0.25 (every midpoint of the 2/3/4-bit codebooks is below 0.22).  A coordinate closer than
+// kTcMarginBits (1.6e-4 >= 3e-5 + 2 * 6.1e-5) to a midpoint is recomputed with the exact chain and the exact
+// rule, so every emitted code equals the code of the chain.
+constexpr uint32_t kTcMarginBits = 0x093f093fu;   // half2 {1.601e-4, 1.601e-4}
 
 // per-level constants of the fp16 decision: positive midpoints (padded with +inf) and the code offset
 struct LevelConst {
@@ -261,20 +264,21 @@ __device__ __forceinline__ void patch_code(uint32_t *__restrict__ row_words, int
 
 // One CTA serves one side (even blocks: keys, odd blocks: values) with two independent groups of 256
 // threads; each group walks over half tiles of 64 tokens with its own buffers and its own named barrier,
-// so the latency-bound steps of one group run under the arithmetic of the other.  The fp32 rotation of
-// the side (for the exact chains) and its fp16 copy (for the tensor cores) are shared by both groups.
+// so the latency-bound steps of one group run under the arithmetic of the other.  The fp16 high and low limbs
+// of the side's rotation (for the tensor cores) are shared by both groups; the exact chains read its fp32 rows
+// from global memory (a few dozen rows per item).
 // Per item: rows -> fp32 shared tile; norm (one ascending FMA chain per row, IEEE square root); IEEE
-// division; the 64x128x128 rotation on the tensor cores with fp16 operands; an fp16 decision per
+// division; the 64x128x128 rotation on the tensor cores (fp16 limb pairs, three products); an fp16 decision per
 // coordinate, packed straight into the row's bit stream in shared memory (a thread owns eight consecutive
 // coordinates of a row); every coordinate closer to a decision boundary than the tensor-core error bound
 // is queued and recomputed with the exact fp32 chain (ascending contraction index, one FMA per term) and
 // the exact nearest-centroid rule, then patched into the packed row -- so the codes are those of the
 // chain, bit for bit; copy-out.  The next item's rows, bit widths and slot bases are fetched into
 // registers under the decision step of the current one.
-constexpr int kQueueCap = 2048;   // queued coordinates per item; beyond that the whole item is redone exactly
-constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + kQRows * sizeof(double) + (size_t)kQRows * kLdH * 2 +
+constexpr int kQueueCap = 512;    // queued coordinates per item (about 30 are expected); beyond that the whole item is redone exactly
+constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + kQRows * sizeof(double) + 2 * (size_t)kQRows * kLdH * 2 +
                                    (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + (size_t)kQueueCap * 2;
-constexpr size_t kQuantKernelSmem = (size_t)(kD * kLd + 4 * 256) * sizeof(float) + (size_t)kD * kLdH * 2 + 3 * sizeof(LevelConst) +
+constexpr size_t kQuantKernelSmem = (size_t)(4 * 256) * sizeof(float) + 2 * (size_t)kD * kLdH * 2 + 3 * sizeof(LevelConst) +
                                     2 * kQuantGroupSmem;
 
 __device__ __forceinline__ void group_sync(int gid) {
@@ -284,17 +288,18 @@ __device__ __forceinline__ void group_sync(int gid) {
 template <int DT>
 __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    float *Pf = reinterpret_cast<float *>(smem_raw);                 // [128][kLd] fp32 rotation (exact chains)
-    float *cb = Pf + kD * kLd;                                       // [4][256]
-    __half *Ph = reinterpret_cast<__half *>(cb + 4 * 256);           // [128][kLdH] fp16 rotation, rows permuted
-    LevelConst *lc = reinterpret_cast<LevelConst *>(Ph + kD * kLdH); // [3] 2, 3, 4 bits
+    float *cb = reinterpret_cast<float *>(smem_raw);                 // [4][256]
+    __half *Ph = reinterpret_cast<__half *>(cb + 4 * 256);           // [128][kLdH] fp16 high limbs of the rotation, rows permuted
+    __half *Pl = Ph + kD * kLdH;                                     // [128][kLdH] fp16 low limbs
+    LevelConst *lc = reinterpret_cast<LevelConst *>(Pl + kD * kLdH); // [3] 2, 3, 4 bits
     const int gid = threadIdx.x >> 8, tid = threadIdx.x & 255;       // group, thread within the group
     unsigned char *gbase = reinterpret_cast<unsigned char *>(lc + 3) + (size_t)gid * kQuantGroupSmem;
     float *Xs = reinterpret_cast<float *>(gbase);                    // [64][kLd] fp32 rows, normalised in place
     float *nrm = Xs + kQRows * kLd;                                  // [64]
     double *rinv = reinterpret_cast<double *>(nrm + kQRows);         // [64] 1 / (norm + 1e-10) in fp64
-    __half *Xh = reinterpret_cast<__half *>(rinv + kQRows);          // [64][kLdH] fp16 normalised rows
-    int *cls = reinterpret_cast<int *>(Xh + kQRows * kLdH);          // [128]
+    __half *Xh = reinterpret_cast<__half *>(rinv + kQRows);          // [64][kLdH] fp16 high limbs of the normalised rows
+    __half *Xl = Xh + kQRows * kLdH;                                 // [64][kLdH] fp16 low limbs
+    int *cls = reinterpret_cast<int *>(Xl + kQRows * kLdH);          // [128]
     int *slot = cls + kTile;                                         // [128]
     int *wcnt = slot + kTile;                                        // [4][6]
     int *tbase = wcnt + 4 * kNumClasses;                             // [8] slot base of this plan tile per class
@@ -314,10 +319,14 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
         const int q = g >> 5, i4 = g & 31;
         const int j = (q & ~31) + 8 * ((q & 7) >> 1) + 2 * ((q >> 3) & 3) + (q & 1);
         const float4 f = *reinterpret_cast<const float4 *>(pi + j * kD + 4 * i4);
+        const __half2 h01 = __floats2half2_rn(f.x, f.y), h23 = __floats2half2_rn(f.z, f.w);
         __half2 *dst = reinterpret_cast<__half2 *>(Ph + q * kLdH + 4 * i4);
-        dst[0] = __floats2half2_rn(f.x, f.y);
-        dst[1] = __floats2half2_rn(f.z, f.w);
-        *reinterpret_cast<float4 *>(Pf + q * kLd + 4 * i4) = *reinterpret_cast<const float4 *>(pi + q * kD + 4 * i4);
+        dst[0] = h01;
+        dst[1] = h23;
+        const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+        __half2 *dlo = reinterpret_cast<__half2 *>(Pl + q * kLdH + 4 * i4);
+        dlo[0] = __floats2half2_rn(f.x - b01.x, f.y - b01.y);
+        dlo[1] = __floats2half2_rn(f.z - b23.x, f.w - b23.y);
     }
     for (int g = threadIdx.x; g < 4 * 256; g += 512) cb[g] = a.codebooks[g];
     if (threadIdx.x < 3 * 8) {
@@ -421,9 +430,14 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
                 v.z = __double2float_rn(__dmul_rn((double)v.z, ri));
                 v.w = __double2float_rn(__dmul_rn((double)v.w, ri));
                 *p = v;
+                const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
                 __half2 *hd = reinterpret_cast<__half2 *>(Xh + r * kLdH + 4 * i4);
-                hd[0] = __floats2half2_rn(v.x, v.y);
-                hd[1] = __floats2half2_rn(v.z, v.w);
+                hd[0] = h01;
+                hd[1] = h23;
+                const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+                __half2 *ld = reinterpret_cast<__half2 *>(Xl + r * kLdH + 4 * i4);
+                ld[0] = __floats2half2_rn(v.x - b01.x, v.y - b01.y);
+                ld[1] = __floats2half2_rn(v.z - b23.x, v.w - b23.y);
             }
             group_sync(gid);
             // ---- approximate rotation on the tensor cores: acc[mb][nb] = 16x8 block of X Pi^T
@@ -436,18 +450,28 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
                     for (int e = 0; e < 4; ++e) acc[mb][nb][e] = 0.f;
 #pragma unroll
             for (int ks = 0; ks < kD / 16; ++ks) {
-                uint32_t af[2][4], bf[2][4];
+                uint32_t ah[2][4], al[2][4], bh[2][4], bl[2][4];
+#pragma unroll
+                for (int mb = 0; mb < 2; ++mb) {
+                    const int off = (32 * wm + 16 * mb + (lane & 15)) * kLdH + 16 * ks + 8 * (lane >> 4);
+                    ldmatrix_x4(ah[mb], Xh + off);
+                    ldmatrix_x4(al[mb], Xl + off);
+                }
+#pragma unroll
+                for (int np = 0; np < 2; ++np) {
+                    const int off = (32 * wn + 16 * np + 8 * (lane >> 4) + (lane & 7)) * kLdH + 16 * ks + 8 * ((lane >> 3) & 1);
+                    ldmatrix_x4(bh[np], Ph + off);
+                    ldmatrix_x4(bl[np], Pl + off);
+                }
 #pragma unroll
                 for (int mb = 0; mb < 2; ++mb)
-                    ldmatrix_x4(af[mb], Xh + (32 * wm + 16 * mb + (lane & 15)) * kLdH + 16 * ks + 8 * (lane >> 4));
 #pragma unroll
-                for (int np = 0; np < 2; ++np)
-                    ldmatrix_x4(bf[np], Ph + (32 * wn + 16 * np + 8 * (lane >> 4) + (lane & 7)) * kLdH + 16 * ks + 8 * ((lane >> 3) & 1));
-#pragma unroll
-                for (int mb = 0; mb < 2; ++mb)
-#pragma unroll
-                    for (int nb = 0; nb < 4; ++nb)
-                        hmma_16816(acc[mb][nb], af[mb], bf[nb >> 1][2 * (nb & 1)], bf[nb >> 1][2 * (nb & 1) + 1]);
+                    for (int nb = 0; nb < 4; ++nb) {
+                        const int np = nb >> 1, o = 2 * (nb & 1);
+                        hmma_16816(acc[mb][nb], al[mb], bh[np][o], bh[np][o + 1]);
+                        hmma_16816(acc[mb][nb], ah[mb], bl[np][o], bl[np][o + 1]);
+                        hmma_16816(acc[mb][nb], ah[mb], bh[np][o], bh[np][o + 1]);
+                    }
             }
             group_sync(gid);   // every warp is done with Xh: the packed rows reuse its space
             prefetch(w + w_step);
@@ -548,11 +572,11 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
                 const int li = cls[h0 + r] - 1;
                 if (li < 0 || li > 3) continue;
                 const float4 *xr = reinterpret_cast<const float4 *>(Xs + r * kLd);
-                const float4 *pr = reinterpret_cast<const float4 *>(Pf + col * kLd);
+                const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);   // few entries: read through L2
                 float y = 0.0f;
 #pragma unroll 8
                 for (int i = 0; i < kD / 4; ++i) {
-                    const float4 xv = xr[i], pv = pr[i];
+                    const float4 xv = xr[i], pv = __ldg(pr + i);
                     y = fmaf(xv.x, pv.x, y);
                     y = fmaf(xv.y, pv.y, y);
                     y = fmaf(xv.z, pv.z, y);
