@@ -419,25 +419,37 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
             //      product is within 2^-52 of the quotient, while a quotient of two fp32 numbers is never closer
             //      than 2^-49 (relative) to a rounding boundary of fp32 and never on one, so the final rounding
             //      lands where the division's would.  fp32 result in place, fp16 copy for the tensor cores.
+            {
+                // all loads first, then the arithmetic, then the stores: the eight pieces of a thread are independent
+                constexpr int kPieces = kQRows * kD / 4 / 256;
+                float4 v[kPieces];
+                double ri[kPieces];
 #pragma unroll
-            for (int u = 0; u < kQRows * kD / 4 / 256; ++u) {
-                const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
-                const double ri = rinv[r];
-                float4 *p = reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4);
-                float4 v = *p;
-                v.x = __double2float_rn(__dmul_rn((double)v.x, ri));
-                v.y = __double2float_rn(__dmul_rn((double)v.y, ri));
-                v.z = __double2float_rn(__dmul_rn((double)v.z, ri));
-                v.w = __double2float_rn(__dmul_rn((double)v.w, ri));
-                *p = v;
-                const __half2 h01 = __floats2half2_rn(v.x, v.y), h23 = __floats2half2_rn(v.z, v.w);
-                __half2 *hd = reinterpret_cast<__half2 *>(Xh + r * kLdH + 4 * i4);
-                hd[0] = h01;
-                hd[1] = h23;
-                const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
-                __half2 *ld = reinterpret_cast<__half2 *>(Xl + r * kLdH + 4 * i4);
-                ld[0] = __floats2half2_rn(v.x - b01.x, v.y - b01.y);
-                ld[1] = __floats2half2_rn(v.z - b23.x, v.w - b23.y);
+                for (int u = 0; u < kPieces; ++u) {
+                    const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
+                    v[u] = *reinterpret_cast<const float4 *>(Xs + r * kLd + 4 * i4);
+                    ri[u] = rinv[r];
+                }
+#pragma unroll
+                for (int u = 0; u < kPieces; ++u) {
+                    v[u].x = __double2float_rn(__dmul_rn((double)v[u].x, ri[u]));
+                    v[u].y = __double2float_rn(__dmul_rn((double)v[u].y, ri[u]));
+                    v[u].z = __double2float_rn(__dmul_rn((double)v[u].z, ri[u]));
+                    v[u].w = __double2float_rn(__dmul_rn((double)v[u].w, ri[u]));
+                }
+#pragma unroll
+                for (int u = 0; u < kPieces; ++u) {
+                    const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
+                    *reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4) = v[u];
+                    const __half2 h01 = __floats2half2_rn(v[u].x, v[u].y), h23 = __floats2half2_rn(v[u].z, v[u].w);
+                    const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
+                    uint2 hw, lw;
+                    hw.x = h2u(h01); hw.y = h2u(h23);
+                    lw.x = h2u(__floats2half2_rn(v[u].x - b01.x, v[u].y - b01.y));
+                    lw.y = h2u(__floats2half2_rn(v[u].z - b23.x, v[u].w - b23.y));
+                    *reinterpret_cast<uint2 *>(Xh + r * kLdH + 4 * i4) = hw;
+                    *reinterpret_cast<uint2 *>(Xl + r * kLdH + 4 * i4) = lw;
+                }
             }
             group_sync(gid);
             // ---- approximate rotation on the tensor cores: acc[mb][nb] = 16x8 block of X Pi^T
