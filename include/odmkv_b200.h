@@ -201,7 +201,8 @@ int odmkv_export_positions(const odmkv_chunk *chunk, int class_idx, const int32_
  *   tail_k/tail_v [B, H, tail_cap, 128] cache dtype (may be NULL when tail_len = 0): the first
  *   tail_len tokens of every (b, h) are attended exactly
  *   lse  [B, H*G] fp32 out or NULL (log-sum-exp of the scaled logits)
- *   n_splits: CTAs per (b, h); 0 lets the library choose.
+ *   n_splits: partial-result slots per (b, h), at least 1 (odmkv_decode_default_splits gives a good value):
+ *   odmkv_decode_attn runs that many CTAs per (b, h), at most 64.
  */
 size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits);
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head);
@@ -213,7 +214,9 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
 
 /* Tensor-core variant of odmkv_decode_attn (same contract and arguments): the 2-, 3- and 4-bit banks
  * are consumed with mma.sync m16n8k16 tiles straight from the tile layout; 8-bit, exact and tail
- * tokens take the CUDA-core kernel in a second launch; n_splits may go up to 128.
+ * tokens take the CUDA-core kernel in a second launch on a forked stream.  The kernel is persistent: it picks
+ * its own grid (one CTA pair per SM, shared evenly by the (b, h) units) such that at most n_splits CTAs overlap one
+ * unit; n_splits may go up to 128 and only bounds the workspace.
  *   lut_scales: host float[3] or NULL (= 1.0): per level a factor s such that fp16(c * s) carries the
  *   centroids of the 2-, 3-, 4-bit codebooks with less rounding error; divided out again in fp32. */
 int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
