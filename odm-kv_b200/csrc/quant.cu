@@ -149,7 +149,9 @@ __device__ inline void store_linear_codes(const uint8_t *__restrict__ row, int l
     pack_lane_codes(row, li, rows + (size_t)slot * 16 * qbits(li), lane, lane);
 }
 
-constexpr int kQRows = 64;   // tokens per work item of quantize_kernel: one half of a plan tile
+constexpr int kQRows = 32;      // tokens per work item of quantize_kernel: a quarter of a plan tile
+constexpr int kGroups = 4;      // independent groups per CTA
+constexpr int kGroupThreads = 128;
 constexpr int kLdH = 136;    // padded fp16 row stride (272 bytes: conflict-free ldmatrix rows)
 
 // Decision margin of the tensor-core pass.  The rotation is first evaluated on the tensor cores with every
@@ -206,7 +208,7 @@ __device__ __forceinline__ void hmma_16816(float (&d)[4], const uint32_t (&a)[4]
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// the 16-byte pieces of a half tile that one thread moves (64 rows of 128 elements, 256 threads)
+// the 16-byte pieces of a quarter tile that one thread moves (32 rows of 128 elements, 128 threads)
 template <int DT>
 struct RawPieces {
     static constexpr int kN = (DT == kF32) ? 8 : 4;
@@ -220,7 +222,7 @@ __device__ __forceinline__ void load_pieces(const void *__restrict__ src, size_t
                                                         row0 * sizeof(typename Elem<DT>::T));
 #pragma unroll
     for (int u = 0; u < RawPieces<DT>::kN; ++u) {
-        const int g = tid + 256 * u, row = g / kPerRow;
+        const int g = tid + kGroupThreads * u, row = g / kPerRow;
         r.v[u] = row < rows_left ? __ldg(base + g) : make_uint4(0u, 0u, 0u, 0u);
     }
 }
@@ -230,7 +232,7 @@ __device__ __forceinline__ void store_pieces_f32(const RawPieces<DT> &r, int tid
     constexpr int kPerRow = (DT == kF32) ? 32 : 16;
 #pragma unroll
     for (int u = 0; u < RawPieces<DT>::kN; ++u) {
-        const int g = tid + 256 * u, row = g / kPerRow, pc = g % kPerRow;
+        const int g = tid + kGroupThreads * u, row = g / kPerRow, pc = g % kPerRow;
         const uint32_t w[4] = {r.v[u].x, r.v[u].y, r.v[u].z, r.v[u].w};
         if constexpr (DT == kF32) {
             *reinterpret_cast<float4 *>(Xs + row * kLd + 4 * pc) =
@@ -262,8 +264,8 @@ __device__ __forceinline__ void patch_code(uint32_t *__restrict__ row_words, int
     }
 }
 
-// One CTA serves one side (even blocks: keys, odd blocks: values) with two independent groups of 256
-// threads; each group walks over half tiles of 64 tokens with its own buffers and its own named barrier,
+// One CTA serves one side (even blocks: keys, odd blocks: values) with four independent groups of 128
+// threads; each group walks over quarter tiles of 32 tokens with its own buffers and its own named barrier,
 // so the latency-bound steps of one group run under the arithmetic of the other.  The fp16 high and low limbs
 // of the side's rotation (for the tensor cores) are shared by both groups; the exact chains read its fp32 rows
 // from global memory (a few dozen rows per item).
@@ -279,10 +281,10 @@ constexpr int kQueueCap = 512;    // queued coordinates per item (about 30 are e
 constexpr size_t kQuantGroupSmem = (size_t)(kQRows * kLd + kQRows) * sizeof(float) + kQRows * sizeof(double) + 2 * (size_t)kQRows * kLdH * 2 +
                                    (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + (size_t)kQueueCap * 2;
 constexpr size_t kQuantKernelSmem = (size_t)(4 * 256) * sizeof(float) + 2 * (size_t)kD * kLdH * 2 + 3 * sizeof(LevelConst) +
-                                    2 * kQuantGroupSmem;
+                                    kGroups * kQuantGroupSmem;
 
 __device__ __forceinline__ void group_sync(int gid) {
-    asm volatile("bar.sync %0, 256;\n" ::"r"(gid + 1) : "memory");
+    asm volatile("bar.sync %0, 128;\n" ::"r"(gid + 1) : "memory");
 }
 
 template <int DT>
@@ -292,20 +294,20 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     __half *Ph = reinterpret_cast<__half *>(cb + 4 * 256);           // [128][kLdH] fp16 high limbs of the rotation, rows permuted
     __half *Pl = Ph + kD * kLdH;                                     // [128][kLdH] fp16 low limbs
     LevelConst *lc = reinterpret_cast<LevelConst *>(Pl + kD * kLdH); // [3] 2, 3, 4 bits
-    const int gid = threadIdx.x >> 8, tid = threadIdx.x & 255;       // group, thread within the group
+    const int gid = threadIdx.x >> 7, tid = threadIdx.x & 127;       // group, thread within the group
     unsigned char *gbase = reinterpret_cast<unsigned char *>(lc + 3) + (size_t)gid * kQuantGroupSmem;
-    float *Xs = reinterpret_cast<float *>(gbase);                    // [64][kLd] fp32 rows, normalised in place
-    float *nrm = Xs + kQRows * kLd;                                  // [64]
-    double *rinv = reinterpret_cast<double *>(nrm + kQRows);         // [64] 1 / (norm + 1e-10) in fp64
-    __half *Xh = reinterpret_cast<__half *>(rinv + kQRows);          // [64][kLdH] fp16 high limbs of the normalised rows
-    __half *Xl = Xh + kQRows * kLdH;                                 // [64][kLdH] fp16 low limbs
+    float *Xs = reinterpret_cast<float *>(gbase);                    // [32][kLd] fp32 rows, normalised in place
+    float *nrm = Xs + kQRows * kLd;                                  // [32]
+    double *rinv = reinterpret_cast<double *>(nrm + kQRows);         // [32] 1 / (norm + 1e-10) in fp64
+    __half *Xh = reinterpret_cast<__half *>(rinv + kQRows);          // [32][kLdH] fp16 high limbs of the normalised rows
+    __half *Xl = Xh + kQRows * kLdH;                                 // [32][kLdH] fp16 low limbs
     int *cls = reinterpret_cast<int *>(Xl + kQRows * kLdH);          // [128]
     int *slot = cls + kTile;                                         // [128]
     int *wcnt = slot + kTile;                                        // [4][6]
     int *tbase = wcnt + 4 * kNumClasses;                             // [8] slot base of this plan tile per class
     int *flags = tbase + 8;                                          // [0] any quantised row, [1] queue length
     uint16_t *queue = reinterpret_cast<uint16_t *>(flags + 8);       // [kQueueCap] coordinates to recompute
-    unsigned char *PK = reinterpret_cast<unsigned char *>(Xh);       // [64][kLdC] packed rows (after the product)
+    unsigned char *PK = reinterpret_cast<unsigned char *>(Xh);       // [32][kLdC] packed rows (after the product)
 
     const int lane = tid & 31, warp = tid >> 5;
     const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
@@ -341,16 +343,16 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
         }
     }
 
-    const long long n_work = (long long)BH * a.ntiles * 2;
-    const long long w_step = (long long)(gridDim.x >> 1) * 2;   // two groups per CTA, half of the CTAs per side
-    const long long w_first = (long long)(blockIdx.x >> 1) * 2 + gid;
+    const long long n_work = (long long)BH * a.ntiles * 4;
+    const long long w_step = (long long)(gridDim.x >> 1) * kGroups;   // four groups per CTA, half of the CTAs per side
+    const long long w_first = (long long)(blockIdx.x >> 1) * kGroups + gid;
     // fetched ahead: rows, this thread's bit width (threads < 128) and slot base (threads < 6)
     RawPieces<DT> raw;
     int pf_bits = 0, pf_base = 0;
     auto prefetch = [&](long long w) {
         if (w >= n_work) return;
-        const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
-        const int tile = rem >> 1, half = rem & 1;
+        const int bh = (int)(w / (4 * a.ntiles)), rem = (int)(w % (4 * a.ntiles));
+        const int tile = rem >> 2, half = rem & 3;
         const int t0 = tile * kTile, h0 = half * kQRows;
         if (t0 + h0 >= T) return;
         load_pieces<DT>(src, ((size_t)bh * T + t0 + h0) * kD, T - t0 - h0, tid, raw);
@@ -361,12 +363,12 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     prefetch(w_first);
     __syncthreads();
 
-    // tensor-core tiling: warp (wm, wn) owns rows [32 wm, +32) and columns [32 wn, +32)
-    const int wm = warp & 1, wn = warp >> 1, g8 = lane >> 2, t4 = lane & 3;
+    // tensor-core tiling: warp wn owns the item's 32 rows and columns [32 wn, +32)
+    const int wm = 0, wn = warp, g8 = lane >> 2, t4 = lane & 3;
 
     for (long long w = w_first; w < n_work; w += w_step) {
-        const int bh = (int)(w / (2 * a.ntiles)), rem = (int)(w % (2 * a.ntiles));
-        const int tile = rem >> 1, half = rem & 1;
+        const int bh = (int)(w / (4 * a.ntiles)), rem = (int)(w % (4 * a.ntiles));
+        const int tile = rem >> 2, half = rem & 3;
         const int t0 = tile * kTile, h0 = half * kQRows;
         if (t0 + h0 >= T) { prefetch(w + w_step); continue; }
         if (tid == 0) { flags[0] = 0; flags[1] = 0; }
@@ -389,14 +391,14 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
             if (c >= 0) {
                 s = tbase[c] + rank;
                 for (int ww = 0; ww < warp; ++ww) s += wcnt[ww * kNumClasses + c];
-                if (c >= 1 && c <= 4 && (tid >> 6) == half) flags[0] = 1;
+                if (c >= 1 && c <= 4 && (tid >> 5) == half) flags[0] = 1;
             }
             cls[tid] = c;
             slot[tid] = s;
         }
         // ---- fp32 norm: one ascending FMA chain of squares, IEEE square root
-        if (tid >= 192) {
-            const int r = tid - 192;
+        if (tid >= kGroupThreads - kQRows) {
+            const int r = tid - (kGroupThreads - kQRows);
             float acc = 0.0f;
             const float *xr = Xs + r * kLd;
 #pragma unroll 8
@@ -421,12 +423,12 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
             //      lands where the division's would.  fp32 result in place, fp16 copy for the tensor cores.
             {
                 // all loads first, then the arithmetic, then the stores: the eight pieces of a thread are independent
-                constexpr int kPieces = kQRows * kD / 4 / 256;
+                constexpr int kPieces = kQRows * kD / 4 / kGroupThreads;
                 float4 v[kPieces];
                 double ri[kPieces];
 #pragma unroll
                 for (int u = 0; u < kPieces; ++u) {
-                    const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
+                    const int g = tid + kGroupThreads * u, r = g >> 5, i4 = g & 31;
                     v[u] = *reinterpret_cast<const float4 *>(Xs + r * kLd + 4 * i4);
                     ri[u] = rinv[r];
                 }
@@ -439,7 +441,7 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
                 }
 #pragma unroll
                 for (int u = 0; u < kPieces; ++u) {
-                    const int g = tid + 256 * u, r = g >> 5, i4 = g & 31;
+                    const int g = tid + kGroupThreads * u, r = g >> 5, i4 = g & 31;
                     *reinterpret_cast<float4 *>(Xs + r * kLd + 4 * i4) = v[u];
                     const __half2 h01 = __floats2half2_rn(v[u].x, v[u].y), h23 = __floats2half2_rn(v[u].z, v[u].w);
                     const float2 b01 = __half22float2(h01), b23 = __half22float2(h23);
@@ -579,7 +581,7 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
             const int qn = flags[1];
             const bool redo_all = qn > kQueueCap;   // queue overflow: every coordinate of the item is exact work
             const int n_fix = redo_all ? kQRows * kD : qn;
-            for (int e = tid; e < n_fix; e += 256) {
+            for (int e = tid; e < n_fix; e += kGroupThreads) {
                 const int r = redo_all ? (e >> 7) : (queue[e] >> 7), col = redo_all ? (e & 127) : (queue[e] & 127);
                 const int li = cls[h0 + r] - 1;
                 if (li < 0 || li > 3) continue;
@@ -990,7 +992,7 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
             off += 2 * bytes;
         }
     }
-    long long n_work = (long long)BH * a.ntiles * 2;   // half tiles; each is visited by a key group and a value group
+    long long n_work = (long long)BH * a.ntiles * 4;   // quarter tiles; each is visited by a key group and a value group
     int grid = 2 * (int)((n_work + 1) / 2 < num_sms() / 2 ? (n_work + 1) / 2 : num_sms() / 2);
     dim3 pad_grid(BH, kNumClasses);
     cudaError_t e;
