@@ -381,6 +381,28 @@ def run_ours(args):
         e2e_step()
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    # the same end-to-end step (host query in, host output out) as one CUDA graph: copy node, the decode call's
+    # launches, copy node
+    e2e_graph_ms = None
+    if not args.eager:
+        try:
+            eg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(eg, capture_error_mode="thread_local"):
+                q_dev.copy_(q_host, non_blocking=True)
+                eo = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+                out_host.copy_(eo, non_blocking=True)
+            for _ in range(3):
+                eg.replay()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                eg.replay()
+            torch.cuda.synchronize()
+            e2e_graph_ms = (time.perf_counter() - t0) * 1e3
+        except Exception:
+            e2e_graph_ms = None
     # keep the same decode load running until the sampler has seen it for a while
     t_load = time.perf_counter()
     while rank == 0 and time.perf_counter() - t_load < 0.6:
@@ -433,7 +455,9 @@ def run_ours(args):
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,
                      "frac_of_8000": achieved / 8000.0, "other_kernels_ms": parts_ms},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
-                "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps},
+                "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps,
+                "call": "eager tensor-level call per step (host wall clock)",
+                "graph_replay_ms_per_step": None if e2e_graph_ms is None else e2e_graph_ms / args.steps},
         "gpu_launches": 4 * args.steps,
         "gather_per_step": None if tp_ms is None else {
             "schedule": "KV heads of one layer sharded over the ranks: outputs all-gathered (NCCL) after every step",
