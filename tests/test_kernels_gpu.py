@@ -97,7 +97,8 @@ def test_quantize_pack_rejects_bad_input(pkg, cuda):
 
 
 @pytest.mark.parametrize("dtype,B,H,G,T", [(torch.float16, 1, 2, 4, 320), (torch.bfloat16, 2, 2, 7, 200), (torch.float16, 1, 8, 4, 4096),
-                                           (torch.float32, 1, 1, 1, 6), (torch.float16, 2, 4, 8, 777), (torch.float16, 1, 2, 4, 3)])
+                                           (torch.float32, 1, 1, 1, 6), (torch.float16, 2, 4, 8, 777), (torch.float16, 1, 2, 4, 3),
+                                           (torch.float16, 1, 2, 12, 300), (torch.float32, 1, 2, 4, 1500), (torch.bfloat16, 1, 1, 8, 5000)])
 def test_score_prefill_matches_oracle(pkg, orc, cuda, dtype, B, H, G, T):
     K16, V16, Qw16, _ = orc.synth_inputs(H, T, G, 128, 64, 3, B)
     Kt, Vt = torch.from_numpy(K16).to(dtype), torch.from_numpy(V16).to(dtype)
