@@ -62,6 +62,9 @@ const char *odmkv_status_string(int status);
  * T <= n_sink gives all ones (kvquant/scorer.py:388-389).
  */
 size_t odmkv_score_workspace_bytes(int B, int H, int G, int T);
+/* Offset (bytes) inside the score workspace of a 32-bit status word: 0 after a clean call, 1 when a bounded wait of
+ * a sweep on one of its bulk copies expired (scores invalid).  No counterpart in the reference. */
+size_t odmkv_score_status_offset(int B, int H, int G, int T, int n_sink);
 int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu, int B, int H, int G, int T,
                         int n_sink, float eps, float *scores, void *workspace, size_t workspace_bytes,
                         void *stream);

@@ -69,6 +69,7 @@ _PROTOTYPES = {
     "odmkv_abi_version": (c_int, []),
     "odmkv_status_string": (c_char_p, [c_int]),
     "odmkv_score_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "odmkv_score_status_offset": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "odmkv_score_prefill": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_void_p, c_void_p, c_size_t, c_void_p]),
     "odmkv_score_with_attn": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]),

@@ -712,6 +712,16 @@ size_t odmkv_score_workspace_bytes(int B, int H, int G, int T) {
     return score_ws_layout(B, H, G, T, 0, nullptr, nullptr) + 256;
 }
 
+// byte offset, inside a score workspace, of the 32-bit word that a sweep sets to 1 when one of its bounded waits
+// on a bulk copy expired (the scores of that call are then invalid); 0 after a clean call
+size_t odmkv_score_status_offset(int B, int H, int G, int T, int n_sink) {
+    if (B <= 0 || H <= 0 || G <= 0 || T <= n_sink) return 0;
+    ScoreWs ws;
+    unsigned char *base = reinterpret_cast<unsigned char *>(256);   // any non-null base: only differences are used
+    score_ws_layout(B, H, G, T, n_sink, &ws, base);
+    return (size_t)(reinterpret_cast<unsigned char *>(ws.status) - base);
+}
+
 int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu, int B, int H, int G, int T,
                         int n_sink, float eps, float *scores, void *workspace, size_t workspace_bytes,
                         void *stream) {

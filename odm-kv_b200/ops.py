@@ -13,7 +13,7 @@ import torch
 
 from . import _lib
 from ._lib import (CLASS_BITS, CODE_BYTES, HEAD_DIM, NUM_CLASSES, NUM_QLEVELS, QLEVEL_BITS, REF_CODE_BYTES, AllocReport,
-                   Chunk, check, dtype_code, lib, ptr, require_cuda, stream_ptr)
+                   Chunk, OdmkvError, check, dtype_code, lib, ptr, require_cuda, stream_ptr)
 from .codebook import codebook_f32
 
 
@@ -48,8 +48,10 @@ def codebook_table(device, dim: int = HEAD_DIM) -> torch.Tensor:
 # scorer
 # ---------------------------------------------------------------------------------------------
 
-def score_prefill(K: torch.Tensor, V: torch.Tensor, mu: torch.Tensor, n_sink: int = 4, eps: float = 1e-2) -> torch.Tensor:
-    """K, V [B, H, T, 128] (fp16/bf16/fp32), mu [B, H*G, 128] fp32 -> scores [B, H, T] fp32."""
+def score_prefill(K: torch.Tensor, V: torch.Tensor, mu: torch.Tensor, n_sink: int = 4, eps: float = 1e-2,
+                  check_status: bool = False) -> torch.Tensor:
+    """K, V [B, H, T, 128] (fp16/bf16/fp32), mu [B, H*G, 128] fp32 -> scores [B, H, T] fp32.
+    ``check_status`` synchronises and raises if a sweep reported an expired wait on one of its bulk copies."""
     require_cuda(K, "keys")
     if K.shape != V.shape or K.dim() != 4 or K.shape[-1] != HEAD_DIM:
         raise ValueError(f"expected keys/values [B, H, T, {HEAD_DIM}], got {tuple(K.shape)} / {tuple(V.shape)}")
@@ -64,6 +66,10 @@ def score_prefill(K: torch.Tensor, V: torch.Tensor, mu: torch.Tensor, n_sink: in
     ws = _ws(nbytes, K.device)
     check(lib().odmkv_score_prefill(ptr(K), ptr(V), dtype_code(K.dtype), ptr(mu), B, H, G, T, int(n_sink), float(eps),
                                     ptr(scores), ptr(ws), ws.numel(), stream_ptr(K.device)), "odmkv_score_prefill")
+    if check_status and T > n_sink:
+        off = lib().odmkv_score_status_offset(B, H, G, T, int(n_sink))
+        if int(ws[off:off + 4].view(torch.int32).item()) != 0:
+            raise OdmkvError("odmkv_score_prefill: a bounded wait on a bulk copy expired; the scores are invalid")
     return scores
 
 

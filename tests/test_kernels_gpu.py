@@ -109,6 +109,15 @@ def test_score_prefill_matches_oracle(pkg, orc, cuda, dtype, B, H, G, T):
     assert rel.max() < 1e-4, rel.max()   # tolerance: 1e-4 relative on scores
 
 
+def test_score_status_word_is_clean(pkg, orc, cuda):
+    """The sweeps wait on their bulk copies with a bound and report an expired wait through a status word."""
+    g = torch.Generator().manual_seed(5)
+    K = torch.randn(2, 2, 3000, 128, generator=g).half().to(cuda)
+    V = torch.randn(2, 2, 3000, 128, generator=g).half().to(cuda)
+    mu = torch.randn(2, 8, 128, generator=g).to(cuda)
+    pkg.ops.score_prefill(K, V, mu, 4, 1e-2, check_status=True)   # raises when the word is set
+
+
 def test_score_prefill_matches_golden_reference(pkg, cuda, golden):
     g = golden["small_g7_b2"]
     got = pkg.ops.score_prefill(torch.from_numpy(g["K"]).to(cuda), torch.from_numpy(g["V"]).to(cuda),
