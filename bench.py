@@ -46,7 +46,6 @@ def parse():
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--group", type=int, default=4)
     ap.add_argument("--target-bits", type=float, default=2.0)
-    ap.add_argument("--decode-impl", default="auto")
     ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
@@ -276,7 +275,7 @@ def run_ours(args):
     q_steps = [qd.clone() for _ in range(2)]
 
     def step(i):
-        return ops.decode_attn(q_steps[i & 1], [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+        return ops.decode_attn(q_steps[i & 1], [chunk], pi_k, pi_v, n_splits=n_splits)
 
     # clocks are sampled from the warm-up through the end-to-end loop: the timed region alone lasts only
     # a few milliseconds, less than one nvidia-smi sampling period
@@ -298,7 +297,7 @@ def run_ours(args):
             graph = torch.cuda.CUDAGraph()
             # thread-local capture mode: other threads (the NCCL watchdog under torchrun) may keep making CUDA calls
             with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                g_out = ops.decode_attn(gq, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+                g_out = ops.decode_attn(gq, [chunk], pi_k, pi_v, n_splits=n_splits)
             for _ in range(3):
                 graph.replay()
             torch.cuda.synchronize()
@@ -368,7 +367,7 @@ def run_ours(args):
 
     def e2e_step():
         q_dev.copy_(q_host, non_blocking=True)
-        o = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+        o = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits)
         out_host.copy_(o, non_blocking=True)
 
     for _ in range(3):
@@ -389,7 +388,7 @@ def run_ours(args):
             eg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(eg, capture_error_mode="thread_local"):
                 q_dev.copy_(q_host, non_blocking=True)
-                eo = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits, impl=args.decode_impl)
+                eo = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits)
                 out_host.copy_(eo, non_blocking=True)
             for _ in range(3):
                 eg.replay()
@@ -449,7 +448,7 @@ def run_ours(args):
                    "timing": "CUDA events on the launching stream, max over ranks; per-kernel times from a second, eager pass of the same steps",
                    "level_counts": {str(b): int(c) for b, c in zip(LEVELS, cnt)},
                    "stored_token_heads": stored, "bytes_per_step_per_rank": bytes_per_step,
-                   "decode_impl": args.decode_impl, "n_splits": n_splits,
+                   "n_splits": n_splits,
                    "multi_gpu": "each rank holds its own (layer, sample, KV head) units: no exchange inside a step, outputs all-gathered once after the timed steps" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,

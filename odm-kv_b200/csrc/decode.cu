@@ -363,12 +363,12 @@ using namespace odmkv;
 extern "C" {
 
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
-    // Partial slots per (sample, KV head) that let the tensor-core kernel run one CTA pair per SM of a
-    // 148-SM device: the CTAs that can overlap one unit, plus one.  The plain kernel uses the same number of
+    // Partial slots per (sample, KV head) that let the tensor-core kernel run four workers per SM of a
+    // 148-SM device: the workers that can overlap one unit, plus one.  The plain kernel uses the same number of
     // equal splits (at most 64), shortened for short contexts.
     if (B <= 0 || H <= 0) return 1;
     const long long BH = (long long)B * H;
-    long long n = (2 * 148 + BH - 1) / BH + 1;
+    long long n = (4 * 148 + BH - 1) / BH + 1;
     const long long by_len = (max_tokens_per_head + 255) / 256 + 1;
     if (n > by_len) n = by_len;
     if (n < 2) n = 2;
@@ -380,6 +380,12 @@ int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
 size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits) {
     if (B <= 0 || H <= 0 || G <= 0 || n_splits <= 0) return 0;
     return decode_ws_layout(B, H, G, n_splits + 8, nullptr, nullptr) + 256;
+}
+
+// the status word is the first word of the workspace, whatever the sizes
+size_t odmkv_decode_status_offset(int B, int H, int G, int n_splits) {
+    (void)B; (void)H; (void)G; (void)n_splits;
+    return 0;
 }
 
 int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,

@@ -363,32 +363,17 @@ def export_exact_rows(ch: PackedChunk) -> Tuple[torch.Tensor, torch.Tensor, torc
 # decode attention
 # ---------------------------------------------------------------------------------------------
 
-_LUT_SCALES = None
-
-
-def lut_scales():
-    """Per level (2, 3, 4 bits) a factor s in [1, 2) that minimises the worst relative error of
-    fp16(c * s) / s over the level's centroids; the tensor-core kernel stores fp16(c * s) in its tables."""
-    global _LUT_SCALES
-    if _LUT_SCALES is None:
-        cand = np.linspace(1.0, 2.0, 40001, dtype=np.float64)[:-1]
-        best = []
-        for b in QLEVEL_BITS[:3]:
-            c = codebook_f32(b).astype(np.float64)
-            prod = (c[None, :] * cand[:, None]).astype(np.float32)
-            back = prod.astype(np.float16).astype(np.float64) / cand[:, None]
-            err = np.abs(back - c[None, :]) / np.abs(c[None, :])
-            best.append(float(np.float32(cand[int(np.argmin(err.max(axis=1)))])))
-        _LUT_SCALES = (ctypes.c_float * 3)(*best)
-    return _LUT_SCALES
-
-
 def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tensor, pi_v: torch.Tensor,
                 tail_k: Optional[torch.Tensor] = None, tail_v: Optional[torch.Tensor] = None, tail_len: int = 0,
                 scale: Optional[float] = None, n_splits: int = 0, out_dtype: Optional[torch.dtype] = None,
-                return_lse: bool = False, impl: str = "auto", cache_dtype: Optional[torch.dtype] = None):
+                return_lse: bool = False, cache_dtype: Optional[torch.dtype] = None, plain: bool = False,
+                check_status: bool = False):
     """q [B, H*G, 128] -> out [B, H*G, 128]: softmax(q K_hat^T scale) V_hat over every token stored in
-    ``chunks`` plus the first ``tail_len`` tokens of the dense tail [B, H, cap, 128]."""
+    ``chunks`` plus the first ``tail_len`` tokens of the dense tail [B, H, cap, 128].
+
+    Calls ``odmkv_decode_attn_mma`` (tensor cores for the 2- and 3-bit banks).  ``plain=True`` calls
+    ``odmkv_decode_attn`` instead, the CUDA-core reader of every level that the tests use as a second opinion.
+    ``check_status`` synchronises and raises when a bounded device-side wait of the tensor-core kernel expired."""
     require_cuda(q, "query")
     if q.dim() != 3 or q.shape[-1] != HEAD_DIM:
         raise ValueError(f"expected query [B, Hq, {HEAD_DIM}], got {tuple(q.shape)}")
@@ -413,7 +398,7 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
     if n_splits <= 0:
         per_head = sum(c.stored_tokens() for c in chunks) // max(B * H, 1) + tail_len
         n_splits = L.odmkv_decode_default_splits(B, H, per_head)
-    if impl in ("v1", "cuda_core"):
+    if plain:
         n_splits = min(n_splits, 64)
     out = torch.empty(B, Hq, HEAD_DIM, dtype=out_dtype or q.dtype, device=dev)
     lse = torch.empty(B, Hq, dtype=torch.float32, device=dev) if return_lse else None
@@ -426,10 +411,12 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
     common = (ptr(q), dtype_code(q.dtype), arr, len(chunks), dtype_code(cdt), ptr(tail_k), ptr(tail_v), int(tail_len), int(cap),
               ptr(pi_k), ptr(pi_v), ptr(codebook_table(dev)), B, H, G, scale, ptr(out), dtype_code(out.dtype), ptr(lse),
               int(n_splits), ptr(ws), ws.numel())
-    if impl in ("auto", "mma"):
-        check(L.odmkv_decode_attn_mma(*common, lut_scales(), stream_ptr(dev)), "odmkv_decode_attn_mma")
-    elif impl in ("v1", "cuda_core"):
+    if plain:
         check(L.odmkv_decode_attn(*common, stream_ptr(dev)), "odmkv_decode_attn")
     else:
-        raise ValueError(f"unknown decode implementation {impl!r}")
+        check(L.odmkv_decode_attn_mma(*common, stream_ptr(dev)), "odmkv_decode_attn_mma")
+        if check_status:
+            off = L.odmkv_decode_status_offset(B, H, G, int(n_splits))
+            if int(ws[off:off + 4].view(torch.int32).item()) != 0:
+                raise OdmkvError("odmkv_decode_attn_mma: a bounded device-side wait expired; the output is invalid")
     return (out, lse) if return_lse else out

@@ -277,7 +277,7 @@ class TurboQuantAdaptiveKVCacheState:
         return mp[:, 0], mp[:, 1], mp[:, 2]
 
     def decode_attention(self, query: torch.Tensor, scale: Optional[float] = None, pending_k=None, pending_v=None,
-                         out_dtype=None, impl: str = "auto") -> torch.Tensor:
+                         out_dtype=None) -> torch.Tensor:
         """softmax(q K_hat^T scale) V_hat over the stored cache for one query per head.
         query [B, Hq, d]; optional pending_k/v [B, H, t, d] are attended as well (tokens of the running
         forward pass that have not been appended yet).  Returns [B, Hq, d]."""
@@ -289,7 +289,7 @@ class TurboQuantAdaptiveKVCacheState:
         if len(self.chunks) > ops._lib.MAX_CHUNKS:
             raise ops._lib.OdmkvError(f"more than {ops._lib.MAX_CHUNKS} chunks: compact the cache first")
         return ops.decode_attn(query, self.chunks, self.pi_k, self.pi_v, tail_k=self.tail_k, tail_v=self.tail_v,
-                               tail_len=tail_len, scale=scale, out_dtype=out_dtype, impl=impl, cache_dtype=self.dtype)
+                               tail_len=tail_len, scale=scale, out_dtype=out_dtype, cache_dtype=self.dtype)
 
     def packed_bytes(self) -> int:
         return sum(c.packed_bytes() for c in self.chunks) + \
