@@ -43,8 +43,10 @@ constexpr int kTileSlots = kPlaneTile;         // 128 tokens per tile
 constexpr int kTmemCols = 512;
 constexpr int kWgCols = 128;                   // per worker: A [0, 64), D keys [64, 96), D values [96, 128)
 constexpr int kColDK = 64, kColDV = 96;
-constexpr unsigned kUmmaPolls = 1u << 20;
+constexpr unsigned kUmmaPolls = 1u << 12;       // polls per wait; each may suspend the thread for up to kSuspendNs
+constexpr unsigned kSuspendNs = 1000000u;
 constexpr float kNegBig = -1.0e30f;
+constexpr int kProducerThread = 96;            // lane 0 of the worker's last warp issues the bulk copies (warp 0 issues the products)
 constexpr int kMaxTcClass = 2;                 // classes 1 (2-bit) and 2 (3-bit) take this kernel
 constexpr int kSlotBytes = 3 * 4096 + 1024;    // largest tile: 3-bit keys + values (2 x 6144) + two norm rows
 
@@ -118,8 +120,8 @@ __host__ __device__ constexpr uint32_t idesc_i8(int N, bool b_signed, bool b_mn_
 
 __device__ __forceinline__ bool mbar_poll(uint32_t bar, unsigned parity) {
     uint32_t ok;
-    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
     return ok != 0;
 }
 
@@ -131,6 +133,13 @@ __device__ __forceinline__ void mbar_wait_or_abort(uint32_t bar, unsigned parity
         if (mbar_poll(bar, parity)) return;
     *abort_flag = 1;
     atomicExch(status, 1u);
+}
+
+// one lane of a converged warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n.reg .pred P1;\nelect.sync _|P1, 0xffffffff;\nselp.u32 %0, 1, 0, P1;\n}\n" : "=r"(pred));
+    return pred != 0;
 }
 
 __device__ __forceinline__ int fkey(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7FFFFFFF); }
@@ -381,7 +390,8 @@ __device__ inline void process_tile(WorkerState<NT> &st, const WgSmem<NT> &sm, c
                                     unsigned *status) {
     constexpr int N = 16 * NT, NH = 4 * NT, E = Planes<B>::kEff, NCH = E / 2;
     constexpr uint32_t kIdescK = idesc_i8(N, true, false), kIdescV = idesc_i8(N, false, true);
-    const int warp = tw >> 5;
+    const int warp = __shfl_sync(0xffffffffu, tw >> 5, 0);
+    const uint64_t desc_k = smem_desc(smem_addr(sm.bk), (N / 8) * 128, 128), desc_v = smem_desc(smem_addr(sm.pbuf), (N / 16) * 128, 128);
     const uint8_t *kplanes = slot, *vplanes = slot + B * 2048;
     const float kn = reinterpret_cast<const float *>(slot + 2 * B * 2048)[tw];
     const float vn = reinterpret_cast<const float *>(slot + 2 * B * 2048 + 512)[tw];
@@ -396,13 +406,14 @@ __device__ inline void process_tile(WorkerState<NT> &st, const WgSmem<NT> &sm, c
         tmem_st_wait();
         tc_fence_before();
         wg_bar(wg);
-        if (tw == 0 && !aborted) {
-            tc_fence_after();
-            const uint32_t b0 = smem_addr(sm.bk) + cc * (256 * N);
+        if (warp == 0) {   // warp-uniform: the operands of the tensor-core instructions stay in uniform registers
+            if (elect_one() && !aborted) {
+                tc_fence_after();
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-                umma_i8(tmem_wg + kColDK, tmem_wg + 8 * s, smem_desc(b0 + s * 32 * N, (N / 8) * 128, 128), kIdescK, (cc | s) ? 1u : 0u);
-            umma_commit(bar_k);
+                for (int s = 0; s < 8; ++s)
+                    umma_i8(tmem_wg + kColDK, tmem_wg + 8 * s, desc_k + (uint64_t)((cc * 256 * N + s * 32 * N) >> 4), kIdescK, (cc | s) ? 1u : 0u);
+                umma_commit(bar_k);
+            }
         }
         mbar_wait_or_abort(bar_k, ph_k, sm.abort_flag, status);
         ph_k ^= 1u;
@@ -475,13 +486,14 @@ __device__ inline void process_tile(WorkerState<NT> &st, const WgSmem<NT> &sm, c
         tc_fence_before();
         proxy_fence();
         wg_bar(wg);
-        if (tw == 0 && !aborted) {
-            tc_fence_after();
-            const uint32_t b0 = smem_addr(sm.pbuf);
+        if (warp == 0) {
+            if (elect_one() && !aborted) {
+                tc_fence_after();
 #pragma unroll
-            for (int s = 0; s < 8; ++s)
-                umma_i8(tmem_wg + kColDV, tmem_wg + 8 * s, smem_desc(b0 + s * 32 * N, (N / 16) * 128, 128), kIdescV, (cc | s) ? 1u : 0u);
-            umma_commit(bar_v);
+                for (int s = 0; s < 8; ++s)
+                    umma_i8(tmem_wg + kColDV, tmem_wg + 8 * s, desc_v + (uint64_t)((s * 32 * N) >> 4), kIdescV, (cc | s) ? 1u : 0u);
+                umma_commit(bar_v);
+            }
         }
         mbar_wait_or_abort(bar_v, ph_v, sm.abort_flag, status);
         ph_v ^= 1u;
@@ -509,7 +521,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
     __shared__ uint32_t tmem_base_s;
     __shared__ LevelCoefs coefs_s[2];
     constexpr int NH = 4 * NT, S = umma_stages(NT);
-    const int tid = threadIdx.x, wg = tid >> 7, tw = tid & 127, warp = tid >> 5;
+    const int tid = threadIdx.x, tw = tid & 127;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0), wg = warp >> 2;   // warp-uniform by construction
     const int BH = a.B * a.H, G = a.G, n = a.n_workers;
     const int w = blockIdx.x * kWgPerCta + wg;
     const WgSmem<NT> sm = wg_smem<NT>(dyn, wg);
@@ -534,15 +547,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_wg = tmem_base_s + wg * kWgCols;
+    const uint32_t tmem_wg = __shfl_sync(0xffffffffu, tmem_base_s, 0) + wg * kWgCols;
     const uint32_t tmem_lane = tmem_wg + ((uint32_t)((warp & 3) * 32) << 16);
 
     if (w < n) {
-        // producer state (thread 0 of the worker): the tile sequence, `S` tiles ahead of the consumers
+        // producer state (one thread of the worker): the tile sequence, `S` tiles ahead of the consumers
         TileSeq prod;
         prod.init(w, BH);
         int issued = 0;
-        if (tw == 0) {
+        if (tw == kProducerThread) {
             for (; issued < S; ++issued) {
                 int cls, chunk_i, slot0;
                 if (!prod.next_tile(chunks, BH, n, cls, chunk_i, slot0)) break;
@@ -579,7 +592,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
                         ++consumed;
                         // every thread has read its part of the stage (the last reads precede the barrier of the
                         // value product): refill it with the tile `S` ahead
-                        if (tw == 0 && !*sm.abort_flag) {
+                        if (tw == kProducerThread && !*sm.abort_flag) {
                             int cls, chunk_i, slot0;
                             if (prod.next_tile(chunks, BH, n, cls, chunk_i, slot0)) {
                                 issue_tile(chunks, cls, chunk_i, slot0, sm.ring + (size_t)stage * kSlotBytes, sm.bars + stage);
@@ -619,7 +632,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
             }
         }
         // copies still in flight after an abort target this CTA's shared memory: give them a bounded chance to land
-        if (tw == 0 && *sm.abort_flag) {
+        if (tw == kProducerThread && *sm.abort_flag) {
             for (int i = consumed; i < issued; ++i) {
                 const uint32_t bar = smem_addr(sm.bars + i % S);
                 for (unsigned it = 0; it < kUmmaPolls; ++it)
