@@ -367,12 +367,12 @@ using namespace odmkv;
 extern "C" {
 
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
-    // Partial slots per (sample, KV head) that let the tensor-core kernel run four workers per SM of a
+    // Partial slots per (sample, KV head) that let the tensor-core kernel run two pipelines per SM of a
     // 148-SM device: the workers that can overlap one unit, plus one.  The plain kernel uses the same number of
     // equal splits (at most 64), shortened for short contexts.
     if (B <= 0 || H <= 0) return 1;
     const long long BH = (long long)B * H;
-    long long n = (4 * 148 + BH - 1) / BH + 1;
+    long long n = (2 * 148 + BH - 1) / BH + 1;
     const long long by_len = (max_tokens_per_head + 255) / 256 + 1;
     if (n > by_len) n = by_len;
     if (n < 2) n = 2;

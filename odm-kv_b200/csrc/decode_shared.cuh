@@ -43,7 +43,7 @@ inline size_t decode_ws_layout(int B, int H, int G, int nslots, DecodeWs *ws, un
     const size_t BH = (size_t)B * H, GP = round_gp(G);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
-    size_t o_st = take(256), o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nslots * GP * 2 * 4),
+    size_t o_st = take(512), o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nslots * GP * 2 * 4),
            o_acc = take(BH * nslots * GP * 2 * kD * 4);
     if (ws && base) {
         ws->status = (unsigned *)(base + o_st);

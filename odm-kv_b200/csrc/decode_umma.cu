@@ -14,49 +14,58 @@
 // one 32-bit word of a plane into four bytes of an unsigned 8-bit matrix row (value 2^k * bit).  Those bytes are
 // the A operand of an integer tensor-core product whose B operand carries the other factor (rotated query or
 // softmax weight) as four 8-bit limbs per head, pre-shifted by 7 - k so that every bit position weighs the same.
-// The integer product is exact; limbs are recombined in fp32.  Per 128-token tile a thread does ~64 logic
-// operations per side and no shared-memory table look-up at all.
+// The integer product is exact; limbs are recombined in fp32.
 //
-// Mapping.  A CTA holds four independent groups of 128 threads ("workers").  Worker w owns the slice
-// [w, w + 1) / n_workers of every (sample, KV head) unit laid end to end, like a split-K CTA, and streams its tiles
-// through a ring of shared-memory stages filled by one-dimensional bulk copies (TMA, mbarrier transaction
-// counts).  Per tile of 128 tokens and per chunk of two bit planes:
-//   keys:   thread = token.  Plane words -> 64 registers -> tcgen05.st -> A (128 tokens x 256 plane bits) in
-//           tensor memory; B (shared memory, K-major, s8) = query limbs; D (128 x 4 heads x 4 limbs, s32) comes
-//           back with tcgen05.ld; the thread owns the logits of its token for every head;
-//   softmax: running maximum per head over the worker (tile maximum exchanged through shared memory), weights
-//           W = 2^(z - M) <= 1, written as u32 = four u8 limbs per head into the B operand of the value product;
-//   values: thread = coordinate.  The value bank stores planes transposed (bits of a word = tokens), so the same
-//           extraction gives A (128 coordinates x 256 (token, plane) bits); D = sum_j W_j bit_j per coordinate and
-//           head, accumulated in fp32 registers (one per head) with the running-maximum rescale.
+// Mapping.  A CTA runs two independent pipelines.  Pipeline w owns the slice [w, w + 1) / n_workers of every
+// (sample, KV head) unit laid end to end, like a split-K CTA, and streams its tiles of 128 tokens through a ring of
+// shared-memory stages filled by one-dimensional bulk copies (TMA, mbarrier transaction counts).  Its warps have
+// fixed roles that meet only through mbarriers, so the stages of consecutive tiles overlap:
+//   key stagers (4 warps, thread = token): plane words -> 64 registers -> tcgen05.st -> A (128 tokens x 256 plane
+//       bits) in tensor memory;
+//   value stagers (4 warps, thread = coordinate): the value bank stores planes transposed (bits of a word =
+//       tokens), so the same extraction gives A (128 coordinates x 256 (token, plane) bits);
+//   issuer (one elected lane): S = A_keys . query limbs (B in shared memory, K-major, s8) into one of two
+//       accumulator buffers, and, one tile behind, O^T = A_values . weight limbs (B = the softmax warps' output,
+//       MN-major, u8); tcgen05.commit signals the consumers;
+//   softmax warps (4 warps): tcgen05.ld of S, logits of the thread's token for every head, running maximum per head
+//       (tile maximum exchanged through shared memory), weights W = 2^(z - M) <= 1 written as u32 = four u8 limbs
+//       per head; then tcgen05.ld of the previous tile's O^T, whose limbs are recombined and added to the
+//       thread's coordinate of the accumulators (one fp32 register per head);
+//   producer (one lane): bulk copies, a ring ahead.
 // 8-bit, 4-bit, exact and tail tokens go through the CUDA-core kernel of decode.cu; one merge kernel combines all
-// partials.  Every wait is bounded; an expired wait marks the worker as aborted (it keeps the control flow so that
-// no barrier is left waiting) and sets the status word of the workspace.
+// partials.  Every wait is bounded; an expired wait marks the pipeline as aborted (it keeps the control flow so
+// that no barrier is left waiting) and sets the status word of the workspace.
 #include "decode_shared.cuh"
 
 namespace odmkv {
 
-constexpr int kWgThreads = 128;
-constexpr int kWgPerCta = 4;
-constexpr int kUmmaThreads = kWgThreads * kWgPerCta;
+constexpr int kPipes = 2;                      // pipelines per CTA
+constexpr int kPipeWarps = 12;                 // key stagers 0-3, value stagers 4-7, softmax 8-11
+constexpr int kCtrlWarp0 = kPipes * kPipeWarps;            // issuer warps: kCtrlWarp0 + pipe
+constexpr int kProdWarp0 = kCtrlWarp0 + kPipes;            // producer warps: kProdWarp0 + pipe
+constexpr int kUmmaThreads = 32 * (kProdWarp0 + kPipes);   // 28 warps
+constexpr int kSegBarThreads = 32 * (kPipeWarps + 1);      // the twelve role warps and the issuer warp
 constexpr int kTileSlots = kPlaneTile;         // 128 tokens per tile
 constexpr int kTmemCols = 512;
-constexpr int kWgCols = 128;                   // per worker: A [0, 64), D keys [64, 96), D values [96, 128)
-constexpr int kColDK = 64, kColDV = 96;
+constexpr int kPipeCols = 256;                 // per pipeline: A keys [0, 64), A values [64, 128), S at 128 + 32 buf, O^T at 192 + 32 buf
+constexpr int kColAK = 0, kColAV = 64, kColDK = 128, kColDV = 192;
 constexpr unsigned kUmmaPolls = 1u << 12;       // polls per wait; each may suspend the thread for up to kSuspendNs
 constexpr unsigned kSuspendNs = 1000000u;
 constexpr float kNegBig = -1.0e30f;
-constexpr int kProducerThread = 96;            // lane 0 of the worker's last warp issues the bulk copies (warp 0 issues the products)
 constexpr int kMaxTcClass = 2;                 // classes 1 (2-bit) and 2 (3-bit) take this kernel
 constexpr int kSlotBytes = 3 * 4096 + 1024;    // largest tile: 3-bit keys + values (2 x 6144) + two norm rows
+constexpr int kStages = 4;
 
-__host__ __device__ constexpr int umma_stages(int NT) { return NT == 1 ? 3 : 2; }
-__host__ __device__ constexpr int umma_bk_bytes(int NT) { return 2 * 256 * 16 * NT; }   // two chunks (3-bit) of 256 plane bits x N bytes
-__host__ __device__ constexpr int umma_p_bytes(int NT) { return 256 * 16 * NT; }
-__host__ __device__ constexpr int umma_wg_bytes(int NT) {
-    return umma_stages(NT) * kSlotBytes + umma_bk_bytes(NT) + umma_p_bytes(NT) + 512;
+// barrier slots of a pipeline
+enum : int { kBarRF = 0, kBarRE = kStages, kBarAKF = 2 * kStages, kBarAKE, kBarAVF, kBarAVE, kBarDKF, kBarDKE = kBarDKF + 2,
+             kBarDVF = kBarDKE + 2, kBarDVE = kBarDVF + 2, kBarPF = kBarDVE + 2, kNumBars = kBarPF + 2 };
+
+__host__ __device__ constexpr int umma_bk_bytes(int NT) { return 2 * 256 * 16 * NT; }    // two chunks (3-bit) of 256 plane bits x N bytes
+__host__ __device__ constexpr int umma_p_bytes(int NT) { return 2 * 256 * 16 * NT; }     // one tile: up to four planes x 128 tokens x N bytes
+__host__ __device__ constexpr int umma_pipe_bytes(int NT) {
+    return kStages * kSlotBytes + umma_bk_bytes(NT) + 2 * umma_p_bytes(NT) + 1024;
 }
-__host__ __device__ constexpr int umma_smem_bytes(int NT) { return kWgPerCta * umma_wg_bytes(NT) + 1024; }
+__host__ __device__ constexpr int umma_smem_bytes(int NT) { return kPipes * umma_pipe_bytes(NT) + 1024; }
 
 struct UmmaArgs {
     const float *qrot;
@@ -71,7 +80,8 @@ struct UmmaArgs {
 // ---- small PTX wrappers ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void wg_bar(int wg) { asm volatile("bar.sync %0, %1;\n" ::"r"(wg + 1), "n"(kWgThreads) : "memory"); }
+__device__ __forceinline__ void named_bar(int id, int nthreads) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory"); }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -120,8 +130,13 @@ __host__ __device__ constexpr uint32_t idesc_i8(int N, bool b_signed, bool b_mn_
 
 __device__ __forceinline__ bool mbar_poll(uint32_t bar, unsigned parity) {
     uint32_t ok;
+#ifdef ODMKV_NO_SUSPEND_HINT
+    asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+#else
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
                  : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
+#endif
     return ok != 0;
 }
 
@@ -211,39 +226,40 @@ __device__ inline void plane_coefs(const float *cb, float (&w)[Planes<B>::kEff],
 
 struct LevelCoefs { float w[4]; float c0; float wmax; };
 
-// ---- per-worker shared memory ------------------------------------------------------------------------------------
+// ---- per-pipeline shared memory -----------------------------------------------------------------------------------
 template <int NT>
-struct WgSmem {
-    uint8_t *ring;      // stages x kSlotBytes
+struct PipeSmem {
+    uint8_t *ring;      // kStages x kSlotBytes
     uint8_t *bk;        // key-side B operand: per chunk 8 steps x [2 K halves][N / 8 row groups][8 rows][16 bytes]
-    uint8_t *pbuf;      // value-side B operand of one chunk: 8 steps x [4 K groups][N / 16 column groups][8 rows][16 bytes]
-    float *xch;         // [2][4 warps][8]: per-warp maxima / sums
+    uint8_t *pbuf;      // value-side B operand, two tiles: per chunk 8 steps x [4 K groups][N / 16 column groups][8 rows][16 bytes]
+    float *xch;         // [2][4 warps][8]: per-warp maxima / sums of the softmax warps
     float *hq;          // [2][8]: per head: integer product -> plane sum factor, c0 * sum(q')
-    uint64_t *bars;     // full[stages], keys done, values done
+    uint64_t *bars;     // kNumBars
     volatile int *abort_flag;
 };
 
 template <int NT>
-__device__ inline WgSmem<NT> wg_smem(uint8_t *base, int wg) {
-    uint8_t *p = base + (size_t)wg * umma_wg_bytes(NT);
-    WgSmem<NT> s;
-    s.ring = p; p += umma_stages(NT) * kSlotBytes;
+__device__ inline PipeSmem<NT> pipe_smem(uint8_t *base, int pipe) {
+    uint8_t *p = base + (size_t)pipe * umma_pipe_bytes(NT);
+    PipeSmem<NT> s;
+    s.ring = p; p += kStages * kSlotBytes;
     s.bk = p; p += umma_bk_bytes(NT);
-    s.pbuf = p; p += umma_p_bytes(NT);
+    s.pbuf = p; p += 2 * umma_p_bytes(NT);
     s.xch = reinterpret_cast<float *>(p); p += 256;
     s.hq = reinterpret_cast<float *>(p); p += 128;
-    s.bars = reinterpret_cast<uint64_t *>(p); p += 64;
+    s.bars = reinterpret_cast<uint64_t *>(p); p += 8 * kNumBars;
     s.abort_flag = reinterpret_cast<volatile int *>(p);
     return s;
 }
+static_assert(256 + 128 + 8 * kNumBars + 16 <= 1024, "small area of a pipeline");
 
-// ---- tile sequence of a worker ------------------------------------------------------------------------------------
-// Worker w owns [w * BH, (w + 1) * BH) of the line of BH units, each n_workers long: the fraction [r0, r1) / n_workers
+// ---- tile sequence of a pipeline ------------------------------------------------------------------------------------
+// Pipeline w owns [w * BH, (w + 1) * BH) of the line of BH units, each n_workers long: the fraction [r0, r1) / n_workers
 // of every segment of each unit it overlaps.  Order inside a unit: level-major (all chunks of the 2-bit level, then the
-// 3-bit level), tiles ascending.  The producer (bulk copies) and the consumers walk the same sequence.
+// 3-bit level), tiles ascending.  The producer (bulk copies) and every role walk the same sequence.
 struct TileSeq {
     long long pos, end;
-    int bh, r0, r1, c, ci, t, t_hi, s0;
+    int bh, r0, r1, c, ci, t, t_hi, s0, cnt;
     bool in_unit;
     __device__ void init(int w, int BH) { pos = (long long)w * BH; end = pos + BH; in_unit = false; }
     __device__ bool next_unit(int n) {
@@ -257,11 +273,20 @@ struct TileSeq {
     __device__ void open_run(const DecodeChunks &chunks, int BH, int n, int c_, int ci_) {
         c = c_; ci = ci_;
         const odmkv_chunk &ch = chunks.ch[ci];
-        const int cnt = ch.seg_count[c * BH + bh];
+        cnt = ch.seg_count[c * BH + bh];
         const int ntiles = (cnt + kTileSlots - 1) / kTileSlots;
         t = (int)((long long)ntiles * r0 / n);
         t_hi = (int)((long long)ntiles * r1 / n);
         s0 = ch.seg_start[c * BH + bh];
+    }
+    // tiles of level c_ of the current unit, over all chunks
+    __device__ int level_tiles(const DecodeChunks &chunks, int BH, int n, int c_) const {
+        int total = 0;
+        for (int i = 0; i < chunks.n; ++i) {
+            const int ntiles = (chunks.ch[i].seg_count[c_ * BH + bh] + kTileSlots - 1) / kTileSlots;
+            total += (int)((long long)ntiles * r1 / n) - (int)((long long)ntiles * r0 / n);
+        }
+        return total;
     }
     // producer view: next tile in sequence order, or false at the end
     __device__ bool next_tile(const DecodeChunks &chunks, int BH, int n, int &cls, int &chunk_i, int &slot0) {
@@ -279,9 +304,6 @@ struct TileSeq {
         }
     }
 };
-
-template <int B>
-__device__ __forceinline__ uint32_t tile_bytes() { return (uint32_t)(2 * B * 2048 + 1024); }
 
 __device__ inline void issue_tile(const DecodeChunks &chunks, int cls, int chunk_i, int slot0, uint8_t *slot_smem, uint64_t *bar) {
     const odmkv_chunk &ch = chunks.ch[chunk_i];
@@ -301,12 +323,29 @@ __device__ inline void issue_tile(const DecodeChunks &chunks, int cls, int chunk
                  ::"r"(dst + 2 * code_bytes + 512), "l"(ch.v_norm[li] + slot0), "n"(512), "r"(bar_a) : "memory");
 }
 
-// ---- key-side B operand of one (unit, level): query limbs ---------------------------------------------------------
+// Everything a role needs to wait: the pipeline's abort flag and the status word
+struct Waiter {
+    volatile int *abort_flag;
+    unsigned *status;
+#ifdef ODMKV_PROFILE
+    long long *prof;
+    __device__ __forceinline__ void wait(uint32_t bar, unsigned parity, int cat = 6) const {
+        const long long t0 = clock64();
+        mbar_wait_or_abort(bar, parity, abort_flag, status);
+        prof[cat] += clock64() - t0;
+    }
+#else
+    __device__ __forceinline__ void wait(uint32_t bar, unsigned parity, int = 0) const { mbar_wait_or_abort(bar, parity, abort_flag, status); }
+#endif
+    __device__ __forceinline__ bool aborted() const { return *abort_flag != 0; }
+};
+
+// ---- key-side B operand of one (unit, level): query limbs (softmax warps, tw = 0..127) ------------------------------
 // For plane bit kk of chunk cc (word jw = kk / 32, bit position k = (kk % 32) / 4, byte b = kk % 4): effective plane
 // e = 2 cc + jw / 4, coordinate i = 32 (jw % 4) + 8 b + k.  Row n = 4 h + limb holds the balanced base-256 digits of
 // round(q'[h][i] * w_e * S_h) << (7 - k), so that sum_kk A[kk] B[n][kk] = 128 * sum bit * round(...) exactly.
 template <int B, int NT>
-__device__ inline void build_bk(const WgSmem<NT> &sm, const float *__restrict__ qrot, int bh, int G, const LevelCoefs &lc, int tw, int wg) {
+__device__ inline void build_bk(const PipeSmem<NT> &sm, const float *__restrict__ qrot, int bh, int G, const LevelCoefs &lc, int tw, int bar_id) {
     constexpr int N = 16 * NT, E = Planes<B>::kEff, NH = 4 * NT;
     const int warp = tw >> 5, lane = tw & 31;
     // per head: max |q'| and sum q' (thread = coordinate)
@@ -321,7 +360,7 @@ __device__ inline void build_bk(const WgSmem<NT> &sm, const float *__restrict__ 
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (lane == 0) { sm.xch[warp * 8 + h] = m; sm.xch[32 + warp * 8 + h] = s; }
     }
-    wg_bar(wg);
+    named_bar(bar_id, 128);
     float S[NH];
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
@@ -335,7 +374,7 @@ __device__ inline void build_bk(const WgSmem<NT> &sm, const float *__restrict__ 
         }
     }
     // thread tw fills plane bits tw, tw + 128, ... of every chunk
-    for (int kx = tw; kx < E * 128; kx += kWgThreads) {
+    for (int kx = tw; kx < E * 128; kx += 128) {
         const int cc = kx >> 8, kk = kx & 255, jw = kk >> 5, k = (kk & 31) >> 2, b = kk & 3;
         const int e = 2 * cc + (jw >> 2), i = 32 * (jw & 3) + 8 * b + k;
         const float we = lc.w[e];
@@ -354,12 +393,11 @@ __device__ inline void build_bk(const WgSmem<NT> &sm, const float *__restrict__ 
         }
     }
     proxy_fence();
-    wg_bar(wg);
 }
 
-// sum over the worker's 128 threads of up to NH values per thread (result valid in every thread)
+// sum over the 128 softmax threads of up to NH values per thread (result valid in every thread)
 template <int NH>
-__device__ inline void wg_sum(float (&v)[NH], float *xch, int tw, int wg) {
+__device__ inline void sm_sum(float (&v)[NH], float *xch, int tw, int bar_id) {
     const int warp = tw >> 5, lane = tw & 31;
 #pragma unroll
     for (int h = 0; h < NH; ++h) {
@@ -368,151 +406,45 @@ __device__ inline void wg_sum(float (&v)[NH], float *xch, int tw, int wg) {
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (lane == 0) xch[warp * 8 + h] = s;
     }
-    wg_bar(wg);
+    named_bar(bar_id, 128);
 #pragma unroll
     for (int h = 0; h < NH; ++h) v[h] = (xch[h] + xch[8 + h]) + (xch[16 + h] + xch[24 + h]);
-    wg_bar(wg);
+    named_bar(bar_id, 128);
 }
 
 template <int NT>
-struct WorkerState {
+struct SoftmaxState {
     static constexpr int NH = 4 * NT;
-    float M[NH];     // running maximum (log2 domain, includes log2 of the value norm); identical in every thread of the worker
+    float M[NH];     // running maximum (log2 domain, includes log2 of the value norm); identical in every softmax thread
     float l[NH];     // this thread's share of the denominators (token role)
     float lw[NH];    // this thread's share of sum W of the current level (token role): the constant term of the value planes
     float O[NH];     // this thread's coordinate of the code-space accumulators (coordinate role)
 };
 
-// one tile of 128 tokens of a B-bit level
-template <int B, int NT>
-__device__ inline void process_tile(WorkerState<NT> &st, const WgSmem<NT> &sm, const uint8_t *slot, int nvalid, const LevelCoefs &lc,
-                                    uint32_t tmem_wg, uint32_t tmem_lane, float scale_log2, int tw, int wg, unsigned &ph_k, unsigned &ph_v,
-                                    unsigned *status) {
-    constexpr int N = 16 * NT, NH = 4 * NT, E = Planes<B>::kEff, NCH = E / 2;
-    constexpr uint32_t kIdescK = idesc_i8(N, true, false), kIdescV = idesc_i8(N, false, true);
-    const int warp = __shfl_sync(0xffffffffu, tw >> 5, 0);
-    const uint64_t desc_k = smem_desc(smem_addr(sm.bk), (N / 8) * 128, 128), desc_v = smem_desc(smem_addr(sm.pbuf), (N / 16) * 128, 128);
-    const uint8_t *kplanes = slot, *vplanes = slot + B * 2048;
-    const float kn = reinterpret_cast<const float *>(slot + 2 * B * 2048)[tw];
-    const float vn = reinterpret_cast<const float *>(slot + 2 * B * 2048 + 512)[tw];
-    const uint32_t bar_k = smem_addr(sm.bars + 4), bar_v = smem_addr(sm.bars + 5);
-    const bool aborted = *sm.abort_flag != 0;
-
-    // ---- keys: S = planes . query limbs
+// ---- stagers: one tile of a B-bit level, keys (thread = token) or values (thread = coordinate) ------------------------
+// `group` counts the (tile, chunk) products of this side since the kernel started; the A region is free again once
+// product group - 1 has completed (bar_empty), and bar_full collects the four stager warps.
+template <int B>
+__device__ __forceinline__ void stage_tile(const uint8_t *planes, int tw, uint32_t tmem_a, uint32_t bar_empty, uint32_t bar_full,
+                                           uint32_t bar_slot, unsigned &group, const Waiter &wt) {
+    constexpr int NCH = Planes<B>::kEff / 2;
+    const uint8_t *row = planes + tw * 16;
 #pragma unroll
     for (int cc = 0; cc < NCH; ++cc) {
-        plane_to_tmem(tmem_lane, load_eplane<B>(kplanes + tw * 16, 2 * cc));
-        plane_to_tmem(tmem_lane + 32, load_eplane<B>(kplanes + tw * 16, 2 * cc + 1));
+        const uint4 w0 = load_eplane<B>(row, 2 * cc), w1 = load_eplane<B>(row, 2 * cc + 1);
+        if (group > 0) wt.wait(bar_empty, (group - 1) & 1u, 1);
+        tc_fence_after();
+        plane_to_tmem(tmem_a, w0);
+        plane_to_tmem(tmem_a + 32, w1);
         tmem_st_wait();
         tc_fence_before();
-        wg_bar(wg);
-        if (warp == 0) {   // warp-uniform: the operands of the tensor-core instructions stay in uniform registers
-            if (elect_one() && !aborted) {
-                tc_fence_after();
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    umma_i8(tmem_wg + kColDK, tmem_wg + 8 * s, desc_k + (uint64_t)((cc * 256 * N + s * 32 * N) >> 4), kIdescK, (cc | s) ? 1u : 0u);
-                umma_commit(bar_k);
-            }
+        __syncwarp();
+        if ((tw & 31) == 0) {
+            mbar_arrive(bar_full);
+            if (cc == NCH - 1) mbar_arrive(bar_slot);   // this warp has read everything it needs from the ring stage
         }
-        mbar_wait_or_abort(bar_k, ph_k, sm.abort_flag, status);
-        ph_k ^= 1u;
-        tc_fence_after();
+        ++group;
     }
-    // ---- logits of this thread's token (log2 domain, plus log2 of the value norm)
-    float z[NH];
-    {
-        uint32_t d[N];
-#pragma unroll
-        for (int c16 = 0; c16 < NT; ++c16) tmem_ld16(tmem_lane + kColDK + 16 * c16, reinterpret_cast<uint32_t(&)[16]>(d[16 * c16]));
-        tmem_ld_wait();
-        const bool valid = tw < nvalid;
-        const float vnc = fmaxf(vn, 1e-30f);
-        const float lv = valid ? __log2f(vnc) : kNegBig;
-        const float kf = kn * scale_log2;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            const int lo = (int)d[4 * h] + 256 * (int)d[4 * h + 1], hi = (int)d[4 * h + 2] + 256 * (int)d[4 * h + 3];
-            const float f = fmaf(65536.f, (float)hi, (float)lo);
-            const float s = fmaf(f, sm.hq[h], sm.hq[8 + h]);
-            z[h] = valid ? fmaf(s, kf, lv) : kNegBig;
-        }
-    }
-    // ---- tile maximum per head over the worker, running-maximum update
-#pragma unroll
-    for (int h = 0; h < NH; ++h) {
-        const float m = warp_max_f(z[h]);
-        if ((tw & 31) == 0) sm.xch[warp * 8 + h] = m;
-    }
-    tc_fence_before();
-    wg_bar(wg);
-    float W[NH];
-    {
-        const float rv = tw < nvalid ? __fdividef(1.0f, fmaxf(vn, 1e-30f)) : 0.f;
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            const float mt = fmaxf(fmaxf(sm.xch[h], sm.xch[8 + h]), fmaxf(sm.xch[16 + h], sm.xch[24 + h]));
-            const float mn = fmaxf(st.M[h], mt);
-            const float corr = fast_ex2(st.M[h] - mn);   // 1 when unchanged, 0 for the first tile
-            st.M[h] = mn;
-            st.l[h] *= corr; st.lw[h] *= corr; st.O[h] *= corr;
-            W[h] = fast_ex2(z[h] - mn);                  // <= 1; 0 for padding slots
-            st.l[h] = fmaf(W[h], rv, st.l[h]);
-            st.lw[h] += W[h];
-        }
-    }
-    // ---- values: O^T += planes^T . weight limbs
-    const int jk = tw & 7, jb = (tw & 31) >> 3, jw = tw >> 5;   // this token's place in the plane words of the value bank
-#pragma unroll
-    for (int cc = 0; cc < NCH; ++cc) {
-        // weight rows of this token for the two planes of the chunk: u32 = four u8 limbs per head
-#pragma unroll
-        for (int pp = 0; pp < 2; ++pp) {
-            const int e = 2 * cc + pp;
-            const float ps = (lc.w[e] / lc.wmax) * (float)(1u << (31 - jk));
-            const int kk = 32 * (4 * pp + jw) + 4 * jk + jb;              // row of the chunk's B operand
-            uint8_t *row = sm.pbuf + (kk >> 5) * (32 * N) + ((kk & 31) >> 3) * (N / 16) * 128 + (kk & 7) * 16;
-#pragma unroll
-            for (int g4 = 0; g4 < NT; ++g4) {
-                uint4 v;
-                v.x = __float2uint_rn(W[4 * g4] * ps); v.y = __float2uint_rn(W[4 * g4 + 1] * ps);
-                v.z = __float2uint_rn(W[4 * g4 + 2] * ps); v.w = __float2uint_rn(W[4 * g4 + 3] * ps);
-                *reinterpret_cast<uint4 *>(row + g4 * 128) = v;
-            }
-        }
-        plane_to_tmem(tmem_lane, load_eplane<B>(vplanes + tw * 16, 2 * cc));
-        plane_to_tmem(tmem_lane + 32, load_eplane<B>(vplanes + tw * 16, 2 * cc + 1));
-        tmem_st_wait();
-        tc_fence_before();
-        proxy_fence();
-        wg_bar(wg);
-        if (warp == 0) {
-            if (elect_one() && !aborted) {
-                tc_fence_after();
-#pragma unroll
-                for (int s = 0; s < 8; ++s)
-                    umma_i8(tmem_wg + kColDV, tmem_wg + 8 * s, desc_v + (uint64_t)((s * 32 * N) >> 4), kIdescV, (cc | s) ? 1u : 0u);
-                umma_commit(bar_v);
-            }
-        }
-        mbar_wait_or_abort(bar_v, ph_v, sm.abort_flag, status);
-        ph_v ^= 1u;
-        tc_fence_after();
-    }
-    {
-        uint32_t d[N];
-#pragma unroll
-        for (int c16 = 0; c16 < NT; ++c16) tmem_ld16(tmem_lane + kColDV + 16 * c16, reinterpret_cast<uint32_t(&)[16]>(d[16 * c16]));
-        tmem_ld_wait();
-        const float os = lc.wmax * (1.0f / 2147483648.0f);
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-            const uint32_t lo = d[4 * h] + 256u * d[4 * h + 1], hi = d[4 * h + 2] + 256u * d[4 * h + 3];
-            const float f = fmaf(65536.f, (float)hi, (float)lo);
-            st.O[h] = fmaf(f, os, st.O[h]);
-        }
-    }
-    tc_fence_before();
 }
 
 template <int NT>
@@ -520,21 +452,46 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
     extern __shared__ __align__(1024) uint8_t dyn[];
     __shared__ uint32_t tmem_base_s;
     __shared__ LevelCoefs coefs_s[2];
-    constexpr int NH = 4 * NT, S = umma_stages(NT);
-    const int tid = threadIdx.x, tw = tid & 127;
-    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0), wg = warp >> 2;   // warp-uniform by construction
+    constexpr int NH = 4 * NT, N = 16 * NT;
+    constexpr uint32_t kIdescK = idesc_i8(N, true, false), kIdescV = idesc_i8(N, false, true);
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // warp-uniform by construction
     const int BH = a.B * a.H, G = a.G, n = a.n_workers;
-    const int w = blockIdx.x * kWgPerCta + wg;
-    const WgSmem<NT> sm = wg_smem<NT>(dyn, wg);
+    // role of this warp
+    const int pipe = warp < kCtrlWarp0 ? warp / kPipeWarps : (warp - kCtrlWarp0) % kPipes;
+    const int role = warp < kCtrlWarp0 ? (warp % kPipeWarps) / 4 : (warp < kProdWarp0 ? 3 : 4);   // 0 keys, 1 values, 2 softmax, 3 issuer, 4 producer
+    const int tw = warp < kCtrlWarp0 ? 32 * (warp & 3) + lane : lane;                              // token / coordinate of a role thread
+    const int w = blockIdx.x * kPipes + pipe;
+    const PipeSmem<NT> sm = pipe_smem<NT>(dyn, pipe);
+#ifdef ODMKV_PROFILE
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_t0 = clock64();
+    const Waiter wt{sm.abort_flag, a.status, prof};
+#else
+    const Waiter wt{sm.abort_flag, a.status};
+#endif
 
-    if (tw == 0) {
-        for (int i = 0; i < S; ++i) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + i)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + 4)) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + 5)) : "memory");
+    if (role == 3 && lane == 0) {
+        for (int i = 0; i < kStages; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + kBarRF + i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_addr(sm.bars + kBarRE + i)), "n"(kPipeWarps) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(smem_addr(sm.bars + kBarAKF)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + kBarAKE)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(smem_addr(sm.bars + kBarAVF)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + kBarAVE)) : "memory");
+        for (int i = 0; i < 2; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + kBarDKF + i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(smem_addr(sm.bars + kBarDKE + i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_addr(sm.bars + kBarDVF + i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(smem_addr(sm.bars + kBarDVE + i)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 4;\n" ::"r"(smem_addr(sm.bars + kBarPF + i)) : "memory");
+        }
         *sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (tid == 0) {
+        coefs_s[0].w[2] = coefs_s[0].w[3] = 0.f;
         plane_coefs<2>(a.codebooks, reinterpret_cast<float(&)[2]>(coefs_s[0].w), coefs_s[0].c0);
         coefs_s[0].wmax = fmaxf(coefs_s[0].w[0], coefs_s[0].w[1]);
         plane_coefs<3>(a.codebooks + 256, coefs_s[1].w, coefs_s[1].c0);
@@ -547,99 +504,298 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) decode_umma_kernel(const Deco
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_wg = __shfl_sync(0xffffffffu, tmem_base_s, 0) + wg * kWgCols;
-    const uint32_t tmem_lane = tmem_wg + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t tmem_pipe = __shfl_sync(0xffffffffu, tmem_base_s, 0) + pipe * kPipeCols;
+    const uint32_t tmem_lane = tmem_pipe + ((uint32_t)((warp & 3) * 32) << 16);
+    const int seg_bar = 1 + pipe, sm_bar = 1 + kPipes + pipe;
+    const uint32_t bar0 = smem_addr(sm.bars);
+    auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
     if (w < n) {
-        // producer state (one thread of the worker): the tile sequence, `S` tiles ahead of the consumers
-        TileSeq prod;
-        prod.init(w, BH);
-        int issued = 0;
-        if (tw == kProducerThread) {
-            for (; issued < S; ++issued) {
+        if (role == 4) {
+            // ---- producer: bulk copies, up to kStages tiles ahead of the slowest consumer
+            if (lane == 0) {
+                TileSeq prod;
+                prod.init(w, BH);
+                unsigned g = 0;
                 int cls, chunk_i, slot0;
-                if (!prod.next_tile(chunks, BH, n, cls, chunk_i, slot0)) break;
-                issue_tile(chunks, cls, chunk_i, slot0, sm.ring + (size_t)issued * kSlotBytes, sm.bars + issued);
+                while (prod.next_tile(chunks, BH, n, cls, chunk_i, slot0)) {
+                    const int stage = g % kStages;
+                    if (g >= kStages) wt.wait(bar(kBarRE + stage), ((g / kStages) - 1) & 1u);
+                    if (!wt.aborted()) issue_tile(chunks, cls, chunk_i, slot0, sm.ring + (size_t)stage * kSlotBytes, sm.bars + kBarRF + stage);
+                    ++g;
+                }
+                // copies still in flight after an abort target this CTA's shared memory: give them a bounded chance to land
+                if (wt.aborted()) {
+                    for (unsigned i = g > (unsigned)kStages ? g - kStages : 0u; i < g; ++i)
+                        for (unsigned it = 0; it < kUmmaPolls; ++it)
+                            if (mbar_poll(bar(kBarRF + (int)(i % kStages)), (i / kStages) & 1u)) break;
+                }
             }
-        }
-        unsigned ph_k = 0, ph_v = 0;
-        int consumed = 0;
-        TileSeq seq;
-        seq.init(w, BH);
-        while (seq.next_unit(n)) {
-            const int bh = seq.bh;
-            WorkerState<NT> st;
+        } else {
+            TileSeq seq;
+            seq.init(w, BH);
+            unsigned g = 0;            // tiles of this pipeline so far (same in every role)
+            unsigned kgrp = 0, vgrp = 0;   // (tile, chunk) products so far, keys / values
+            SoftmaxState<NT> st;
+            while (seq.next_unit(n)) {
+                const int bh = seq.bh;
+                if (role == 2) {
 #pragma unroll
-            for (int h = 0; h < NH; ++h) { st.M[h] = kNegBig; st.l[h] = 0.f; st.lw[h] = 0.f; st.O[h] = 0.f; }
-            for (int c = 1; c <= kMaxTcClass; ++c) {
-                const LevelCoefs lc = coefs_s[c - 1];
-                bool built = false;
-                for (int ci = 0; ci < chunks.n; ++ci) {
-                    seq.open_run(chunks, BH, n, c, ci);
-                    const int cnt = chunks.ch[ci].seg_count[c * BH + bh];
-                    for (int t = seq.t; t < seq.t_hi; ++t) {
-                        if (!built) {
-                            if (c == 1) build_bk<2, NT>(sm, a.qrot, bh, G, lc, tw, wg);
-                            else build_bk<3, NT>(sm, a.qrot, bh, G, lc, tw, wg);
-                            built = true;
+                    for (int h = 0; h < NH; ++h) { st.M[h] = kNegBig; st.l[h] = 0.f; st.lw[h] = 0.f; st.O[h] = 0.f; }
+                }
+                for (int c = 1; c <= kMaxTcClass; ++c) {
+                    const int ntl = seq.level_tiles(chunks, BH, n, c);
+                    if (ntl == 0) continue;
+                    const LevelCoefs lc = coefs_s[c - 1];
+                    const int nch = c == 1 ? 1 : 2;
+                    // every product of the previous segment has completed (the softmax warps waited for the last one)
+                    named_bar(seg_bar, kSegBarThreads);
+                    if (role == 2) {
+                        if (c == 1) build_bk<2, NT>(sm, a.qrot, bh, G, lc, tw, sm_bar);
+                        else build_bk<3, NT>(sm, a.qrot, bh, G, lc, tw, sm_bar);
+                    }
+                    named_bar(seg_bar, kSegBarThreads);
+
+                    if (role == 0 || role == 1) {
+                        // ---- stagers
+                        for (int ci = 0; ci < chunks.n; ++ci) {
+                            seq.open_run(chunks, BH, n, c, ci);
+                            for (int t = seq.t; t < seq.t_hi; ++t) {
+                                const int stage = g % kStages;
+                                wt.wait(bar(kBarRF + stage), (g / kStages) & 1u, 0);
+                                const uint8_t *slot = sm.ring + (size_t)stage * kSlotBytes;
+                                if (role == 0) {
+                                    if (c == 1) stage_tile<2>(slot, tw, tmem_lane + kColAK, bar(kBarAKE), bar(kBarAKF), bar(kBarRE + stage), kgrp, wt);
+                                    else stage_tile<3>(slot, tw, tmem_lane + kColAK, bar(kBarAKE), bar(kBarAKF), bar(kBarRE + stage), kgrp, wt);
+                                } else {
+                                    if (c == 1) stage_tile<2>(slot + 2 * 2048, tw, tmem_lane + kColAV, bar(kBarAVE), bar(kBarAVF), bar(kBarRE + stage), vgrp, wt);
+                                    else stage_tile<3>(slot + 3 * 2048, tw, tmem_lane + kColAV, bar(kBarAVE), bar(kBarAVF), bar(kBarRE + stage), vgrp, wt);
+                                }
+                                ++g;
+                            }
                         }
-                        const int stage = consumed % S;
-                        mbar_wait_or_abort(smem_addr(sm.bars + stage), (unsigned)(consumed / S) & 1u, sm.abort_flag, a.status);
-                        const uint8_t *slot = sm.ring + (size_t)stage * kSlotBytes;
-                        const int nvalid = min(kTileSlots, cnt - t * kTileSlots);
-                        if (c == 1) process_tile<2, NT>(st, sm, slot, nvalid, lc, tmem_wg, tmem_lane, a.scale_log2, tw, wg, ph_k, ph_v, a.status);
-                        else process_tile<3, NT>(st, sm, slot, nvalid, lc, tmem_wg, tmem_lane, a.scale_log2, tw, wg, ph_k, ph_v, a.status);
-                        ++consumed;
-                        // every thread has read its part of the stage (the last reads precede the barrier of the
-                        // value product): refill it with the tile `S` ahead
-                        if (tw == kProducerThread && !*sm.abort_flag) {
-                            int cls, chunk_i, slot0;
-                            if (prod.next_tile(chunks, BH, n, cls, chunk_i, slot0)) {
-                                issue_tile(chunks, cls, chunk_i, slot0, sm.ring + (size_t)stage * kSlotBytes, sm.bars + stage);
-                                ++issued;
+                    } else if (role == 3) {
+                        // ---- issuer: keys of tile t, then values of tile t - 1
+                        const uint64_t desc_k = smem_desc(smem_addr(sm.bk), (N / 8) * 128, 128);
+                        const uint64_t desc_v0 = smem_desc(smem_addr(sm.pbuf), (N / 16) * 128, 128);
+                        const bool lead = elect_one();
+                        for (int t = 0; t <= ntl; ++t) {
+                            if (t < ntl) {
+                                const unsigned buf = g & 1u;
+                                for (int cc = 0; cc < nch; ++cc) {
+                                    wt.wait(bar(kBarAKF), kgrp & 1u, 0);
+                                    if (cc == 0 && g >= 2) wt.wait(bar(kBarDKE + buf), ((g >> 1) - 1) & 1u, 1);
+                                    tc_fence_after();
+                                    if (lead && !wt.aborted()) {
+#pragma unroll
+                                        for (int s = 0; s < 8; ++s)
+                                            umma_i8(tmem_pipe + kColDK + 32 * buf, tmem_pipe + kColAK + 8 * s,
+                                                    desc_k + (uint64_t)((cc * 256 * N + s * 32 * N) >> 4), kIdescK, (cc | s) ? 1u : 0u);
+                                        umma_commit(bar(kBarAKE));
+                                        if (cc == nch - 1) umma_commit(bar(kBarDKF + buf));
+                                    }
+                                    __syncwarp();
+                                    ++kgrp;
+                                }
+                                ++g;
+                            }
+                            if (t > 0) {
+                                const unsigned gv = g - (t < ntl ? 2u : 1u);   // global index of tile t - 1
+                                const unsigned buf = gv & 1u;
+                                wt.wait(bar(kBarPF + buf), (gv >> 1) & 1u, 2);
+                                if (gv >= 2) wt.wait(bar(kBarDVE + buf), ((gv >> 1) - 1) & 1u, 3);
+                                for (int cc = 0; cc < nch; ++cc) {
+                                    wt.wait(bar(kBarAVF), vgrp & 1u, 4);
+                                    tc_fence_after();
+                                    if (lead && !wt.aborted()) {
+#pragma unroll
+                                        for (int s = 0; s < 8; ++s)
+                                            umma_i8(tmem_pipe + kColDV + 32 * buf, tmem_pipe + kColAV + 8 * s,
+                                                    desc_v0 + (uint64_t)((buf * umma_p_bytes(NT) + cc * 256 * N + s * 32 * N) >> 4), kIdescV, (cc | s) ? 1u : 0u);
+                                        umma_commit(bar(kBarAVE));
+                                        if (cc == nch - 1) umma_commit(bar(kBarDVF + buf));
+                                    }
+                                    __syncwarp();
+                                    ++vgrp;
+                                }
+                            }
+                        }
+                    } else {
+                        // ---- softmax warps (role 2): thread = token for S, thread = coordinate for O^T
+                        const float os = lc.wmax * (1.0f / 2147483648.0f);
+                        const int jk = tw & 7, jb = (tw & 31) >> 3, jw = tw >> 5;   // this token's place in the plane words of the value bank
+                        float ps[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) ps[e] = (lc.w[e] / lc.wmax) * (float)(1u << (31 - jk));
+                        int t_seg = 0;
+                        float corr[NH];
+                        for (int ci = 0; ci < chunks.n; ++ci) {
+                            seq.open_run(chunks, BH, n, c, ci);
+                            for (int t = seq.t; t < seq.t_hi; ++t, ++t_seg) {
+                                const int stage = g % kStages;
+                                const unsigned buf = g & 1u;
+                                const int nvalid = min(kTileSlots, seq.cnt - t * kTileSlots);
+                                wt.wait(bar(kBarRF + stage), (g / kStages) & 1u, 0);
+                                const uint8_t *slot = sm.ring + (size_t)stage * kSlotBytes;
+                                const int bq = c + 1;
+                                const float kn = reinterpret_cast<const float *>(slot + 2 * bq * 2048)[tw];
+                                const float vn = reinterpret_cast<const float *>(slot + 2 * bq * 2048 + 512)[tw];
+                                // ---- logits of this thread's token (log2 domain, plus log2 of the value norm)
+                                float z[NH];
+                                {
+                                    wt.wait(bar(kBarDKF + buf), (g >> 1) & 1u, 1);
+                                    tc_fence_after();
+                                    uint32_t d[N];
+#pragma unroll
+                                    for (int c16 = 0; c16 < NT; ++c16)
+                                        tmem_ld16(tmem_lane + kColDK + 32 * buf + 16 * c16, reinterpret_cast<uint32_t(&)[16]>(d[16 * c16]));
+                                    tmem_ld_wait();
+                                    tc_fence_before();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(bar(kBarDKE + buf));
+                                    const bool valid = tw < nvalid;
+                                    const float vnc = fmaxf(vn, 1e-30f);
+                                    const float lv = valid ? __log2f(vnc) : kNegBig;
+                                    const float kf = kn * a.scale_log2;
+#pragma unroll
+                                    for (int h = 0; h < NH; ++h) {
+                                        const int lo = (int)d[4 * h] + 256 * (int)d[4 * h + 1], hi = (int)d[4 * h + 2] + 256 * (int)d[4 * h + 3];
+                                        const float f = fmaf(65536.f, (float)hi, (float)lo);
+                                        const float s = fmaf(f, sm.hq[h], sm.hq[8 + h]);
+                                        z[h] = valid ? fmaf(s, kf, lv) : kNegBig;
+                                    }
+                                }
+                                // ---- tile maximum per head over the four warps, running-maximum update
+#pragma unroll
+                                for (int h = 0; h < NH; ++h) {
+                                    const float m = warp_max_f(z[h]);
+                                    if (lane == 0) sm.xch[(t_seg & 1) * 32 + (warp & 3) * 8 + h] = m;
+                                }
+#ifdef ODMKV_PROFILE
+                                const long long tb0 = clock64();
+#endif
+                                named_bar(sm_bar, 128);
+#ifdef ODMKV_PROFILE
+                                prof[3] += clock64() - tb0;
+#endif
+                                float W[NH];
+                                {
+                                    const float rv = tw < nvalid ? __fdividef(1.0f, fmaxf(vn, 1e-30f)) : 0.f;
+                                    const float *xm = sm.xch + (t_seg & 1) * 32;
+#pragma unroll
+                                    for (int h = 0; h < NH; ++h) {
+                                        const float mt = fmaxf(fmaxf(xm[h], xm[8 + h]), fmaxf(xm[16 + h], xm[24 + h]));
+                                        const float mn = fmaxf(st.M[h], mt);
+                                        corr[h] = fast_ex2(st.M[h] - mn);   // 1 when unchanged, 0 for the first tile
+                                        st.M[h] = mn;
+                                        W[h] = fast_ex2(z[h] - mn);         // <= 1; 0 for padding slots
+                                        st.l[h] = fmaf(st.l[h], corr[h], W[h] * rv);
+                                        st.lw[h] = fmaf(st.lw[h], corr[h], W[h]);
+                                    }
+                                }
+                                // ---- weight rows of this token, every plane of the tile: u32 = four u8 limbs per head
+                                // (the buffer is free: the products of tile g - 2 completed before its O^T was read)
+                                {
+                                    uint8_t *pb = sm.pbuf + buf * umma_p_bytes(NT);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        if (e < 2 * nch) {
+                                            const int kk = 32 * (4 * (e & 1) + jw) + 4 * jk + jb;   // row inside the chunk's B operand
+                                            uint8_t *row = pb + (e >> 1) * (256 * N) + (kk >> 5) * (32 * N) + ((kk & 31) >> 3) * (N / 16) * 128 + (kk & 7) * 16;
+#pragma unroll
+                                            for (int g4 = 0; g4 < NT; ++g4) {
+                                                uint4 v;
+                                                v.x = __float2uint_rn(W[4 * g4] * ps[e]); v.y = __float2uint_rn(W[4 * g4 + 1] * ps[e]);
+                                                v.z = __float2uint_rn(W[4 * g4 + 2] * ps[e]); v.w = __float2uint_rn(W[4 * g4 + 3] * ps[e]);
+                                                *reinterpret_cast<uint4 *>(row + g4 * 128) = v;
+                                            }
+                                        }
+                                    }
+                                    proxy_fence();
+                                    __syncwarp();
+                                    if (lane == 0) { mbar_arrive(bar(kBarPF + buf)); mbar_arrive(bar(kBarRE + stage)); }
+                                }
+                                // ---- O^T of the previous tile (weights relative to the maximum before this tile's update)
+                                if (t_seg > 0) {
+                                    const unsigned gp = g - 1, pbuf_i = gp & 1u;
+                                    wt.wait(bar(kBarDVF + pbuf_i), (gp >> 1) & 1u, 2);
+                                    tc_fence_after();
+                                    uint32_t d[N];
+#pragma unroll
+                                    for (int c16 = 0; c16 < NT; ++c16)
+                                        tmem_ld16(tmem_lane + kColDV + 32 * pbuf_i + 16 * c16, reinterpret_cast<uint32_t(&)[16]>(d[16 * c16]));
+                                    tmem_ld_wait();
+                                    tc_fence_before();
+                                    __syncwarp();
+                                    if (lane == 0) mbar_arrive(bar(kBarDVE + pbuf_i));
+#pragma unroll
+                                    for (int h = 0; h < NH; ++h) {
+                                        const uint32_t lo = d[4 * h] + 256u * d[4 * h + 1], hi = d[4 * h + 2] + 256u * d[4 * h + 3];
+                                        st.O[h] = fmaf(fmaf(65536.f, (float)hi, (float)lo), os, st.O[h]);
+                                    }
+                                }
+#pragma unroll
+                                for (int h = 0; h < NH; ++h) st.O[h] *= corr[h];
+                                ++g;
+                            }
+                        }
+                        // ---- drain: O^T of the segment's last tile, then the constant term of the level's planes
+                        {
+                            const unsigned gp = g - 1, pbuf_i = gp & 1u;
+                            wt.wait(bar(kBarDVF + pbuf_i), (gp >> 1) & 1u, 2);
+                            tc_fence_after();
+                            uint32_t d[N];
+#pragma unroll
+                            for (int c16 = 0; c16 < NT; ++c16)
+                                tmem_ld16(tmem_lane + kColDV + 32 * pbuf_i + 16 * c16, reinterpret_cast<uint32_t(&)[16]>(d[16 * c16]));
+                            tmem_ld_wait();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(bar(kBarDVE + pbuf_i));
+#pragma unroll
+                            for (int h = 0; h < NH; ++h) {
+                                const uint32_t lo = d[4 * h] + 256u * d[4 * h + 1], hi = d[4 * h + 2] + 256u * d[4 * h + 3];
+                                st.O[h] = fmaf(fmaf(65536.f, (float)hi, (float)lo), os, st.O[h]);
+                            }
+                            float lw[NH];
+#pragma unroll
+                            for (int h = 0; h < NH; ++h) lw[h] = st.lw[h];
+                            sm_sum<NH>(lw, sm.xch, tw, sm_bar);
+#pragma unroll
+                            for (int h = 0; h < NH; ++h) { st.O[h] = fmaf(lc.c0, lw[h], st.O[h]); st.lw[h] = 0.f; }
+                        }
+                    }
+                }
+                // ---- partial of this (pipeline, unit): natural-log maximum, denominator, code-space accumulator
+                if (role == 2) {
+                    float l[NH];
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) l[h] = st.l[h];
+                    sm_sum<NH>(l, sm.xch, tw, sm_bar);
+                    const int GP = round_gp(G);
+                    const int slot_i = w - (int)(((long long)bh * n) / BH);
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) {
+                        if (h < GP) {
+                            const size_t pi = ((size_t)bh * a.nslots + a.slot_base + slot_i) * GP + h;
+                            a.part_acc[pi * 2 * kD + tw] = h < G ? st.O[h] : 0.f;
+                            a.part_acc[pi * 2 * kD + kD + tw] = 0.f;
+                            if (tw == 0) {
+                                a.part_ml[pi * 2] = (h < G && st.M[h] > kNegBig) ? st.M[h] * 0.6931471805599453f : -INFINITY;
+                                a.part_ml[pi * 2 + 1] = h < G ? l[h] : 0.f;
                             }
                         }
                     }
                 }
-                if (built) {
-                    // constant term of this level's value planes: c0 * sum_j W_j for every coordinate
-                    float lw[NH];
-#pragma unroll
-                    for (int h = 0; h < NH; ++h) lw[h] = st.lw[h];
-                    wg_sum<NH>(lw, sm.xch, tw, wg);
-#pragma unroll
-                    for (int h = 0; h < NH; ++h) { st.O[h] = fmaf(lc.c0, lw[h], st.O[h]); st.lw[h] = 0.f; }
-                }
-            }
-            // ---- partial of this (worker, unit): natural-log maximum, denominator, code-space accumulator
-            float l[NH];
-#pragma unroll
-            for (int h = 0; h < NH; ++h) l[h] = st.l[h];
-            wg_sum<NH>(l, sm.xch, tw, wg);
-            const int GP = round_gp(G);
-            const int slot_i = w - (int)(((long long)bh * n) / BH);
-#pragma unroll
-            for (int h = 0; h < NH; ++h) {
-                if (h < GP) {
-                    const size_t pi = ((size_t)bh * a.nslots + a.slot_base + slot_i) * GP + h;
-                    a.part_acc[pi * 2 * kD + tw] = h < G ? st.O[h] : 0.f;
-                    a.part_acc[pi * 2 * kD + kD + tw] = 0.f;
-                    if (tw == 0) {
-                        a.part_ml[pi * 2] = (h < G && st.M[h] > kNegBig) ? st.M[h] * 0.6931471805599453f : -INFINITY;
-                        a.part_ml[pi * 2 + 1] = h < G ? l[h] : 0.f;
-                    }
-                }
-            }
-        }
-        // copies still in flight after an abort target this CTA's shared memory: give them a bounded chance to land
-        if (tw == kProducerThread && *sm.abort_flag) {
-            for (int i = consumed; i < issued; ++i) {
-                const uint32_t bar = smem_addr(sm.bars + i % S);
-                for (unsigned it = 0; it < kUmmaPolls; ++it)
-                    if (mbar_poll(bar, (unsigned)(i / S) & 1u)) break;
             }
         }
     }
+#ifdef ODMKV_PROFILE
+    if (blockIdx.x == 7 && pipe == 0 && lane == 0 && (role >= 3 || (warp & 3) == 0)) {
+        prof[7] = clock64() - prof_t0;
+        for (int i = 0; i < 8; ++i) reinterpret_cast<long long *>(a.status)[2 + role * 8 + i] = prof[i];
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_s), "r"((uint32_t)kTmemCols) : "memory");
@@ -711,11 +867,11 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     }
     UmmaArgs m;
     m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc; m.status = ws.status;
-    // workers: four per SM, fewer when the cache is short (at least two tiles each) or when the caller's slot count
-    // bounds the workers that may overlap one unit
+    // workers (pipelines): two per SM, fewer when the cache is short (at least two tiles each) or when the caller's slot
+    // count bounds the workers that may overlap one unit
     long long total_tiles = 0;
     for (int i = 0; i < n_chunks; ++i) total_tiles += ((long long)chunks[i].cap[1] + chunks[i].cap[2]) / kPlaneTile;
-    long long n_workers = (long long)kWgPerCta * num_sms_cached();
+    long long n_workers = (long long)kPipes * num_sms_cached();
     if (n_workers > total_tiles / 2) n_workers = total_tiles / 2;
     if (n_splits >= 2) {
         if (n_workers > (long long)(n_splits - 1) * BH) n_workers = (long long)(n_splits - 1) * BH;
@@ -726,7 +882,7 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     if (n_workers < 1) n_workers = 1;
     m.B = B; m.H = H; m.G = G; m.n_workers = (int)n_workers; m.slot_base = 0; m.nslots = nslots;
     m.scale_log2 = scale * 1.4426950408889634f;
-    dim3 grid((unsigned)((n_workers + kWgPerCta - 1) / kWgPerCta));
+    dim3 grid((unsigned)((n_workers + kPipes - 1) / kPipes));
     {
         static bool attr_set[64] = {};   // per device: the opt-in only has to happen once
         int dev = 0;

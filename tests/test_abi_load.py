@@ -45,5 +45,5 @@ def test_status_strings_and_host_queries(pkg):
     assert L.odmkv_pack_plan_workspace_bytes(1, 8, 4096) == 2 * 8 * 32 * 6 * 4
     assert L.odmkv_alloc_num_rounds(6) == 74 + 25
     assert L.odmkv_alloc_num_rounds(1) == 1
-    assert L.odmkv_decode_default_splits(1, 8, 131072) == 75 and L.odmkv_decode_default_splits(8, 8, 131072) == 11
+    assert L.odmkv_decode_default_splits(1, 8, 131072) == 38 and L.odmkv_decode_default_splits(8, 8, 131072) == 6
     assert L.odmkv_score_workspace_bytes(1, 8, 4, 4096) > 8 * 4 * 4096 * 4
