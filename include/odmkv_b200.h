@@ -35,7 +35,7 @@ extern "C" {
 #define ODMKV_HEAD_DIM 128
 #define ODMKV_NUM_QLEVELS 4   /* 2, 3, 4, 8 bits */
 #define ODMKV_NUM_CLASSES 6   /* evicted, 2, 3, 4, 8, exact-16 (class index = position in this list) */
-#define ODMKV_SEG_ALIGN 128   /* every (batch, head) segment of a bank starts on a multiple of 128 slots */
+#define ODMKV_SEG_ALIGN 16    /* every (batch, head) segment of a bank starts on a multiple of 16 slots */
 #define ODMKV_TILE 128        /* tokens per quantise tile */
 #define ODMKV_MAX_LEVELS 8    /* candidate widths of one Lagrangian problem */
 
@@ -123,7 +123,7 @@ int odmkv_alloc_finish(void *workspace, int32_t *bits, odmkv_alloc_report *repor
  *
  * A "chunk" is the packed form of one [B, H, T] block of tokens.  Per class c it holds a bank
  * whose slots are ordered (b, h, t) -- the row order of the reference's mask.nonzero() -- with
- * each (b, h) segment starting on a multiple of 128 slots (padding slots have pos = -1, zero codes and norms).
+ * each (b, h) segment starting on a multiple of 16 slots (padding slots have pos = -1).
  *
  * Step 1 (plan): count classes, lay out segments.
  *   bits      [B, H, T] int32 with values in {0, 2, 3, 4, 8, 16}
@@ -136,13 +136,14 @@ size_t odmkv_pack_plan_workspace_bytes(int B, int H, int T);
 int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start, int32_t *seg_count,
                     int32_t *totals, void *plan_workspace, size_t plan_workspace_bytes, void *stream);
 
-/* Bank storage of one chunk; all device pointers, sized from `totals` (cap[c] slots, a multiple of 128).
+/* Bank storage of one chunk; all device pointers, sized from `totals` (cap[c] slots, a multiple of 16).
  * Code bytes per slot: 32 (2-bit), 48 (3-bit, a true 3 bits per code), 64 (4-bit), 128 (8-bit).
- * The 8-bit bank is token-major (byte d of a slot = code of coordinate d).  The 2/3/4-bit banks (b bits) are stored
- * in tiles of 128 slots (2048*b bytes) as bit planes, the form the tensor-core decode kernel consumes: plane p
- * (bit p of every code) occupies bytes [2048 p, 2048 (p + 1)) of the tile; keys: 16 bytes per slot j at 16 j, bit d
- * = coordinate d; values: 16 bytes per coordinate d at 16 d, bit j = slot j.  odmkv_export_bank converts any bank
- * to the reference's byte layout. */
+ * The 8-bit bank is token-major (byte d of a slot = code of coordinate d).  The 2/3/4-bit banks are
+ * stored in tiles of 16 slots arranged for the tensor-core fragments of the decode kernel: lane
+ * (g, t) = (lane / 4, lane % 4) of a warp owns the 8*b bytes at tile + lane*8*b as 32 little-endian
+ * pair fields of 2*b bits; keys: field 4s+2odd+hi = coordinates (32t+4s+2odd, +1) of slot g+8hi;
+ * values: field 4m+2hi+a = coordinate 16m+g+8a of slots (2t+8hi, 2t+8hi+1) -- in both cases four consecutive
+ * fields are the A registers of one HMMA step.  odmkv_export_bank converts any bank to the reference's byte layout. */
 typedef struct odmkv_chunk {
     uint8_t *k_codes[ODMKV_NUM_QLEVELS];
     uint8_t *v_codes[ODMKV_NUM_QLEVELS];
@@ -214,19 +215,18 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
                       int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                       void *stream);
 
-/* Tensor-core variant of odmkv_decode_attn (same contract and arguments): the 2- and 3-bit banks are consumed as
- * bit planes by tcgen05.mma integer products (the A operand goes from registers to tensor memory, bank tiles arrive
- * in shared memory by bulk asynchronous copies); 4-bit, 8-bit, exact and tail tokens take the CUDA-core kernel in a
- * second launch on a forked stream.  The kernel is persistent: four workers of 128 threads per SM share the (b, h)
- * units evenly, at most n_splits - 1 workers overlap one unit; n_splits may go up to 128 and only bounds the workspace.
- * Every device-side wait is bounded; an expired wait sets the 32-bit status word at
- * workspace + odmkv_decode_status_offset(...) to 1 (the launcher clears it) and the results are invalid. */
-size_t odmkv_decode_status_offset(int B, int H, int G, int n_splits);
+/* Tensor-core variant of odmkv_decode_attn (same contract and arguments): the 2-, 3- and 4-bit banks
+ * are consumed with mma.sync m16n8k16 tiles straight from the tile layout; 8-bit, exact and tail
+ * tokens take the CUDA-core kernel in a second launch on a forked stream.  The kernel is persistent: it picks
+ * its own grid (one CTA pair per SM, shared evenly by the (b, h) units) such that at most n_splits CTAs overlap one
+ * unit; n_splits may go up to 128 and only bounds the workspace.
+ *   lut_scales: host float[3] or NULL (= 1.0): per level a factor s such that fp16(c * s) carries the
+ *   centroids of the 2-, 3-, 4-bit codebooks with less rounding error; divided out again in fp32. */
 int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
                           const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
                           const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
                           int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
-                          void *stream);
+                          const float *lut_scales, void *stream);
 
 /* Decode attention without a caller-supplied workspace (no counterpart in the reference).  For hosts
  * that cannot allocate device memory on the decode path -- a serving loop with a frozen memory pool, a
@@ -238,13 +238,13 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
  * resolves the array's address and should come before any stream capture.  All calls on a device share
  * the array: calls that overlap on the GPU race, so keep them on one stream.  It calls no cudaMalloc,
  * cudaFree or other routine that allocates device memory; the first decode call on a device (through any
- * entry point) also creates one helper stream and two events and sets the kernels' shared-memory attribute,
- * which is one more reason to make it before a capture. */
+ * entry point) also creates one helper stream and two events and sets the kernels' shared-memory attribute
+ * (host objects only), which is one more reason to make it before a capture. */
 size_t odmkv_decode_attn_noalloc_scratch_bytes(void);
 int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
                               const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
                               const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
-                              int out_dtype, float *lse, int n_splits, void *stream);
+                              int out_dtype, float *lse, int n_splits, const float *lut_scales, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Optional kernel timing (no counterpart in the reference).  When enabled, the launchers bracket

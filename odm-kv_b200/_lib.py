@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libodmkv_b200.so")
 
 NUM_QLEVELS = 4
 NUM_CLASSES = 6
-SEG_ALIGN = 128
+SEG_ALIGN = 16
 TILE = 128
 HEAD_DIM = 128
 MAX_LEVELS = 8
@@ -95,12 +95,11 @@ _PROTOTYPES = {
     "odmkv_export_positions": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p]),
     "odmkv_decode_attn_mma": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int,
-                                      c_void_p, c_size_t, c_void_p]),
-    "odmkv_decode_status_offset": (c_size_t, [c_int, c_int, c_int, c_int]),
+                                      c_void_p, c_size_t, POINTER(c_float), c_void_p]),
     "odmkv_decode_attn_noalloc_scratch_bytes": (c_size_t, []),
     "odmkv_decode_attn_noalloc": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
-                                          c_int, c_void_p]),
+                                          c_int, POINTER(c_float), c_void_p]),
     "odmkv_timing_enable": (None, [c_int]),
     "odmkv_timing_read": (c_int, [c_char_p, POINTER(c_double), POINTER(c_longlong)]),
     "odmkv_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),

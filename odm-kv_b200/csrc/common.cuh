@@ -119,16 +119,16 @@ __device__ inline int nearest_centroid(float y, const float *c, int k) {
 // ---- bank layouts ---------------------------------------------------------------------------------
 // 8-bit bank (li = 3): token-major, 128 bytes per slot, byte d = code of coordinate d (keys and values).
 //
-// 2/3/4-bit banks (li = 0..2, b bits per code): slots are grouped in tiles of 128 (2048*b bytes per tile), stored
-// as BIT PLANES -- plane p holds bit p of every code -- because the tensor-core decode kernel consumes planes
-// directly (decode_umma.cu).  Inside a tile, plane p occupies bytes [2048 p, 2048 (p + 1)):
-//   keys:   16 bytes per slot j at 2048 p + 16 j; bit d of those 128 bits (bit d % 8 of byte d / 8) = bit p of the
-//           code of coordinate d of slot j;
-//   values: 16 bytes per coordinate d at 2048 p + 16 d; bit j of those 128 bits = bit p of the code of coordinate d
-//           of slot j (the transpose: a word holds 32 tokens).
+// 2/3/4-bit banks (li = 0..2, b bits per code): slots are grouped in tiles of 16 (256*b bytes per tile).
+// A tile is laid out for the m16n8k16 tensor-core fragments of the decode kernel: lane (g, t) of a warp
+// (g = lane / 4, t = lane % 4) owns the 8*b bytes at tile + lane * 8 * b, as 32 "pair fields" of 2*b bits
+// (low code in the low bits), packed little-endian in ascending field order.
+//   keys:   field 4 s + 2 odd + hi holds coordinates (32 t + 4 s + 2 odd, + 1) of slot g + 8 hi, i.e. the
+//           four fields of step s are the A registers a0..a3 of that HMMA step, in order;
+//   values: field 4 m + 2 hi + a holds coordinate 16 m + g + 8 a of tokens (2 t + 8 hi, 2 t + 8 hi + 1),
+//           again a0..a3 of step m.
 // The "linear" layout (scratch and odmkv_encode_pack output) is the plain little-endian bit stream of the
 // 128 codes of one slot, 16*b bytes per slot.
-constexpr int kPlaneTile = 128;
 __host__ __device__ inline int qbits(int li) { return li == 0 ? 2 : li == 1 ? 3 : li == 2 ? 4 : 8; }
 
 __device__ inline uint32_t read_bits(const uint8_t *p, int bitoff, int nbits) {
@@ -141,20 +141,19 @@ __device__ inline uint32_t read_bits(const uint8_t *p, int bitoff, int nbits) {
 __device__ inline int k_code(const uint8_t *bank, int li, long long slot, int d) {
     if (li == 3) return bank[(size_t)slot * 128 + d];
     const int b = qbits(li);
-    const uint8_t *row = bank + (size_t)(slot >> 7) * 2048 * b + (size_t)(slot & 127) * 16 + (d >> 3);
-    int code = 0;
-    for (int p = 0; p < b; ++p) code |= ((row[(size_t)p * 2048] >> (d & 7)) & 1) << p;
-    return code;
+    const long long tile = slot >> 4;
+    const int r = (int)(slot & 15), g = r & 7, hi = r >> 3, t = d >> 5, f = (d & 31) >> 1;
+    const int field = 4 * (f >> 1) + 2 * (f & 1) + hi;
+    return (int)read_bits(bank + (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b, field * 2 * b + (d & 1) * b, b);
 }
 
 __device__ inline int v_code(const uint8_t *bank, int li, long long slot, int d) {
     if (li == 3) return bank[(size_t)slot * 128 + d];
     const int b = qbits(li);
-    const int j = (int)(slot & 127);
-    const uint8_t *row = bank + (size_t)(slot >> 7) * 2048 * b + (size_t)d * 16 + (j >> 3);
-    int code = 0;
-    for (int p = 0; p < b; ++p) code |= ((row[(size_t)p * 2048] >> (j & 7)) & 1) << p;
-    return code;
+    const long long tile = slot >> 4;
+    const int r = (int)(slot & 15), m = d >> 4, dd = d & 15, g = dd & 7, a = dd >> 3;
+    const int t = (r & 7) >> 1, e = r & 1, hi = r >> 3;
+    return (int)read_bits(bank + (size_t)tile * 256 * b + (size_t)(g * 4 + t) * 8 * b, (4 * m + hi * 2 + a) * 2 * b + e * b, b);
 }
 
 __device__ inline int linear_code(const uint8_t *rows, int li, long long slot, int d) {

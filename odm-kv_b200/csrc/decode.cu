@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
     __shared__ __align__(16) float qs[kD * GP];   // rotated queries, [i][g]
     __shared__ __align__(16) float qx[kD * GP];   // plain queries, [i][g]
     __shared__ float lut[4 * 256];
-    __shared__ float red_acc[kDecWarps][2][kD];   // one head at a time: keeps the CTA small enough to run beside the tensor-core kernel
+    __shared__ float red_acc[kDecWarps][GP][2][kD];
     __shared__ float red_m[kDecWarps][GP], red_l[kDecWarps][GP];
 
     const int bh = blockIdx.y, split = blockIdx.x;
@@ -217,37 +217,33 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
         }
     }
 
-    // ---- combine the warps of this CTA, one query head at a time
-    if (lane == 0) {
-#pragma unroll
-        for (int g = 0; g < GP; ++g) { red_m[warp][g] = st.m[g]; red_l[warp][g] = st.l[g]; }
-    }
+    // ---- combine the warps of this CTA
+    __syncthreads();
 #pragma unroll
     for (int g = 0; g < GP; ++g) {
-        __syncthreads();   // the previous head's sums have been read
+        if (lane == 0) { red_m[warp][g] = st.m[g]; red_l[warp][g] = st.l[g]; }
 #pragma unroll
         for (int d = 0; d < 4; ++d) {
-            red_acc[warp][0][4 * lane + d] = st.ar[g][d];
-            red_acc[warp][1][4 * lane + d] = st.ae[g][d];
+            red_acc[warp][g][0][4 * lane + d] = st.ar[g][d];
+            red_acc[warp][g][1][4 * lane + d] = st.ae[g][d];
         }
-        __syncthreads();
+    }
+    __syncthreads();
+    for (int e = tid; e < GP * 2 * kD; e += kDecThreads) {
+        const int g = e / (2 * kD), rest = e % (2 * kD);
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, red_m[w][g]);
-        float f[kDecWarps], l = 0.f;
+        float v = 0.f, l = 0.f;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) {
-            f[w] = red_m[w][g] == -INFINITY ? 0.f : __expf(red_m[w][g] - mm);
-            l += red_l[w][g] * f[w];
+            float f = red_m[w][g] == -INFINITY ? 0.f : __expf(red_m[w][g] - mm);
+            v += (&red_acc[w][g][0][0])[rest] * f;
+            l += red_l[w][g] * f;
         }
         const size_t pi = ((size_t)bh * a.nslots + a.slot_base + split) * GP + g;
-        for (int rest = tid; rest < 2 * kD; rest += kDecThreads) {
-            float v = 0.f;
-#pragma unroll
-            for (int w = 0; w < kDecWarps; ++w) v += (&red_acc[w][0][0])[rest] * f[w];
-            a.part_acc[pi * 2 * kD + rest] = v;
-        }
-        if (tid == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = l; }
+        a.part_acc[pi * 2 * kD + rest] = v;
+        if (rest == 0) { a.part_ml[pi * 2] = mm; a.part_ml[pi * 2 + 1] = l; }
     }
 }
 
@@ -367,8 +363,8 @@ using namespace odmkv;
 extern "C" {
 
 int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
-    // Partial slots per (sample, KV head) that let the tensor-core kernel run two pipelines per SM of a
-    // 148-SM device: the workers that can overlap one unit, plus one.  The plain kernel uses the same number of
+    // Partial slots per (sample, KV head) that let the tensor-core kernel run one CTA pair per SM of a
+    // 148-SM device: the CTAs that can overlap one unit, plus one.  The plain kernel uses the same number of
     // equal splits (at most 64), shortened for short contexts.
     if (B <= 0 || H <= 0) return 1;
     const long long BH = (long long)B * H;
@@ -384,12 +380,6 @@ int odmkv_decode_default_splits(int B, int H, long long max_tokens_per_head) {
 size_t odmkv_decode_workspace_bytes(int B, int H, int G, int n_splits) {
     if (B <= 0 || H <= 0 || G <= 0 || n_splits <= 0) return 0;
     return decode_ws_layout(B, H, G, n_splits + 8, nullptr, nullptr) + 256;
-}
-
-// the status word is the first word of the workspace, whatever the sizes
-size_t odmkv_decode_status_offset(int B, int H, int G, int n_splits) {
-    (void)B; (void)H; (void)G; (void)n_splits;
-    return 0;
 }
 
 int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,

@@ -1,4 +1,4 @@
-// Pieces shared by the two decode-attention launchers (decode.cu, decode_umma.cu).
+// Pieces shared by the two decode-attention launchers (decode.cu, decode_mma.cu).
 #pragma once
 #include "common.cuh"
 
@@ -17,7 +17,6 @@ struct DecodeWs {
     float *qf;        // [B*H*G, 128]  q as fp32
     float *part_ml;   // [BH, nslots, GP, 2]
     float *part_acc;  // [BH, nslots, GP, 2, 128]
-    unsigned *status; // one word: set to 1 by a kernel whose bounded wait expired
 };
 
 struct DecodeArgs {
@@ -43,10 +42,9 @@ inline size_t decode_ws_layout(int B, int H, int G, int nslots, DecodeWs *ws, un
     const size_t BH = (size_t)B * H, GP = round_gp(G);
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
-    size_t o_st = take(512), o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nslots * GP * 2 * 4),
+    size_t o_qr = take(BH * G * kD * 4), o_qf = take(BH * G * kD * 4), o_ml = take(BH * nslots * GP * 2 * 4),
            o_acc = take(BH * nslots * GP * 2 * kD * 4);
     if (ws && base) {
-        ws->status = (unsigned *)(base + o_st);
         ws->qrot = (float *)(base + o_qr); ws->qf = (float *)(base + o_qf);
         ws->part_ml = (float *)(base + o_ml); ws->part_acc = (float *)(base + o_acc);
     }

@@ -53,14 +53,14 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
                           const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
                           const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
                           int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
-                          void *stream);
+                          const float *lut_scales, void *stream);
 
 size_t odmkv_decode_attn_noalloc_scratch_bytes(void) { return kNoAllocScratchBytes; }
 
 int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
                               const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
                               const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
-                              int out_dtype, float *lse, int n_splits, void *stream) {
+                              int out_dtype, float *lse, int n_splits, const float *lut_scales, void *stream) {
     if (B <= 0 || H <= 0 || G <= 0 || G > 8 || n_splits <= 0 || n_splits > 128) return ODMKV_ERR_SHAPE;
     // the tensor-core launcher adds up to 8 partial slots for exact / tail tokens
     if (decode_ws_layout(B, H, G, n_splits + 8, nullptr, nullptr) > kNoAllocScratchBytes) return ODMKV_ERR_LIMIT;
@@ -68,7 +68,7 @@ int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chu
     int rc = scratch_for_current_device(&scratch);
     if (rc) return rc;
     return odmkv_decode_attn_mma(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len, tail_cap, pi_k, pi_v, codebooks,
-                                 B, H, G, scale, out, out_dtype, lse, n_splits, scratch, kNoAllocScratchBytes, stream);
+                                 B, H, G, scale, out, out_dtype, lse, n_splits, scratch, kNoAllocScratchBytes, lut_scales, stream);
 }
 
 }  // extern "C"

@@ -61,7 +61,7 @@ __global__ void scan_tiles_kernel(const int32_t *__restrict__ tile_counts, int n
     if (lane == 0) seg_count[c * BH + bh] = carry;
 }
 
-// one block; warp c lays out the (b, h) segments of class c on kSegAlign-slot boundaries
+// one block; warp c lays out the (b, h) segments of class c on 16-slot boundaries
 __global__ void scan_segs_kernel(const int32_t *__restrict__ seg_count, int BH, int32_t *__restrict__ seg_start,
                                  int32_t *__restrict__ totals) {
     const int c = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -636,7 +636,7 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     }
 }
 
-// zero the padding slots between a segment's last token and the next kSegAlign-slot boundary
+// zero the padding slots between a segment's last token and the next 16-slot boundary
 template <int DT>
 __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *k_scratch0, uint8_t *k_scratch1, uint8_t *k_scratch2,
                                     uint8_t *v_scratch0, uint8_t *v_scratch1, uint8_t *v_scratch2) {
@@ -676,69 +676,37 @@ __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *k_scratch0, u
     }
 }
 
-// Re-tile the codes of one 2/3/4-bit bank: linear scratch rows -> bit-plane tiles (layout in common.cuh).
-// One warp per tile of 128 slots.  A warp-wide ballot is a 32 x 1 bit transpose, so a plane word is one ballot of
-// "bit p of my code":
-//   keys:   lane = coordinate inside a 32-coordinate group of one slot; the four words of a (slot, plane) land in
-//           lanes 0..3, which store them;
-//   values: lane = slot inside a 32-slot group, each lane keeps its own linear row in registers; the word of
-//           (coordinate d, plane, slot group) lands in lane d % 32, and after the four slot groups every lane
-//           stores 16 bytes per (coordinate, plane).
+// re-tile the codes of one 2/3/4-bit bank: linear scratch rows -> tensor-core tile layout
+// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes; KEYS selects the field map)
 template <int B, bool KEYS>
-__global__ void __launch_bounds__(256) retile_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
+__global__ void retile_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
     constexpr int LI = B - 2;
-    constexpr int kRowWords = 4 * B;   // 16 * B bytes per linear row
-    const int lane = threadIdx.x & 31;
+    const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     for (int tile = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tile < ntiles; tile += gridDim.x * (blockDim.x >> 5)) {
-        uint8_t *tbase = bank + (size_t)tile * 2048 * B;
-        if (KEYS) {
-            for (int j = 0; j < kPlaneTile; ++j) {
-                const long long slot = (long long)tile * kPlaneTile + j;
-                uint32_t mine[B];
+        uint32_t out[2 * B];
 #pragma unroll
-                for (int p = 0; p < B; ++p) mine[p] = 0;
+        for (int w = 0; w < 2 * B; ++w) out[w] = 0;
 #pragma unroll
-                for (int wi = 0; wi < 4; ++wi) {
-                    const uint32_t code = (uint32_t)linear_code(rows, LI, slot, 32 * wi + lane);
-#pragma unroll
-                    for (int p = 0; p < B; ++p) {
-                        const uint32_t word = __ballot_sync(0xffffffffu, (code >> p) & 1u);
-                        if (lane == wi) mine[p] = word;
-                    }
-                }
-                if (lane < 4) {
-#pragma unroll
-                    for (int p = 0; p < B; ++p) *reinterpret_cast<uint32_t *>(tbase + p * 2048 + j * 16 + lane * 4) = mine[p];
-                }
+        for (int f = 0; f < 32; ++f) {
+            uint32_t field;
+            if (KEYS) {
+                const int s = f >> 2, odd = (f >> 1) & 1, hi = f & 1;
+                const long long slot = (long long)tile * 16 + g + 8 * hi;
+                const int dim = 32 * t + 4 * s + 2 * odd;
+                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot, dim + 1) << B);
+            } else {
+                const int m = f >> 2, hi = (f >> 1) & 1, a = f & 1;
+                const int dim = 16 * m + g + 8 * a;
+                const long long slot = (long long)tile * 16 + 2 * t + 8 * hi;
+                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot + 1, dim) << B);
             }
-        } else {
-            uint32_t out[B][4][4];   // [plane][coordinate group of 32][slot group]: word of coordinate 32 cg + lane
-#pragma unroll
-            for (int sg = 0; sg < 4; ++sg) {
-                const long long slot = (long long)tile * kPlaneTile + 32 * sg + lane;
-                uint32_t w[kRowWords];
-                const uint32_t *src = reinterpret_cast<const uint32_t *>(rows + (size_t)slot * 16 * B);
-#pragma unroll
-                for (int i = 0; i < kRowWords; ++i) w[i] = src[i];
-#pragma unroll
-                for (int d = 0; d < kD; ++d) {
-                    const int off = d * B, wi = off >> 5, sh = off & 31;
-                    uint32_t code = w[wi] >> sh;
-                    if (sh + B > 32) code |= w[wi + 1] << (32 - sh);
-#pragma unroll
-                    for (int p = 0; p < B; ++p) {
-                        const uint32_t word = __ballot_sync(0xffffffffu, (code >> p) & 1u);
-                        if (lane == (d & 31)) out[p][d >> 5][sg] = word;
-                    }
-                }
-            }
-#pragma unroll
-            for (int p = 0; p < B; ++p)
-#pragma unroll
-                for (int cg = 0; cg < 4; ++cg)
-                    *reinterpret_cast<uint4 *>(tbase + p * 2048 + (32 * cg + lane) * 16) =
-                        make_uint4(out[p][cg][0], out[p][cg][1], out[p][cg][2], out[p][cg][3]);
+            const int off = f * 2 * B, w = off >> 5, sh = off & 31;
+            out[w] |= field << sh;
+            if (sh + 2 * B > 32) out[w + 1] |= field >> (32 - sh);
         }
+        uint32_t *dst = reinterpret_cast<uint32_t *>(bank + (size_t)tile * 256 * B + (size_t)lane * 8 * B);
+#pragma unroll
+        for (int w = 0; w < 2 * B; ++w) dst[w] = out[w];
     }
 }
 
@@ -1005,7 +973,7 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     if (rc) return rc;
     if (((uintptr_t)workspace & 255) != 0 || workspace_bytes < odmkv_quantize_workspace_bytes(chunk->cap)) return ODMKV_ERR_WORKSPACE;
     for (int c = 1; c <= 3; ++c)
-        if (chunk->cap[c] % kPlaneTile != 0) return ODMKV_ERR_SHAPE;
+        if (chunk->cap[c] % 16 != 0) return ODMKV_ERR_SHAPE;
     if (chunk->T <= 0) return ODMKV_ERR_SHAPE;
     if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
     cudaStream_t st = (cudaStream_t)stream;
@@ -1039,9 +1007,9 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     timing_end(st);
     if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
 #undef ODMKV_LAUNCH_Q
-    // 2/3/4-bit banks: linear scratch -> bit-plane tiles of 128 slots
+    // 2/3/4-bit banks: linear scratch -> tile layout
     for (int li = 0; li < 3; ++li) {
-        const int ntile = chunk->cap[li + 1] / kPlaneTile;
+        const int ntile = chunk->cap[li + 1] / 16;
         if (ntile <= 0) continue;
         int rg = (ntile + 7) / 8;
         if (rg > 16 * num_sms()) rg = 16 * num_sms();

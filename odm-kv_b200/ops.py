@@ -363,17 +363,35 @@ def export_exact_rows(ch: PackedChunk) -> Tuple[torch.Tensor, torch.Tensor, torc
 # decode attention
 # ---------------------------------------------------------------------------------------------
 
+_LUT_SCALES = None
+
+
+def lut_scales():
+    """Per level (2, 3, 4 bits) a factor s in [1, 2) that minimises the worst relative error of
+    fp16(c * s) / s over the level's centroids; the tensor-core kernel stores fp16(c * s) in its tables."""
+    global _LUT_SCALES
+    if _LUT_SCALES is None:
+        cand = np.linspace(1.0, 2.0, 40001, dtype=np.float64)[:-1]
+        best = []
+        for b in QLEVEL_BITS[:3]:
+            c = codebook_f32(b).astype(np.float64)
+            prod = (c[None, :] * cand[:, None]).astype(np.float32)
+            back = prod.astype(np.float16).astype(np.float64) / cand[:, None]
+            err = np.abs(back - c[None, :]) / np.abs(c[None, :])
+            best.append(float(np.float32(cand[int(np.argmin(err.max(axis=1)))])))
+        _LUT_SCALES = (ctypes.c_float * 3)(*best)
+    return _LUT_SCALES
+
+
 def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tensor, pi_v: torch.Tensor,
                 tail_k: Optional[torch.Tensor] = None, tail_v: Optional[torch.Tensor] = None, tail_len: int = 0,
                 scale: Optional[float] = None, n_splits: int = 0, out_dtype: Optional[torch.dtype] = None,
-                return_lse: bool = False, cache_dtype: Optional[torch.dtype] = None, plain: bool = False,
-                check_status: bool = False):
+                return_lse: bool = False, cache_dtype: Optional[torch.dtype] = None, plain: bool = False):
     """q [B, H*G, 128] -> out [B, H*G, 128]: softmax(q K_hat^T scale) V_hat over every token stored in
     ``chunks`` plus the first ``tail_len`` tokens of the dense tail [B, H, cap, 128].
 
-    Calls ``odmkv_decode_attn_mma`` (tensor cores for the 2- and 3-bit banks).  ``plain=True`` calls
-    ``odmkv_decode_attn`` instead, the CUDA-core reader of every level that the tests use as a second opinion.
-    ``check_status`` synchronises and raises when a bounded device-side wait of the tensor-core kernel expired."""
+    Calls ``odmkv_decode_attn_mma`` (tensor cores for the 2-, 3- and 4-bit banks).  ``plain=True`` calls
+    ``odmkv_decode_attn`` instead, the CUDA-core reader of every level that the tests use as a second opinion."""
     require_cuda(q, "query")
     if q.dim() != 3 or q.shape[-1] != HEAD_DIM:
         raise ValueError(f"expected query [B, Hq, {HEAD_DIM}], got {tuple(q.shape)}")
@@ -414,9 +432,5 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
     if plain:
         check(L.odmkv_decode_attn(*common, stream_ptr(dev)), "odmkv_decode_attn")
     else:
-        check(L.odmkv_decode_attn_mma(*common, stream_ptr(dev)), "odmkv_decode_attn_mma")
-        if check_status:
-            off = L.odmkv_decode_status_offset(B, H, G, int(n_splits))
-            if int(ws[off:off + 4].view(torch.int32).item()) != 0:
-                raise OdmkvError("odmkv_decode_attn_mma: a bounded device-side wait expired; the output is invalid")
+        check(L.odmkv_decode_attn_mma(*common, lut_scales(), stream_ptr(dev)), "odmkv_decode_attn_mma")
     return (out, lse) if return_lse else out

@@ -273,8 +273,7 @@ def test_decode_attn_matches_dense_attention_over_dequantised_cache(pkg, orc, cu
     Kh, Vh, keep = orc.materialize(st)
     want = orc.decode_attention(qd.float().numpy(), Kh, Vh, keep)
     for ns in (0, 1, 3):
-        got = pkg.ops.decode_attn(qd.to(cuda), [ch], pk, pv, n_splits=ns, out_dtype=torch.float32, plain=plain,
-                                  check_status=not plain).cpu().numpy()
+        got = pkg.ops.decode_attn(qd.to(cuda), [ch], pk, pv, n_splits=ns, out_dtype=torch.float32, plain=plain).cpu().numpy()
         assert_attn_close(got, want, (ns,))
 
 

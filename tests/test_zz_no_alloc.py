@@ -23,7 +23,8 @@ def call_noalloc(pkg, q, chunks, pk, pv, n_splits, tail_k=None, tail_v=None, tai
     rc = L.odmkv_decode_attn_noalloc(lib_.ptr(q), lib_.dtype_code(q.dtype), arr, len(chunks), lib_.dtype_code(chunks[0].dtype),
                                      lib_.ptr(tail_k), lib_.ptr(tail_v), tail_len, 0 if tail_k is None else tail_k.shape[2],
                                      lib_.ptr(pk), lib_.ptr(pv), lib_.ptr(pkg.ops.codebook_table(q.device)), B, H, Hq // H,
-                                     1.0 / 128 ** 0.5, lib_.ptr(out), lib_.DTYPE_F32, None, n_splits, lib_.stream_ptr(q.device))
+                                     1.0 / 128 ** 0.5, lib_.ptr(out), lib_.DTYPE_F32, None, n_splits, pkg.ops.lut_scales(),
+                                     lib_.stream_ptr(q.device))
     return rc, out
 
 
