@@ -56,7 +56,7 @@ const char *odmkv_status_string(int status);
  * "global" (kvquant/scorer.py:321-325): per sample, softmax over the positions after the sinks
  * of mu.k/sqrt(d), mean over the G query heads of a KV head, then
  * s = (p + eps)^2 (|v|^2 + |k|^2/d |v - o|^2); sink slots receive the maximum over the sample.
- *   K, V   [B, H, T, 128] contiguous, dtype code `dtype`
+ *   K, V   [B, H, T, 128] contiguous, dtype code `dtype`, 16-byte aligned (ODMKV_ERR_ARG otherwise)
  *   mu     [B, H*G, 128] fp32 -- the averaged-RoPE'd mean query (query head index is KV-major)
  *   scores [B, H, T] fp32 out
  * T <= n_sink gives all ones (kvquant/scorer.py:388-389).

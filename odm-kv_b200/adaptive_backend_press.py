@@ -207,6 +207,9 @@ class TurboQuantPerTokenBackendPress:
         levels = sorted(set(self.bit_levels) | {16})
         lv = torch.tensor(levels, device=bits.device, dtype=bits.dtype)
         counts = (bulk.reshape(B * H_kv, T_bulk, 1) == lv.view(1, 1, -1)).sum(dim=1).cpu()   # one read-back
+        status = getattr(self.scorer, "last_status", None)
+        if status is not None and int(status.item()) != 0:   # already synchronised by the read-back above
+            raise ops._lib.OdmkvError("the scorer reported an expired bounded wait: the scores of this layer are invalid")
         for row_idx in range(B * H_kv):
             h = row_idx % H_kv
             row = counts[row_idx]

@@ -41,6 +41,16 @@ def packed_decode(module, query: torch.Tensor, key: torch.Tensor, value: torch.T
     return out.unsqueeze(1)   # [B, 1, Hq, d], the layout attention functions return
 
 
+def _mask_is_open(attention_mask) -> bool:
+    """True when the mask hides no key from the query (no padding in the batch).  The packed decode kernels take
+    no mask, so a call with hidden keys keeps the reference's route (fake keys + stock attention)."""
+    if attention_mask is None:
+        return True
+    if attention_mask.dtype == torch.bool:
+        return bool(attention_mask.all())
+    return not bool((attention_mask != 0).any())
+
+
 def _attention_patch(func):
     if getattr(func, _PATCH_ATTR, False):
         return func
@@ -52,7 +62,7 @@ def _attention_patch(func):
             module.masked_key_indices = None
             module._odmkv_state = None
         elif (state is not None and query.shape[2] == 1 and query.is_cuda and key.shape[2] >= state.seq_len
-              and getattr(module, "_odmkv_decode", True)):
+              and getattr(module, "_odmkv_decode", True) and _mask_is_open(attention_mask)):
             scaling = kwargs.get("scaling", None)
             if scaling is None:
                 scaling = getattr(module, "scaling", None)

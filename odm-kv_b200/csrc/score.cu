@@ -736,6 +736,7 @@ int odmkv_score_prefill(const void *K, const void *V, int dtype, const float *mu
     }
     if (!workspace) return ODMKV_ERR_ARG;
     if (((uintptr_t)workspace & 255) != 0) return ODMKV_ERR_WORKSPACE;
+    if ((((uintptr_t)K | (uintptr_t)V) & 15) != 0) return ODMKV_ERR_ARG;   // rows are sources of 16-byte aligned bulk copies
     ScoreWs ws;
     size_t need = score_ws_layout(B, H, G, T, n_sink, &ws, (unsigned char *)workspace);
     if (workspace_bytes < need) return ODMKV_ERR_WORKSPACE;

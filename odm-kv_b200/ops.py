@@ -49,9 +49,11 @@ def codebook_table(device, dim: int = HEAD_DIM) -> torch.Tensor:
 # ---------------------------------------------------------------------------------------------
 
 def score_prefill(K: torch.Tensor, V: torch.Tensor, mu: torch.Tensor, n_sink: int = 4, eps: float = 1e-2,
-                  check_status: bool = False) -> torch.Tensor:
+                  check_status: bool = False, return_status: bool = False):
     """K, V [B, H, T, 128] (fp16/bf16/fp32), mu [B, H*G, 128] fp32 -> scores [B, H, T] fp32.
-    ``check_status`` synchronises and raises if a sweep reported an expired wait on one of its bulk copies."""
+    ``check_status`` synchronises and raises if a sweep reported an expired wait on one of its bulk copies;
+    ``return_status`` returns ``(scores, status)`` instead, ``status`` a one-element int32 device tensor (0 = clean)
+    that the caller can read at a point where it synchronises anyway."""
     require_cuda(K, "keys")
     if K.shape != V.shape or K.dim() != 4 or K.shape[-1] != HEAD_DIM:
         raise ValueError(f"expected keys/values [B, H, T, {HEAD_DIM}], got {tuple(K.shape)} / {tuple(V.shape)}")
@@ -60,17 +62,23 @@ def score_prefill(K: torch.Tensor, V: torch.Tensor, mu: torch.Tensor, n_sink: in
         raise ValueError(f"expected mean query [B, H*G, {HEAD_DIM}], got {tuple(mu.shape)}")
     G = mu.shape[1] // H
     K, V = K.contiguous(), V.contiguous()
+    if K.data_ptr() % 16:   # the sweeps stream rows with bulk copies, which need 16-byte aligned sources
+        K = K.clone()
+    if V.data_ptr() % 16:
+        V = V.clone()
     mu = mu.to(device=K.device, dtype=torch.float32).contiguous()
     scores = torch.empty(B, H, T, dtype=torch.float32, device=K.device)
     nbytes = lib().odmkv_score_workspace_bytes(B, H, G, T)
     ws = _ws(nbytes, K.device)
     check(lib().odmkv_score_prefill(ptr(K), ptr(V), dtype_code(K.dtype), ptr(mu), B, H, G, T, int(n_sink), float(eps),
                                     ptr(scores), ptr(ws), ws.numel(), stream_ptr(K.device)), "odmkv_score_prefill")
-    if check_status and T > n_sink:
+    status = None
+    if T > n_sink:
         off = lib().odmkv_score_status_offset(B, H, G, T, int(n_sink))
-        if int(ws[off:off + 4].view(torch.int32).item()) != 0:
+        status = ws[off:off + 4].view(torch.int32)
+        if check_status and int(status.item()) != 0:
             raise OdmkvError("odmkv_score_prefill: a bounded wait on a bulk copy expired; the scores are invalid")
-    return scores
+    return (scores, status) if return_status else scores
 
 
 def score_with_attn(K: torch.Tensor, V: torch.Tensor, p: torch.Tensor, eps: float = 1e-2) -> torch.Tensor:

@@ -198,7 +198,9 @@ class RiskScorer(ExpectedAttentionScorer):
         except (AttributeError, NotImplementedError, ValueError):
             # same defensive fallback as the reference (kvquant/scorer.py:390-393): norm scoring
             return torch.stack([self._fallback.score_prefill(k, v, layer_idx) for k, v in zip(keys, values)])
-        scores = ops.score_prefill(keys, values, mu.float(), self.n_sink, float(self.epsilon))
+        # the sweeps' status word (non-zero: a bounded wait expired, scores invalid) is kept for the caller to read
+        # where it synchronises anyway (the press does, when it records the level ratios)
+        scores, self.last_status = ops.score_prefill(keys, values, mu.float(), self.n_sink, float(self.epsilon), return_status=True)
         return scores if self.normalize_grain == "global" else torch.stack([self._maybe_normalize(s) for s in scores])
 
     def score_prefill(self, keys, values, layer_idx, *, module=None, hidden_states=None):

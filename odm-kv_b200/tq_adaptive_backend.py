@@ -225,11 +225,16 @@ class TurboQuantAdaptiveKVCacheState:
         bits = torch.where(known, bits, torch.full_like(bits, 16))   # unrouted tokens stay exact (529-532)
         k = self.tail_k[:, :, lo:self.tail_len].contiguous()
         v = self.tail_v[:, :, lo:self.tail_len].contiguous()
+        if lo > 0:
+            # Tokens in front of the buffer (a pinned multi-token pass) stay exact but leave the tail as a chunk of
+            # their own, so that the tail is empty afterwards and tail index i keeps meaning position tail_start + i.
+            pinned = torch.full((B, H, lo), 16, dtype=torch.int32, device=self.device)
+            self.chunks.append(ops.quantize_pack(self.tail_k[:, :, :lo].contiguous(), self.tail_v[:, :, :lo].contiguous(), pinned,
+                                                 self.pi_k, self.pi_v, t_offset=self.tail_start))
         chunk = ops.quantize_pack(k, v, bits, self.pi_k, self.pi_v, t_offset=self.tail_start + lo)
         self.chunks.append(chunk)
-        self.tail_len = lo
-        if self.tail_len == 0:
-            self.tail_start = self.seq_len
+        self.tail_len = 0
+        self.tail_start = self.seq_len
         return chunk
 
     # ------------------------------------------------------------------ reads

@@ -12,7 +12,9 @@ fp16 inputs (its CPU torch path).
 
 Outputs (``tests/golden/*.npz``) hold the inputs of the small cases in full, the reference's
 scores, bit allocations, banks, dequantised cache and dense decode attention, and for the larger
-"config 0" case digests and samples only (its inputs are regenerated from the seed).  The script
+"config 0" case the scores, bit allocations, digests and samples (its inputs are regenerated from the seed); two
+"press" cases record where the reference press puts every token of a tiny random-init Llama after prefill, an
+optional question pass and decode steps through the decode buffer.  The script
 also runs the oracle on the same inputs and stores how many values differ, so the fixtures
 document where the oracle and the reference legitimately part (summation order of the rotation).
 """
@@ -71,7 +73,7 @@ def sha(a: np.ndarray) -> str:
     return hashlib.sha1(np.ascontiguousarray(a).tobytes()).hexdigest()
 
 
-def run_case(name, B, H, G, T, seed, targets, store_inputs, outdir, layer_idx=0):
+def run_case(name, B, H, G, T, seed, targets, store_inputs, outdir, layer_idx=0, store_scores_bits=False):
     from kvquant.scorer import RiskScorer
     from kvquant.allocator import optimal_scores_to_bits, calibrate_epsilon
     from kvquant.tq_adaptive_backend import TurboQuantAdaptiveKVCacheState
@@ -116,9 +118,9 @@ def run_case(name, B, H, G, T, seed, targets, store_inputs, outdir, layer_idx=0)
     out["scores_oracle_max_rel"] = np.array(rel.max())
     print(f"[{name}] scores: min {scores.min():.7g} max {scores.max():.7g} sum {scores.astype(np.float64).sum():.8g} "
           f"oracle max rel {rel.max():.3g}")
-    if store_inputs:
+    if store_inputs or store_scores_bits:
         out["scores"] = scores
-    else:
+    if not store_inputs:
         out["scores_sample"] = scores[:, :, ::97].copy()
         out["scores_stats"] = np.array([scores.min(), scores.max(), scores.astype(np.float64).sum()], np.float64)
 
@@ -145,7 +147,7 @@ def run_case(name, B, H, G, T, seed, targets, store_inputs, outdir, layer_idx=0)
         out[f"{tag}_bits_oracle_mismatch"] = np.array(o_mismatch)
         out[f"{tag}_bits_sha"] = np.frombuffer(sha(bits).encode(), np.uint8)
         out[f"{tag}_bits_hist"] = np.array([hist[l] for l in LEVELS], np.int64)
-        if store_inputs:
+        if store_inputs or store_scores_bits:
             out[f"{tag}_bits"] = bits.astype(np.int8)
 
         # ---- window override + state.prefill (adaptive_backend_press.py:306-316)
@@ -250,17 +252,98 @@ def kats(outdir):
     print("wrote kats.npz")
 
 
+def tiny_llama(dtype=torch.float32, layers=2):
+    """The random-init model the press tests use (same seed and initialisation on either side)."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(vocab_size=512, hidden_size=512, intermediate_size=1024, num_hidden_layers=layers, num_attention_heads=8,
+                      num_key_value_heads=2, head_dim=128, max_position_embeddings=4096, rope_theta=10000.0,
+                      attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg)
+    for p in model.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    return model.to(dtype).eval()
+
+
+def press_inputs(B, T, n_question, n_decode, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, 512, (B, T), generator=g)
+    qids = torch.randint(0, 512, (B, n_question), generator=g) if n_question else None
+    toks = torch.randint(0, 512, (B, n_decode), generator=g)   # teacher-forced decode tokens
+    return ids, qids, toks
+
+
+def state_bits_map(state, B, H, T_total):
+    """[B, H, T_total] int8: 0 evicted, 2/3/4/8 quantised level, 16 exact, -1 not stored."""
+    m = np.full((B, H, T_total), -1, np.int8)
+    mp = state._masked_positions
+    if mp.numel():
+        mp = mp.cpu().numpy()
+        m[mp[:, 0], mp[:, 1], mp[:, 2]] = 0
+    for level, bank in state._quantized_banks.items():
+        if bank.size:
+            p = bank.positions.cpu().numpy()
+            m[p[:, 0], p[:, 1], p[:, 2]] = level
+    eb = state._exact_bank
+    if eb.size:
+        p = eb.positions.cpu().numpy()
+        m[p[:, 0], p[:, 1], p[:, 2]] = 16
+    return m
+
+
+@torch.no_grad()
+def press_case(name, B, T, n_question, n_decode, buffer_size, outdir, target=2.6):
+    """The reference press on the tiny model (CPU, fp32): prefill, an optional multi-token question pass, then
+    single-token decode steps through the decode buffer; records where every token ended up."""
+    from transformers import DynamicCache
+    from benchmark.core.press_factory import make_press
+    model = tiny_llama()
+    press = make_press({"mode": "backend_per_token", "bits": list(LEVELS), "target_avg_bits": target, "eviction_cost": EVICTION_COST}, seed=SEED)
+    press.buffer_size = buffer_size
+    ids, qids, toks = press_inputs(B, T, n_question, n_decode, seed=11)
+    cache = DynamicCache()
+    out = {"meta": np.array([B, T, n_question, n_decode, buffer_size, 11], np.int64), "target": np.array(target)}
+    with press(model):
+        model.model(input_ids=ids, past_key_values=cache)
+        for li in range(len(model.model.layers)):
+            out[f"prefill_bits_L{li}"] = state_bits_map(press._states[li], B, 2, T)
+        if qids is not None:
+            model(input_ids=qids, past_key_values=cache)
+        logits = None
+        for s in range(n_decode):
+            logits = model(input_ids=toks[:, s:s + 1], past_key_values=cache).logits
+        T_total = T + n_question + n_decode
+        for li in range(len(model.model.layers)):
+            st = press._states[li]
+            assert st.seq_len == T_total
+            out[f"final_bits_L{li}"] = state_bits_map(st, B, 2, T_total)
+            out[f"buffer_L{li}"] = np.array([press._buffer_start_seqs[li], press._buffer_counts[li]], np.int64)
+        out["last_logits"] = logits[:, -1].float().numpy()
+    hist = {int(v): int((out["final_bits_L0"] == v).sum()) for v in np.unique(out["final_bits_L0"])}
+    print(f"[{name}] final layer-0 placement {hist}, buffer {out['buffer_L0']}")
+    path = os.path.join(outdir, f"{name}.npz")
+    np.savez_compressed(path, **out)
+    print(f"[{name}] wrote {path} ({os.path.getsize(path) / 1024:.0f} KiB)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds kvquant/)")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"))
+    ap.add_argument("--only-press", action="store_true", help="regenerate the two press fixtures only")
     args = ap.parse_args()
     torch.set_num_threads(os.cpu_count() or 1)
     install_reference(args.reference)
+    if args.only_press:
+        press_case("press_b1_question", B=1, T=160, n_question=6, n_decode=40, buffer_size=16, outdir=args.out)
+        press_case("press_b2", B=2, T=150, n_question=0, n_decode=36, buffer_size=16, outdir=args.out)
+        return
     kats(args.out)
     run_case("small_g4", B=1, H=2, G=4, T=320, seed=1, targets=(2.0, 3.0), store_inputs=True, outdir=args.out)
     run_case("small_g7_b2", B=2, H=2, G=7, T=200, seed=2, targets=(2.0,), store_inputs=True, outdir=args.out, layer_idx=1)
-    run_case("config0", B=1, H=8, G=4, T=4096, seed=0, targets=(2.0, 3.0), store_inputs=False, outdir=args.out)
+    run_case("config0", B=1, H=8, G=4, T=4096, seed=0, targets=(2.0, 3.0), store_inputs=False, outdir=args.out, store_scores_bits=True)
+    press_case("press_b1_question", B=1, T=160, n_question=6, n_decode=40, buffer_size=16, outdir=args.out)
+    press_case("press_b2", B=2, T=150, n_question=0, n_decode=36, buffer_size=16, outdir=args.out)
 
 
 if __name__ == "__main__":
