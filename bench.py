@@ -47,9 +47,23 @@ def parse():
     ap.add_argument("--group", type=int, default=4)
     ap.add_argument("--target-bits", type=float, default=2.0)
     ap.add_argument("--splits", type=int, default=0)
+    ap.add_argument("--preset", default=None, choices=["config2", "config3-layer", "config4-layer"],
+                    help="head shape and batch of one layer of a BASELINE configuration: config2 = GQA 32/8 batch 8 (default), "
+                         "config3-layer = 28/4 batch 16 (Qwen2.5-7B shape), config4-layer = 64/8 batch 8 (Llama-3.1-70B shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
-    return ap.parse_args()
+    args = ap.parse_args()
+    if args.preset == "config3-layer":
+        args.kv_heads, args.group, args.batch = 4, 7, 16
+    elif args.preset == "config4-layer":
+        args.kv_heads, args.group, args.batch = 8, 8, 8
+    return args
+
+
+def shared_config(args) -> dict:
+    """The configuration both arms report (identical keys and values)."""
+    return {"workload": workload_name(args.ctx, args.batch, args.kv_heads, args.group, args.target_bits),
+            "l2": "inputs larger than L2: the packed cache of a step is re-read from HBM every step, no explicit flush"}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -154,27 +168,62 @@ def cpu_reference_leg(ctx, H, G, keep_frac, bytes_per_unit, steps, warmup, seed=
 # reference arm
 # ------------------------------------------------------------------------------------------------
 
+def host_threads() -> int:
+    """Every host core for the numpy/BLAS baseline, whatever the launcher exported (torch.distributed.run sets
+    OMP_NUM_THREADS=1).  Must run before numpy is imported."""
+    n = os.cpu_count() or 1
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = str(n)
+    return n
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
+    cores = host_threads()
     bpt = algorithmic_bytes_per_token_head(args.target_bits)
     bytes_per_unit = bpt * args.ctx
-    steps = max(1, min(args.steps, 10))
-    gbs, sec, sample = cpu_reference_leg(args.ctx, args.kv_heads, args.group, 0.883, bytes_per_unit, steps, min(args.warmup, 1))
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    gbs, sec, sample = cpu_reference_leg(args.ctx, args.kv_heads, args.group, 0.883, bytes_per_unit, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
-        "warmup": min(args.warmup, 1), "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(args.ctx, args.batch, args.kv_heads, args.group, args.target_bits),
-                   "timing": "host wall clock; each step is a bounded sample (one batch element, all KV heads) scaled per (sample, KV head) unit",
-                   "reference_path": "dense fp32 softmax(q K^T) V over the dequantised cache with evicted keys masked, as the reference's decode step does on CPU"},
+        "config": shared_config(args),
+        "detail": {"timing": "host wall clock; each step is a bounded sample (one batch element, all KV heads) scaled per (sample, KV head) unit",
+                   "reference_path": "dense fp32 softmax(q K^T) V over the dequantised cache with evicted keys masked, as the reference's "
+                                     "decode step does on CPU; numpy restatement (the reference is Python and is not present on the GPU box)",
+                   "host_threads": cores},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
+
+
+def cpu_compress_leg(H, G, T, target_bits, seed=0):
+    """Times the oracle's compress stages on the host for one sample (all KV heads) at context T:
+    score_prefill, optimal_scores_to_bits, state_prefill (route + quantise + pack).  Returns seconds per stage."""
+    import numpy as np
+    from oracle import odmkv_oracle as orc
+    orc.build_c()
+    K16, V16, Qw16, _ = orc.synth_inputs(H, T, G, 128, 64, seed, 1)
+    K, V = K16[0].astype(np.float32), V16[0].astype(np.float32)
+    mu = Qw16[0].astype(np.float32).mean(axis=1)
+    eps = orc.calibrate_epsilon(128, LEVELS, seed=42)
+    sink = np.zeros((H, T), bool)
+    sink[:, :4] = True
+    pi_k, pi_v = orc.random_rotation(128, 42), orc.random_rotation(128, 2042)
+    t0 = time.perf_counter()
+    scores = orc.score_prefill(K, V, mu, 4, 1e-2)
+    t1 = time.perf_counter()
+    bits = orc.optimal_scores_to_bits(scores, LEVELS, target_bits, eps, sink, eviction_cost=0.5)
+    bits[:, -128:] = 16
+    t2 = time.perf_counter()
+    orc.state_prefill(K[None], V[None], bits[None], LEVELS, 42, pi_k, pi_v)
+    t3 = time.perf_counter()
+    return {"score": t1 - t0, "allocate": t2 - t1, "quantize": t3 - t2}
 
 
 # ------------------------------------------------------------------------------------------------
@@ -210,6 +259,110 @@ def synth_kv(torch, B, H, T, G, dev, seed):
     return K, V, Qw.mean(dim=2).float(), qd
 
 
+def strong_scaling_block(args, pkg, dev, world, rank, eps_list):
+    """ONE layer of the workload with its KV heads split over the ranks (strong scaling): every rank scores and packs
+    its heads, the per-layer Lagrangian runs with its counts all-reduced over NCCL, every decode step all-gathers the
+    per-head outputs.  All ranks draw the same layer (same seed) and keep their own heads."""
+    import torch
+    import torch.distributed as dist
+    ops = pkg.ops
+    B, H, G, T = args.batch, args.kv_heads, args.group, args.ctx
+    lo, hi = pkg.dist.shard_range(H, world, rank)
+    Hl = hi - lo
+    # the same layer on every rank, drawn head by head so that a rank only materialises its own heads
+    K = torch.empty(B, Hl, T, 128, device=dev, dtype=torch.float16)
+    V = torch.empty_like(K)
+    g = torch.Generator(device=dev)
+    g.manual_seed(4242)
+    e = torch.randn(128, generator=g, device=dev)
+    e = e / e.norm()
+    mu_all = torch.randn(B, H * G, 128, generator=g, device=dev) * 0.125 + 3.0 * e
+    qd_all = (torch.randn(B, H * G, 128, generator=g, device=dev) + 3.0 * e).to(torch.float16)
+    for h in range(H):
+        gh = torch.Generator(device=dev)
+        gh.manual_seed(5000 + h)
+        if lo <= h < hi:
+            k = torch.randn(B, T, 128, generator=gh, device=dev, dtype=torch.float16)
+            k[..., 0:4] *= 10.0
+            k[:, 0:4, :] += ((8.0 * math.sqrt(128) / 3.0) * e).to(torch.float16)
+            K[:, h - lo] = k
+            V[:, h - lo] = torch.randn(B, T, 128, generator=gh, device=dev, dtype=torch.float16)
+    mu = mu_all[:, lo * G:hi * G].contiguous()
+    qd = qd_all[:, lo * G:hi * G].contiguous()
+    sink = torch.zeros(Hl, T, dtype=torch.bool, device=dev)
+    sink[:, :4] = True
+    State = pkg.tq_adaptive_backend.TurboQuantAdaptiveKVCacheState
+
+    def compress():
+        scores = ops.score_prefill(K, V, mu, 4, 1e-2)
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        bits, _ = pkg.dist.allocate_bits_kv_sharded(scores, sink, LEVELS, eps_list, args.target_bits, head_lo=lo, T=T)
+        a1.record()
+        bits = bits.reshape(B, Hl, T).clone()
+        bits[..., -128:] = 16
+        st = State(head_dim=128, bit_levels=LEVELS, device=dev, dtype=torch.float16, key_quantizer="mse", value_quantizer="mse", seed=42)
+        st.prefill(K, V, bits)
+        return st, (a0, a1)
+
+    st, _ = compress()
+    torch.cuda.synchronize()
+    dist.barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    st, (a0, a1) = compress()
+    c1.record()
+    torch.cuda.synchronize()
+    compress_ms, alloc_ms = c0.elapsed_time(c1), a0.elapsed_time(a1)
+    del K, V
+    out = st.decode_attention(qd)
+    gathered = torch.empty(world, *out.shape, dtype=out.dtype, device=dev)
+    dist.all_gather_into_tensor(gathered, out)
+    # one CUDA graph per step: the decode call's launches and the NCCL all-gather of the outputs
+    graph = None
+    try:
+        gq = qd.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            go = st.decode_attention(gq)
+            dist.all_gather_into_tensor(gathered, go)
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+    except Exception:
+        graph = None
+
+    def one_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            dist.all_gather_into_tensor(gathered, st.decode_attention(qd))
+
+    for _ in range(max(args.warmup, 3)):
+        one_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        one_step()
+    s1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    vals = torch.tensor([s0.elapsed_time(s1) / args.steps, compress_ms, alloc_ms, float(st.chunks[0].packed_bytes())], dtype=torch.float64, device=dev)
+    mx = vals.clone()
+    dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    sm = vals.clone()
+    dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+    step_ms, bytes_all = mx[0].item(), sm[3].item()
+    return {"scaling": "strong", "what": f"one layer, {H} KV heads split over {world} ranks ({Hl} per rank), batch {B}, ctx {T}",
+            "ms_per_step": step_ms, "value": bytes_all / (step_ms * 1e-3) / 1e9, "unit": "GB/s",
+            "step": "CUDA graph of the decode call and the all-gather" if graph is not None else "eager decode call and all-gather",
+            "collectives": "per step: NCCL all-gather of [B, Hq / N, 128] fp16 outputs; compress: NCCL all-reduce of 16 int64 counters per "
+                           "allocator pass (a 64 K-bin histogram per gap-closure pass)",
+            "compress_ms": mx[1].item(), "allocate_sharded_ms": mx[2].item(), "mtok_per_s": B * T / (mx[1].item() * 1e-3) / 1e6}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -230,19 +383,22 @@ def run_ours(args):
     # ---- build the packed cache with this library's compress path (timed: compress throughput)
     eps = pkg.allocator.calibrate_epsilon(128, LEVELS, seed=42, device=dev)
     eps_list = [eps[b] * (0.5 if b == 0 else 1.0) for b in LEVELS]
-    pi_k = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=42)
-    pi_v = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=2042)
     K, V, mu, qd = synth_kv(torch, B, H, T, G, dev, seed=1000 + rank)
     sink = torch.zeros(H, T, dtype=torch.uint8, device=dev)
     sink[:, :4] = 1
     sink = sink.reshape(-1)
 
+    State = pkg.tq_adaptive_backend.TurboQuantAdaptiveKVCacheState
+
     def compress():
+        """score -> allocate -> window override -> state.prefill (route, quantise, pack): what the press hook does for a layer."""
         scores = ops.score_prefill(K, V, mu, 4, 1e-2)
         bits, rep = ops.allocate_bits(scores.reshape(B, H * T), sink, LEVELS, eps_list, args.target_bits)
         bits = bits.reshape(B, H, T)
         bits[..., -128:] = 16
-        return ops.quantize_pack(K, V, bits, pi_k, pi_v), rep
+        state = State(head_dim=128, bit_levels=LEVELS, device=dev, dtype=torch.float16, key_quantizer="mse", value_quantizer="mse", seed=42)
+        state.prefill(K, V, bits)
+        return state, rep
 
     L.odmkv_timing_enable(0)
     for _ in range(2):                # warm-up; freed so that the timed run reuses its device blocks
@@ -253,7 +409,8 @@ def run_ours(args):
     L.odmkv_timing_enable(1)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    chunk, rep = compress()           # timed; also the cache the decode steps read
+    state, rep = compress()           # timed; also the cache the decode steps read
+    chunk = state.chunks[0]
     e1.record()
     torch.cuda.synchronize()
     compress_ms = e0.elapsed_time(e1)
@@ -264,6 +421,7 @@ def run_ours(args):
         stage_ms[name] = tot.value
     L.odmkv_timing_enable(0)
     reports = ops.read_reports(rep)
+    pi_k, pi_v = state.pi_k, state.pi_v
     cnt = chunk.seg_count_host().sum(axis=1)
     stored = int(cnt[1:].sum())
     bytes_per_step = chunk.packed_bytes()
@@ -365,21 +523,27 @@ def run_ours(args):
     out_host = torch.empty(B, H * G, 128, dtype=torch.float16).pin_memory()
     q_dev = torch.empty_like(qd)
 
-    def e2e_step():
+    def e2e_step(plugin=True):
+        """Host query in, attention output out.  plugin=True: the cache-state call the attention override makes
+        (state.decode_attention); False: the tensor-level op underneath it."""
         q_dev.copy_(q_host, non_blocking=True)
-        o = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits)
+        o = state.decode_attention(q_dev) if plugin else ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits)
         out_host.copy_(o, non_blocking=True)
 
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    def e2e_time(plugin):
+        for _ in range(3):
+            e2e_step(plugin)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step(plugin)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) * 1e3
+
+    e2e_ms = e2e_time(True)
+    e2e_ops_ms = e2e_time(False)
     # the same end-to-end step (host query in, host output out) as one CUDA graph: copy node, the decode call's
     # launches, copy node
     e2e_graph_ms = None
@@ -388,7 +552,7 @@ def run_ours(args):
             eg = torch.cuda.CUDAGraph()
             with torch.cuda.graph(eg, capture_error_mode="thread_local"):
                 q_dev.copy_(q_host, non_blocking=True)
-                eo = ops.decode_attn(q_dev, [chunk], pi_k, pi_v, n_splits=n_splits)
+                eo = state.decode_attention(q_dev)
                 out_host.copy_(eo, non_blocking=True)
             for _ in range(3):
                 eg.replay()
@@ -411,6 +575,7 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
 
     # ---- max over ranks, totals over ranks
+    strong = strong_scaling_block(args, pkg, dev, world, rank, eps_list) if world > 1 and H % world == 0 else None
     stats = torch.tensor([total_ms, e2e_ms, float(bytes_per_step), main_ms, compress_ms, tp_ms or 0.0], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone()
@@ -443,24 +608,28 @@ def run_ours(args):
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms_per_step, "us_per_step": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f16 codes -> f32 accumulate", "data": "synthetic",
-        "config": {"workload": workload_name(T, B, H, G, args.target_bits),
-                   "l2": "packed cache per rank %.0f MB > 126 MB L2, re-read every step" % (bytes_per_step / 1e6),
+        "config": shared_config(args),
+        "detail": {"packed_cache_mb_per_rank": bytes_per_step / 1e6,
                    "timing": "CUDA events on the launching stream, max over ranks; per-kernel times from a second, eager pass of the same steps",
                    "level_counts": {str(b): int(c) for b, c in zip(LEVELS, cnt)},
                    "stored_token_heads": stored, "bytes_per_step_per_rank": bytes_per_step,
                    "n_splits": n_splits,
-                   "multi_gpu": "each rank holds its own (layer, sample, KV head) units: no exchange inside a step, outputs all-gathered once after the timed steps" if world > 1 else "single GPU"},
+                   "multi_gpu": "weak scaling of independent replicas: each rank holds its own (layer, sample, KV head) units, no exchange "
+                                "inside a step, outputs all-gathered once after the timed steps; the KV-head-sharded schedule of ONE layer "
+                                "(strong scaling, collectives inside) is the `strong_scaling` block" if world > 1 else "single GPU"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": traffic, "peak_kind": f"of {peak_kind}", "kernel": "decode_main", "kernel_ms": main_ms,
                      "frac_of_8000": achieved / 8000.0, "other_kernels_ms": parts_ms},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(q_host.numel() * 2 * world),
                 "d2h_bytes_per_step": int(out_host.numel() * 2 * world), "ms_per_step": e2e_ms / args.steps,
-                "call": "eager tensor-level call per step (host wall clock)",
+                "call": "state.decode_attention(q) of the cache-state API per step, eager, host wall clock: pinned query in, output out",
+                "ops_level_ms_per_step": e2e_ops_ms / args.steps,
                 "graph_replay_ms_per_step": None if e2e_graph_ms is None else e2e_graph_ms / args.steps},
         "gpu_launches": 4 * args.steps,
         "gather_per_step": None if tp_ms is None else {
             "schedule": "KV heads of one layer sharded over the ranks: outputs all-gathered (NCCL) after every step",
             "ms_per_step": tp_ms / args.steps, "value": bytes_all / (tp_ms / args.steps * 1e-3) / 1e9},
+        "strong_scaling": strong,
         "step_mode": {"timed_step": step_mode, "graph_vs_eager_max_abs_diff": graph_err,
                       "eager_ms_per_step_with_kernel_events": eager_ms},
         "clocks": clocks,
@@ -474,6 +643,15 @@ def run_ours(args):
         gbs, sec, sample = cpu_reference_leg(T, H, G, stored / float(B * H * T), bytes_per_step / float(B * H), 5, 1)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample,
                                 "sec_per_step_of_sample": sec}
+        # compress on the host: one sample at a shorter context; every stage is linear in the tokens except the
+        # allocator's sort (n log n), so tokens / second carries over to the full context within a few per cent
+        Tc = min(T, 8192)
+        cs = cpu_compress_leg(H, G, Tc, args.target_bits)
+        tot = sum(cs.values())
+        line["compress"]["cpu_baseline"] = {
+            "mtok_per_s": Tc / tot / 1e6, "stage_s": cs, "cores": cores, "kind": "port",
+            "sample": f"1 sample x {H} KV heads x {Tc} tokens: oracle score_prefill + optimal_scores_to_bits + state_prefill (numpy + C)",
+            "scaling_rule": "tokens per second measured on the sample stands for the full context (stages linear in tokens)"}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

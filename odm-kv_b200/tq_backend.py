@@ -21,15 +21,25 @@ def random_rotation(dim: int, device, dtype: torch.dtype, seed: Optional[int] = 
     The matrix is always drawn with torch's CPU generator and then moved: a CUDA generator would
     yield a different rotation for the same seed, and packed caches must not depend on where they
     were built."""
+    key = None
     gen = None
     if seed is not None:
+        key = (int(dim), int(seed), str(torch.device(device)), dtype)
+        if key in _ROTATIONS:
+            return _ROTATIONS[key]
         gen = torch.Generator(device="cpu")
         gen.manual_seed(int(seed))
     mat = torch.randn(dim, dim, dtype=torch.float32, generator=gen)
     q, r = torch.linalg.qr(mat)
     diag = torch.diag(r)
     signs = torch.where(diag >= 0, torch.ones_like(diag), -torch.ones_like(diag))
-    return (q * signs.unsqueeze(0)).contiguous().to(device=device, dtype=dtype)
+    rot = (q * signs.unsqueeze(0)).contiguous().to(device=device, dtype=dtype)
+    if key is not None:
+        _ROTATIONS[key] = rot   # seeded rotations are read-only inputs of the kernels: one copy per (seed, device)
+    return rot
+
+
+_ROTATIONS: dict = {}
 
 
 def _load_or_compute_codebook(bits: int, dim: int, device, dtype: torch.dtype) -> torch.Tensor:

@@ -33,6 +33,23 @@ assert torch.equal(mine, full.reshape(P, H, T)[:, lo:hi]), "sharded allocation d
 out = torch.full((2, 4, 128), float(rank), device=dev, dtype=torch.float16)
 allh = pkg.dist.gather_head_outputs(out)
 assert allh.shape == (2, 4 * world, 128) and all(float(allh[0, 4 * r, 0]) == r for r in range(world))
+# head-sharded decode attention: every rank packs and attends its own KV heads, the gathered outputs equal
+# what one device computes over all heads
+B, G, Td = 2, 4, 700
+g = torch.Generator(device="cpu").manual_seed(3)            # same layer on every rank
+Kf = torch.randn(B, H, Td, 128, generator=g).half().to(dev)
+Vf = torch.randn(B, H, Td, 128, generator=g).half().to(dev)
+q = torch.randn(B, H * G, 128, generator=g).half().to(dev)
+bits = torch.from_numpy(rng.choice(np.array(LEVELS, np.int32), size=(B, H, Td), p=(0.1, 0.5, 0.25, 0.05, 0.05, 0.05)).astype(np.int32)).to(dev)
+pk = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=42)
+pv = pkg.tq_backend.random_rotation(128, dev, torch.float32, seed=2042)
+whole = pkg.ops.decode_attn(q, [pkg.ops.quantize_pack(Kf, Vf, bits, pk, pv)], pk, pv, out_dtype=torch.float32)
+mine = pkg.ops.decode_attn(q[:, lo * G:hi * G].contiguous(),
+                           [pkg.ops.quantize_pack(Kf[:, lo:hi].contiguous(), Vf[:, lo:hi].contiguous(), bits[:, lo:hi].contiguous(), pk, pv)],
+                           pk, pv, out_dtype=torch.float32)
+gathered = pkg.dist.gather_head_outputs(mine)
+assert gathered.shape == whole.shape
+assert float((gathered - whole).abs().max() / whole.abs().max()) < 1e-5, "head-sharded decode differs from the single-device result"
 dist.barrier()
 if rank == 0:
     print("MULTI_GPU_OK")
