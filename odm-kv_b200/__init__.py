@@ -13,7 +13,7 @@ from . import _lib, codebook, ops  # noqa: F401
 from ._lib import OdmkvError  # noqa: F401
 
 _SUBMODULES = ["_lib", "codebook", "ops", "build", "tq_backend", "allocator", "scorer", "tq_adaptive_backend",
-               "attention_patch", "base_press", "press", "adaptive_backend_press", "press_factory", "dist"]
+               "attention_patch", "packed_cache", "adaptive_backend_press", "press_factory", "dist"]
 
 for _name in _SUBMODULES:
     try:
@@ -25,7 +25,7 @@ for _name in _SUBMODULES:
     sys.modules.setdefault(f"odmkv_b200.{_name}", _mod)
 sys.modules.setdefault("odmkv_b200", sys.modules[__name__])
 
-for _exported in ("allocator", "scorer", "adaptive_backend_press", "press_factory", "base_press", "tq_adaptive_backend"):
+for _exported in ("allocator", "scorer", "adaptive_backend_press", "press_factory", "tq_adaptive_backend", "packed_cache"):
     _m = sys.modules.get(f"odmkv_b200.{_exported}")
     if _m is not None:
         for _k in getattr(_m, "__all__", []):

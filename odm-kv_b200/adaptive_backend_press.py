@@ -9,8 +9,10 @@ Differences that do not change results:
   * with ``layerwise=True`` every layer is compressed in its own hook instead of after the last layer
     (each layer's Lagrangian is independent), so full-precision KV of earlier layers is not kept around;
   * all samples of a batch are scored and allocated in one launch each;
-  * decode steps attend over the packed state directly (see ``attention_patch``); the dense HF cache is
-    still kept in sync like the reference does, so code that reads ``cache.layers[i].keys`` keeps working.
+  * decode steps attend over the packed state directly (see ``attention_patch``); by default the dense HF cache is
+    still kept in sync like the reference does, so code that reads ``cache.layers[i].keys`` keeps working; with
+    ``packed_cache=True`` a compressed layer drops its dense tensors and stops growing by concatenation
+    (``packed_cache.PackedCacheLayer``).
 """
 from __future__ import annotations
 
@@ -38,7 +40,7 @@ class TurboQuantPerTokenBackendPress:
                  target_avg_bits: Optional[float] = None, eviction_cost: float = 5.0, above_target_alpha: float = 1.0,
                  n_outlier_channels: int = 0, outlier_min_bits: int = 4, seed: int = 42, decode_quant: bool = True,
                  sink_tokens: int = 0, layerwise: bool = False, buffer_size: int = 128, initial_layers_fp16: int = 0,
-                 allow_decode_eviction: bool = False):
+                 allow_decode_eviction: bool = False, packed_cache: bool = False):
         if scorer is None:
             raise ValueError("TurboQuantPerTokenBackendPress requires an explicit scorer.")
         if str(key_quantizer).lower() not in ("mse", "turboquant_mse", "turboquantmse"):
@@ -69,6 +71,9 @@ class TurboQuantPerTokenBackendPress:
         self.allow_decode_eviction = bool(allow_decode_eviction)
         self.buffer_size = buffer_size
         self.initial_layers_fp16 = initial_layers_fp16
+        # True: a compressed layer keeps no dense keys / values (packed_cache.PackedCacheLayer); False: the dense HF
+        # cache stays in sync with the dequantised tokens as in the reference
+        self.packed_cache = bool(packed_cache)
         if self.allow_decode_eviction:
             self._decode_bit_levels = tuple(bit_levels)
         else:
@@ -183,6 +188,13 @@ class TurboQuantPerTokenBackendPress:
         self._states[layer_idx] = state
         return state
 
+    @staticmethod
+    def _is_packed_layer(cache, layer_idx: int) -> bool:
+        if not hasattr(cache, "layers"):
+            return False
+        from .packed_cache import PackedCacheLayer
+        return isinstance(cache.layers[layer_idx], PackedCacheLayer)
+
     def _attach(self, cache, layer_idx: int, module: nn.Module, state) -> None:
         module.masked_key_indices = state.masked_key_indices()
         module._odmkv_state = state
@@ -246,6 +258,15 @@ class TurboQuantPerTokenBackendPress:
             bits[..., -min(self.buffer_size, bits.shape[-1]):] = 16
         state = self._get_or_create_state(layer_idx, keys)
         state.prefill(keys, values, bits.to(dtype=torch.int32, device=keys.device))
+        if self.packed_cache and hasattr(cache, "layers") and keys.is_cuda:
+            from .packed_cache import convert_layer
+            convert_layer(cache.layers[layer_idx], state)   # no dense write-back: the packed state is the cache
+            self._attach(cache, layer_idx, module, state)
+            module._odmkv_packed_cache = True
+            if self.buffer_size > 0:
+                self._buffer_start_seqs[layer_idx] = int(state.seq_len)
+                self._buffer_counts[layer_idx] = 0
+            return
         if keys.is_contiguous() and values.is_contiguous():
             state.materialize_quantized_into(keys, values)
         else:
@@ -294,8 +315,9 @@ class TurboQuantPerTokenBackendPress:
         if self._head_dim is None:
             self._head_dim = keys.shape[-1]
         q_len, cache_len = hidden_states.shape[1], keys.shape[2]
+        packed = self._is_packed_layer(cache, layer_idx)   # keys / values are then the new tokens only
 
-        if cache_len == q_len:                      # fresh prefill
+        if cache_len == q_len and not packed:       # fresh prefill
             scores = self._score_layer(module, hidden_states, keys, values, layer_idx)
             sink_mask = self._build_sink_mask(keys.shape[1], keys.shape[2], keys.device)
             if self.layerwise:
@@ -347,9 +369,10 @@ class TurboQuantPerTokenBackendPress:
         bits = torch.stack(batch_bits, dim=0).to(dtype=torch.int32, device=keys.device)
         n_before = len(state.chunks)
         state.append(new_k.contiguous(), new_v.contiguous(), bits)
-        k2, v2 = keys.contiguous(), values.contiguous()
-        state.materialize_quantized_into(k2, v2, chunks=state.chunks[n_before:])
-        self._set_cache_tensors(cache, layer_idx, k2, v2)
+        if not packed:
+            k2, v2 = keys.contiguous(), values.contiguous()
+            state.materialize_quantized_into(k2, v2, chunks=state.chunks[n_before:])
+            self._set_cache_tensors(cache, layer_idx, k2, v2)
         self._attach(cache, layer_idx, module, state)
         return output
 
@@ -438,7 +461,7 @@ class TurboQuantPerTokenBackendPress:
         chunk = state.flush_buffer(buffer_start, bits)
         self._buffer_start_seqs[layer_idx] = state.seq_len
         self._buffer_counts[layer_idx] = 0
-        if chunk is not None:
+        if chunk is not None and not self._is_packed_layer(cache, layer_idx):
             keys, values = self._get_cache_tensors(cache, layer_idx)
             if keys.shape[2] >= state.seq_len:
                 k2, v2 = keys.contiguous(), values.contiguous()
@@ -471,6 +494,7 @@ class TurboQuantPerTokenBackendPress:
                     attn.layer_idx = i
                 attn.masked_key_indices = None
                 attn._odmkv_state = None
+                attn._odmkv_packed_cache = False
                 if hasattr(lm, "rotary_emb"):
                     try:
                         attn.rotary_emb = lm.rotary_emb

@@ -41,6 +41,17 @@ def packed_decode(module, query: torch.Tensor, key: torch.Tensor, value: torch.T
     return out.unsqueeze(1)   # [B, 1, Hq, d], the layout attention functions return
 
 
+def packed_multi(module, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scaling):
+    """A pass of several new tokens (question encoding) over a layer whose cache is packed only: query j attends the
+    packed state and the new tokens 0..j, one decode call per query.  ``key`` / ``value`` hold the new tokens only."""
+    state = module._odmkv_state
+    outs = []
+    for j in range(query.shape[2]):
+        outs.append(state.decode_attention(query[:, :, j, :], scale=scaling, pending_k=key[:, :, : j + 1, :],
+                                           pending_v=value[:, :, : j + 1, :], out_dtype=query.dtype))
+    return torch.stack(outs, dim=1)   # [B, q_len, Hq, d]
+
+
 def _mask_is_open(attention_mask) -> bool:
     """True when the mask hides no key from the query (no padding in the batch).  The packed decode kernels take
     no mask, so a call with hidden keys keeps the reference's route (fake keys + stock attention)."""
@@ -51,6 +62,19 @@ def _mask_is_open(attention_mask) -> bool:
     return not bool((attention_mask != 0).any())
 
 
+def _causal_or_open(attention_mask, q_len: int) -> bool:
+    """True when, over the packed tokens (all but the last q_len key columns), the mask hides nothing -- i.e. it is
+    absent or plain causal, which ``packed_multi`` applies itself."""
+    if attention_mask is None:
+        return True
+    old = attention_mask[..., : attention_mask.shape[-1] - q_len]
+    if old.numel() == 0:
+        return True
+    if attention_mask.dtype == torch.bool:
+        return bool(old.all())
+    return not bool((old != 0).any())
+
+
 def _attention_patch(func):
     if getattr(func, _PATCH_ATTR, False):
         return func
@@ -58,9 +82,28 @@ def _attention_patch(func):
     @functools.wraps(func)
     def wrapper(module, query, key, value, attention_mask, dropout, **kwargs):
         state = getattr(module, "_odmkv_state", None)
-        if query.shape[2] == key.shape[2]:
+        if state is not None and getattr(module, "_odmkv_packed_cache", False) and query.is_cuda:
+            # the layer's cache is packed only: key / value are the new tokens, everything older is in the state
+            scaling = kwargs.get("scaling", None)
+            if scaling is None:
+                scaling = getattr(module, "scaling", None)
+            if query.shape[2] == 1 and _mask_is_open(attention_mask):
+                out = state.decode_attention(query[:, :, 0, :], scale=scaling, pending_k=key, pending_v=value, out_dtype=query.dtype)
+                return out.unsqueeze(1), None
+            if _causal_or_open(attention_mask, query.shape[2]):
+                return packed_multi(module, query, key, value, scaling), None
+            # a mask that hides keys (padding in the batch): dense dequantised cache plus the new tokens, then the
+            # reference's route below (fake keys over the evicted positions, stock attention)
+            Kd, Vd = state.materialize()
+            key = torch.cat([Kd.to(key.dtype), key], dim=2)
+            value = torch.cat([Vd.to(value.dtype), value], dim=2)
+            dense_from_packed = True
+        else:
+            dense_from_packed = False
+        if query.shape[2] == key.shape[2] and not dense_from_packed:
             module.masked_key_indices = None
             module._odmkv_state = None
+            module._odmkv_packed_cache = False
         elif (state is not None and query.shape[2] == 1 and query.is_cuda and key.shape[2] >= state.seq_len
               and getattr(module, "_odmkv_decode", True) and _mask_is_open(attention_mask)):
             scaling = kwargs.get("scaling", None)

@@ -166,3 +166,56 @@ def test_decode_buffer_flush_and_truncate(pkg, cuda):
         assert pos.numel() == 0 or int(pos[:, 2].max()) < T - 50
         Kt, _ = state.materialize_fp32()
         assert Kt.shape[2] == T - 50 and torch.equal(Kt, Kf[:, :, : T - 50] * state.keep_mask().unsqueeze(-1))
+
+
+@torch.no_grad()
+def test_packed_cache_layer_replaces_dense_cache(pkg, cuda):
+    """packed_cache=True: a compressed layer keeps no dense keys / values, decode steps and a multi-token pass read
+    the packed state only, and the logits agree with the dense-in-sync mode of the same press."""
+    from transformers import DynamicCache
+    model = tiny_llama(cuda, dtype=torch.bfloat16)
+    B, T = 2, 300
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 512, (B, T), generator=g).to(cuda)
+    qids = torch.randint(0, 512, (B, 5), generator=g).to(cuda)
+    toks = torch.randint(0, 512, (B, 20), generator=g).to(cuda)
+
+    def run(packed):
+        press = make_press(pkg, buffer_size=8)
+        press.packed_cache = packed
+        cache = DynamicCache()
+        logits = []
+        with press(model):
+            model.model(input_ids=ids, past_key_values=cache)
+            logits.append(model(input_ids=qids, past_key_values=cache).logits.float())       # multi-token pass
+            for s in range(toks.shape[1]):
+                logits.append(model(input_ids=toks[:, s:s + 1], past_key_values=cache).logits.float())
+            states = {i: (st.seq_len, len(st.chunks), st.tail_len) for i, st in press._states.items()}
+            shapes = [(l.keys.shape[2], l.values.shape[2], l.get_seq_length(), type(l)) for l in cache.layers]
+            if packed:
+                # rewind as the runner does between questions (benchmark/core/pipeline.py:211-228), then go on decoding
+                for layer in cache.layers:
+                    layer._tq_backend_state.truncate(T)
+                    for attr in ("keys", "values"):
+                        t = getattr(layer, attr)
+                        if t.shape[2] > T:
+                            setattr(layer, attr, t[:, :, :T])
+                    assert layer.get_seq_length() == T
+                out = model(input_ids=toks[:, :1], past_key_values=cache).logits
+                assert torch.isfinite(out).all() and cache.get_seq_length(0) == T + 1
+        return shapes, states, logits
+
+    shapes_p, states_p, logits_p = run(True)
+    shapes_d, states_d, logits_d = run(False)
+    for li in range(len(shapes_p)):
+        assert shapes_p[li][3] is pkg.PackedCacheLayer
+        assert shapes_p[li][:3] == (1, 1, T + 5 + 20)                            # the newest token only
+        assert shapes_d[li][:3] == (T + 5 + 20, T + 5 + 20, T + 5 + 20)          # the reference mode keeps growing it
+        assert states_p[li] == states_d[li] == (T + 5 + 20, 4, 4)   # prefill, pinned pass + flush, flush; 4 buffered
+    # the multi-token pass goes through per-query packed decode calls in one mode and through the stock attention with
+    # fake keys over the dequantised bf16 cache in the other: equal up to bf16 rounding of that dense route
+    err0 = (logits_p[0] - logits_d[0]).abs().max() / logits_d[0].abs().max()
+    assert err0 < 5e-2, err0
+    for a, b in zip(logits_p[1:], logits_d[1:]):
+        err = (a - b).abs().max() / b.abs().max()
+        assert err < 5e-2, err
