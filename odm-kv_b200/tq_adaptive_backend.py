@@ -276,10 +276,16 @@ class TurboQuantAdaptiveKVCacheState:
         return keep
 
     def masked_key_indices(self):
+        """(b, h, t) index tensors of the evicted tokens, or None.  Chunks are immutable, so the result is kept until
+        the chunk list changes (a flush, an append or a truncation)."""
+        version = tuple(id(c) for c in self.chunks)
+        cached = getattr(self, "_masked_cache", None)
+        if cached is not None and cached[0] == version:
+            return cached[1]
         mp = self._masked_positions
-        if mp.numel() == 0:
-            return None
-        return mp[:, 0], mp[:, 1], mp[:, 2]
+        out = None if mp.numel() == 0 else (mp[:, 0], mp[:, 1], mp[:, 2])
+        self._masked_cache = (version, out)
+        return out
 
     def decode_attention(self, query: torch.Tensor, scale: Optional[float] = None, pending_k=None, pending_v=None,
                          out_dtype=None) -> torch.Tensor:

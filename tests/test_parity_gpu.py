@@ -278,3 +278,61 @@ def test_press_token_placement_matches_reference_run(pkg, cuda, golden, name):
         ref = g["last_logits"]
         err = np.abs(logits[:, -1].float().cpu().numpy() - ref).max() / np.abs(ref).max()
         assert err < 2e-2, err   # same model over the two dequantised caches (placement may differ in a few ties)
+
+
+# ------------------------------------------------------------------------------------------------ model-shaped layers
+@torch.no_grad()
+def test_llama8b_shaped_layers_under_the_press(pkg, orc, cuda):
+    """Two layers of the Llama-3.1-8B shape (hidden 4096, 32 query / 8 KV heads, random-init bf16) through the press
+    with the packed cache: per-layer scores against the oracle (the model runs in bf16, so the mean query carries
+    bf16 rounding: 5e-3), bits bit-exact given the library's own scores, then decode steps with two flushes."""
+    import importlib
+    from transformers import DynamicCache
+    mb = importlib.import_module("odm-kv_b200.model_bench")
+    model = mb.build_model(torch, "llama", 2, 4096, 14336, 32, 8, 4096, cuda)
+    B, T, n_decode = 1, 2048, 40
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 4096, (B, T), generator=g).to(cuda)
+    toks = torch.randint(0, 4096, (B, n_decode), generator=g).to(cuda)
+    exp = {"mode": "backend_per_token", "bits": list(LEVELS), "target_avg_bits": 2.0, "eviction_cost": 0.5, "packed_cache": True}
+    press = pkg.press_factory.make_press(exp, seed=42)
+    press.buffer_size = 16
+    cache = DynamicCache()
+    captured = {}
+
+    def grab(module, args, kwargs, output):
+        layer = cache.layers[module.layer_idx]
+        if layer.keys.shape[2] == T and module.layer_idx not in captured:
+            captured[module.layer_idx] = (layer.keys.clone(), layer.values.clone(), kwargs["hidden_states"].clone())
+
+    with press(model):
+        hooks = [l.self_attn.register_forward_hook(grab, with_kwargs=True, prepend=True) for l in model.model.layers]
+        model.model(input_ids=ids, past_key_values=cache)
+        for h in hooks:
+            h.remove()
+        eps = press._epsilon
+        sink = np.zeros((8, T), bool)
+        sink[:, :4] = True
+        for li, layer in enumerate(model.model.layers):
+            attn = layer.self_attn
+            K0, V0, h0 = captured[li]
+            scores = press.scorer.score_prefill_batched(K0, V0, li, module=attn, hidden_states=h0).cpu().numpy()
+            wq = attn.q_proj.weight.float().cpu().numpy()
+            pos = torch.arange(T, T + 512, device=cuda).unsqueeze(0)
+            cos, sin = model.model.rotary_emb(h0[:1].float(), pos)
+            cb, sb = orc.avg_rope_vectors(cos[0].float().cpu().numpy(), sin[0].float().cpu().numpy())
+            mu = orc.apply_avg_rope(orc.mean_query(h0[0].float().cpu().numpy(), wq, None, 32, 128, 4), cb, sb)
+            want_s = orc.score_prefill(K0[0].float().cpu().numpy(), V0[0].float().cpu().numpy(), mu, 4, 1e-2)
+            rel = np.abs(scores[0] - want_s) / np.maximum(want_s, 1e-30)
+            assert rel.max() < 5e-3, (li, rel.max())
+            want_bits = orc.optimal_scores_to_bits(scores[0], LEVELS, 2.0, eps, sink, eviction_cost=0.5)
+            want_bits[:, -16:] = 16                                   # the protection window is the decode buffer's size
+            got = _bits_map(press._states[li], B, 8, T)[0]
+            assert np.array_equal(got, want_bits.astype(np.int8)), li
+            assert isinstance(cache.layers[li], pkg.PackedCacheLayer) and cache.layers[li].keys.shape[2] == 0
+        for s in range(n_decode):
+            logits = model(input_ids=toks[:, s:s + 1], past_key_values=cache).logits
+        assert torch.isfinite(logits).all()
+        for li in range(2):
+            st = press._states[li]
+            assert st.seq_len == T + n_decode and len(st.chunks) == 3 and st.tail_len == n_decode - 32
