@@ -194,6 +194,16 @@ int odmkv_export_bank(const odmkv_chunk *chunk, int class_idx, const int32_t *ro
 int odmkv_export_positions(const odmkv_chunk *chunk, int class_idx, const int32_t *row_start,
                            int64_t *positions, void *stream);
 
+/* Merge n_src chunks (HOST array, at most 12, same B and H) into the chunk `dst` (HOST struct; banks allocated by the
+ * caller from the summed segment counts, each (b, h) segment on a multiple of 16 slots, pos arrays preset to -1 and
+ * norms to 0).  Inside every (b, h) segment of every class the tokens of chunk 0 come first, then chunk 1, ...; with
+ * chunks in time order that is ascending position, the order the reference's growing banks have
+ * (kvquant/tq_adaptive_backend.py:149-174, 481-532: flushed tokens are appended to the banks).
+ *   dst_off [n_src, 6, B*H] int32 (device): first destination slot of chunk i inside the destination segment
+ *   workspace: odmkv_quantize_workspace_bytes(dst->cap) bytes, 256-byte aligned. */
+int odmkv_compact_chunks(const odmkv_chunk *src, int n_src, const odmkv_chunk *dst, const int32_t *dst_off, int dtype,
+                         void *workspace, size_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Decode attention over packed chunks.  Replaces, for q_len = 1, the attention call the
  * reference's wrapper forwards to after masking evicted keys (kvquant/attention_patch.py:30-55)

@@ -93,6 +93,7 @@ _PROTOTYPES = {
                                     c_int, c_void_p]),
     "odmkv_export_bank": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "odmkv_export_positions": (c_int, [POINTER(Chunk), c_int, c_void_p, c_void_p, c_void_p]),
+    "odmkv_compact_chunks": (c_int, [POINTER(Chunk), c_int, POINTER(Chunk), c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "odmkv_decode_attn_mma": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int,
                                       c_void_p, c_size_t, POINTER(c_float), c_void_p]),

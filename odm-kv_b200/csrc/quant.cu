@@ -1,10 +1,11 @@
 // Quantise-and-pack, dequantise and bank export kernels (sm_100a).
 //
 // Replaces the reference's routing + TurboQuantMSE path (kvquant/tq_adaptive_backend.py:350-374,
-// 149-174, 205-242; kvquant/tq_backend.py:103-145, 185-203).  The 128x128 rotation of a tile of
-// 128 tokens is an fp32 register-blocked product whose every output coordinate is one ascending
-// fused-multiply-add chain over the contraction index -- the same chain the CPU oracle uses, so
-// codes are reproducible bit for bit.
+// 149-174, 205-242; kvquant/tq_backend.py:103-145, 185-203).  The 128x128 rotation of a 32-token item runs on the
+// tensor cores (mma.sync, operands as fp16 high/low limb pairs, three products, fp32 accumulate); every coordinate
+// whose distance to a decision boundary is inside the proven error margin is recomputed with one ascending fp32
+// fused-multiply-add chain over the contraction index -- the chain the CPU oracle uses -- so codes are reproducible
+// bit for bit.
 #include "common.cuh"
 
 namespace odmkv {
@@ -906,6 +907,63 @@ __global__ void export_positions_kernel(const odmkv_chunk ch, int c, const int32
     }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Compaction: several chunks -> one (same slot order inside every (b, h) segment: chunk after chunk)
+// ----------------------------------------------------------------------------------------------
+struct CompactArgs {
+    odmkv_chunk src[kMaxChunks];
+    odmkv_chunk dst;
+    const int32_t *dst_off;     // [n_src, 6, B*H]: first destination slot of chunk i's tokens inside the destination segment
+    uint8_t *k_scratch[3];      // linear-layout codes of the destination's 2/3/4-bit banks before re-tiling
+    uint8_t *v_scratch[3];
+    int n_src;
+};
+
+// grid (B*H, n_src, 6 classes); a warp moves one slot at a time
+template <int DT>
+__global__ void compact_gather_kernel(const CompactArgs a) {
+    __shared__ uint8_t stage[8][kD];
+    const int bh = blockIdx.x, i = blockIdx.y, c = blockIdx.z;
+    const odmkv_chunk &src = a.src[i];
+    const int BH = a.dst.B * a.dst.H;
+    const int cnt = src.seg_count[c * BH + bh];
+    if (cnt == 0) return;
+    const int s0 = src.seg_start[c * BH + bh];
+    const int d0 = a.dst.seg_start[c * BH + bh] + a.dst_off[((size_t)i * kNumClasses + c) * BH + bh];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int k = warp; k < cnt; k += blockDim.x >> 5) {
+        const long long s = (long long)s0 + k, d = (long long)d0 + k;
+        if (c == 0) {
+            if (lane == 0) a.dst.evicted_pos[d] = src.evicted_pos[s];
+        } else if (c == 5) {
+            using T = typename Elem<DT>::T;
+            const T *ks = reinterpret_cast<const T *>(src.exact_k) + (size_t)s * kD, *vs = reinterpret_cast<const T *>(src.exact_v) + (size_t)s * kD;
+            T *kd = reinterpret_cast<T *>(a.dst.exact_k) + (size_t)d * kD, *vd = reinterpret_cast<T *>(a.dst.exact_v) + (size_t)d * kD;
+            for (int e = lane; e < kD; e += 32) { kd[e] = ks[e]; vd[e] = vs[e]; }
+            if (lane == 0) a.dst.exact_pos[d] = src.exact_pos[s];
+        } else {
+            const int li = c - 1;
+            for (int side = 0; side < 2; ++side) {
+                const uint8_t *bank = side ? src.v_codes[li] : src.k_codes[li];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int dim = 4 * lane + q;
+                    stage[warp][dim] = (uint8_t)(side ? v_code(bank, li, s, dim) : k_code(bank, li, s, dim));
+                }
+                __syncwarp();
+                uint8_t *rows = li == 3 ? (side ? a.dst.v_codes[3] : a.dst.k_codes[3]) : (side ? a.v_scratch[li] : a.k_scratch[li]);
+                store_linear_codes(stage[warp], li, rows, d, lane);
+                __syncwarp();
+            }
+            if (lane == 0) {
+                a.dst.k_norm[li][d] = src.k_norm[li][s];
+                a.dst.v_norm[li][d] = src.v_norm[li][s];
+                a.dst.pos[li][d] = src.pos[li][s];
+            }
+        }
+    }
+}
+
 static int num_sms() {
     static int n = 0;
     if (n == 0) {
@@ -1022,6 +1080,56 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
         } else {
             retile_kernel<4, true><<<rg, 256, 0, st>>>(a.k_scratch[2], chunk->k_codes[2], ntile);
             retile_kernel<4, false><<<rg, 256, 0, st>>>(a.v_scratch[2], chunk->v_codes[2], ntile);
+        }
+    }
+    return launch_status();
+}
+
+int odmkv_compact_chunks(const odmkv_chunk *src, int n_src, const odmkv_chunk *dst, const int32_t *dst_off, int dtype,
+                         void *workspace, size_t workspace_bytes, void *stream) {
+    if (!src || !dst || !dst_off || !workspace) return ODMKV_ERR_ARG;
+    if (n_src <= 0 || n_src > kMaxChunks) return ODMKV_ERR_LIMIT;
+    int rc = check_chunk(dst);
+    if (rc) return rc;
+    for (int i = 0; i < n_src; ++i) {
+        rc = check_chunk(&src[i]);
+        if (rc) return rc;
+        if (src[i].B != dst->B || src[i].H != dst->H) return ODMKV_ERR_SHAPE;
+    }
+    if (dtype < 0 || dtype > 2) return ODMKV_ERR_UNSUPPORTED;
+    if (((uintptr_t)workspace & 255) != 0 || workspace_bytes < odmkv_quantize_workspace_bytes(dst->cap)) return ODMKV_ERR_WORKSPACE;
+    for (int c = 1; c <= 3; ++c)
+        if (dst->cap[c] % 16 != 0) return ODMKV_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    CompactArgs a;
+    for (int i = 0; i < n_src; ++i) a.src[i] = src[i];
+    a.dst = *dst; a.dst_off = dst_off; a.n_src = n_src;
+    size_t off = 0;
+    for (int li = 0; li < 3; ++li) {
+        const size_t bytes = ((size_t)dst->cap[li + 1] * 16 * qbits(li) + 255) / 256 * 256;
+        a.k_scratch[li] = (uint8_t *)workspace + off;
+        a.v_scratch[li] = (uint8_t *)workspace + off + bytes;
+        off += 2 * bytes;
+    }
+    cudaMemsetAsync(workspace, 0, off, st);   // padding slots of the linear rows: zero codes
+    dim3 grid(dst->B * dst->H, n_src, kNumClasses);
+    if (dtype == kF16) compact_gather_kernel<kF16><<<grid, 256, 0, st>>>(a);
+    else if (dtype == kBF16) compact_gather_kernel<kBF16><<<grid, 256, 0, st>>>(a);
+    else compact_gather_kernel<kF32><<<grid, 256, 0, st>>>(a);
+    for (int li = 0; li < 3; ++li) {
+        const int ntile = dst->cap[li + 1] / 16;
+        if (ntile <= 0) continue;
+        int rg = (ntile + 7) / 8;
+        if (rg > 16 * num_sms()) rg = 16 * num_sms();
+        if (li == 0) {
+            retile_kernel<2, true><<<rg, 256, 0, st>>>(a.k_scratch[0], dst->k_codes[0], ntile);
+            retile_kernel<2, false><<<rg, 256, 0, st>>>(a.v_scratch[0], dst->v_codes[0], ntile);
+        } else if (li == 1) {
+            retile_kernel<3, true><<<rg, 256, 0, st>>>(a.k_scratch[1], dst->k_codes[1], ntile);
+            retile_kernel<3, false><<<rg, 256, 0, st>>>(a.v_scratch[1], dst->v_codes[1], ntile);
+        } else {
+            retile_kernel<4, true><<<rg, 256, 0, st>>>(a.k_scratch[2], dst->k_codes[2], ntile);
+            retile_kernel<4, false><<<rg, 256, 0, st>>>(a.v_scratch[2], dst->v_codes[2], ntile);
         }
     }
     return launch_status();

@@ -301,6 +301,47 @@ def quantize_pack(K: torch.Tensor, V: torch.Tensor, bits: torch.Tensor, pi_k: to
     return ch
 
 
+def compact_chunks(chunks: Sequence[PackedChunk]) -> PackedChunk:
+    """Merge chunks (time order) into one: inside every (b, h) segment of every class the tokens keep their order,
+    chunk after chunk.  Host work: the summed segment table (from the chunks' cached counts)."""
+    if not chunks:
+        raise ValueError("compact_chunks needs at least one chunk")
+    first = chunks[0]
+    B, H, dev = first.B, first.H, first.device
+    counts = np.stack([c.seg_count_host() for c in chunks]).astype(np.int64)          # [n, 6, BH]
+    new_count = counts.sum(axis=0)
+    padded = (new_count + _lib.SEG_ALIGN - 1) // _lib.SEG_ALIGN * _lib.SEG_ALIGN
+    new_start = np.concatenate([np.zeros((NUM_CLASSES, 1), np.int64), np.cumsum(padded, axis=1)[:, :-1]], axis=1)
+    totals = padded.sum(axis=1).tolist()
+    dst_off = np.concatenate([np.zeros((1, NUM_CLASSES, B * H), np.int64), np.cumsum(counts, axis=0)[:-1]], axis=0)
+    t_lo = min(c.t_offset for c in chunks)
+    t_hi = max(c.t_offset + c.T for c in chunks)
+    out = PackedChunk(B=B, H=H, T=t_hi - t_lo, t_offset=t_lo, dtype=first.dtype, device=dev,
+                      seg_start=torch.from_numpy(new_start.astype(np.int32)).to(dev),
+                      seg_count=torch.from_numpy(new_count.astype(np.int32)).to(dev), totals=[int(t) for t in totals])
+    out._seg_count_host = new_count.astype(np.int32)
+    for li in range(NUM_QLEVELS):
+        n = max(totals[li + 1], 1)
+        out.k_codes.append(torch.zeros(n, CODE_BYTES[li], dtype=torch.uint8, device=dev))
+        out.v_codes.append(torch.zeros(n, CODE_BYTES[li], dtype=torch.uint8, device=dev))
+        out.k_norm.append(torch.zeros(n, dtype=torch.float32, device=dev))
+        out.v_norm.append(torch.zeros(n, dtype=torch.float32, device=dev))
+        out.pos.append(torch.full((n,), -1, dtype=torch.int32, device=dev))
+    n16 = max(totals[5], 1)
+    out.exact_k = torch.zeros(n16, HEAD_DIM, dtype=first.dtype, device=dev)
+    out.exact_v = torch.zeros(n16, HEAD_DIM, dtype=first.dtype, device=dev)
+    out.exact_pos = torch.full((n16,), -1, dtype=torch.int32, device=dev)
+    out.evicted_pos = torch.full((max(totals[0], 1),), -1, dtype=torch.int32, device=dev)
+    arr = (Chunk * len(chunks))(*[c.c_struct() for c in chunks])
+    cs = out.c_struct()
+    off_d = torch.from_numpy(dst_off.astype(np.int32)).to(dev)
+    L = lib()
+    ws = _ws(L.odmkv_quantize_workspace_bytes(cs.cap), dev)
+    check(L.odmkv_compact_chunks(arr, len(chunks), ctypes.byref(cs), ptr(off_d), dtype_code(first.dtype), ptr(ws), ws.numel(),
+                                 stream_ptr(dev)), "odmkv_compact_chunks")
+    return out
+
+
 def encode_pack(y: torch.Tensor, bits: int) -> torch.Tensor:
     """Nearest centroid + pack of rotated coordinates y [n, 128] fp32 -> uint8 [n, code_bytes]."""
     require_cuda(y, "y")

@@ -129,6 +129,7 @@ class TurboQuantAdaptiveKVCacheState:
         self.chunks.append(chunk)
         self.seq_len += int(keys.shape[2])
         self.tail_start = self.seq_len
+        self._bound_chunks()
 
     def append_all_exact(self, keys: torch.Tensor, values: torch.Tensor) -> None:
         """Keep new tokens verbatim (tq_adaptive_backend.py:380-425): they go to the dense tail."""
@@ -235,7 +236,21 @@ class TurboQuantAdaptiveKVCacheState:
         self.chunks.append(chunk)
         self.tail_len = 0
         self.tail_start = self.seq_len
+        self._bound_chunks()
         return chunk
+
+    def compact(self, keep_first: int = 1) -> None:
+        """Merge the chunks after the first ``keep_first`` into one (the reference's banks simply grow with every flush,
+        kvquant/tq_adaptive_backend.py:481-532; here a state holds a bounded list of immutable chunks instead)."""
+        if len(self.chunks) - keep_first < 2:
+            return
+        merged = ops.compact_chunks(self.chunks[keep_first:])
+        self.chunks = self.chunks[:keep_first] + [merged]
+
+    def _bound_chunks(self) -> None:
+        """Keeps the chunk list within what one decode call accepts: the flushed chunks are merged when the list is full."""
+        if len(self.chunks) >= ops._lib.MAX_CHUNKS:
+            self.compact(keep_first=1)
 
     # ------------------------------------------------------------------ reads
     def materialize(self):
@@ -298,7 +313,7 @@ class TurboQuantAdaptiveKVCacheState:
                 self.batch_size, self.num_heads = int(pending_k.shape[0]), int(pending_k.shape[1])
             tail_len = self.stage_pending(pending_k, pending_v)
         if len(self.chunks) > ops._lib.MAX_CHUNKS:
-            raise ops._lib.OdmkvError(f"more than {ops._lib.MAX_CHUNKS} chunks: compact the cache first")
+            self.compact(keep_first=1)
         return ops.decode_attn(query, self.chunks, self.pi_k, self.pi_v, tail_k=self.tail_k, tail_v=self.tail_v,
                                tail_len=tail_len, scale=scale, out_dtype=out_dtype, cache_dtype=self.dtype)
 

@@ -347,3 +347,45 @@ def test_runs_are_deterministic(pkg, orc, cuda):
     a = pkg.ops.decode_attn(qd.to(cuda), [ch], pk, pv, out_dtype=torch.float32)
     b = pkg.ops.decode_attn(qd.to(cuda), [ch], pk, pv, out_dtype=torch.float32)
     assert torch.equal(a, b)
+
+
+def test_chunk_compaction_keeps_decode_banks_and_truncation(pkg, orc, cuda):
+    """Fourteen flushes: the state merges its flushed chunks when its list is full (a decode call takes at most twelve
+    chunk descriptors).  Decode attention, the dequantised cache and truncation must not notice."""
+    B, H, G, T0, n_flush, m = 2, 2, 4, 200, 14, 24
+    T = T0 + n_flush * m
+    K16, V16, _, qd16 = orc.synth_inputs(H, T, G, 128, 8, 31, B)
+    rng = np.random.default_rng(5)
+    bits = random_bits(rng, B, H, T)
+    bits[..., :4] = 16
+    Kt, Vt, bt = torch.from_numpy(K16).to(cuda), torch.from_numpy(V16).to(cuda), torch.from_numpy(bits).to(cuda)
+    State = pkg.tq_adaptive_backend.TurboQuantAdaptiveKVCacheState
+    state = State(head_dim=128, bit_levels=LEVELS, device=cuda, dtype=torch.float16, key_quantizer="mse", value_quantizer="mse", seed=42)
+    state.prefill(Kt[:, :, :T0].contiguous(), Vt[:, :, :T0].contiguous(), bt[:, :, :T0].contiguous())
+    max_chunks = 0
+    for f in range(n_flush):
+        a, b = T0 + f * m, T0 + (f + 1) * m
+        state.append_all_exact(Kt[:, :, a:b], Vt[:, :, a:b])
+        state.flush_buffer(a, bt[:, :, a:b])
+        max_chunks = max(max_chunks, len(state.chunks))
+    assert max_chunks <= pkg._lib.MAX_CHUNKS and len(state.chunks) < 1 + n_flush and state.seq_len == T and state.tail_len == 0
+    pi_k, pi_v = state.pi_k.cpu().numpy(), state.pi_v.cpu().numpy()
+    q = torch.from_numpy(qd16).to(cuda)
+
+    def check(T_now):
+        st = orc.state_prefill(K16[:, :, :T_now].astype(np.float32), V16[:, :, :T_now].astype(np.float32), bits[:, :, :T_now], LEVELS, 42, pi_k, pi_v)
+        Kh, Vh, keep = orc.materialize(st)
+        want = orc.decode_attention(qd16.astype(np.float32), Kh, Vh, keep)
+        assert_attn_close(state.decode_attention(q, out_dtype=torch.float32).cpu().numpy(), want, (T_now,))
+        Kf, Vf = state.materialize_fp32()
+        assert np.array_equal(Kf.cpu().numpy()[keep], Kh[keep]) and np.array_equal(Vf.cpu().numpy()[keep], Vh[keep])
+        assert np.array_equal(state.keep_mask().cpu().numpy(), keep)
+        banks = state._quantized_banks
+        for level in (2, 3, 4, 8):
+            assert banks[level].size == int((bits[:, :, :T_now] == level).sum())
+
+    check(T)
+    state.truncate(T0 + 5 * m + 3)       # inside the merged chunk
+    check(T0 + 5 * m + 3)
+    state.truncate(T0 - 7)               # inside the prefill chunk
+    check(T0 - 7)
