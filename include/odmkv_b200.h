@@ -238,6 +238,18 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
                           int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
                           const float *lut_scales, void *stream);
 
+/* odmkv_decode_attn_mma with the tail length in device memory (no counterpart in the reference, whose decode step
+ * concatenates onto dense tensors, transformers/cache_utils.py DynamicLayer.update).  The launch attends
+ * min(*tail_len_dev + tail_len_add, tail_cap) tokens of the tail, read when the kernel runs; tail_len_bound
+ * (1..tail_cap) is the largest value it may take and only sizes the launch.  A decode step captured into a CUDA
+ * graph therefore stays valid while the tail grows: the host replays it and a device counter advances. */
+int odmkv_decode_attn_mma_devtail(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                                  const void *tail_k, const void *tail_v, const int32_t *tail_len_dev, int tail_len_add,
+                                  int tail_len_bound, int tail_cap, const float *pi_k, const float *pi_v,
+                                  const float *codebooks, int B, int H, int G, float scale, void *out, int out_dtype,
+                                  float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                                  const float *lut_scales, void *stream);
+
 /* Decode attention without a caller-supplied workspace (no counterpart in the reference).  For hosts
  * that cannot allocate device memory on the decode path -- a serving loop with a frozen memory pool, a
  * thread that may not take the driver's allocation lock, a plug-in that only ever receives raw device

@@ -97,6 +97,9 @@ _PROTOTYPES = {
     "odmkv_decode_attn_mma": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                       c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int,
                                       c_void_p, c_size_t, POINTER(c_float), c_void_p]),
+    "odmkv_decode_attn_mma_devtail": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int,
+                                              c_void_p, c_int, c_void_p, c_size_t, POINTER(c_float), c_void_p]),
     "odmkv_decode_attn_noalloc_scratch_bytes": (c_size_t, []),
     "odmkv_decode_attn_noalloc": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,

@@ -87,7 +87,9 @@ def _attention_patch(func):
             scaling = kwargs.get("scaling", None)
             if scaling is None:
                 scaling = getattr(module, "scaling", None)
-            if query.shape[2] == 1 and _mask_is_open(attention_mask):
+            # (a step that is being captured into a graph may not read the mask back; its caller vouches that the
+            #  batch has no padding, and a single new token then sees every key)
+            if query.shape[2] == 1 and (getattr(module, "_odmkv_mask_known_open", False) or _mask_is_open(attention_mask)):
                 out = state.decode_attention(query[:, :, 0, :], scale=scaling, pending_k=key, pending_v=value, out_dtype=query.dtype)
                 return out.unsqueeze(1), None
             if _causal_or_open(attention_mask, query.shape[2]):

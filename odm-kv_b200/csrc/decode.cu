@@ -207,12 +207,15 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
             }
         }
     }
-    if (a.tail_len > 0 && ((a.class_mask >> 6) & 1)) {
-        const int ngroups = (a.tail_len + 31) / 32;
+    // the tail length is a launch argument, or lives in device memory when the launch is replayed from a graph
+    // while the tail grows
+    const int tail_len = a.tail_len_dev ? max(0, min(__ldg(a.tail_len_dev) + a.tail_len_add, a.tail_cap)) : a.tail_len;
+    if (tail_len > 0 && ((a.class_mask >> 6) & 1)) {
+        const int ngroups = (tail_len + 31) / 32;
         const int g_lo = (int)((long long)ngroups * split / a.nsplit), g_hi = (int)((long long)ngroups * (split + 1) / a.nsplit);
         const size_t base = (size_t)bh * a.tail_cap;
         for (int gi = g_lo + warp; gi < g_hi; gi += kDecWarps) {
-            const size_t rb = base + (size_t)gi * 32, re = min(base + (size_t)a.tail_len, rb + 32);
+            const size_t rb = base + (size_t)gi * 32, re = min(base + (size_t)tail_len, rb + 32);
             process_exact<CDT, GP>(st, a.tail_k, a.tail_v, rb, re, qx, a.scale, lane);
         }
     }
@@ -400,6 +403,7 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
+    a.tail_len_dev = nullptr; a.tail_len_add = 0;
     a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.slot_base = 0; a.nslots = n_splits; a.class_mask = 0x7e; a.scale = scale;
     timing_begin("decode_main", st);
     launch_decode_cuda_core(dc, a, cache_dtype, st);

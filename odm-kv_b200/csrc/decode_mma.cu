@@ -546,16 +546,13 @@ static SideStream *side_stream() {
 
 using namespace odmkv;
 
-extern "C" {
-
-// Same arguments as odmkv_decode_attn plus `lut_scales` (host float[3] or NULL for 1.0): per level a
-// factor s such that fp16(c * s) represents the centroids of the 2-, 3- and 4-bit codebooks with less
-// rounding error than fp16(c); the kernel divides it out again in fp32.
-int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
-                          const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
-                          const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
-                          int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
-                          const float *lut_scales, void *stream) {
+// Shared body of the tensor-core entry points.  With tail_len_dev the kernels read the tail length from device
+// memory (plus tail_len_add) and `tail_len` only bounds it for the sizing of the launch.
+static int decode_attn_mma_impl(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                                const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                                const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                                int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                                const float *lut_scales, void *stream, const int32_t *tail_len_dev, int tail_len_add) {
     DecodeChunks dc;
     int rc = decode_check_args(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len, tail_cap, pi_k, pi_v, codebooks,
                                B, H, G, out, out_dtype, n_splits, workspace, &dc);
@@ -616,6 +613,7 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
+    a.tail_len_dev = tail_len_dev; a.tail_len_add = tail_len_add;
     a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
     a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
     // the exact / tail kernel only needs the rotated queries, so it runs beside the tensor-core kernel on a
@@ -637,6 +635,35 @@ int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks,
     launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st, n_splits, (int)n_cta);
     timing_end(st);
     return launch_status();
+}
+
+extern "C" {
+
+// Same arguments as odmkv_decode_attn plus `lut_scales` (host float[3] or NULL for 1.0): per level a
+// factor s such that fp16(c * s) represents the centroids of the 2-, 3- and 4-bit codebooks with less
+// rounding error than fp16(c); the kernel divides it out again in fp32.
+int odmkv_decode_attn_mma(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                          const void *tail_k, const void *tail_v, int tail_len, int tail_cap, const float *pi_k,
+                          const float *pi_v, const float *codebooks, int B, int H, int G, float scale, void *out,
+                          int out_dtype, float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                          const float *lut_scales, void *stream) {
+    return decode_attn_mma_impl(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len, tail_cap, pi_k, pi_v, codebooks,
+                                B, H, G, scale, out, out_dtype, lse, n_splits, workspace, workspace_bytes, lut_scales, stream,
+                                nullptr, 0);
+}
+
+// The same call with the tail length in device memory: the launch attends min(*tail_len_dev + tail_len_add,
+// tail_cap) tail tokens, so one captured launch stays valid while a counter on the device advances.
+int odmkv_decode_attn_mma_devtail(const void *q, int q_dtype, const odmkv_chunk *chunks, int n_chunks, int cache_dtype,
+                                  const void *tail_k, const void *tail_v, const int32_t *tail_len_dev, int tail_len_add,
+                                  int tail_len_bound, int tail_cap, const float *pi_k, const float *pi_v,
+                                  const float *codebooks, int B, int H, int G, float scale, void *out, int out_dtype,
+                                  float *lse, int n_splits, void *workspace, size_t workspace_bytes,
+                                  const float *lut_scales, void *stream) {
+    if (!tail_len_dev || !tail_k || !tail_v || tail_len_add < 0 || tail_len_bound < 1 || tail_len_bound > tail_cap) return ODMKV_ERR_ARG;
+    return decode_attn_mma_impl(q, q_dtype, chunks, n_chunks, cache_dtype, tail_k, tail_v, tail_len_bound, tail_cap, pi_k, pi_v,
+                                codebooks, B, H, G, scale, out, out_dtype, lse, n_splits, workspace, workspace_bytes, lut_scales,
+                                stream, tail_len_dev, tail_len_add);
 }
 
 }  // extern "C"

@@ -28,6 +28,8 @@ struct DecodeArgs {
     float *part_ml;
     float *part_acc;
     int tail_len, tail_cap;
+    const int32_t *tail_len_dev;   // when set: the tail length is read from device memory (plus tail_len_add), bounded by tail_cap
+    int tail_len_add;
     int B, H, G;
     int nsplit;        // CTAs per (b, h) of this launch
     int slot_base;     // first partial slot this launch writes

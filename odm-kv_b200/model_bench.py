@@ -82,6 +82,7 @@ def main():
     ap.add_argument("--target-bits", type=float, default=2.0)
     ap.add_argument("--dense-cache", action="store_true", help="keep the dense HF cache in sync (the reference's behaviour)")
     ap.add_argument("--no-press", action="store_true", help="plain model with its dense cache, for comparison")
+    ap.add_argument("--graph", action="store_true", help="replay the decode step from a CUDA graph (packed cache only)")
     args = ap.parse_args()
     import torch
     from transformers import DynamicCache
@@ -129,12 +130,23 @@ def main():
         mem_after_prefill = torch.cuda.memory_allocated()
         # a few untimed steps, then the timed decode loop (teacher-forced tokens)
         warm = min(3, decode)
+        dec = None
+        if args.graph:
+            if press is None or args.dense_cache:
+                raise SystemExit("--graph needs the press with the packed cache")
+            dec = pkg.packed_cache.GraphedDecoder(model, press, cache)
+            L.odmkv_timing_enable(0)            # event pairs around kernels do not belong in a captured step
+
+        def one_step(s):
+            tok = toks[:, s:s + 1]
+            return dec.step(tok) if dec is not None else model(input_ids=tok, past_key_values=cache).logits
+
         for s in range(warm):
-            model(input_ids=toks[:, s:s + 1], past_key_values=cache)
+            one_step(s)
         stage_times(L)
         t2 = sync()
         for s in range(warm, decode):
-            logits = model(input_ids=toks[:, s:s + 1], past_key_values=cache).logits
+            logits = one_step(s)
         t3 = sync()
         decode_stages = stage_times(L)
         L.odmkv_timing_enable(0)
@@ -145,7 +157,9 @@ def main():
     line = {
         "config": args.config, "family": family, "layers": layers, "hidden": hidden, "q_heads": hq, "kv_heads": hkv, "batch": batch,
         "prefill_tokens": prefill, "decode_steps": decode, "target_bits": args.target_bits,
-        "mode": "no press (dense DynamicCache)" if press is None else ("press, dense cache in sync" if args.dense_cache else "press, packed cache only"),
+        "mode": "no press (dense DynamicCache)" if press is None else ("press, dense cache in sync" if args.dense_cache else
+                                                                      "press, packed cache only" + (", decode step replayed from a CUDA graph" if args.graph else "")),
+        "graph": None if dec is None else {"captures": dec.captures, "replays": dec.replays, "eager_steps": dec.eager_steps},
         "prefill_s": t1 - t0,
         "compress_kernel_ms_per_layer": None if press is None else {k: prefill_stages[k][0] / layers for k in ("score", "allocate", "quantize")},
         "decode_ms_per_step": (t3 - t2) * 1e3 / n_timed,

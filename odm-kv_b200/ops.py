@@ -435,12 +435,16 @@ def lut_scales():
 def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tensor, pi_v: torch.Tensor,
                 tail_k: Optional[torch.Tensor] = None, tail_v: Optional[torch.Tensor] = None, tail_len: int = 0,
                 scale: Optional[float] = None, n_splits: int = 0, out_dtype: Optional[torch.dtype] = None,
-                return_lse: bool = False, cache_dtype: Optional[torch.dtype] = None, plain: bool = False):
+                return_lse: bool = False, cache_dtype: Optional[torch.dtype] = None, plain: bool = False,
+                tail_len_dev: Optional[torch.Tensor] = None, tail_len_add: int = 0):
     """q [B, H*G, 128] -> out [B, H*G, 128]: softmax(q K_hat^T scale) V_hat over every token stored in
     ``chunks`` plus the first ``tail_len`` tokens of the dense tail [B, H, cap, 128].
 
     Calls ``odmkv_decode_attn_mma`` (tensor cores for the 2-, 3- and 4-bit banks).  ``plain=True`` calls
-    ``odmkv_decode_attn`` instead, the CUDA-core reader of every level that the tests use as a second opinion."""
+    ``odmkv_decode_attn`` instead, the CUDA-core reader of every level that the tests use as a second opinion.
+    With ``tail_len_dev`` (int32 device tensor of one element) the tail length is ``tail_len_dev + tail_len_add``,
+    read on the device when the kernel runs, and ``tail_len`` is only its upper bound
+    (``odmkv_decode_attn_mma_devtail``): the form a captured decode step uses."""
     require_cuda(q, "query")
     if q.dim() != 3 or q.shape[-1] != HEAD_DIM:
         raise ValueError(f"expected query [B, Hq, {HEAD_DIM}], got {tuple(q.shape)}")
@@ -478,7 +482,18 @@ def decode_attn(q: torch.Tensor, chunks: Sequence[PackedChunk], pi_k: torch.Tens
     common = (ptr(q), dtype_code(q.dtype), arr, len(chunks), dtype_code(cdt), ptr(tail_k), ptr(tail_v), int(tail_len), int(cap),
               ptr(pi_k), ptr(pi_v), ptr(codebook_table(dev)), B, H, G, scale, ptr(out), dtype_code(out.dtype), ptr(lse),
               int(n_splits), ptr(ws), ws.numel())
-    if plain:
+    if tail_len_dev is not None:
+        if plain or tail_k is None:
+            raise ValueError("a device-side tail length needs the tensor-core path and a tail buffer")
+        require_cuda(tail_len_dev, "tail_len_dev")
+        if tail_len_dev.dtype != torch.int32 or tail_len_dev.numel() != 1:
+            raise ValueError("tail_len_dev must be one int32 element")
+        check(L.odmkv_decode_attn_mma_devtail(ptr(q), dtype_code(q.dtype), arr, len(chunks), dtype_code(cdt), ptr(tail_k), ptr(tail_v),
+                                              ptr(tail_len_dev), int(tail_len_add), int(tail_len), int(cap), ptr(pi_k), ptr(pi_v),
+                                              ptr(codebook_table(dev)), B, H, G, scale, ptr(out), dtype_code(out.dtype), ptr(lse),
+                                              int(n_splits), ptr(ws), ws.numel(), lut_scales(), stream_ptr(dev)),
+              "odmkv_decode_attn_mma_devtail")
+    elif plain:
         check(L.odmkv_decode_attn(*common, stream_ptr(dev)), "odmkv_decode_attn")
     else:
         check(L.odmkv_decode_attn_mma(*common, lut_scales(), stream_ptr(dev)), "odmkv_decode_attn_mma")

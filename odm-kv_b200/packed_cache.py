@@ -14,7 +14,7 @@ from __future__ import annotations
 import torch
 from transformers.cache_utils import DynamicLayer
 
-__all__ = ["PackedCacheLayer", "convert_layer"]
+__all__ = ["PackedCacheLayer", "convert_layer", "GraphedDecoder"]
 
 
 class PackedCacheLayer(DynamicLayer):
@@ -49,3 +49,132 @@ def convert_layer(layer, state) -> None:
     layer._tq_backend_state = state
     empty = torch.empty(state.batch_size, state.num_heads, 0, state.head_dim, dtype=state.dtype, device=state.device)
     layer.keys, layer.values = empty, empty.clone()
+
+
+class GraphedDecoder:
+    """Single-token decode steps of a model under the press, replayed from a CUDA graph.
+
+    The reference's runner issues one eager forward pass per generated token (benchmark/core/pipeline.py:164-209),
+    which for a small batch is bound by the host launching a few hundred kernels per step.  With every layer on a
+    ``PackedCacheLayer`` the step has no shape that grows: the packed chunks are immutable between two flushes of
+    the decode buffer and the tail is a preallocated buffer whose length lives in device memory
+    (``TurboQuantAdaptiveKVCacheState.begin_device_tail``), so one captured step stays valid until the next flush.
+    ``step`` replays it, advances the host-side counters the press hook would have advanced, and falls back to an
+    eager pass for the step that flushes (scoring and re-quantisation run host logic); the step after a flush is
+    captured again over the new chunk list.
+
+    The batch must be free of padding (no attention mask that hides keys): a captured step cannot inspect a mask.
+    ``step`` returns a buffer that the next replay overwrites.
+
+    Use inside ``with press(model):`` after the prefill, with ``packed_cache=True``::
+
+        dec = GraphedDecoder(model, press, cache)
+        logits = dec.step(next_tokens)          # [B, 1] token ids on the device -> [B, 1, vocab]
+    """
+
+    def __init__(self, model, press, cache):
+        self.model, self.press, self.cache = model, press, cache
+        self.graph = None
+        self.logits = None
+        self.ids = None
+        self.pos = None
+        self._warm = False
+        self.captures = 0
+        self.replays = 0
+        self.eager_steps = 0
+
+    # -- bookkeeping -------------------------------------------------------------------------
+    def _layer_states(self):
+        states = self.press._states
+        return [(i, states[i]) for i in sorted(states)]
+
+    def _replayable(self) -> bool:
+        press, layers = self.press, getattr(self.cache, "layers", None)
+        if layers is None or not press._states or not press.decode_quant or press.buffer_size <= 1:
+            return False
+        for i, layer in enumerate(layers):
+            st = press._states.get(i)
+            if not isinstance(layer, PackedCacheLayer) or st is None or getattr(layer, "_tq_backend_state", None) is not st:
+                return False
+            if press._buffer_counts.get(i, 0) + 1 >= press.buffer_size:      # this step fills the buffer: it flushes
+                return False
+            start = press._buffer_start_seqs.get(i)
+            if start is None or start > st.seq_len:                            # the hook would rewind its counters
+                return False
+        return True
+
+    def _room(self) -> int:
+        press = self.press
+        return min(press.buffer_size - 1 - press._buffer_counts.get(i, 0) for i, _ in self._layer_states())
+
+    def drop_graph(self) -> None:
+        """Forget the captured step (after anything that changes a state: a flush, a rewind, a new prefill)."""
+        if self.graph is not None:
+            self.graph = None
+            self.logits = None
+        for _, st in self._layer_states():
+            st.end_device_tail()
+
+    def _forward(self, ids, pos=None):
+        if pos is None:
+            return self.model(input_ids=ids, past_key_values=self.cache, use_cache=True).logits
+        B = ids.shape[0]
+        return self.model(input_ids=ids, position_ids=pos.view(1, 1).expand(B, 1), cache_position=pos,
+                          past_key_values=self.cache, use_cache=True).logits
+
+    def _capture(self, tokens: torch.Tensor) -> None:
+        press = self.press
+        dev = tokens.device
+        if self.ids is None or self.ids.shape != tokens.shape:
+            self.ids = torch.zeros_like(tokens)
+            self.pos = torch.zeros(1, dtype=torch.long, device=dev)
+        room = self._room()
+        pairs = self._layer_states()
+        for _, st in pairs:
+            st.begin_device_tail(room)
+        snap = [(st.seq_len, st.tail_len, st.tail_start) for _, st in pairs]
+        counts, starts = dict(press._buffer_counts), dict(press._buffer_start_seqs)
+        self.pos.fill_(pairs[0][1].seq_len)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        # recording runs the host side of the step once (hooks included) without executing a kernel: the host
+        # counters it advanced are put back, the device counter did not move
+        modules = list(press._layer_modules.values())
+        for m in modules:
+            m._odmkv_mask_known_open = True      # no padding in a batch decoded this way: the mask cannot hide a key
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                self.logits = self._forward(self.ids, self.pos)
+        finally:
+            for m in modules:
+                m._odmkv_mask_known_open = False
+        for (_, st), (sl, tl, ts) in zip(pairs, snap):
+            st.seq_len, st.tail_len, st.tail_start = sl, tl, ts
+        press._buffer_counts.clear()
+        press._buffer_counts.update(counts)
+        press._buffer_start_seqs.clear()
+        press._buffer_start_seqs.update(starts)
+        self.graph = graph
+        self.captures += 1
+
+    # -- the step ----------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, tokens: torch.Tensor) -> torch.Tensor:
+        if not self._warm or not self._replayable():
+            # the first step (library handles, helper stream, kernel attributes) and every flushing step run eagerly
+            self.drop_graph()
+            self._warm = True
+            self.eager_steps += 1
+            return self._forward(tokens)
+        if self.graph is None or self.ids.shape != tokens.shape:
+            self.drop_graph()
+            self._capture(tokens)
+        pairs = self._layer_states()
+        self.ids.copy_(tokens)
+        self.pos.fill_(pairs[0][1].seq_len)
+        self.graph.replay()
+        for i, st in pairs:
+            st.advance_host(1)
+            self.press._buffer_counts[i] = self.press._buffer_counts.get(i, 0) + 1
+        self.replays += 1
+        return self.logits

@@ -83,6 +83,8 @@ class TurboQuantAdaptiveKVCacheState:
         self.tail_v: Optional[torch.Tensor] = None
         self.tail_start = 0      # sequence position of the first tail token
         self.tail_len = 0
+        self._tail_len_dev = None   # int32 [1] on the device while a captured decode step owns the tail counter
+        self._tail_room = 0
 
     def _validate_shapes(self, keys, values, bits=None) -> None:
         if keys.shape != values.shape:
@@ -139,9 +141,13 @@ class TurboQuantAdaptiveKVCacheState:
             return
         if self.tail_len == 0:
             self.tail_start = self.seq_len
-        self._ensure_tail(self.tail_len + T)
-        self.tail_k[:, :, self.tail_len:self.tail_len + T] = keys
-        self.tail_v[:, :, self.tail_len:self.tail_len + T] = values
+        if self._tail_len_dev is not None:
+            self._write_tail_at_counter(keys, values)
+            self._tail_len_dev.add_(T)
+        else:
+            self._ensure_tail(self.tail_len + T)
+            self.tail_k[:, :, self.tail_len:self.tail_len + T] = keys
+            self.tail_v[:, :, self.tail_len:self.tail_len + T] = values
         self.tail_len += T
         self.seq_len += T
 
@@ -150,10 +156,48 @@ class TurboQuantAdaptiveKVCacheState:
         the tail, without committing them; returns the tail length a decode call should attend."""
         T = int(keys.shape[2])
         self._validate_shapes(keys, values)
+        if self._tail_len_dev is not None:
+            self._write_tail_at_counter(keys, values)
+            return self.tail_len + T
         self._ensure_tail(self.tail_len + T)
         self.tail_k[:, :, self.tail_len:self.tail_len + T] = keys
         self.tail_v[:, :, self.tail_len:self.tail_len + T] = values
         return self.tail_len + T
+
+    # ------------------------------------------------------------------ device-side tail counter (captured decode steps)
+    def begin_device_tail(self, room: int) -> None:
+        """Switch the tail bookkeeping to a counter in device memory, for a decode step that is captured into a
+        CUDA graph and replayed while the tail grows by one token per replay: tail writes go to the slot the counter
+        names and the decode kernels read the tail length from it.  ``room`` = tokens the tail may still take before
+        ``end_device_tail`` (the buffer is grown now, never while the counter is in use).  The host counters keep
+        advancing as usual in an eager pass; after a replay the caller advances them with ``advance_host(1)``."""
+        if self.batch_size == 0:
+            raise RuntimeError("begin_device_tail() needs a prefilled state")
+        self._ensure_tail(self.tail_len + int(room) + 1)
+        self._tail_room = self.tail_len + int(room) + 1
+        if self._tail_len_dev is None:
+            self._tail_len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._tail_len_dev.fill_(self.tail_len)
+
+    def end_device_tail(self) -> None:
+        self._tail_len_dev = None
+
+    def advance_host(self, n: int = 1) -> None:
+        """Mirror on the host what a replayed decode step did on the device: ``n`` tokens joined the tail."""
+        if self.tail_len == 0:
+            self.tail_start = self.seq_len
+        self.tail_len += int(n)
+        self.seq_len += int(n)
+
+    def _write_tail_at_counter(self, keys: torch.Tensor, values: torch.Tensor) -> None:
+        T = int(keys.shape[2])
+        if T != 1:
+            raise ValueError("the device-side tail counter serves single-token decode steps")
+        if self.tail_len + T > self._tail_room:
+            raise RuntimeError("the tail outgrew the room reserved by begin_device_tail()")
+        idx = self._tail_len_dev.to(torch.int64)
+        self.tail_k.index_copy_(2, idx, keys.to(self.dtype))
+        self.tail_v.index_copy_(2, idx, values.to(self.dtype))
 
     def truncate(self, seq_len: int) -> None:
         """Drop every token at position >= seq_len (tq_adaptive_backend.py:427-437)."""
@@ -308,12 +352,18 @@ class TurboQuantAdaptiveKVCacheState:
         query [B, Hq, d]; optional pending_k/v [B, H, t, d] are attended as well (tokens of the running
         forward pass that have not been appended yet).  Returns [B, Hq, d]."""
         tail_len = self.tail_len
+        n_pending = 0
         if pending_k is not None:
             if self.batch_size == 0:
                 self.batch_size, self.num_heads = int(pending_k.shape[0]), int(pending_k.shape[1])
+            n_pending = int(pending_k.shape[2])
             tail_len = self.stage_pending(pending_k, pending_v)
         if len(self.chunks) > ops._lib.MAX_CHUNKS:
             self.compact(keep_first=1)
+        if self._tail_len_dev is not None:
+            return ops.decode_attn(query, self.chunks, self.pi_k, self.pi_v, tail_k=self.tail_k, tail_v=self.tail_v,
+                                   tail_len=self._tail_room, scale=scale, out_dtype=out_dtype, cache_dtype=self.dtype,
+                                   tail_len_dev=self._tail_len_dev, tail_len_add=n_pending)
         return ops.decode_attn(query, self.chunks, self.pi_k, self.pi_v, tail_k=self.tail_k, tail_v=self.tail_v,
                                tail_len=tail_len, scale=scale, out_dtype=out_dtype, cache_dtype=self.dtype)
 
