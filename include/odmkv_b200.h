@@ -269,6 +269,24 @@ int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chu
                               int out_dtype, float *lse, int n_splits, const float *lut_scales, void *stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Column statistics of causal softmax attention.  Replaces _chunked_attention_qk
+ * (kvquant/attention_utils.py:160-211), the reference's windowed-attention building block whose column sums feed
+ * RiskScorer.score_with_attn (kvquant/scorer.py:406-416): logits q_r.k_j / scale, keys j > r + q_offset hidden from
+ * query r (the reference's mask is q_offset = 0; a window of the last Tq positions takes q_offset = Tkv - Tq),
+ * softmax over the keys per query, mean over the G query heads of a KV head, and per key the sum, the maximum and
+ * the sum of squares of that mean over the queries.
+ *   Q [B, H*G, Tq, 128], K [B, H, Tkv, 128]: fp16 or bf16 (dtype code), contiguous, 16-byte aligned
+ *   sum_attn, max_attn, sum_sq_attn: [B, H, Tkv] fp32 out
+ *   workspace: odmkv_window_stats_workspace_bytes(B, H, G, Tq) bytes; the 32-bit word at
+ *   odmkv_window_stats_status_offset(...) is 0 after a clean run, 1 if a bounded wait expired (results invalid)
+ * G <= 16.  Runs on the tcgen05 tensor cores (two passes: log-sum-exp per query, then the statistics per key). */
+size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq);
+size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq);
+int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int H, int G, int Tq, int Tkv, int q_offset,
+                            float scale, float *sum_attn, float *max_attn, float *sum_sq_attn, void *workspace,
+                            size_t workspace_bytes, void *stream);
+
+/* ------------------------------------------------------------------------------------------
  * Optional kernel timing (no counterpart in the reference).  When enabled, the launchers bracket
  * their dominant kernel with CUDA events on the launching stream under the names "score",
  * "allocate", "quantize", "decode_main"; odmkv_timing_read waits for the events recorded since the

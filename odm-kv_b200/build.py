@@ -11,7 +11,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["quant.cu", "score.cu", "alloc.cu", "decode.cu", "decode_mma.cu", "noalloc.cu", "timing.cu"]
+SOURCES = ["quant.cu", "score.cu", "alloc.cu", "decode.cu", "decode_mma.cu", "noalloc.cu", "timing.cu", "window_stats.cu"]
 LIB = os.path.join(HERE, "libodmkv_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

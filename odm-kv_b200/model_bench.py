@@ -144,9 +144,20 @@ def main():
         for s in range(warm):
             one_step(s)
         stage_times(L)
+        kinds = {"replay": [0.0, 0], "capture+replay": [0.0, 0], "eager": [0.0, 0]}
         t2 = sync()
         for s in range(warm, decode):
+            if dec is None:
+                logits = one_step(s)
+                continue
+            # per-kind times of the graphed run (one synchronisation per step, negligible against a step)
+            before = (dec.captures, dec.replays)
+            ta = time.perf_counter()
             logits = one_step(s)
+            tb = sync()
+            kind = "eager" if dec.replays == before[1] else ("capture+replay" if dec.captures != before[0] else "replay")
+            kinds[kind][0] += tb - ta
+            kinds[kind][1] += 1
         t3 = sync()
         decode_stages = stage_times(L)
         L.odmkv_timing_enable(0)
@@ -159,7 +170,9 @@ def main():
         "prefill_tokens": prefill, "decode_steps": decode, "target_bits": args.target_bits,
         "mode": "no press (dense DynamicCache)" if press is None else ("press, dense cache in sync" if args.dense_cache else
                                                                       "press, packed cache only" + (", decode step replayed from a CUDA graph" if args.graph else "")),
-        "graph": None if dec is None else {"captures": dec.captures, "replays": dec.replays, "eager_steps": dec.eager_steps},
+        "graph": None if dec is None else {"captures": dec.captures, "replays": dec.replays, "eager_steps": dec.eager_steps,
+                                           "ms_per_step_by_kind": {k: (v[0] * 1e3 / v[1] if v[1] else None) for k, v in kinds.items()},
+                                           "steps_by_kind": {k: v[1] for k, v in kinds.items()}},
         "prefill_s": t1 - t0,
         "compress_kernel_ms_per_layer": None if press is None else {k: prefill_stages[k][0] / layers for k in ("score", "allocate", "quantize")},
         "decode_ms_per_step": (t3 - t2) * 1e3 / n_timed,

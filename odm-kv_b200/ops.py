@@ -93,6 +93,40 @@ def score_with_attn(K: torch.Tensor, V: torch.Tensor, p: torch.Tensor, eps: floa
     return out
 
 
+def window_attn_stats(Q: torch.Tensor, K: torch.Tensor, scale: Optional[float] = None, q_offset: int = 0,
+                      check_status: bool = True):
+    """Q [B, H*G, Tq, 128], K [B, H, Tkv, 128] (fp16 / bf16) -> (sum_attn, max_attn, sum_sq_attn), each [B, H, Tkv] fp32:
+    per key the sum / maximum / sum of squares over the queries of the head-averaged causal softmax weight (key j is
+    hidden from query r when j > r + q_offset).  ``check_status`` synchronises and raises if a bounded wait expired."""
+    require_cuda(Q, "queries")
+    if Q.dim() != 4 or K.dim() != 4 or Q.shape[-1] != HEAD_DIM or K.shape[-1] != HEAD_DIM or Q.shape[0] != K.shape[0]:
+        raise ValueError(f"expected queries [B, Hq, Tq, {HEAD_DIM}] and keys [B, H, Tkv, {HEAD_DIM}], got {tuple(Q.shape)} / {tuple(K.shape)}")
+    if Q.dtype not in (torch.float16, torch.bfloat16) or K.dtype != Q.dtype:
+        raise NotImplementedError("window_attn_stats takes fp16 or bf16 queries and keys of one dtype")
+    B, Hq, Tq, _ = Q.shape
+    H, Tkv = K.shape[1], K.shape[2]
+    if Hq % H:
+        raise ValueError(f"query heads {Hq} not a multiple of KV heads {H}")
+    G = Hq // H
+    Q, K = Q.contiguous(), K.contiguous()
+    if Q.data_ptr() % 16:
+        Q = Q.clone()
+    if K.data_ptr() % 16:
+        K = K.clone()
+    dev = Q.device
+    outs = [torch.empty(B, H, Tkv, dtype=torch.float32, device=dev) for _ in range(3)]
+    L = lib()
+    ws = _ws(L.odmkv_window_stats_workspace_bytes(B, H, G, Tq), dev)
+    scale = float(HEAD_DIM ** 0.5) if scale is None else float(scale)
+    check(L.odmkv_window_attn_stats(ptr(Q), ptr(K), dtype_code(Q.dtype), B, H, G, Tq, Tkv, int(q_offset), scale, ptr(outs[0]),
+                                    ptr(outs[1]), ptr(outs[2]), ptr(ws), ws.numel(), stream_ptr(dev)), "odmkv_window_attn_stats")
+    if check_status:
+        off = L.odmkv_window_stats_status_offset(B, H, G, Tq)
+        if int(ws[off:off + 4].view(torch.int32).item()) != 0:
+            raise OdmkvError("odmkv_window_attn_stats: a bounded wait on the tensor cores expired; the statistics are invalid")
+    return tuple(outs)
+
+
 # ---------------------------------------------------------------------------------------------
 # allocator
 # ---------------------------------------------------------------------------------------------

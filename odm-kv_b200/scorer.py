@@ -14,7 +14,7 @@ from torch import nn
 
 from . import ops
 
-__all__ = ["BaseScorer", "ExpectedAttentionScorer", "RiskScorer"]
+__all__ = ["BaseScorer", "ExpectedAttentionScorer", "RiskScorer", "_chunked_attention_qk"]
 
 
 # ---- attention helpers (kvquant/attention_utils.py) ---------------------------------------------
@@ -104,6 +104,23 @@ def mean_query_states(module: nn.Module, hidden_states: torch.Tensor, n_sink: in
 
 
 # ---- scorers --------------------------------------------------------------------------------------
+
+def _chunked_attention_qk(query_states: torch.Tensor, expanded_keys_t: torch.Tensor, T_kv: int, H_kv: int, n_groups: int,
+                          scale: float, chunk_size: int, device, dtype):
+    """Attention statistics per KV position, same signature and result as the reference's helper
+    (kvquant/attention_utils.py:160-211): ``query_states`` [1, H_q, T_q, d], ``expanded_keys_t`` [1, H_q, d, T_kv] (the
+    G-expanded, transposed keys the reference multiplies with) -> ``(sum_attn, max_attn, sum_sq_attn)``, each
+    [H_kv, T_kv] in ``dtype``.  One pass of the tensor-core kernels (``ops.window_attn_stats``); ``chunk_size`` only
+    bounded the reference's temporaries and is ignored."""
+    if query_states.dim() != 4 or query_states.shape[0] != 1 or expanded_keys_t.shape[-1] != T_kv:
+        raise ValueError("expected query_states [1, H_q, T_q, d] and expanded_keys_t [1, H_q, d, T_kv]")
+    keys = expanded_keys_t[:, ::n_groups].transpose(-1, -2)                       # [1, H_kv, T_kv, d]
+    if keys.shape[1] != H_kv:
+        raise ValueError(f"expanded keys hold {expanded_keys_t.shape[1]} heads, expected {H_kv} x {n_groups}")
+    cdt = query_states.dtype if query_states.dtype in (torch.float16, torch.bfloat16) else torch.float16
+    s, m, q = ops.window_attn_stats(query_states.to(device=device, dtype=cdt), keys.to(device=device, dtype=cdt), scale=scale)
+    return s[0].to(dtype), m[0].to(dtype), q[0].to(dtype)
+
 
 def _normalize_scores(raw: torch.Tensor, *, grain: str = "layer") -> torch.Tensor:
     """Min-max normalisation with the reference's grains (kvquant/scorer.py:100-135)."""
@@ -215,3 +232,19 @@ class RiskScorer(ExpectedAttentionScorer):
 
     def score_with_attn(self, keys, values, attn_weights, *, module=None):
         return ops.score_with_attn(keys, values, attn_weights, float(self.epsilon))
+
+    def score_windowed(self, keys: torch.Tensor, values: torch.Tensor, query_window: torch.Tensor) -> torch.Tensor:
+        """Risk scores from the attention the last W queries actually pay: keys / values [H, T, d], ``query_window``
+        [H_q, W, d] = the position-encoded queries of positions T - W .. T - 1 -> scores [H, T] fp32.  The reference
+        ships the two halves of this -- the column sums of causal softmax attention (kvquant/attention_utils.py:160-211)
+        and the risk formula for given weights (kvquant/scorer.py:406-416) -- and this method composes them: the
+        weight of key j is its column sum divided by the number of window queries that can see it."""
+        H, T, _ = keys.shape
+        W = int(query_window.shape[1])
+        if W < 1 or W > T:
+            raise ValueError(f"window of {W} queries over {T} keys")
+        cdt = keys.dtype if keys.dtype in (torch.float16, torch.bfloat16) else torch.float16
+        s, _, _ = ops.window_attn_stats(query_window.unsqueeze(0).to(cdt), keys.unsqueeze(0).to(cdt), q_offset=T - W)
+        pos = torch.arange(T, device=keys.device)
+        seen_by = (W - (pos - (T - W)).clamp(min=0)).to(torch.float32)          # queries r with j <= r + (T - W)
+        return ops.score_with_attn(keys, values, s[0] / seen_by, float(self.epsilon))

@@ -290,6 +290,34 @@ def score_with_attn(K: np.ndarray, V: np.ndarray, p: np.ndarray, eps: float = 1e
     return risk_from_p(K, V, p, eps)
 
 
+def chunked_attention_qk(Q: np.ndarray, K: np.ndarray, scale: float, q_offset: int = 0):
+    """_chunked_attention_qk (kvquant/attention_utils.py:160-211) in fp32, without the chunking (which only bounds the
+    reference's temporaries): Q [Hq, Tq, d], K [H, Tkv, d] -> (sum_attn, max_attn, sum_sq_attn), each [H, Tkv].
+    logits = q.k / scale (184), keys with q_pos < k_pos hidden (187-190; here k_pos > q_pos + q_offset), softmax over
+    the keys (192), mean over the G query heads of a KV head (195), then sum / max / sum of squares over the queries
+    (199-205)."""
+    Q = np.asarray(Q, np.float32)
+    K = np.asarray(K, np.float32)
+    Hq, Tq, _ = Q.shape
+    H, Tkv, _ = K.shape
+    G = Hq // H
+    s_sum = np.zeros((H, Tkv), np.float32)
+    s_max = np.zeros((H, Tkv), np.float32)
+    s_sq = np.zeros((H, Tkv), np.float32)
+    hidden = np.arange(Tkv)[None, :] > (np.arange(Tq)[:, None] + q_offset)           # [Tq, Tkv]
+    for h in range(H):
+        logits = np.einsum("gqd,kd->gqk", Q[h * G:(h + 1) * G], K[h]).astype(np.float32) / np.float32(scale)
+        logits[:, hidden] = -np.inf
+        logits -= logits.max(axis=-1, keepdims=True)
+        w = np.exp(logits, dtype=np.float32)
+        w /= w.sum(axis=-1, keepdims=True, dtype=np.float32)
+        m = w.mean(axis=0, dtype=np.float32)                                           # [Tq, Tkv]
+        s_sum[h] = m.sum(axis=0, dtype=np.float32)
+        s_max[h] = m.max(axis=0)
+        s_sq[h] = (m * m).sum(axis=0, dtype=np.float32)
+    return s_sum, s_max, s_sq
+
+
 # ---------------------------------------------------------------------------
 # Allocator (kvquant/allocator.py:46-148, 333-342, 352-452, 459-663)
 # ---------------------------------------------------------------------------

@@ -326,14 +326,34 @@ def press_case(name, B, T, n_question, n_decode, buffer_size, outdir, target=2.6
     print(f"[{name}] wrote {path} ({os.path.getsize(path) / 1024:.0f} KiB)")
 
 
+def window_case(name, H, G, Tq, Tkv, seed, outdir):
+    """The reference's _chunked_attention_qk (kvquant/attention_utils.py:160-211) on fp16-representable inputs in
+    fp32, with the G-expanded transposed keys it expects; chunk size 64 so that the chunk loop runs more than once."""
+    from kvquant.attention_utils import _chunked_attention_qk, _repeat_kv
+    g = torch.Generator().manual_seed(seed)
+    Q = (torch.randn(1, H * G, Tq, 128, generator=g) * 1.5).half().float()
+    K = torch.randn(1, H, Tkv, 128, generator=g).half().float()
+    K[:, :, :4] *= 3.0        # a few dominant early keys, as attention sinks are
+    K = K.half().float()
+    expanded_t = _repeat_kv(K, G).transpose(-1, -2).contiguous()
+    s, m, q = _chunked_attention_qk(Q, expanded_t, Tkv, H, G, math.sqrt(128.0), 64, torch.device("cpu"), torch.float32)
+    np.savez_compressed(os.path.join(outdir, name + ".npz"), Q=Q[0].numpy().astype(np.float16), K=K[0].numpy().astype(np.float16),
+                        sum_attn=s.numpy(), max_attn=m.numpy(), sum_sq_attn=q.numpy(), G=np.int32(G))
+    print(name, "sum", float(s.sum()), "max", float(m.max()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="checkout of the reference project (the directory that holds kvquant/)")
     ap.add_argument("--out", default=os.path.join(ROOT, "tests", "golden"))
     ap.add_argument("--only-press", action="store_true", help="regenerate the two press fixtures only")
+    ap.add_argument("--only-window", action="store_true", help="regenerate the windowed-attention fixture only")
     args = ap.parse_args()
     torch.set_num_threads(os.cpu_count() or 1)
     install_reference(args.reference)
+    if args.only_window:
+        window_case("window_g4", H=2, G=4, Tq=200, Tkv=200, seed=5, outdir=args.out)
+        return
     if args.only_press:
         press_case("press_b1_question", B=1, T=160, n_question=6, n_decode=40, buffer_size=16, outdir=args.out)
         press_case("press_b2", B=2, T=150, n_question=0, n_decode=36, buffer_size=16, outdir=args.out)
@@ -344,6 +364,7 @@ def main():
     run_case("config0", B=1, H=8, G=4, T=4096, seed=0, targets=(2.0, 3.0), store_inputs=False, outdir=args.out, store_scores_bits=True)
     press_case("press_b1_question", B=1, T=160, n_question=6, n_decode=40, buffer_size=16, outdir=args.out)
     press_case("press_b2", B=2, T=150, n_question=0, n_decode=36, buffer_size=16, outdir=args.out)
+    window_case("window_g4", H=2, G=4, Tq=200, Tkv=200, seed=5, outdir=args.out)
 
 
 if __name__ == "__main__":

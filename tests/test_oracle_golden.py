@@ -110,3 +110,13 @@ def test_config0_digests(orc, golden):
         assert np.abs(hist - g[f"{tag}_bits_hist"]).max() <= 8
         nonsink = bits[:, 4:]
         assert abs(nonsink.sum() - target * nonsink.size) <= 0.5 + 1e-9
+
+
+def test_window_attention_stats_match_reference(orc, golden):
+    """The oracle's restatement of _chunked_attention_qk against the reference's own output (fp32 run)."""
+    g = golden["window_g4"]
+    s, m, q = orc.chunked_attention_qk(g["Q"].astype(np.float32), g["K"].astype(np.float32), np.sqrt(128.0))
+    for got, want in ((s, g["sum_attn"]), (m, g["max_attn"]), (q, g["sum_sq_attn"])):
+        assert np.abs(got - want).max() <= 2e-5 * np.abs(want).max()
+    # every query's weights sum to one, so the column sums add up to the number of queries per KV head
+    assert np.allclose(s.sum(axis=1), g["Q"].shape[1], rtol=1e-5)
