@@ -125,6 +125,56 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def measured_peak_tflops():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def window_stats_block(args, pkg, K, dev, W=128):
+    """The windowed-query variant of the score stage on the tensor cores: column statistics of the causal softmax
+    attention of the last W queries over the whole context of this layer (same keys as the compress pass).  Reported
+    against the tensor peak and against the special-function unit, which executes one exponential per logit and pass
+    and is the actual bound (16 per clock and SM)."""
+    import ctypes
+    import torch
+    ops, L = pkg.ops, pkg._lib.lib()
+    B, H, T, G = K.shape[0], K.shape[1], K.shape[2], args.group
+    g = torch.Generator(device=dev).manual_seed(77)
+    Qw = (torch.randn(B, H * G, W, 128, generator=g, device=dev) * 1.2).to(K.dtype)
+    for _ in range(3):
+        ops.window_attn_stats(Qw, K, q_offset=T - W)
+    L.odmkv_timing_enable(1)
+    reps = 5
+    for _ in range(reps):
+        ops.window_attn_stats(Qw, K, q_offset=T - W, check_status=False)
+    ms = {}
+    for name in ("window_lse", "window_cols"):
+        tot, n = ctypes.c_double(), ctypes.c_longlong()
+        L.odmkv_timing_read(name.encode(), ctypes.byref(tot), ctypes.byref(n))
+        ms[name] = tot.value / max(n.value, 1)
+    L.odmkv_timing_enable(0)
+    # visible (query, key) pairs: query r of the window sees T - W + r + 1 keys
+    pairs = B * H * G * (W * (T - W) + W * (W + 1) // 2)
+    flops = 2.0 * 2 * 128 * pairs                       # two passes of q.k over every visible pair
+    total_ms = ms["window_lse"] + ms["window_cols"]
+    peak, kind = measured_peak_tflops()
+    try:
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    except Exception:
+        sms = 148
+    exp_peak = 16.0 * sms * 1.965e9                     # exponentials per second at the maximum SM clock
+    return {"workload": f"last {W} queries x {T} keys, batch {B}, GQA {H * G}/{H}, fp16", "ms": total_ms, "kernel_ms": ms,
+            "tflops": flops / (total_ms * 1e-3) / 1e12, "tensor_peak_tflops": peak, "tensor_frac": flops / (total_ms * 1e-3) / 1e12 / peak,
+            "peak_kind": f"of {kind}", "bound": "special-function unit (one ex2 per logit and pass)",
+            "exp_per_s": 2.0 * pairs / (total_ms * 1e-3), "exp_frac_of_16_per_clk_sm": 2.0 * pairs / (total_ms * 1e-3) / exp_peak,
+            "key_bytes_read_once_gb": B * H * T * 256 / 1e9}
+
+
 def workload_name(ctx, batch, kv_heads, group, target_bits) -> str:
     return (f"decode attention over packed cache: ctx {ctx}, batch {batch}, GQA {kv_heads * group}/{kv_heads}, d 128, target "
             f"{target_bits} bits over {list(LEVELS)}, fp16 cache")
@@ -420,6 +470,7 @@ def run_ours(args):
         L.odmkv_timing_read(name.encode(), ctypes.byref(tot), ctypes.byref(n))
         stage_ms[name] = tot.value
     L.odmkv_timing_enable(0)
+    window = window_stats_block(args, pkg, K, dev)
     reports = ops.read_reports(rep)
     pi_k, pi_v = state.pi_k, state.pi_v
     cnt = chunk.seg_count_host().sum(axis=1)
@@ -636,7 +687,8 @@ def run_ours(args):
         "compress": {"mtok_per_s": B * T / (compress_ms * 1e-3) / 1e6, "ms_per_layer": compress_ms, "stage_ms": stage_ms,
                      "stage_roofline": compress_rooflines(stage_ms, B * H * T, bytes_per_step, peak),
                      "tokens": B * T, "alloc_evaluations": reports[0]["evaluations"], "alloc_moved": reports[0]["moved"],
-                     "ties_lambda": sum(r["ties_lambda"] for r in reports), "ties_cut": sum(r["ties_cut"] for r in reports)},
+                     "ties_lambda": sum(r["ties_lambda"] for r in reports), "ties_cut": sum(r["ties_cut"] for r in reports),
+                     "window_stats": window},
     }
     if not args.no_cpu_baseline and world == 1:
         cores = os.cpu_count() or 1

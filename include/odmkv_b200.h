@@ -279,9 +279,13 @@ int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chu
  *   sum_attn, max_attn, sum_sq_attn: [B, H, Tkv] fp32 out
  *   workspace: odmkv_window_stats_workspace_bytes(B, H, G, Tq) bytes; the 32-bit word at
  *   odmkv_window_stats_status_offset(...) is 0 after a clean run, 1 if a bounded wait expired (results invalid)
- * G <= 16.  Runs on the tcgen05 tensor cores (two passes: log-sum-exp per query, then the statistics per key). */
+ * G <= 16.  Runs on the tcgen05 tensor cores (two passes: log-sum-exp per query, then the statistics per key),
+ * operand tiles staged by TMA tensor copies where the shapes allow. */
 size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq);
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq);
+/* how the last call on this process staged its operand tiles: 1 = one tensor copy (TMA) per tile -- taken when Tq and
+ * Tkv are multiples of 8 and Q, K are 128-byte aligned --, 0 = 16-byte copies by the threads, -1 = no call yet */
+int odmkv_window_stats_last_path(void);
 int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int H, int G, int Tq, int Tkv, int q_offset,
                             float scale, float *sum_attn, float *max_attn, float *sum_sq_attn, void *workspace,
                             size_t workspace_bytes, void *stream);

@@ -14,18 +14,24 @@
 //          dimension; the thread that owns a key reads its row, turns it into probabilities with the stored
 //          log-sum-exps, averages the G heads of each query in registers and accumulates the three statistics --
 //          no exchange between threads, no atomics: a CTA owns its keys.
-// Operand tiles are copied by the threads (cp.async, 16 bytes each) into the canonical K-major layout without
-// swizzle: 8-row x 16-byte core matrices, 128 bytes between K-neighbours, 2048 bytes between row groups.
+// Operand tiles sit in shared memory in the canonical K-major layout without swizzle: 8-row x 16-byte core matrices,
+// 128 bytes between K-neighbours, 2048 bytes between row groups.  When the sequence lengths are multiples of eight a
+// tile is ONE tensor copy (TMA, cp.async.bulk.tensor): the row-major global tensor is described as (8 elements, 8
+// rows, 16 chunks, row groups, heads), whose box order is exactly that layout; rows past the end read as zeros.
+// Otherwise the threads copy 16-byte pieces themselves (cp.async).
 // The exponentials bound both passes (one per logit and pass on the special-function unit), not the products.
 // Every wait on an mbarrier is bounded; an expired wait sets the status word and the CTA runs out without waiting
 // again, releasing its tensor memory.
 #include "common.cuh"
 
+#include <cuda.h>
+#include <cstring>
+
 namespace odmkv {
 
 namespace {
 
-constexpr int kWThreads = 128;
+constexpr int kWThreads = 256;                    // two threads per tensor-memory lane: each takes half of the columns
 constexpr int kWRows = 128;                       // rows of the A tile = tensor-memory lanes
 constexpr uint32_t kLbo = 128, kSbo = 2048;       // bytes between K-adjacent core matrices / between 8-row groups
 constexpr int kTileBytes = kWRows * kD * 2;       // 32 KiB per 128 rows
@@ -42,6 +48,12 @@ struct WinArgs {
     int B, H, G, Tq, Tkv, q_offset, RB;
     float c;                // log2(e) / scale
     int bf16;
+};
+
+struct WinMaps {
+    CUtensorMap q_tile;     // box: 128 rows of one query head (pass 1)
+    CUtensorMap q_blk;      // box: RB rows of each of the G heads of a KV head (pass 2)
+    CUtensorMap k_tile;     // box: 128 rows of one KV head
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -84,11 +96,25 @@ __device__ __forceinline__ bool mbar_poll(uint32_t bar, unsigned parity) {
     return ok != 0;
 }
 // bounded wait: false when it expired (the caller stops issuing work and reports through the status word)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity) {
-    for (unsigned it = 0; it < kPolls; ++it)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity, const volatile int *abort_flag = nullptr) {
+    for (unsigned it = 0; it < kPolls; ++it) {
         if (mbar_poll(bar, parity)) return true;
+        if (abort_flag && *abort_flag) return false;
+    }
     return false;
 }
+// one tensor copy of a box into shared memory, completion counted in bytes on an mbarrier
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, int c3, int c4, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
+                 ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(0), "r"(c3), "r"(c4), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
@@ -110,14 +136,25 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
-// Copy `groups` groups of eight rows into the canonical layout at `tile`: piece (row 8 gi + tid % 8, 16-byte chunk
-// c) lands at gi * 2048 + c * 128 + (tid % 8) * 16, so the 32 stores of a warp fill 512 consecutive bytes.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
+// Copy `groups` groups of eight rows into the canonical layout at `tile`: the piece (row 8 gi + r, 16-byte chunk c)
+// lands at gi * 2048 + c * 128 + r * 16.  Two neighbouring lanes take the two halves of one 32-byte sector of a row
+// (a 16-byte asynchronous copy fetches a whole sector; with one lane per row every sector was fetched twice), eight
+// lanes cover four rows, a warp eight rows x four chunks; the price is a two-way bank conflict on the shared-memory
+// side, which has room.  Warps 0-3 / 4-7 take alternate groups.
 // row_ptr(row) returns the row's address in global memory, or nullptr for a row that does not exist: such a row is
 // zero-filled (a copy of zero source bytes, which still names a valid global address, `any_row`).
 template <class RowPtr>
 __device__ __forceinline__ void stage_rows(unsigned char *tile, int groups, int tid, const unsigned char *any_row, RowPtr row_ptr) {
-    const int r8 = tid & 7, c0 = tid >> 3;       // 16 chunk columns: every thread takes chunk c0 of one row per group
-    for (int gi = 0; gi < groups; ++gi) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int r8 = (lane >> 1) & 7, c0 = (warp & 3) * 4 + (lane >> 4) * 2 + (lane & 1);
+    for (int gi = warp >> 2; gi < groups; gi += kWThreads / 128) {
         const unsigned char *src = reinterpret_cast<const unsigned char *>(row_ptr(gi * 8 + r8));
         const uint32_t dst = smem_u32(tile) + gi * kSbo + c0 * kLbo + r8 * 16;
         cp_async16(dst, src ? src + c0 * 16 : any_row, src != nullptr);
@@ -151,14 +188,21 @@ __device__ __forceinline__ void tmem_free(uint32_t base, int cols, int warp) {
 }
 
 // ---- pass 1: log2-sum-exp per (query head, query) -----------------------------------------------------------------
-// grid: (ceil(Tq / 128), B * Hq); shared memory: Q tile + two K tiles
-__global__ void __launch_bounds__(kWThreads) win_lse_kernel(const WinArgs a) {
+// grid: (ceil(Tq / 128), B * Hq); shared memory: Q tile + two K tiles; tensor memory: two 128-column accumulators.
+// Eight warps: warp w reads tensor-memory lanes 32 (w % 4) .. +31 (a row each), warps 0-3 the first 64 columns of a
+// tile and warps 4-7 the last 64; the two partial (maximum, sum) pairs of a row meet once, at the end.
+// Pipeline: while the threads turn tile kt into exponentials, the tensor cores already form tile kt + 1 in the other
+// accumulator and the copies of tile kt + 2 are in flight; one block-wide barrier per tile.
+template <bool TMA>
+__global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of K tile kt land on full_bar[kt & 1]
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
+    __shared__ float2 part_s[kWRows];
     unsigned char *q_tile = smem, *k_tiles = smem + kTileBytes;
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = warp >> 2;
     const int Hq = a.H * a.G;
     const int bq = blockIdx.y, b = bq / Hq, hq = bq % Hq, h = hq / a.G;
     const int r0 = blockIdx.x * kWRows;
@@ -166,102 +210,157 @@ __global__ void __launch_bounds__(kWThreads) win_lse_kernel(const WinArgs a) {
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)bq * a.Tq) * kD * esz;
     const unsigned char *Kb = reinterpret_cast<const unsigned char *>(a.K) + ((size_t)(b * a.H + h) * a.Tkv) * kD * esz;
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bar)) : "memory");
+        mbar_init(&bar, 1);
+        mbar_init(&full_bar[0], 1);
+        mbar_init(&full_bar[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_s = 0;
     }
-    const uint32_t tmem = tmem_alloc(&tmem_slot, 128, warp);
-    const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tmem = tmem_alloc(&tmem_slot, 256, warp);
+    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + half * 64;
 
     // keys this query tile can see: j <= r + q_offset for its last row
     const int r_last = min(r0 + kWRows, a.Tq) - 1;
     const int n_keys = max(0, min(a.Tkv, r_last + a.q_offset + 1));
     const int n_kt = (n_keys + kWRows - 1) / kWRows;
-    stage_rows(q_tile, 16, tid, Qb, [&](int row) { return r0 + row < a.Tq ? Qb + (size_t)(r0 + row) * kD * esz : nullptr; });
+    if constexpr (!TMA)
+        stage_rows(q_tile, 16, tid, Qb, [&](int row) { return r0 + row < a.Tq ? Qb + (size_t)(r0 + row) * kD * esz : nullptr; });
     auto stage_k = [&](int kt) {
-        stage_rows(k_tiles + (kt & 1) * kTileBytes, 16, tid, Kb,
-                   [&](int row) { return kt * kWRows + row < a.Tkv ? Kb + (size_t)(kt * kWRows + row) * kD * esz : nullptr; });
+        if constexpr (TMA) {
+            // one thread, one copy per tile (the first barrier also counts the Q tile)
+            if (tid == 0 && kt < n_kt) {
+                const uint32_t fb = smem_u32(&full_bar[kt & 1]);
+                mbar_expect_tx(fb, kt == 0 ? 2 * kTileBytes : kTileBytes);
+                if (kt == 0) tma_load_5d(smem_u32(q_tile), &maps.q_tile, r0 / 8, bq, fb);
+                tma_load_5d(smem_u32(k_tiles + (kt & 1) * kTileBytes), &maps.k_tile, kt * (kWRows / 8), b * a.H + h, fb);
+            }
+        } else {
+            if (kt < n_kt)
+                stage_rows(k_tiles + (kt & 1) * kTileBytes, 16, tid, Kb,
+                           [&](int row) { return kt * kWRows + row < a.Tkv ? Kb + (size_t)(kt * kWRows + row) * kD * esz : nullptr; });
+            cp_async_commit();
+        }
     };
-    if (n_kt > 0) stage_k(0);
-    cp_async_commit();
+    auto issue = [&](int kt) {   // warp 0, converged
+        tc_fence_after();
+        if (elect_one()) {
+            bool ok = true;
+            if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s);
+            if (ok) {
+                issue_product(tmem + (kt & 1) * 128, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&bar));
+            } else {
+                abort_s = 1;
+                atomicExch(a.status, 1u);
+            }
+        }
+        __syncwarp();
+    };
+    stage_k(0);
+    stage_k(1);
+    if constexpr (!TMA) {
+        cp_async_wait<1>();
+        proxy_fence();
+    }
+    __syncthreads();
+    if (warp == 0 && n_kt > 0) issue(0);
 
-    const int r = r0 + tid;
+    const int row = (warp & 3) * 32 + lane;
+    const int r = r0 + row;
     const int vis = r + a.q_offset;          // last visible key of this row
     float m = kMasked, l = 0.f;
     bool dead = false;
     for (int kt = 0; kt < n_kt; ++kt) {
-        if (kt + 1 < n_kt) stage_k(kt + 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        proxy_fence();
-        __syncthreads();
-        dead = dead || abort_s != 0;
-        if (warp == 0 && !dead) {
-            tc_fence_after();
-            if (elect_one()) issue_product(tmem, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&bar));
-            __syncwarp();
-        }
-        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(kt & 1))) {
+        // product kt is complete: its K buffer may take tile kt + 2
+        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(kt & 1), &abort_s)) {
             dead = true;
             abort_s = 1;
             atomicExch(a.status, 1u);
         }
+        stage_k(kt + 2);
+        if constexpr (!TMA) {
+            cp_async_wait<1>();                 // tile kt + 1 has landed
+            proxy_fence();
+        }
+        tc_fence_before();
+        __syncthreads();                        // ... for every thread, and everyone is done with accumulator (kt + 1) & 1
+        dead = dead || abort_s != 0;
+        if (warp == 0 && !dead && kt + 1 < n_kt) issue(kt + 1);
         dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
         tc_fence_after();
         if (!dead) {
-            const int j0 = kt * kWRows;
-            // two sweeps over the row: maximum first, then one exponential per visible logit
-            float tile_max = kMasked;
+            const int j0 = kt * kWRows + half * 64;
+            const uint32_t acc_addr = tmem_lane + (kt & 1) * 128;
+            // a tile every row of this CTA sees completely needs no mask (all but the last tiles of a row block)
+            const bool open = kt * kWRows + kWRows - 1 <= r0 + a.q_offset && (kt + 1) * kWRows <= a.Tkv;
 #pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
+            for (int cb = 0; cb < 2; ++cb) {
                 uint32_t v[32];
-                tmem_ld32(tmem_lane + cb * 32, v);
+                tmem_ld32(acc_addr + cb * 32, v);
                 tmem_ld_wait();
+                float cmax = kMasked;
+                if (open) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int j = j0 + cb * 32 + i;
-                    if (j <= vis && j < a.Tkv) tile_max = fmaxf(tile_max, __uint_as_float(v[i]) * a.c);
-                }
-            }
-            // (every thread of a warp takes both sweeps: the tensor-memory loads are warp-wide; a row that sees no key
-            //  of this tile adds nothing and keeps its maximum)
-            const float m_new = fmaxf(m, tile_max);
-            float acc = 0.f;
-#pragma unroll 1
-            for (int cb = 0; cb < 4; ++cb) {
-                uint32_t v[32];
-                tmem_ld32(tmem_lane + cb * 32, v);
-                tmem_ld_wait();
+                    for (int i = 0; i < 32; ++i) cmax = fmaxf(cmax, __uint_as_float(v[i]));
+                    cmax *= a.c;
+                } else {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int j = j0 + cb * 32 + i;
-                    if (j <= vis && j < a.Tkv) acc += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
+                    for (int i = 0; i < 32; ++i) {
+                        const int j = j0 + cb * 32 + i;
+                        if (j <= vis && j < a.Tkv) cmax = fmaxf(cmax, __uint_as_float(v[i]) * a.c);
+                    }
                 }
+                const float m_new = fmaxf(m, cmax);
+                float acc0 = 0.f, acc1 = 0.f;
+                if (open) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
+                        acc1 += ex2f(fmaf(__uint_as_float(v[i + 1]), a.c, -m_new));
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int j = j0 + cb * 32 + i;
+                        if (j <= vis && j < a.Tkv) acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
+                    }
+                }
+                l = l * ex2f(m - m_new) + (acc0 + acc1);     // both at the masked value: factor 1, nothing added
+                m = m_new;
             }
-            l = l * ex2f(m - m_new) + acc;
-            m = m_new;
         }
-        tc_fence_before();
-        __syncthreads();   // the accumulator and this K buffer are free again
     }
-    cp_async_wait<0>();
-    if (r < a.Tq) a.lse2[(size_t)bq * a.Tq + r] = l > 0.f ? m + log2f(l) : -kMasked;   // no visible key: every probability 0
-    tmem_free(tmem, 128, warp);
+    if constexpr (!TMA) cp_async_wait<0>();
+    if (half == 1) part_s[row] = make_float2(m, l);
+    __syncthreads();
+    if (half == 0 && r < a.Tq) {
+        const float2 o = part_s[row];
+        const float mm = fmaxf(m, o.x);
+        const float ll = l * ex2f(m - mm) + o.y * ex2f(o.x - mm);
+        a.lse2[(size_t)bq * a.Tq + r] = ll > 0.f ? mm + log2f(ll) : -kMasked;   // no visible key: every probability 0
+    }
+    tmem_free(tmem, 256, warp);
 }
 
 // ---- pass 2: sum / max / sum of squares per key of the head-averaged probabilities -------------------------------
-// grid: (ceil(Tkv / 128), B * H); shared memory: K tile + two query blocks of RB * G rows + their log-sum-exps
-template <int RB>
-__global__ void __launch_bounds__(kWThreads) win_cols_kernel(const WinArgs a) {
+// grid: (ceil(Tkv / 128), B * H); shared memory: K tile + two query blocks of RB * G rows + four rows of their
+// log-sum-exps; tensor memory: two accumulators of N = RB * G columns.  Warps 0-3 take the first RB / 2 queries of a
+// block, warps 4-7 the others (every head of them); the two partial statistics of a key meet once, at the end.
+// Same pipeline as pass 1, over query blocks.
+template <int RB, bool TMA>
+__global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of query block `it` land on full_bar[it & 1]
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
+    __shared__ float part_s[3][kWRows];
+    constexpr int HB = RB / 2;
     const int G = a.G, N = RB * G;
     const int blk_bytes = N * kD * 2;
+    const int acc_stride = N <= 128 ? 128 : 256, tmem_cols = 2 * acc_stride;
     unsigned char *k_tile = smem, *q_blks = smem + kTileBytes;
-    float *lse_s = reinterpret_cast<float *>(smem + kTileBytes + 2 * blk_bytes);   // [2][N]
-    const int tid = threadIdx.x, warp = tid >> 5;
+    float *lse_s = reinterpret_cast<float *>(smem + kTileBytes + 2 * blk_bytes);   // [4][N]: block it + 2 is written while slower warps may still read block it - 1
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = warp >> 2;
     const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
     const int Hq = a.H * G;
     const int j0 = blockIdx.x * kWRows;
@@ -270,98 +369,182 @@ __global__ void __launch_bounds__(kWThreads) win_cols_kernel(const WinArgs a) {
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)(b * Hq + h * G) * a.Tq) * kD * esz;
     const float *lse_b = a.lse2 + (size_t)(b * Hq + h * G) * a.Tq;
     if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&bar)) : "memory");
+        mbar_init(&bar, 1);
+        mbar_init(&full_bar[0], 1);
+        mbar_init(&full_bar[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_s = 0;
     }
-    const uint32_t tmem = tmem_alloc(&tmem_slot, 256, warp);
-    const uint32_t tmem_lane = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t tmem = tmem_alloc(&tmem_slot, tmem_cols, warp);
+    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + half * HB;
 
-    stage_rows(k_tile, 16, tid, Kb, [&](int row) { return j0 + row < a.Tkv ? Kb + (size_t)(j0 + row) * kD * esz : nullptr; });
+    if constexpr (!TMA)
+        stage_rows(k_tile, 16, tid, Kb, [&](int row) { return j0 + row < a.Tkv ? Kb + (size_t)(j0 + row) * kD * esz : nullptr; });
     // query blocks that can see a key of this tile: r + q_offset >= j0
     const int n_rb = (a.Tq + RB - 1) / RB;
     const int rb_first = max(0, j0 - a.q_offset) / RB;
-    auto stage_q = [&](int rb) {
-        const int buf = (rb - rb_first) & 1;
-        // row n = g * RB + rr of the block is query rb * RB + rr of head g
-        stage_rows(q_blks + buf * blk_bytes, N / 8, tid, Qb, [&](int row) {
-            const int g = row / RB, rr = rb * RB + row % RB;
-            return rr < a.Tq ? Qb + ((size_t)g * a.Tq + rr) * kD * esz : nullptr;
-        });
-        for (int n = tid; n < N; n += kWThreads) {
-            const int g = n / RB, rr = rb * RB + n % RB;
-            lse_s[buf * N + n] = rr < a.Tq ? lse_b[(size_t)g * a.Tq + rr] : -kMasked;
+    const int n_it = n_rb - rb_first;
+    auto stage_q = [&](int it) {
+        if (it < n_it) {
+            const int rb = rb_first + it;
+            // row n = g * RB + rr of the block is query rb * RB + rr of head g
+            if constexpr (TMA) {
+                if (tid == 0) {   // one copy: RB rows of each of the G heads (the first barrier also counts the K tile)
+                    const uint32_t fb = smem_u32(&full_bar[it & 1]);
+                    mbar_expect_tx(fb, (uint32_t)blk_bytes + (it == 0 ? (uint32_t)kTileBytes : 0u));
+                    if (it == 0) tma_load_5d(smem_u32(k_tile), &maps.k_tile, j0 / 8, bh, fb);
+                    tma_load_5d(smem_u32(q_blks + (it & 1) * blk_bytes), &maps.q_blk, rb * (RB / 8), b * Hq + h * G, fb);
+                }
+            } else {
+                stage_rows(q_blks + (it & 1) * blk_bytes, N / 8, tid, Qb, [&](int row) {
+                    const int g = row / RB, rr = rb * RB + row % RB;
+                    return rr < a.Tq ? Qb + ((size_t)g * a.Tq + rr) * kD * esz : nullptr;
+                });
+            }
+            float *ls = lse_s + (it & 3) * N;
+            for (int n = tid; n < N; n += kWThreads) {
+                const int g = n / RB, rr = rb * RB + n % RB;
+                ls[n] = rr < a.Tq ? lse_b[(size_t)g * a.Tq + rr] : -kMasked;   // past Tq: probability 0
+            }
         }
+        if constexpr (!TMA) cp_async_commit();
     };
-    if (rb_first < n_rb) stage_q(rb_first);
-    cp_async_commit();
+    auto issue = [&](int it) {   // warp 0, converged
+        tc_fence_after();
+        if (elect_one()) {
+            bool ok = true;
+            if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s);
+            if (ok) {
+                issue_product(tmem + (it & 1) * acc_stride, k_tile, q_blks + (it & 1) * blk_bytes, N, a.bf16, smem_u32(&bar));
+            } else {
+                abort_s = 1;
+                atomicExch(a.status, 1u);
+            }
+        }
+        __syncwarp();
+    };
+    stage_q(0);
+    stage_q(1);
+    if constexpr (!TMA) {
+        cp_async_wait<1>();
+        proxy_fence();
+    }
+    __syncthreads();
+    if (warp == 0 && n_it > 0) issue(0);
 
-    const int j = j0 + tid;
+    const int row = (warp & 3) * 32 + lane;
+    const int j = j0 + row;
     const float inv_g = 1.0f / (float)G;
     float s_sum = 0.f, s_max = 0.f, s_sq = 0.f;
     bool dead = false;
-    for (int rb = rb_first; rb < n_rb; ++rb) {
-        const int it = rb - rb_first, buf = it & 1;
-        if (rb + 1 < n_rb) stage_q(rb + 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        proxy_fence();
-        __syncthreads();
-        dead = dead || abort_s != 0;
-        if (warp == 0 && !dead) {
-            tc_fence_after();
-            if (elect_one()) issue_product(tmem, k_tile, q_blks + buf * blk_bytes, N, a.bf16, smem_u32(&bar));
-            __syncwarp();
-        }
-        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(it & 1))) {
+    for (int it = 0; it < n_it; ++it) {
+        const int rb = rb_first + it;
+        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(it & 1), &abort_s)) {
             dead = true;
             abort_s = 1;
             atomicExch(a.status, 1u);
         }
+        stage_q(it + 2);                        // product `it` is complete: its query buffer is free
+        if constexpr (!TMA) {
+            cp_async_wait<1>();
+            proxy_fence();
+        }
+        tc_fence_before();
+        __syncthreads();
+        dead = dead || abort_s != 0;
+        if (warp == 0 && !dead && it + 1 < n_it) issue(it + 1);
         dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
         tc_fence_after();
         if (!dead) {
-            float mean[RB];
+            float mean[HB];
 #pragma unroll
-            for (int i = 0; i < RB; ++i) mean[i] = 0.f;
-            const float *ls = lse_s + buf * N;
-            const int r_base = rb * RB;
+            for (int i = 0; i < HB; ++i) mean[i] = 0.f;
+            const float *ls = lse_s + (it & 3) * N + half * HB;
+            const uint32_t acc_addr = tmem_lane + (it & 1) * acc_stride;
+            const int r_base = rb * RB + half * HB;
+            // a block whose first query already sees the last key of this tile needs no mask
+            const bool open = j0 + kWRows - 1 <= rb * RB + a.q_offset;
             for (int g = 0; g < G; ++g) {
-                uint32_t v[RB];
-                if constexpr (RB == 32) tmem_ld32(tmem_lane + g * RB, reinterpret_cast<uint32_t(&)[32]>(v));
-                else tmem_ld16(tmem_lane + g * RB, reinterpret_cast<uint32_t(&)[16]>(v));
-                tmem_ld_wait();
+                uint32_t v[HB];
+                if constexpr (HB == 16) tmem_ld16(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[16]>(v));
+                else tmem_ld8(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[8]>(v));
+                float lg[HB];
 #pragma unroll
-                for (int i = 0; i < RB; ++i) {
-                    // key j is visible to query r when j <= r + q_offset; queries past Tq carry a huge log-sum-exp
-                    const float p = (j <= r_base + i + a.q_offset) ? ex2f(fmaf(__uint_as_float(v[i]), a.c, -ls[g * RB + i])) : 0.f;
-                    mean[i] += p;
+                for (int i4 = 0; i4 < HB / 4; ++i4) {
+                    const float4 f = *reinterpret_cast<const float4 *>(ls + g * RB + 4 * i4);
+                    lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                }
+                tmem_ld_wait();
+                if (open) {
+#pragma unroll
+                    for (int i = 0; i < HB; ++i) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < HB; ++i)   // key j is visible to query r when j <= r + q_offset
+                        if (j <= r_base + i + a.q_offset) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
                 }
             }
 #pragma unroll
-            for (int i = 0; i < RB; ++i) {
+            for (int i = 0; i < HB; ++i) {
                 const float mg = mean[i] * inv_g;
                 s_sum += mg;
                 s_max = fmaxf(s_max, mg);
                 s_sq = fmaf(mg, mg, s_sq);
             }
         }
-        tc_fence_before();
-        __syncthreads();
     }
-    cp_async_wait<0>();
-    if (j < a.Tkv) {
+    if constexpr (!TMA) cp_async_wait<0>();
+    if (half == 1) { part_s[0][row] = s_sum; part_s[1][row] = s_max; part_s[2][row] = s_sq; }
+    __syncthreads();
+    if (half == 0 && j < a.Tkv) {
         const size_t o = (size_t)bh * a.Tkv + j;
-        a.sum_attn[o] = s_sum;
-        a.max_attn[o] = s_max;
-        a.sum_sq[o] = s_sq;
+        a.sum_attn[o] = s_sum + part_s[0][row];
+        a.max_attn[o] = fmaxf(s_max, part_s[1][row]);
+        a.sum_sq[o] = s_sq + part_s[2][row];
     }
-    tmem_free(tmem, 256, warp);
+    tmem_free(tmem, tmem_cols, warp);
 }
 
 int pick_rb(int G) { return 32 * G <= 256 ? 32 : 16; }
 
 size_t lse_bytes(int B, int H, int G, int Tq) { return (((size_t)B * H * G * Tq * sizeof(float)) + 255) & ~(size_t)255; }
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link the driver directly)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        cudaGetLastError();
+    }
+    return fn;
+}
+
+// Row-major [heads][T][128] 16-bit tensor seen as (8 elements, 8 rows, 16 chunks, T / 8 row groups, heads): a box
+// (8, 8, 16, groups, box_heads) lands in shared memory as groups x box_heads canonical row groups of 2048 bytes.
+bool make_map(CUtensorMap *map, const void *base, int bf16, long long heads, int T, int box_groups, int box_heads) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[5] = {8, 8, 16, (cuuint64_t)(T / 8), (cuuint64_t)heads};
+    const cuuint64_t strides[4] = {256, 16, 2048, (cuuint64_t)T * 256};
+    const cuuint32_t box[5] = {8, 8, 16, (cuuint32_t)box_groups, (cuuint32_t)box_heads};
+    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(base), dims, strides,
+              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_last_path = -1;   // 1: tiles arrived by tensor copies, 0: copied by the threads, -1: no call yet
+
+template <class Kern>
+cudaError_t allow_smem(Kern kern, int bytes) { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes); }
 
 }  // namespace
 
@@ -377,6 +560,8 @@ size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq) {
 }
 
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq) { return lse_bytes(B, H, G, Tq); }
+
+int odmkv_window_stats_last_path(void) { return g_last_path; }
 
 int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int H, int G, int Tq, int Tkv, int q_offset, float scale,
                             float *sum_attn, float *max_attn, float *sum_sq_attn, void *workspace, size_t workspace_bytes,
@@ -399,21 +584,38 @@ int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int 
     if (e != cudaSuccess) return (int)e;
     const int smem1 = 3 * kTileBytes;
     const int N = a.RB * G;
-    const int smem2 = kTileBytes + 2 * N * kD * 2 + 2 * N * (int)sizeof(float);
-    e = cudaFuncSetAttribute(win_lse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem1);
-    if (e != cudaSuccess) return (int)e;
+    const int smem2 = kTileBytes + 2 * N * kD * 2 + 4 * N * (int)sizeof(float);
+    // tensor copies need whole groups of eight rows (and 128-byte aligned tensors); otherwise the threads copy
+    WinMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    const bool tma = Tq % 8 == 0 && Tkv % 8 == 0 && ((((uintptr_t)Q | (uintptr_t)K) & 127) == 0) &&
+                     make_map(&maps.q_tile, Q, a.bf16, (long long)B * H * G, Tq, 16, 1) &&
+                     make_map(&maps.q_blk, Q, a.bf16, (long long)B * H * G, Tq, a.RB / 8, G) &&
+                     make_map(&maps.k_tile, K, a.bf16, (long long)B * H, Tkv, 16, 1);
+    g_last_path = tma ? 1 : 0;
+    const dim3 grid1((Tq + kWRows - 1) / kWRows, B * H * G), grid2((Tkv + kWRows - 1) / kWRows, B * H);
     timing_begin("window_lse", st);
-    win_lse_kernel<<<dim3((Tq + kWRows - 1) / kWRows, B * H * G), kWThreads, smem1, st>>>(a);
+    if (tma) {
+        if ((e = allow_smem(win_lse_kernel<true>, smem1)) != cudaSuccess) return (int)e;
+        win_lse_kernel<true><<<grid1, kWThreads, smem1, st>>>(a, maps);
+    } else {
+        if ((e = allow_smem(win_lse_kernel<false>, smem1)) != cudaSuccess) return (int)e;
+        win_lse_kernel<false><<<grid1, kWThreads, smem1, st>>>(a, maps);
+    }
     timing_end(st);
     timing_begin("window_cols", st);
-    if (a.RB == 32) {
-        e = cudaFuncSetAttribute(win_cols_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
-        if (e != cudaSuccess) return (int)e;
-        win_cols_kernel<32><<<dim3((Tkv + kWRows - 1) / kWRows, B * H), kWThreads, smem2, st>>>(a);
+    if (a.RB == 32 && tma) {
+        if ((e = allow_smem(win_cols_kernel<32, true>, smem2)) != cudaSuccess) return (int)e;
+        win_cols_kernel<32, true><<<grid2, kWThreads, smem2, st>>>(a, maps);
+    } else if (a.RB == 32) {
+        if ((e = allow_smem(win_cols_kernel<32, false>, smem2)) != cudaSuccess) return (int)e;
+        win_cols_kernel<32, false><<<grid2, kWThreads, smem2, st>>>(a, maps);
+    } else if (tma) {
+        if ((e = allow_smem(win_cols_kernel<16, true>, smem2)) != cudaSuccess) return (int)e;
+        win_cols_kernel<16, true><<<grid2, kWThreads, smem2, st>>>(a, maps);
     } else {
-        e = cudaFuncSetAttribute(win_cols_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
-        if (e != cudaSuccess) return (int)e;
-        win_cols_kernel<16><<<dim3((Tkv + kWRows - 1) / kWRows, B * H), kWThreads, smem2, st>>>(a);
+        if ((e = allow_smem(win_cols_kernel<16, false>, smem2)) != cudaSuccess) return (int)e;
+        win_cols_kernel<16, false><<<grid2, kWThreads, smem2, st>>>(a, maps);
     }
     timing_end(st);
     return launch_status();

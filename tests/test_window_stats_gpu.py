@@ -40,6 +40,9 @@ def test_reference_fixture(pkg, golden, cuda):
     (1, 1, 12, 40, 200, 160, torch.bfloat16),     # G > 8: blocks of 16 queries
     (1, 1, 1, 257, 257, 0, torch.float16),        # G = 1
     (1, 2, 4, 64, 1500, 1500 - 64, torch.float16),
+    (2, 2, 4, 128, 2048, 2048 - 128, torch.bfloat16),   # the press's window shape, tensor copies
+    (1, 1, 8, 256, 1024, 768, torch.float16),           # N = 256 columns, tensor copies
+    (1, 2, 4, 384, 384, 0, torch.float16),              # full causal, three tiles per side
 ])
 def test_against_oracle(pkg, orc, cuda, B, H, G, Tq, Tkv, off, dtype):
     g = torch.Generator().manual_seed(Tq * 7 + Tkv)
@@ -48,6 +51,8 @@ def test_against_oracle(pkg, orc, cuda, B, H, G, Tq, Tkv, off, dtype):
     K[:, :, :4] *= 2.5
     K = K.to(dtype)
     s, m, q = pkg.ops.window_attn_stats(Q.to(cuda), K.to(cuda), q_offset=off)
+    # whole groups of eight rows arrive by tensor copies, ragged lengths by the threads' own copies
+    assert pkg._lib.lib().odmkv_window_stats_last_path() == (1 if Tq % 8 == 0 and Tkv % 8 == 0 else 0)
     for b in range(B):
         ws, wm, wq = orc.chunked_attention_qk(Q[b].float().numpy(), K[b].float().numpy(), math.sqrt(128.0), q_offset=off)
         close(s[b], ws, "sum")
