@@ -283,9 +283,11 @@ int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chu
  * operand tiles staged by TMA tensor copies where the shapes allow. */
 size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq);
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq);
-/* how the last call on this process staged its operand tiles: 1 = one tensor copy (TMA) per tile -- taken when Tq and
- * Tkv are multiples of 8 and Q, K are 128-byte aligned --, 0 = 16-byte copies by the threads, -1 = no call yet */
+/* how the last call on this process staged its operand tiles: 1 = tensor copies (TMA), 0 = 16-byte copies by the
+ * threads (taken when the driver's tensor-map encoder is unavailable, or when forced), -1 = no call yet */
 int odmkv_window_stats_last_path(void);
+/* on != 0: stage by thread copies even where tensor copies are possible (for testing that path) */
+void odmkv_window_stats_force_thread_copies(int on);
 int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int H, int G, int Tq, int Tkv, int q_offset,
                             float scale, float *sum_attn, float *max_attn, float *sum_sq_attn, void *workspace,
                             size_t workspace_bytes, void *stream);

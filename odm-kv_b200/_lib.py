@@ -107,6 +107,7 @@ _PROTOTYPES = {
     "odmkv_window_stats_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "odmkv_window_stats_status_offset": (c_size_t, [c_int, c_int, c_int, c_int]),
     "odmkv_window_stats_last_path": (c_int, []),
+    "odmkv_window_stats_force_thread_copies": (None, [c_int]),
     "odmkv_window_attn_stats": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                         c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "odmkv_timing_enable": (None, [c_int]),

@@ -14,11 +14,12 @@
 //          dimension; the thread that owns a key reads its row, turns it into probabilities with the stored
 //          log-sum-exps, averages the G heads of each query in registers and accumulates the three statistics --
 //          no exchange between threads, no atomics: a CTA owns its keys.
-// Operand tiles sit in shared memory in the canonical K-major layout without swizzle: 8-row x 16-byte core matrices,
-// 128 bytes between K-neighbours, 2048 bytes between row groups.  When the sequence lengths are multiples of eight a
-// tile is ONE tensor copy (TMA, cp.async.bulk.tensor): the row-major global tensor is described as (8 elements, 8
-// rows, 16 chunks, row groups, heads), whose box order is exactly that layout; rows past the end read as zeros.
-// Otherwise the threads copy 16-byte pieces themselves (cp.async).
+// Operand tiles sit in shared memory in the K-major layout with the 128-byte swizzle: a tile of R rows is two blocks
+// of R x 128 bytes (coordinates 0-63 and 64-127), row r of a block at r * 128, its 16-byte chunk c at position
+// c ^ (r % 8).  A tile arrives as two tensor copies (TMA, cp.async.bulk.tensor, boxes of 64 coordinates x R rows --
+// for pass 2 x G heads -- of the row-major global tensor; rows past the end read as zeros); a first version with the
+// unswizzled layout needed 16-byte rows in its boxes and spent 2 300 clocks per tile in the copy engine.  Without the
+// driver's tensor-map encoder the threads copy 16-byte pieces themselves (cp.async) into the same layout.
 // The exponentials bound both passes (one per logit and pass on the special-function unit), not the products.
 // Every wait on an mbarrier is bounded; an expired wait sets the status word and the CTA runs out without waiting
 // again, releasing its tensor memory.
@@ -33,7 +34,7 @@ namespace {
 
 constexpr int kWThreads = 256;                    // two threads per tensor-memory lane: each takes half of the columns
 constexpr int kWRows = 128;                       // rows of the A tile = tensor-memory lanes
-constexpr uint32_t kLbo = 128, kSbo = 2048;       // bytes between K-adjacent core matrices / between 8-row groups
+constexpr uint32_t kSbo = 1024;                   // bytes between 8-row groups of a swizzled block (8 rows x 128 bytes)
 constexpr int kTileBytes = kWRows * kD * 2;       // 32 KiB per 128 rows
 constexpr unsigned kPolls = 1u << 12;
 constexpr unsigned kSuspendNs = 1000000u;
@@ -69,9 +70,11 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool v
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
+// shared-memory matrix descriptor, K-major, 128-byte swizzle: start address, (unused) leading offset, 1024 bytes
+// between 8-row groups, descriptor version 1, layout type 2
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((kLbo >> 4) & 0x3FFF) << 16) | ((uint64_t)((kSbo >> 4) & 0x3FFF) << 32) |
-           (1ull << 46);
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)((kSbo >> 4) & 0x3FFF) << 32) | (1ull << 46) |
+           (2ull << 61);
 }
 // instruction descriptor: fp32 accumulator, A and B fp16 or bf16, both K-major, M = 128
 __device__ __forceinline__ uint32_t idesc_f16(int N, int bf16) {
@@ -104,9 +107,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity, const v
     return false;
 }
 // one tensor copy of a box into shared memory, completion counted in bytes on an mbarrier
-__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *map, int c3, int c4, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n"
-                 ::"r"(dst), "l"(map), "r"(0), "r"(0), "r"(0), "r"(c3), "r"(c4), "r"(bar) : "memory");
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, int x, int row, int head, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(row), "r"(head), "r"(bar) : "memory");
+}
+// both 64-coordinate blocks of a tile of `rows` rows (x = 0 and 64: 128-byte steps, as the copy engine requires)
+__device__ __forceinline__ void tma_load_tile(unsigned char *tile, int rows, const CUtensorMap *map, int row, int head, uint32_t bar) {
+    tma_load_3d(smem_u32(tile), map, 0, row, head, bar);
+    tma_load_3d(smem_u32(tile) + rows * 128, map, 64, row, head, bar);
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
@@ -143,31 +151,34 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&v)[8]) {
                  : "memory");
 }
 
-// Copy `groups` groups of eight rows into the canonical layout at `tile`: the piece (row 8 gi + r, 16-byte chunk c)
-// lands at gi * 2048 + c * 128 + r * 16.  Two neighbouring lanes take the two halves of one 32-byte sector of a row
-// (a 16-byte asynchronous copy fetches a whole sector; with one lane per row every sector was fetched twice), eight
-// lanes cover four rows, a warp eight rows x four chunks; the price is a two-way bank conflict on the shared-memory
-// side, which has room.  Warps 0-3 / 4-7 take alternate groups.
+// Thread copies of `groups` groups of eight rows into the swizzled layout of a tile of 8 * groups rows: the piece
+// (row r, 16-byte chunk c) lands in block c / 8 at r * 128 + ((c % 8) ^ (r % 8)) * 16.  Two neighbouring lanes take
+// the two halves of one 32-byte sector of a row, a warp eight rows x four chunks; warps 0-3 / 4-7 alternate groups.
 // row_ptr(row) returns the row's address in global memory, or nullptr for a row that does not exist: such a row is
 // zero-filled (a copy of zero source bytes, which still names a valid global address, `any_row`).
 template <class RowPtr>
 __device__ __forceinline__ void stage_rows(unsigned char *tile, int groups, int tid, const unsigned char *any_row, RowPtr row_ptr) {
     const int lane = tid & 31, warp = tid >> 5;
     const int r8 = (lane >> 1) & 7, c0 = (warp & 3) * 4 + (lane >> 4) * 2 + (lane & 1);
+    const uint32_t blk = (uint32_t)(c0 >> 3) * (uint32_t)groups * 1024u + (uint32_t)(((c0 & 7) ^ r8) * 16);
     for (int gi = warp >> 2; gi < groups; gi += kWThreads / 128) {
         const unsigned char *src = reinterpret_cast<const unsigned char *>(row_ptr(gi * 8 + r8));
-        const uint32_t dst = smem_u32(tile) + gi * kSbo + c0 * kLbo + r8 * 16;
+        const uint32_t dst = smem_u32(tile) + blk + (gi * 8 + r8) * 128;
         cp_async16(dst, src ? src + c0 * 16 : any_row, src != nullptr);
     }
 }
 
-// one 128 x N x 128 product into tensor memory: eight K = 16 steps, 256 bytes apart in both tiles
+// one 128 x N x 128 product into tensor memory: eight K = 16 steps, 32 bytes apart inside a 64-coordinate block
+// (the swizzle is applied to the address bits by the hardware), the second block after the first
 __device__ __forceinline__ void issue_product(uint32_t tmem, const unsigned char *a_tile, const unsigned char *b_tile, int N, int bf16,
                                               uint32_t bar) {
     const uint32_t idesc = idesc_f16(N, bf16);
     const uint32_t a0 = smem_u32(a_tile), b0 = smem_u32(b_tile);
 #pragma unroll
-    for (int ks = 0; ks < kD / 16; ++ks) umma_f16(tmem, smem_desc(a0 + ks * 256), smem_desc(b0 + ks * 256), idesc, ks ? 1u : 0u);
+    for (int ks = 0; ks < kD / 16; ++ks) {
+        const uint32_t ao = (ks >> 2) * (kWRows * 128) + (ks & 3) * 32, bo = (ks >> 2) * (N * 128) + (ks & 3) * 32;
+        umma_f16(tmem, smem_desc(a0 + ao), smem_desc(b0 + bo), idesc, ks ? 1u : 0u);
+    }
     umma_commit(bar);
 }
 
@@ -196,7 +207,7 @@ __device__ __forceinline__ void tmem_free(uint32_t base, int cols, int warp) {
 template <bool TMA>
 __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t mma_bar[2];    // product kt arrives on mma_bar[kt & 1]
     __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of K tile kt land on full_bar[kt & 1]
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
@@ -210,7 +221,8 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)bq * a.Tq) * kD * esz;
     const unsigned char *Kb = reinterpret_cast<const unsigned char *>(a.K) + ((size_t)(b * a.H + h) * a.Tkv) * kD * esz;
     if (tid == 0) {
-        mbar_init(&bar, 1);
+        mbar_init(&mma_bar[0], 1);
+        mbar_init(&mma_bar[1], 1);
         mbar_init(&full_bar[0], 1);
         mbar_init(&full_bar[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -227,12 +239,12 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
         stage_rows(q_tile, 16, tid, Qb, [&](int row) { return r0 + row < a.Tq ? Qb + (size_t)(r0 + row) * kD * esz : nullptr; });
     auto stage_k = [&](int kt) {
         if constexpr (TMA) {
-            // one thread, one copy per tile (the first barrier also counts the Q tile)
+            // one thread, two copies per tile (the first barrier also counts the Q tile)
             if (tid == 0 && kt < n_kt) {
                 const uint32_t fb = smem_u32(&full_bar[kt & 1]);
                 mbar_expect_tx(fb, kt == 0 ? 2 * kTileBytes : kTileBytes);
-                if (kt == 0) tma_load_5d(smem_u32(q_tile), &maps.q_tile, r0 / 8, bq, fb);
-                tma_load_5d(smem_u32(k_tiles + (kt & 1) * kTileBytes), &maps.k_tile, kt * (kWRows / 8), b * a.H + h, fb);
+                if (kt == 0) tma_load_tile(q_tile, kWRows, &maps.q_tile, r0, bq, fb);
+                tma_load_tile(k_tiles + (kt & 1) * kTileBytes, kWRows, &maps.k_tile, kt * kWRows, b * a.H + h, fb);
             }
         } else {
             if (kt < n_kt)
@@ -247,7 +259,7 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
             bool ok = true;
             if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s);
             if (ok) {
-                issue_product(tmem + (kt & 1) * 128, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&bar));
+                issue_product(tmem + (kt & 1) * 128, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&mma_bar[kt & 1]));
             } else {
                 abort_s = 1;
                 atomicExch(a.status, 1u);
@@ -270,21 +282,23 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
     float m = kMasked, l = 0.f;
     bool dead = false;
     for (int kt = 0; kt < n_kt; ++kt) {
-        // product kt is complete: its K buffer may take tile kt + 2
-        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(kt & 1), &abort_s)) {
+        // Two products stay in flight: tile kt + 1 is issued before tile kt is awaited.  Its accumulator was read
+        // during the previous iteration, hence the barrier first; its K tile must have landed (tensor copies: the
+        // issuing lane waits for their bytes; thread copies: every thread waits for its own pieces here).
+        if constexpr (!TMA) {
+            cp_async_wait<0>();
+            proxy_fence();
+        }
+        tc_fence_before();
+        __syncthreads();
+        dead = dead || abort_s != 0;
+        if (warp == 0 && !dead && kt + 1 < n_kt) issue(kt + 1);
+        if (!dead && !mbar_wait(smem_u32(&mma_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s)) {
             dead = true;
             abort_s = 1;
             atomicExch(a.status, 1u);
         }
-        stage_k(kt + 2);
-        if constexpr (!TMA) {
-            cp_async_wait<1>();                 // tile kt + 1 has landed
-            proxy_fence();
-        }
-        tc_fence_before();
-        __syncthreads();                        // ... for every thread, and everyone is done with accumulator (kt + 1) & 1
-        dead = dead || abort_s != 0;
-        if (warp == 0 && !dead && kt + 1 < n_kt) issue(kt + 1);
+        stage_k(kt + 2);                        // product kt is complete: its K buffer takes tile kt + 2
         dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
         tc_fence_after();
         if (!dead) {
@@ -349,7 +363,7 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
 template <int RB, bool TMA>
 __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) uint64_t mma_bar[2];    // product `it` arrives on mma_bar[it & 1]
     __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of query block `it` land on full_bar[it & 1]
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
@@ -369,7 +383,8 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)(b * Hq + h * G) * a.Tq) * kD * esz;
     const float *lse_b = a.lse2 + (size_t)(b * Hq + h * G) * a.Tq;
     if (tid == 0) {
-        mbar_init(&bar, 1);
+        mbar_init(&mma_bar[0], 1);
+        mbar_init(&mma_bar[1], 1);
         mbar_init(&full_bar[0], 1);
         mbar_init(&full_bar[1], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -389,11 +404,11 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
             const int rb = rb_first + it;
             // row n = g * RB + rr of the block is query rb * RB + rr of head g
             if constexpr (TMA) {
-                if (tid == 0) {   // one copy: RB rows of each of the G heads (the first barrier also counts the K tile)
+                if (tid == 0) {   // two copies: RB rows of each of the G heads (the first barrier also counts the K tile)
                     const uint32_t fb = smem_u32(&full_bar[it & 1]);
                     mbar_expect_tx(fb, (uint32_t)blk_bytes + (it == 0 ? (uint32_t)kTileBytes : 0u));
-                    if (it == 0) tma_load_5d(smem_u32(k_tile), &maps.k_tile, j0 / 8, bh, fb);
-                    tma_load_5d(smem_u32(q_blks + (it & 1) * blk_bytes), &maps.q_blk, rb * (RB / 8), b * Hq + h * G, fb);
+                    if (it == 0) tma_load_tile(k_tile, kWRows, &maps.k_tile, j0, bh, fb);
+                    tma_load_tile(q_blks + (it & 1) * blk_bytes, N, &maps.q_blk, rb * RB, b * Hq + h * G, fb);
                 }
             } else {
                 stage_rows(q_blks + (it & 1) * blk_bytes, N / 8, tid, Qb, [&](int row) {
@@ -415,7 +430,7 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
             bool ok = true;
             if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s);
             if (ok) {
-                issue_product(tmem + (it & 1) * acc_stride, k_tile, q_blks + (it & 1) * blk_bytes, N, a.bf16, smem_u32(&bar));
+                issue_product(tmem + (it & 1) * acc_stride, k_tile, q_blks + (it & 1) * blk_bytes, N, a.bf16, smem_u32(&mma_bar[it & 1]));
             } else {
                 abort_s = 1;
                 atomicExch(a.status, 1u);
@@ -439,20 +454,21 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
     bool dead = false;
     for (int it = 0; it < n_it; ++it) {
         const int rb = rb_first + it;
-        if (!dead && !mbar_wait(smem_u32(&bar), (unsigned)(it & 1), &abort_s)) {
-            dead = true;
-            abort_s = 1;
-            atomicExch(a.status, 1u);
-        }
-        stage_q(it + 2);                        // product `it` is complete: its query buffer is free
+        // two products in flight, as in pass 1: block it + 1 is issued before block `it` is awaited
         if constexpr (!TMA) {
-            cp_async_wait<1>();
+            cp_async_wait<0>();
             proxy_fence();
         }
         tc_fence_before();
         __syncthreads();
         dead = dead || abort_s != 0;
         if (warp == 0 && !dead && it + 1 < n_it) issue(it + 1);
+        if (!dead && !mbar_wait(smem_u32(&mma_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s)) {
+            dead = true;
+            abort_s = 1;
+            atomicExch(a.status, 1u);
+        }
+        stage_q(it + 2);                        // product `it` is complete: its query buffer is free
         dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
         tc_fence_after();
         if (!dead) {
@@ -527,20 +543,21 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Row-major [heads][T][128] 16-bit tensor seen as (8 elements, 8 rows, 16 chunks, T / 8 row groups, heads): a box
-// (8, 8, 16, groups, box_heads) lands in shared memory as groups x box_heads canonical row groups of 2048 bytes.
-bool make_map(CUtensorMap *map, const void *base, int bf16, long long heads, int T, int box_groups, int box_heads) {
+// Row-major [heads][T][128] 16-bit tensor as (128 coordinates, T rows, heads); a box (64, box_rows, box_heads) lands
+// in shared memory as box_heads * box_rows rows of 128 bytes with the 128-byte swizzle.
+bool make_map(CUtensorMap *map, const void *base, int bf16, long long heads, int T, int box_rows, int box_heads) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
-    const cuuint64_t dims[5] = {8, 8, 16, (cuuint64_t)(T / 8), (cuuint64_t)heads};
-    const cuuint64_t strides[4] = {256, 16, 2048, (cuuint64_t)T * 256};
-    const cuuint32_t box[5] = {8, 8, 16, (cuuint32_t)box_groups, (cuuint32_t)box_heads};
-    const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void *>(base), dims, strides,
-              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+    const cuuint64_t dims[3] = {128, (cuuint64_t)T, (cuuint64_t)heads};
+    const cuuint64_t strides[2] = {256, (cuuint64_t)T * 256};
+    const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_heads};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void *>(base), dims, strides,
+              box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool g_force_thread_copies = false;
 int g_last_path = -1;   // 1: tiles arrived by tensor copies, 0: copied by the threads, -1: no call yet
 
 template <class Kern>
@@ -562,6 +579,8 @@ size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq) {
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq) { return lse_bytes(B, H, G, Tq); }
 
 int odmkv_window_stats_last_path(void) { return g_last_path; }
+
+void odmkv_window_stats_force_thread_copies(int on) { g_force_thread_copies = on != 0; }
 
 int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int H, int G, int Tq, int Tkv, int q_offset, float scale,
                             float *sum_attn, float *max_attn, float *sum_sq_attn, void *workspace, size_t workspace_bytes,
@@ -585,13 +604,12 @@ int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int 
     const int smem1 = 3 * kTileBytes;
     const int N = a.RB * G;
     const int smem2 = kTileBytes + 2 * N * kD * 2 + 4 * N * (int)sizeof(float);
-    // tensor copies need whole groups of eight rows (and 128-byte aligned tensors); otherwise the threads copy
+    // tensor copies whenever the driver's encoder is there (and not switched off for a test of the other path)
     WinMaps maps;
     memset(&maps, 0, sizeof(maps));
-    const bool tma = Tq % 8 == 0 && Tkv % 8 == 0 && ((((uintptr_t)Q | (uintptr_t)K) & 127) == 0) &&
-                     make_map(&maps.q_tile, Q, a.bf16, (long long)B * H * G, Tq, 16, 1) &&
-                     make_map(&maps.q_blk, Q, a.bf16, (long long)B * H * G, Tq, a.RB / 8, G) &&
-                     make_map(&maps.k_tile, K, a.bf16, (long long)B * H, Tkv, 16, 1);
+    const bool tma = !g_force_thread_copies && make_map(&maps.q_tile, Q, a.bf16, (long long)B * H * G, Tq, kWRows, 1) &&
+                     make_map(&maps.q_blk, Q, a.bf16, (long long)B * H * G, Tq, a.RB, G) &&
+                     make_map(&maps.k_tile, K, a.bf16, (long long)B * H, Tkv, kWRows, 1);
     g_last_path = tma ? 1 : 0;
     const dim3 grid1((Tq + kWRows - 1) / kWRows, B * H * G), grid2((Tkv + kWRows - 1) / kWRows, B * H);
     timing_begin("window_lse", st);

@@ -50,9 +50,16 @@ def test_against_oracle(pkg, orc, cuda, B, H, G, Tq, Tkv, off, dtype):
     K = torch.randn(B, H, Tkv, 128, generator=g)
     K[:, :, :4] *= 2.5
     K = K.to(dtype)
+    L = pkg._lib.lib()
     s, m, q = pkg.ops.window_attn_stats(Q.to(cuda), K.to(cuda), q_offset=off)
-    # whole groups of eight rows arrive by tensor copies, ragged lengths by the threads' own copies
-    assert pkg._lib.lib().odmkv_window_stats_last_path() == (1 if Tq % 8 == 0 and Tkv % 8 == 0 else 0)
+    assert L.odmkv_window_stats_last_path() == 1            # tiles arrived by tensor copies
+    L.odmkv_window_stats_force_thread_copies(1)             # the other staging path must give the same numbers
+    try:
+        s2, m2, q2 = pkg.ops.window_attn_stats(Q.to(cuda), K.to(cuda), q_offset=off)
+        assert L.odmkv_window_stats_last_path() == 0
+    finally:
+        L.odmkv_window_stats_force_thread_copies(0)
+    assert torch.equal(s, s2) and torch.equal(m, m2) and torch.equal(q, q2)
     for b in range(B):
         ws, wm, wq = orc.chunked_attention_qk(Q[b].float().numpy(), K[b].float().numpy(), math.sqrt(128.0), q_offset=off)
         close(s[b], ws, "sum")
