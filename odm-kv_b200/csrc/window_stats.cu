@@ -198,22 +198,32 @@ __device__ __forceinline__ void tmem_free(uint32_t base, int cols, int warp) {
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(base), "r"((uint32_t)cols) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+constexpr int kWorkWarps = kWThreads / 32;           // warps that turn accumulators into statistics
+constexpr int kTmaThreads = kWThreads + 32;          // plus one warp that drives the copies and the products
+
 // ---- pass 1: log2-sum-exp per (query head, query) -----------------------------------------------------------------
 // grid: (ceil(Tq / 128), B * Hq); shared memory: Q tile + two K tiles; tensor memory: two 128-column accumulators.
-// Eight warps: warp w reads tensor-memory lanes 32 (w % 4) .. +31 (a row each), warps 0-3 the first 64 columns of a
-// tile and warps 4-7 the last 64; the two partial (maximum, sum) pairs of a row meet once, at the end.
-// Pipeline: while the threads turn tile kt into exponentials, the tensor cores already form tile kt + 1 in the other
-// accumulator and the copies of tile kt + 2 are in flight; one block-wide barrier per tile.
+// Eight working warps: warp w reads tensor-memory lanes 32 (w % 4) .. +31 (a row each), warps 0-3 the first 64
+// columns of a tile and warps 4-7 the last 64; the two partial (maximum, sum) pairs of a row meet once, at the end.
+// With tensor copies (TMA = true) a ninth warp drives everything else: one of its lanes issues the copies two tiles
+// ahead and the products one tile ahead, and the working warps only wait for "product kt done" and report
+// "accumulator free" through mbarriers -- no block-wide barrier in the loop.  With thread copies (TMA = false) the
+// eight warps copy, meet at one block-wide barrier per tile, and warp 0 issues the products.
 template <bool TMA>
-__global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
+__global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_lse_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) uint64_t mma_bar[2];    // product kt arrives on mma_bar[kt & 1]
     __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of K tile kt land on full_bar[kt & 1]
+    __shared__ __align__(8) uint64_t free_bar[2];   // the working warps are done with accumulator kt & 1
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
     __shared__ float2 part_s[kWRows];
     unsigned char *q_tile = smem, *k_tiles = smem + kTileBytes;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = warp >> 2;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = (warp >> 2) & 1;
     const int Hq = a.H * a.G;
     const int bq = blockIdx.y, b = bq / Hq, hq = bq % Hq, h = hq / a.G;
     const int r0 = blockIdx.x * kWRows;
@@ -221,10 +231,11 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)bq * a.Tq) * kD * esz;
     const unsigned char *Kb = reinterpret_cast<const unsigned char *>(a.K) + ((size_t)(b * a.H + h) * a.Tkv) * kD * esz;
     if (tid == 0) {
-        mbar_init(&mma_bar[0], 1);
-        mbar_init(&mma_bar[1], 1);
-        mbar_init(&full_bar[0], 1);
-        mbar_init(&full_bar[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&mma_bar[i], 1);
+            mbar_init(&full_bar[i], 1);
+            mbar_init(&free_bar[i], kWorkWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_s = 0;
     }
@@ -235,118 +246,146 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
     const int r_last = min(r0 + kWRows, a.Tq) - 1;
     const int n_keys = max(0, min(a.Tkv, r_last + a.q_offset + 1));
     const int n_kt = (n_keys + kWRows - 1) / kWRows;
-    if constexpr (!TMA)
-        stage_rows(q_tile, 16, tid, Qb, [&](int row) { return r0 + row < a.Tq ? Qb + (size_t)(r0 + row) * kD * esz : nullptr; });
-    auto stage_k = [&](int kt) {
-        if constexpr (TMA) {
-            // one thread, two copies per tile (the first barrier also counts the Q tile)
-            if (tid == 0 && kt < n_kt) {
-                const uint32_t fb = smem_u32(&full_bar[kt & 1]);
-                mbar_expect_tx(fb, kt == 0 ? 2 * kTileBytes : kTileBytes);
-                if (kt == 0) tma_load_tile(q_tile, kWRows, &maps.q_tile, r0, bq, fb);
-                tma_load_tile(k_tiles + (kt & 1) * kTileBytes, kWRows, &maps.k_tile, kt * kWRows, b * a.H + h, fb);
-            }
-        } else {
-            if (kt < n_kt)
-                stage_rows(k_tiles + (kt & 1) * kTileBytes, 16, tid, Kb,
-                           [&](int row) { return kt * kWRows + row < a.Tkv ? Kb + (size_t)(kt * kWRows + row) * kD * esz : nullptr; });
-            cp_async_commit();
-        }
-    };
-    auto issue = [&](int kt) {   // warp 0, converged
-        tc_fence_after();
-        if (elect_one()) {
-            bool ok = true;
-            if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s);
-            if (ok) {
-                issue_product(tmem + (kt & 1) * 128, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&mma_bar[kt & 1]));
-            } else {
-                abort_s = 1;
-                atomicExch(a.status, 1u);
-            }
-        }
-        __syncwarp();
-    };
-    stage_k(0);
-    stage_k(1);
-    if constexpr (!TMA) {
-        cp_async_wait<1>();
-        proxy_fence();
-    }
-    __syncthreads();
-    if (warp == 0 && n_kt > 0) issue(0);
-
     const int row = (warp & 3) * 32 + lane;
     const int r = r0 + row;
     const int vis = r + a.q_offset;          // last visible key of this row
     float m = kMasked, l = 0.f;
-    bool dead = false;
-    for (int kt = 0; kt < n_kt; ++kt) {
-        // Two products stay in flight: tile kt + 1 is issued before tile kt is awaited.  Its accumulator was read
-        // during the previous iteration, hence the barrier first; its K tile must have landed (tensor copies: the
-        // issuing lane waits for their bytes; thread copies: every thread waits for its own pieces here).
-        if constexpr (!TMA) {
-            cp_async_wait<0>();
-            proxy_fence();
-        }
-        tc_fence_before();
-        __syncthreads();
-        dead = dead || abort_s != 0;
-        if (warp == 0 && !dead && kt + 1 < n_kt) issue(kt + 1);
-        if (!dead && !mbar_wait(smem_u32(&mma_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s)) {
-            dead = true;
-            abort_s = 1;
-            atomicExch(a.status, 1u);
-        }
-        stage_k(kt + 2);                        // product kt is complete: its K buffer takes tile kt + 2
-        dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
-        tc_fence_after();
-        if (!dead) {
-            const int j0 = kt * kWRows + half * 64;
-            const uint32_t acc_addr = tmem_lane + (kt & 1) * 128;
-            // a tile every row of this CTA sees completely needs no mask (all but the last tiles of a row block)
-            const bool open = kt * kWRows + kWRows - 1 <= r0 + a.q_offset && (kt + 1) * kWRows <= a.Tkv;
+
+    // one accumulator -> running (maximum, sum) of this thread's half row
+    auto epilogue = [&](int kt) {
+        const int j0 = kt * kWRows + half * 64;
+        const uint32_t acc_addr = tmem_lane + (kt & 1) * 128;
+        // a tile every row of this CTA sees completely needs no mask (all but the last tiles of a row block)
+        const bool open = kt * kWRows + kWRows - 1 <= r0 + a.q_offset && (kt + 1) * kWRows <= a.Tkv;
 #pragma unroll 1
-            for (int cb = 0; cb < 2; ++cb) {
-                uint32_t v[32];
-                tmem_ld32(acc_addr + cb * 32, v);
-                tmem_ld_wait();
-                float cmax = kMasked;
-                if (open) {
+        for (int cb = 0; cb < 2; ++cb) {
+            uint32_t v[32];
+            tmem_ld32(acc_addr + cb * 32, v);
+            tmem_ld_wait();
+            float cmax = kMasked;
+            if (open) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) cmax = fmaxf(cmax, __uint_as_float(v[i]));
-                    cmax *= a.c;
-                } else {
+                for (int i = 0; i < 32; ++i) cmax = fmaxf(cmax, __uint_as_float(v[i]));
+                cmax *= a.c;
+            } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int j = j0 + cb * 32 + i;
-                        if (j <= vis && j < a.Tkv) cmax = fmaxf(cmax, __uint_as_float(v[i]) * a.c);
+                for (int i = 0; i < 32; ++i) {
+                    const int j = j0 + cb * 32 + i;
+                    if (j <= vis && j < a.Tkv) cmax = fmaxf(cmax, __uint_as_float(v[i]) * a.c);
+                }
+            }
+            const float m_new = fmaxf(m, cmax);
+            float acc0 = 0.f, acc1 = 0.f;
+            if (open) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
+                    acc1 += ex2f(fmaf(__uint_as_float(v[i + 1]), a.c, -m_new));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int j = j0 + cb * 32 + i;
+                    if (j <= vis && j < a.Tkv) acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
+                }
+            }
+            l = l * ex2f(m - m_new) + (acc0 + acc1);     // both at the masked value: factor 1, nothing added
+            m = m_new;
+        }
+    };
+
+    if constexpr (TMA) {
+        if (warp == kWorkWarps) {
+            if (lane == 0) {
+                bool ok = true;
+                auto load_k = [&](int kt) {
+                    const uint32_t fb = smem_u32(&full_bar[kt & 1]);
+                    mbar_expect_tx(fb, kt == 0 ? 2 * kTileBytes : kTileBytes);
+                    if (kt == 0) tma_load_tile(q_tile, kWRows, &maps.q_tile, r0, bq, fb);
+                    tma_load_tile(k_tiles + (kt & 1) * kTileBytes, kWRows, &maps.k_tile, kt * kWRows, b * a.H + h, fb);
+                };
+                if (n_kt > 0) load_k(0);
+                if (n_kt > 1) load_k(1);
+                for (int kt = 0; kt < n_kt && ok; ++kt) {
+                    const int bsel = kt & 1;
+                    const unsigned use = (unsigned)(kt >> 1);
+                    if (kt >= 2) ok = mbar_wait(smem_u32(&free_bar[bsel]), (use - 1) & 1, &abort_s);      // epilogue kt - 2 done
+                    if (ok) ok = mbar_wait(smem_u32(&full_bar[bsel]), use & 1, &abort_s);                 // K tile kt landed
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_product(tmem + bsel * 128, q_tile, k_tiles + bsel * kTileBytes, 128, a.bf16, smem_u32(&mma_bar[bsel]));
+                    if (kt + 2 < n_kt) {                                                                  // refill this K buffer
+                        ok = mbar_wait(smem_u32(&mma_bar[bsel]), use & 1, &abort_s);
+                        if (ok) load_k(kt + 2);
                     }
                 }
-                const float m_new = fmaxf(m, cmax);
-                float acc0 = 0.f, acc1 = 0.f;
-                if (open) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
-                        acc1 += ex2f(fmaf(__uint_as_float(v[i + 1]), a.c, -m_new));
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int j = j0 + cb * 32 + i;
-                        if (j <= vis && j < a.Tkv) acc0 += ex2f(fmaf(__uint_as_float(v[i]), a.c, -m_new));
-                    }
+                if (!ok) {
+                    abort_s = 1;
+                    atomicExch(a.status, 1u);
                 }
-                l = l * ex2f(m - m_new) + (acc0 + acc1);     // both at the masked value: factor 1, nothing added
-                m = m_new;
+            }
+            __syncwarp();
+        } else {
+            for (int kt = 0; kt < n_kt; ++kt) {
+                bool ok = mbar_wait(smem_u32(&mma_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s);
+                ok = __all_sync(0xffffffffu, ok);    // the tensor-memory loads are warp-wide instructions
+                if (!ok) {
+                    abort_s = 1;
+                    atomicExch(a.status, 1u);
+                    break;
+                }
+                tc_fence_after();
+                epilogue(kt);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&free_bar[kt & 1]));
             }
         }
+    } else {
+        stage_rows(q_tile, 16, tid, Qb, [&](int row_) { return r0 + row_ < a.Tq ? Qb + (size_t)(r0 + row_) * kD * esz : nullptr; });
+        auto stage_k = [&](int kt) {
+            if (kt < n_kt)
+                stage_rows(k_tiles + (kt & 1) * kTileBytes, 16, tid, Kb,
+                           [&](int row_) { return kt * kWRows + row_ < a.Tkv ? Kb + (size_t)(kt * kWRows + row_) * kD * esz : nullptr; });
+            cp_async_commit();
+        };
+        auto issue = [&](int kt) {   // warp 0, converged
+            tc_fence_after();
+            if (elect_one()) issue_product(tmem + (kt & 1) * 128, q_tile, k_tiles + (kt & 1) * kTileBytes, 128, a.bf16, smem_u32(&mma_bar[kt & 1]));
+            __syncwarp();
+        };
+        stage_k(0);
+        stage_k(1);
+        cp_async_wait<1>();
+        proxy_fence();
+        __syncthreads();
+        if (warp == 0 && n_kt > 0) issue(0);
+        bool dead = false;
+        for (int kt = 0; kt < n_kt; ++kt) {
+            // Two products stay in flight: tile kt + 1 is issued before tile kt is awaited.  Its accumulator was read
+            // during the previous iteration, hence the barrier first; every thread has waited for its own pieces of
+            // K tile kt + 1.
+            cp_async_wait<0>();
+            proxy_fence();
+            tc_fence_before();
+            __syncthreads();
+            dead = dead || abort_s != 0;
+            if (warp == 0 && !dead && kt + 1 < n_kt) issue(kt + 1);
+            if (!dead && !mbar_wait(smem_u32(&mma_bar[kt & 1]), (unsigned)((kt >> 1) & 1), &abort_s)) {
+                dead = true;
+                abort_s = 1;
+                atomicExch(a.status, 1u);
+            }
+            stage_k(kt + 2);                        // product kt is complete: its K buffer takes tile kt + 2
+            dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
+            tc_fence_after();
+            if (!dead) epilogue(kt);
+        }
+        cp_async_wait<0>();
     }
-    if constexpr (!TMA) cp_async_wait<0>();
-    if (half == 1) part_s[row] = make_float2(m, l);
+    if (warp < kWorkWarps && half == 1) part_s[row] = make_float2(m, l);
     __syncthreads();
-    if (half == 0 && r < a.Tq) {
+    if (warp < kWorkWarps && half == 0 && r < a.Tq) {
         const float2 o = part_s[row];
         const float mm = fmaxf(m, o.x);
         const float ll = l * ex2f(m - mm) + o.y * ex2f(o.x - mm);
@@ -356,15 +395,16 @@ __global__ void __launch_bounds__(kWThreads, 2) win_lse_kernel(const WinArgs a, 
 }
 
 // ---- pass 2: sum / max / sum of squares per key of the head-averaged probabilities -------------------------------
-// grid: (ceil(Tkv / 128), B * H); shared memory: K tile + two query blocks of RB * G rows + four rows of their
-// log-sum-exps; tensor memory: two accumulators of N = RB * G columns.  Warps 0-3 take the first RB / 2 queries of a
-// block, warps 4-7 the others (every head of them); the two partial statistics of a key meet once, at the end.
-// Same pipeline as pass 1, over query blocks.
+// grid: (ceil(Tkv / 128), B * H); shared memory: K tile + two query blocks of RB * G rows (+ four rows of their
+// log-sum-exps for the thread-copy form); tensor memory: two accumulators of N = RB * G columns.  Working warps 0-3
+// take the first RB / 2 queries of a block, warps 4-7 the others (every head of them); the two partial statistics of
+// a key meet once, at the end.  Same two forms as pass 1, over query blocks.
 template <int RB, bool TMA>
-__global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
+__global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_cols_kernel(const WinArgs a, const __grid_constant__ WinMaps maps) {
     extern __shared__ __align__(1024) unsigned char smem[];
     __shared__ __align__(8) uint64_t mma_bar[2];    // product `it` arrives on mma_bar[it & 1]
     __shared__ __align__(8) uint64_t full_bar[2];   // tensor copies: bytes of query block `it` land on full_bar[it & 1]
+    __shared__ __align__(8) uint64_t free_bar[2];   // the working warps are done with accumulator it & 1
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
     __shared__ float part_s[3][kWRows];
@@ -373,8 +413,8 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
     const int blk_bytes = N * kD * 2;
     const int acc_stride = N <= 128 ? 128 : 256, tmem_cols = 2 * acc_stride;
     unsigned char *k_tile = smem, *q_blks = smem + kTileBytes;
-    float *lse_s = reinterpret_cast<float *>(smem + kTileBytes + 2 * blk_bytes);   // [4][N]: block it + 2 is written while slower warps may still read block it - 1
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = warp >> 2;
+    float *lse_s = reinterpret_cast<float *>(smem + kTileBytes + 2 * blk_bytes);   // [4][N], thread-copy form only
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = (warp >> 2) & 1;
     const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
     const int Hq = a.H * G;
     const int j0 = blockIdx.x * kWRows;
@@ -383,136 +423,186 @@ __global__ void __launch_bounds__(kWThreads, 2) win_cols_kernel(const WinArgs a,
     const unsigned char *Qb = reinterpret_cast<const unsigned char *>(a.Q) + ((size_t)(b * Hq + h * G) * a.Tq) * kD * esz;
     const float *lse_b = a.lse2 + (size_t)(b * Hq + h * G) * a.Tq;
     if (tid == 0) {
-        mbar_init(&mma_bar[0], 1);
-        mbar_init(&mma_bar[1], 1);
-        mbar_init(&full_bar[0], 1);
-        mbar_init(&full_bar[1], 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&mma_bar[i], 1);
+            mbar_init(&full_bar[i], 1);
+            mbar_init(&free_bar[i], kWorkWarps);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         abort_s = 0;
     }
     const uint32_t tmem = tmem_alloc(&tmem_slot, tmem_cols, warp);
     const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16) + half * HB;
 
-    if constexpr (!TMA)
-        stage_rows(k_tile, 16, tid, Kb, [&](int row) { return j0 + row < a.Tkv ? Kb + (size_t)(j0 + row) * kD * esz : nullptr; });
     // query blocks that can see a key of this tile: r + q_offset >= j0
     const int n_rb = (a.Tq + RB - 1) / RB;
     const int rb_first = max(0, j0 - a.q_offset) / RB;
-    const int n_it = n_rb - rb_first;
-    auto stage_q = [&](int it) {
-        if (it < n_it) {
-            const int rb = rb_first + it;
-            // row n = g * RB + rr of the block is query rb * RB + rr of head g
-            if constexpr (TMA) {
-                if (tid == 0) {   // two copies: RB rows of each of the G heads (the first barrier also counts the K tile)
-                    const uint32_t fb = smem_u32(&full_bar[it & 1]);
-                    mbar_expect_tx(fb, (uint32_t)blk_bytes + (it == 0 ? (uint32_t)kTileBytes : 0u));
-                    if (it == 0) tma_load_tile(k_tile, kWRows, &maps.k_tile, j0, bh, fb);
-                    tma_load_tile(q_blks + (it & 1) * blk_bytes, N, &maps.q_blk, rb * RB, b * Hq + h * G, fb);
-                }
-            } else {
-                stage_rows(q_blks + (it & 1) * blk_bytes, N / 8, tid, Qb, [&](int row) {
-                    const int g = row / RB, rr = rb * RB + row % RB;
-                    return rr < a.Tq ? Qb + ((size_t)g * a.Tq + rr) * kD * esz : nullptr;
-                });
-            }
-            float *ls = lse_s + (it & 3) * N;
-            for (int n = tid; n < N; n += kWThreads) {
-                const int g = n / RB, rr = rb * RB + n % RB;
-                ls[n] = rr < a.Tq ? lse_b[(size_t)g * a.Tq + rr] : -kMasked;   // past Tq: probability 0
-            }
-        }
-        if constexpr (!TMA) cp_async_commit();
-    };
-    auto issue = [&](int it) {   // warp 0, converged
-        tc_fence_after();
-        if (elect_one()) {
-            bool ok = true;
-            if constexpr (TMA) ok = mbar_wait(smem_u32(&full_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s);
-            if (ok) {
-                issue_product(tmem + (it & 1) * acc_stride, k_tile, q_blks + (it & 1) * blk_bytes, N, a.bf16, smem_u32(&mma_bar[it & 1]));
-            } else {
-                abort_s = 1;
-                atomicExch(a.status, 1u);
-            }
-        }
-        __syncwarp();
-    };
-    stage_q(0);
-    stage_q(1);
-    if constexpr (!TMA) {
-        cp_async_wait<1>();
-        proxy_fence();
-    }
-    __syncthreads();
-    if (warp == 0 && n_it > 0) issue(0);
-
+    const int n_it = max(0, n_rb - rb_first);
     const int row = (warp & 3) * 32 + lane;
     const int j = j0 + row;
     const float inv_g = 1.0f / (float)G;
     float s_sum = 0.f, s_max = 0.f, s_sq = 0.f;
-    bool dead = false;
-    for (int it = 0; it < n_it; ++it) {
+
+    // one accumulator -> the three statistics of this thread's key over its half of the block's queries;
+    // ls(g): log-sum-exps of head g for those queries (shared memory, or global memory for a whole block)
+    auto epilogue = [&](int it, auto ls_of) {
         const int rb = rb_first + it;
-        // two products in flight, as in pass 1: block it + 1 is issued before block `it` is awaited
-        if constexpr (!TMA) {
-            cp_async_wait<0>();
-            proxy_fence();
-        }
-        tc_fence_before();
-        __syncthreads();
-        dead = dead || abort_s != 0;
-        if (warp == 0 && !dead && it + 1 < n_it) issue(it + 1);
-        if (!dead && !mbar_wait(smem_u32(&mma_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s)) {
-            dead = true;
-            abort_s = 1;
-            atomicExch(a.status, 1u);
-        }
-        stage_q(it + 2);                        // product `it` is complete: its query buffer is free
-        dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
-        tc_fence_after();
-        if (!dead) {
-            float mean[HB];
+        float mean[HB];
 #pragma unroll
-            for (int i = 0; i < HB; ++i) mean[i] = 0.f;
-            const float *ls = lse_s + (it & 3) * N + half * HB;
-            const uint32_t acc_addr = tmem_lane + (it & 1) * acc_stride;
-            const int r_base = rb * RB + half * HB;
-            // a block whose first query already sees the last key of this tile needs no mask
-            const bool open = j0 + kWRows - 1 <= rb * RB + a.q_offset;
-            for (int g = 0; g < G; ++g) {
-                uint32_t v[HB];
-                if constexpr (HB == 16) tmem_ld16(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[16]>(v));
-                else tmem_ld8(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[8]>(v));
-                float lg[HB];
+        for (int i = 0; i < HB; ++i) mean[i] = 0.f;
+        const uint32_t acc_addr = tmem_lane + (it & 1) * acc_stride;
+        const int r_base = rb * RB + half * HB;
+        // a block whose first query already sees the last key of this tile needs no mask
+        const bool open = j0 + kWRows - 1 <= rb * RB + a.q_offset;
+        for (int g = 0; g < G; ++g) {
+            uint32_t v[HB];
+            if constexpr (HB == 16) tmem_ld16(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[16]>(v));
+            else tmem_ld8(acc_addr + g * RB, reinterpret_cast<uint32_t(&)[8]>(v));
+            float lg[HB];
+            ls_of(g, r_base, lg);
+            tmem_ld_wait();
+            if (open) {
 #pragma unroll
-                for (int i4 = 0; i4 < HB / 4; ++i4) {
-                    const float4 f = *reinterpret_cast<const float4 *>(ls + g * RB + 4 * i4);
-                    lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                for (int i = 0; i < HB; ++i) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
+            } else {
+#pragma unroll
+                for (int i = 0; i < HB; ++i)   // key j is visible to query r when j <= r + q_offset
+                    if (j <= r_base + i + a.q_offset) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < HB; ++i) {
+            const float mg = mean[i] * inv_g;
+            s_sum += mg;
+            s_max = fmaxf(s_max, mg);
+            s_sq = fmaf(mg, mg, s_sq);
+        }
+    };
+
+    if constexpr (TMA) {
+        if (warp == kWorkWarps) {
+            if (lane == 0) {
+                bool ok = true;
+                auto load_q = [&](int it) {   // two copies: RB rows of each of the G heads (the first barrier also counts the K tile)
+                    const uint32_t fb = smem_u32(&full_bar[it & 1]);
+                    mbar_expect_tx(fb, (uint32_t)blk_bytes + (it == 0 ? (uint32_t)kTileBytes : 0u));
+                    if (it == 0) tma_load_tile(k_tile, kWRows, &maps.k_tile, j0, bh, fb);
+                    tma_load_tile(q_blks + (it & 1) * blk_bytes, N, &maps.q_blk, (rb_first + it) * RB, b * Hq + h * G, fb);
+                };
+                if (n_it > 0) load_q(0);
+                if (n_it > 1) load_q(1);
+                for (int it = 0; it < n_it && ok; ++it) {
+                    const int bsel = it & 1;
+                    const unsigned use = (unsigned)(it >> 1);
+                    if (it >= 2) ok = mbar_wait(smem_u32(&free_bar[bsel]), (use - 1) & 1, &abort_s);
+                    if (ok) ok = mbar_wait(smem_u32(&full_bar[bsel]), use & 1, &abort_s);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_product(tmem + bsel * acc_stride, k_tile, q_blks + bsel * blk_bytes, N, a.bf16, smem_u32(&mma_bar[bsel]));
+                    if (it + 2 < n_it) {
+                        ok = mbar_wait(smem_u32(&mma_bar[bsel]), use & 1, &abort_s);
+                        if (ok) load_q(it + 2);
+                    }
                 }
-                tmem_ld_wait();
-                if (open) {
+                if (!ok) {
+                    abort_s = 1;
+                    atomicExch(a.status, 1u);
+                }
+            }
+            __syncwarp();
+        } else {
+            // log-sum-exps straight from global memory (every lane reads the same words): vector loads for a block
+            // inside Tq, guarded scalar loads for the last one
+            auto ls_global = [&](int g, int r_base, float (&lg)[HB]) {
+                const float *src = lse_b + (size_t)g * a.Tq + r_base;
+                if (r_base + HB <= a.Tq && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
 #pragma unroll
-                    for (int i = 0; i < HB; ++i) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
+                    for (int i4 = 0; i4 < HB / 4; ++i4) {
+                        const float4 f = __ldg(reinterpret_cast<const float4 *>(src) + i4);
+                        lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < HB; ++i)   // key j is visible to query r when j <= r + q_offset
-                        if (j <= r_base + i + a.q_offset) mean[i] += ex2f(fmaf(__uint_as_float(v[i]), a.c, -lg[i]));
+                    for (int i = 0; i < HB; ++i) lg[i] = r_base + i < a.Tq ? __ldg(src + i) : -kMasked;   // past Tq: probability 0
                 }
-            }
-#pragma unroll
-            for (int i = 0; i < HB; ++i) {
-                const float mg = mean[i] * inv_g;
-                s_sum += mg;
-                s_max = fmaxf(s_max, mg);
-                s_sq = fmaf(mg, mg, s_sq);
+            };
+            for (int it = 0; it < n_it; ++it) {
+                bool ok = mbar_wait(smem_u32(&mma_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s);
+                ok = __all_sync(0xffffffffu, ok);    // the tensor-memory loads are warp-wide instructions
+                if (!ok) {
+                    abort_s = 1;
+                    atomicExch(a.status, 1u);
+                    break;
+                }
+                tc_fence_after();
+                epilogue(it, ls_global);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&free_bar[it & 1]));
             }
         }
+    } else {
+        stage_rows(k_tile, 16, tid, Kb, [&](int row_) { return j0 + row_ < a.Tkv ? Kb + (size_t)(j0 + row_) * kD * esz : nullptr; });
+        auto stage_q = [&](int it) {
+            if (it < n_it) {
+                const int rb = rb_first + it;
+                // row n = g * RB + rr of the block is query rb * RB + rr of head g
+                stage_rows(q_blks + (it & 1) * blk_bytes, N / 8, tid, Qb, [&](int row_) {
+                    const int g = row_ / RB, rr = rb * RB + row_ % RB;
+                    return rr < a.Tq ? Qb + ((size_t)g * a.Tq + rr) * kD * esz : nullptr;
+                });
+                float *ls = lse_s + (it & 3) * N;
+                for (int n = tid; n < N; n += kWThreads) {
+                    const int g = n / RB, rr = rb * RB + n % RB;
+                    ls[n] = rr < a.Tq ? lse_b[(size_t)g * a.Tq + rr] : -kMasked;   // past Tq: probability 0
+                }
+            }
+            cp_async_commit();
+        };
+        auto issue = [&](int it) {   // warp 0, converged
+            tc_fence_after();
+            if (elect_one()) issue_product(tmem + (it & 1) * acc_stride, k_tile, q_blks + (it & 1) * blk_bytes, N, a.bf16, smem_u32(&mma_bar[it & 1]));
+            __syncwarp();
+        };
+        stage_q(0);
+        stage_q(1);
+        cp_async_wait<1>();
+        proxy_fence();
+        __syncthreads();
+        if (warp == 0 && n_it > 0) issue(0);
+        bool dead = false;
+        for (int it = 0; it < n_it; ++it) {
+            // two products in flight, as in pass 1: block it + 1 is issued before block `it` is awaited
+            cp_async_wait<0>();
+            proxy_fence();
+            tc_fence_before();
+            __syncthreads();
+            dead = dead || abort_s != 0;
+            if (warp == 0 && !dead && it + 1 < n_it) issue(it + 1);
+            if (!dead && !mbar_wait(smem_u32(&mma_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s)) {
+                dead = true;
+                abort_s = 1;
+                atomicExch(a.status, 1u);
+            }
+            stage_q(it + 2);                        // product `it` is complete: its query buffer is free
+            dead = __any_sync(0xffffffffu, dead);   // the tensor-memory loads below are warp-wide instructions
+            tc_fence_after();
+            if (!dead) {
+                const float *lsb = lse_s + (it & 3) * N + half * HB;
+                epilogue(it, [&](int g, int, float (&lg)[HB]) {
+#pragma unroll
+                    for (int i4 = 0; i4 < HB / 4; ++i4) {
+                        const float4 f = *reinterpret_cast<const float4 *>(lsb + g * RB + 4 * i4);
+                        lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                    }
+                });
+            }
+        }
+        cp_async_wait<0>();
     }
-    if constexpr (!TMA) cp_async_wait<0>();
-    if (half == 1) { part_s[0][row] = s_sum; part_s[1][row] = s_max; part_s[2][row] = s_sq; }
+    if (warp < kWorkWarps && half == 1) { part_s[0][row] = s_sum; part_s[1][row] = s_max; part_s[2][row] = s_sq; }
     __syncthreads();
-    if (half == 0 && j < a.Tkv) {
+    if (warp < kWorkWarps && half == 0 && j < a.Tkv) {
         const size_t o = (size_t)bh * a.Tkv + j;
         a.sum_attn[o] = s_sum + part_s[0][row];
         a.max_attn[o] = fmaxf(s_max, part_s[1][row]);
@@ -615,7 +705,7 @@ int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int 
     timing_begin("window_lse", st);
     if (tma) {
         if ((e = allow_smem(win_lse_kernel<true>, smem1)) != cudaSuccess) return (int)e;
-        win_lse_kernel<true><<<grid1, kWThreads, smem1, st>>>(a, maps);
+        win_lse_kernel<true><<<grid1, kTmaThreads, smem1, st>>>(a, maps);
     } else {
         if ((e = allow_smem(win_lse_kernel<false>, smem1)) != cudaSuccess) return (int)e;
         win_lse_kernel<false><<<grid1, kWThreads, smem1, st>>>(a, maps);
@@ -624,13 +714,13 @@ int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int 
     timing_begin("window_cols", st);
     if (a.RB == 32 && tma) {
         if ((e = allow_smem(win_cols_kernel<32, true>, smem2)) != cudaSuccess) return (int)e;
-        win_cols_kernel<32, true><<<grid2, kWThreads, smem2, st>>>(a, maps);
+        win_cols_kernel<32, true><<<grid2, kTmaThreads, smem2, st>>>(a, maps);
     } else if (a.RB == 32) {
         if ((e = allow_smem(win_cols_kernel<32, false>, smem2)) != cudaSuccess) return (int)e;
         win_cols_kernel<32, false><<<grid2, kWThreads, smem2, st>>>(a, maps);
     } else if (tma) {
         if ((e = allow_smem(win_cols_kernel<16, true>, smem2)) != cudaSuccess) return (int)e;
-        win_cols_kernel<16, true><<<grid2, kWThreads, smem2, st>>>(a, maps);
+        win_cols_kernel<16, true><<<grid2, kTmaThreads, smem2, st>>>(a, maps);
     } else {
         if ((e = allow_smem(win_cols_kernel<16, false>, smem2)) != cudaSuccess) return (int)e;
         win_cols_kernel<16, false><<<grid2, kWThreads, smem2, st>>>(a, maps);
