@@ -408,6 +408,7 @@ __global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_cols_ker
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_s;
     __shared__ float part_s[3][kWRows];
+    __shared__ __align__(16) float lse_w[TMA ? kWorkWarps : 1][2][128];   // tensor-copy form: per working warp, two blocks
     constexpr int HB = RB / 2;
     const int G = a.G, N = RB * G;
     const int blk_bytes = N * kD * 2;
@@ -511,21 +512,34 @@ __global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_cols_ker
             }
             __syncwarp();
         } else {
-            // log-sum-exps straight from global memory (every lane reads the same words): vector loads for a block
-            // inside Tq, guarded scalar loads for the last one
-            auto ls_global = [&](int g, int r_base, float (&lg)[HB]) {
-                const float *src = lse_b + (size_t)g * a.Tq + r_base;
-                if (r_base + HB <= a.Tq && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+            // The log-sum-exps of this warp's half of a block (G * HB <= 128 values) are fetched one block ahead into
+            // registers, parked in a per-warp shared-memory row after the current block's arithmetic, and read back as
+            // broadcast vector loads: their latency stays off the dependent chain of the statistics.
+            float *lw = &lse_w[warp][0][0];
+            const int n_ls = G * HB;
+            auto fetch = [&](int it, float (&pre)[4]) {
+                const int r_base = (rb_first + it) * RB + half * HB;
 #pragma unroll
-                    for (int i4 = 0; i4 < HB / 4; ++i4) {
-                        const float4 f = __ldg(reinterpret_cast<const float4 *>(src) + i4);
-                        lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                for (int k = 0; k < 4; ++k) {
+                    const int n = lane + 32 * k;
+                    pre[k] = -kMasked;                                  // past Tq: probability 0
+                    if (n < n_ls && it < n_it) {
+                        const int g = n / HB, rr = r_base + n % HB;
+                        if (rr < a.Tq) pre[k] = __ldg(lse_b + (size_t)g * a.Tq + rr);
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < HB; ++i) lg[i] = r_base + i < a.Tq ? __ldg(src + i) : -kMasked;   // past Tq: probability 0
                 }
             };
+            auto park = [&](int it, const float (&pre)[4]) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int n = lane + 32 * k;
+                    if (n < n_ls) lw[(it & 1) * 128 + n] = pre[k];
+                }
+            };
+            float pre[4];
+            fetch(0, pre);
+            park(0, pre);
+            __syncwarp();
             for (int it = 0; it < n_it; ++it) {
                 bool ok = mbar_wait(smem_u32(&mma_bar[it & 1]), (unsigned)((it >> 1) & 1), &abort_s);
                 ok = __all_sync(0xffffffffu, ok);    // the tensor-memory loads are warp-wide instructions
@@ -534,9 +548,18 @@ __global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_cols_ker
                     atomicExch(a.status, 1u);
                     break;
                 }
+                fetch(it + 1, pre);
                 tc_fence_after();
-                epilogue(it, ls_global);
+                const float *lsb = lw + (it & 1) * 128;
+                epilogue(it, [&](int g, int, float (&lg)[HB]) {
+#pragma unroll
+                    for (int i4 = 0; i4 < HB / 4; ++i4) {
+                        const float4 f = *reinterpret_cast<const float4 *>(lsb + g * HB + 4 * i4);
+                        lg[4 * i4] = f.x; lg[4 * i4 + 1] = f.y; lg[4 * i4 + 2] = f.z; lg[4 * i4 + 3] = f.w;
+                    }
+                });
                 tc_fence_before();
+                park(it + 1, pre);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&free_bar[it & 1]));
             }
