@@ -51,6 +51,8 @@ def parse():
                     help="head shape and batch of one layer of a BASELINE configuration: config2 = GQA 32/8 batch 8 (default), "
                          "config3-layer = 28/4 batch 16 (Qwen2.5-7B shape), config4-layer = 64/8 batch 8 (Llama-3.1-70B shape)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--window-only", action="store_true",
+                    help="run only the windowed attention statistics block (tcgen05 kernels) on random keys of --ctx / --batch and print it")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of a CUDA graph replay")
     args = ap.parse_args()
     if args.preset == "config3-layer":
@@ -709,9 +711,23 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_window_only(args):
+    import importlib
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    dev = torch.device("cuda", 0)
+    pkg = importlib.import_module("odm-kv_b200")
+    g = torch.Generator(device=dev).manual_seed(1)
+    K = torch.randn(args.batch, args.kv_heads, args.ctx, 128, generator=g, device=dev).half()
+    print(json.dumps({"window_stats": window_stats_block(args, pkg, K, dev)}), flush=True)
+
+
 def main():
     args = parse()
-    if args.impl == "reference":
+    if args.window_only:
+        run_window_only(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
