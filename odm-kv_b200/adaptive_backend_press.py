@@ -196,7 +196,9 @@ class TurboQuantPerTokenBackendPress:
         return isinstance(cache.layers[layer_idx], PackedCacheLayer)
 
     def _attach(self, cache, layer_idx: int, module: nn.Module, state) -> None:
-        module.masked_key_indices = state.masked_key_indices()
+        # a packed-only layer never takes the fake-key route with these indices (its masked fallback dequantises and
+        # asks the state then), so the export of the evicted positions is skipped for it
+        module.masked_key_indices = None if self._is_packed_layer(cache, layer_idx) else state.masked_key_indices()
         module._odmkv_state = state
         if hasattr(cache, "layers"):
             cache.layers[layer_idx]._tq_backend_state = state
@@ -400,19 +402,40 @@ class TurboQuantPerTokenBackendPress:
 
     def _allocate_bits_via_cached_ratios(self, scores: torch.Tensor, layer_idx: int, allowed: set) -> Optional[torch.Tensor]:
         """Rank tiers per head from the prefill's level fractions; every sample of a head is pooled in
-        (b, t) order as in the reference (kvquant/adaptive_backend_press.py:198-241).  scores [B, H, n]."""
+        (b, t) order as in the reference (kvquant/adaptive_backend_press.py:198-241, kvquant/allocator.py:46-148):
+        ascending stable rank, tier sizes ``int(round(r * n))`` (Python's rounding), the last tier of a head takes the
+        remainder.  scores [B, H, n].  All heads go through one sort: the tier sizes are host arithmetic, the ranks
+        are compared with per-head cumulative sizes on the device."""
         B, H, n = scores.shape
         if not all((layer_idx, h) in self._observed_ratios for h in range(H)):
             return None
-        bits = torch.empty_like(scores, dtype=torch.int32)
+        n_pool = B * n
+        levels = sorted(allowed)
+        ends = []
         for h in range(H):
-            filt = [(b, r) for b, r in self._observed_ratios[(layer_idx, h)] if b in allowed and r > 0]
+            filt = sorted((b, r) for b, r in self._observed_ratios[(layer_idx, h)] if b in allowed and r > 0)
             if not filt:
                 return None
             total = sum(r for _, r in filt)
-            lv, rt = zip(*[(b, r / total) for b, r in filt])
-            bits[:, h, :] = ratio_scores_to_bits(scores[:, h, :].reshape(-1), tuple(lv), tuple(rt)).reshape(B, n)
-        return bits
+            count = {}
+            cursor = 0
+            for i, (b, r) in enumerate(filt):
+                c = n_pool - cursor if i == len(filt) - 1 else min(int(round(r / total * n_pool)), n_pool - cursor)
+                count[b] = c
+                cursor += c
+            acc, row = 0, []
+            for b in levels:             # levels a head does not use are empty tiers
+                acc += count.get(b, 0)
+                row.append(acc)
+            ends.append(row)
+        dev = scores.device
+        pooled = scores.permute(1, 0, 2).reshape(H, n_pool)
+        order = torch.argsort(pooled, dim=1, stable=True)
+        ranks = torch.empty_like(order)
+        ranks.scatter_(1, order, torch.arange(n_pool, device=dev).expand(H, n_pool))
+        tier = torch.searchsorted(torch.tensor(ends, device=dev, dtype=torch.int64), ranks, right=True)
+        bits = torch.tensor(levels, device=dev, dtype=torch.int32)[tier.clamp_(max=len(levels) - 1)]
+        return bits.view(H, B, n).permute(1, 0, 2).contiguous()
 
     def _flush_decode_buffer(self, state, layer_idx: int, cache, module, hidden_states=None) -> None:
         """Score the buffered decode tokens and re-quantise them (kvquant/adaptive_backend_press.py:464-595)."""

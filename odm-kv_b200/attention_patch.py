@@ -99,6 +99,7 @@ def _attention_patch(func):
             Kd, Vd = state.materialize()
             key = torch.cat([Kd.to(key.dtype), key], dim=2)
             value = torch.cat([Vd.to(value.dtype), value], dim=2)
+            module.masked_key_indices = state.masked_key_indices()   # packed layers do not carry them otherwise
             dense_from_packed = True
         else:
             dense_from_packed = False

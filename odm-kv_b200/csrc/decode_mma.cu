@@ -606,30 +606,39 @@ static int decode_attn_mma_impl(const void *q, int q_dtype, const odmkv_chunk *c
             if (dev >= 0 && dev < 64) attr_set[dev] = true;
         }
     }
-    timing_begin("decode_main", st);
-    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
-    else decode_mma_kernel<2><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
-    timing_end(st);
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
     a.tail_len_dev = tail_len_dev; a.tail_len_add = tail_len_add;
     a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
     a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
-    // the exact / tail kernel only needs the rotated queries, so it runs beside the tensor-core kernel on a
-    // second stream (fork after the rotation, join before the merge)
+    // The exact / tail kernel only needs the rotated queries, so it runs beside the tensor-core kernel: the two are
+    // forked after the rotation and joined before the merge.  The tensor-core kernel fills every SM's registers, so
+    // whichever of the two is launched second starts when CTAs of the first retire.  For a long tensor-core kernel the
+    // small kernel goes second and slips into its tail; for a short one (small batch, short context) that would put
+    // the small kernel's whole latency behind it, so there the small kernel goes first and only delays a few CTAs.
     SideStream *ss = side_stream();
-    if (ss) {
+    const bool side_first = ss && total_tiles < 600ll * n_cta;
+    cudaStream_t st_main = side_first ? ss->stream : st, st_side = side_first || !ss ? st : ss->stream;
+    if (ss && !side_first) cudaStreamWaitEvent(ss->stream, ss->fork, 0);
+    if (side_first) {
+        timing_begin("decode_side", st_side);
+        launch_decode_cuda_core(dc, a, cache_dtype, st_side);
+        timing_end(st_side);
         cudaStreamWaitEvent(ss->stream, ss->fork, 0);
-        timing_begin("decode_side", ss->stream);
-        launch_decode_cuda_core(dc, a, cache_dtype, ss->stream);
-        timing_end(ss->stream);
+    }
+    timing_begin("decode_main", st_main);
+    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st_main>>>(dc, m);
+    else decode_mma_kernel<2><<<grid, kMmaThreads, kStageBytes, st_main>>>(dc, m);
+    timing_end(st_main);
+    if (!side_first) {
+        timing_begin("decode_side", st_side);
+        launch_decode_cuda_core(dc, a, cache_dtype, st_side);
+        timing_end(st_side);
+    }
+    if (ss) {
         cudaEventRecord(ss->join, ss->stream);
         cudaStreamWaitEvent(st, ss->join, 0);
-    } else {
-        timing_begin("decode_side", st);
-        launch_decode_cuda_core(dc, a, cache_dtype, st);
-        timing_end(st);
     }
     timing_begin("decode_merge", st);
     launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st, n_splits, (int)n_cta);
