@@ -139,27 +139,41 @@ __device__ inline void process_exact(WarpState<GP> &st, const void *__restrict__
 #pragma unroll
     for (int g = 0; g < GP; ++g) logit[g] = 0.f;
     if (valid) {
-        for (int i4 = 0; i4 < kD / 4; ++i4) {
-            float4 kv = load4<CDT>(kbase, r * kD + 4 * i4);
-            const float kk[4] = {kv.x, kv.y, kv.z, kv.w};
+        // eight independent loads in flight per step (a lane walks its own row, so nothing here is coalesced and the
+        // loop is bound by load latency unless the loads are issued in batches)
+        for (int i0 = 0; i0 < kD / 4; i0 += 8) {
+            float4 kv[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
+            for (int u = 0; u < 8; ++u) kv[u] = load4<CDT>(kbase, r * kD + 4 * (i0 + u));
 #pragma unroll
-                for (int g = 0; g < GP; ++g) logit[g] = fmaf(kk[e], qx[(4 * i4 + e) * GP + g], logit[g]);
+            for (int u = 0; u < 8; ++u) {
+                const float kk[4] = {kv[u].x, kv[u].y, kv[u].z, kv[u].w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) logit[g] = fmaf(kk[e], qx[(4 * (i0 + u) + e) * GP + g], logit[g]);
+            }
         }
 #pragma unroll
         for (int g = 0; g < GP; ++g) logit[g] *= scale;
     }
     softmax_step<GP>(st, logit, valid, p);
     const int cnt = (int)min((size_t)32, r_end - r_begin);
-    for (int j = 0; j < cnt; ++j) {
-        float4 vv = load4<CDT>(vbase, (r_begin + j) * kD + 4 * lane);
-        const float c[4] = {vv.x, vv.y, vv.z, vv.w};
+    for (int j0 = 0; j0 < cnt; j0 += 8) {     // value rows in batches of eight loads as well (cnt is warp-uniform)
+        float4 vv[8];
 #pragma unroll
-        for (int g = 0; g < GP; ++g) {
-            float pj = __shfl_sync(0xffffffffu, p[g], j);
+        for (int u = 0; u < 8; ++u)
+            vv[u] = j0 + u < cnt ? load4<CDT>(vbase, (r_begin + j0 + u) * kD + 4 * lane) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int d = 0; d < 4; ++d) st.ae[g][d] = fmaf(pj, c[d], st.ae[g][d]);
+        for (int u = 0; u < 8; ++u) {
+            if (j0 + u >= cnt) break;
+            const float c[4] = {vv[u].x, vv[u].y, vv[u].z, vv[u].w};
+#pragma unroll
+            for (int g = 0; g < GP; ++g) {
+                float pj = __shfl_sync(0xffffffffu, p[g], j0 + u);
+#pragma unroll
+                for (int d = 0; d < 4; ++d) st.ae[g][d] = fmaf(pj, c[d], st.ae[g][d]);
+            }
         }
     }
 }

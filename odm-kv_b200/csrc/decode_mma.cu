@@ -618,7 +618,7 @@ static int decode_attn_mma_impl(const void *q, int q_dtype, const odmkv_chunk *c
     // small kernel goes second and slips into its tail; for a short one (small batch, short context) that would put
     // the small kernel's whole latency behind it, so there the small kernel goes first and only delays a few CTAs.
     SideStream *ss = side_stream();
-    const bool side_first = ss && total_tiles < 600ll * n_cta;
+    const bool side_first = ss && total_tiles < 100ll * n_cta;   // under about 20 us of tensor-core kernel
     cudaStream_t st_main = side_first ? ss->stream : st, st_side = side_first || !ss ? st : ss->stream;
     if (ss && !side_first) cudaStreamWaitEvent(ss->stream, ss->fork, 0);
     if (side_first) {

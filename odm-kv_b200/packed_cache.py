@@ -132,6 +132,8 @@ class GraphedDecoder:
         pairs = self._layer_states()
         for _, st in pairs:
             st.begin_device_tail(room)
+            for chunk in st.chunks:
+                chunk.stored_tokens()        # host-side counts are read once, before the capture (it may not copy)
         snap = [(st.seq_len, st.tail_len, st.tail_start) for _, st in pairs]
         counts, starts = dict(press._buffer_counts), dict(press._buffer_start_seqs)
         self.pos.fill_(pairs[0][1].seq_len)
