@@ -283,10 +283,8 @@ int odmkv_decode_attn_noalloc(const void *q, int q_dtype, const odmkv_chunk *chu
  * operand tiles staged by TMA tensor copies where the shapes allow. */
 size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq);
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq);
-/* how the last call on this process ran: 2 = window form (Tq <= 128 and G <= 4: the queries of a KV head stay in
- * shared memory and the keys stream through once per pass; tensor copies), 1 = general form with tensor copies (TMA),
- * 0 = general form with 16-byte copies by the threads (taken when the driver's tensor-map encoder is unavailable, or
- * when forced), -1 = no call yet */
+/* how the last call on this process staged its operand tiles: 1 = tensor copies (TMA), 0 = 16-byte copies by the
+ * threads (taken when the driver's tensor-map encoder is unavailable, or when forced), -1 = no call yet */
 int odmkv_window_stats_last_path(void);
 /* on != 0: stage by thread copies even where tensor copies are possible (for testing that path) */
 void odmkv_window_stats_force_thread_copies(int on);

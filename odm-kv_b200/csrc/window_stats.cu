@@ -634,271 +634,9 @@ __global__ void __launch_bounds__(TMA ? kTmaThreads : kWThreads, 2) win_cols_ker
     tmem_free(tmem, tmem_cols, warp);
 }
 
-// ---- window form: the queries stay in shared memory, the keys stream through once ----------------------------------
-// When the whole query set of a KV head fits four 128-row tiles (Tq <= 128, G <= 4: the press's window of the last
-// 128 positions for a GQA 4 model) both passes take this kernel instead: a CTA owns a range of key tiles of one
-// (sample, KV head), keeps all of that head's queries resident (four tiles, 128 KB), streams its key tiles through two
-// buffers -- every key tile is read from L2 once per pass instead of once per query head or query block -- and forms
-// four products per key tile into a ring of four tensor-memory accumulators (all 512 columns).
-//   PASS 1: product p = queries of head p (rows) x 128 keys (columns): running (maximum, sum) per query row and head over
-//           the CTA's key range, written as one partial per (key range, head, query);
-//   PASS 2: product p = 128 keys (rows) x queries 32 p .. 32 p + 31 of every head (columns); the log-sum-exps are
-//           merged from the partials of pass 1 once, in the prologue; statistics written per key tile.
-// Same roles as above: warp 8 drives copies and products, warps 0-7 do the arithmetic, mbarriers only (plus one
-// named barrier per key tile in pass 2 for the exchange between the two halves of a row).
-constexpr int kResSplitsMax = 32;
-constexpr int kResSmem = 2 * kTileBytes + 4 * kTileBytes + 4 * 128 * (int)sizeof(float);
-
-struct ResArgs {
-    float2 *lse_part;      // [n_split][B * Hq][Tq] (maximum, sum) of pass 1
-    int n_split;
-};
-
-template <int PASS>
-__global__ void __launch_bounds__(kTmaThreads, 1) win_resident_kernel(const WinArgs a, const ResArgs ra, const __grid_constant__ WinMaps maps) {
-    extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ __align__(8) uint64_t mma_bar[4];    // product p of the current key tile
-    __shared__ __align__(8) uint64_t free_bar[4];   // the working warps are done with accumulator p
-    __shared__ __align__(8) uint64_t full_k[2];     // bytes of a key tile
-    __shared__ __align__(8) uint64_t full_q;        // bytes of the resident queries
-    __shared__ uint32_t tmem_slot;
-    __shared__ int abort_s;
-    __shared__ float part_s[4][kWRows][2];
-    unsigned char *k_tiles = smem, *q_res = smem + 2 * kTileBytes;
-    float *lse_res = reinterpret_cast<float *>(smem + 6 * kTileBytes);   // PASS 2: [block p][g * 32 + rr]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, half = (warp >> 2) & 1;
-    const int G = a.G, Hq = a.H * G;
-    const int bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
-    const int head0 = b * Hq + h * G;
-    const int P = PASS == 1 ? G : (a.Tq + 31) / 32;          // products per key tile
-    const int N = PASS == 1 ? 128 : 32 * G;                   // columns of a product
-    // key tiles that any query can see, and this CTA's share of them
-    const int n_keys = max(0, min(a.Tkv, a.Tq - 1 + a.q_offset + 1));
-    const int n_kt = (n_keys + kWRows - 1) / kWRows;
-    const int kt_lo = (int)((long long)n_kt * blockIdx.x / gridDim.x), kt_hi = (int)((long long)n_kt * (blockIdx.x + 1) / gridDim.x);
-    const int n_it = kt_hi - kt_lo;
-    if (tid == 0) {
-        for (int i = 0; i < 4; ++i) {
-            mbar_init(&mma_bar[i], 1);
-            mbar_init(&free_bar[i], kWorkWarps);
-        }
-        mbar_init(&full_k[0], 1);
-        mbar_init(&full_k[1], 1);
-        mbar_init(&full_q, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        abort_s = 0;
-    }
-    const uint32_t tmem = tmem_alloc(&tmem_slot, 512, warp);
-    const uint32_t tmem_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    const int row = (warp & 3) * 32 + lane;
-
-    if (warp == kWorkWarps) {
-        if (lane == 0 && n_it > 0) {
-            bool ok = true;
-            mbar_expect_tx(smem_u32(&full_q), (uint32_t)(P * N * kD * 2));
-            for (int p = 0; p < P; ++p) {
-                if (PASS == 1) tma_load_tile(q_res + p * kTileBytes, kWRows, &maps.q_tile, 0, head0 + p, smem_u32(&full_q));
-                else tma_load_tile(q_res + p * kTileBytes, N, &maps.q_blk, 32 * p, head0, smem_u32(&full_q));
-            }
-            auto load_k = [&](int i) {
-                const uint32_t fb = smem_u32(&full_k[i & 1]);
-                mbar_expect_tx(fb, kTileBytes);
-                tma_load_tile(k_tiles + (i & 1) * kTileBytes, kWRows, &maps.k_tile, (kt_lo + i) * kWRows, bh, fb);
-            };
-            load_k(0);
-            if (n_it > 1) load_k(1);
-            ok = mbar_wait(smem_u32(&full_q), 0, &abort_s);
-            for (int i = 0; i < n_it && ok; ++i) {
-                ok = mbar_wait(smem_u32(&full_k[i & 1]), (unsigned)((i >> 1) & 1), &abort_s);
-                for (int p = 0; p < P && ok; ++p) {
-                    if (i >= 1) ok = mbar_wait(smem_u32(&free_bar[p]), (unsigned)((i - 1) & 1), &abort_s);
-                    if (!ok) break;
-                    tc_fence_after();
-                    const unsigned char *kt_ = k_tiles + (i & 1) * kTileBytes, *qp = q_res + p * kTileBytes;
-                    if (PASS == 1) issue_product(tmem + p * 128, qp, kt_, 128, a.bf16, smem_u32(&mma_bar[p]));
-                    else issue_product(tmem + p * 128, kt_, qp, N, a.bf16, smem_u32(&mma_bar[p]));
-                }
-                if (ok && i + 2 < n_it) {       // the products of this key tile complete in order: then its buffer is free
-                    ok = mbar_wait(smem_u32(&mma_bar[P - 1]), (unsigned)(i & 1), &abort_s);
-                    if (ok) load_k(i + 2);
-                }
-            }
-            if (!ok) {
-                abort_s = 1;
-                atomicExch(a.status, 1u);
-            }
-        }
-        __syncwarp();
-    } else if (PASS == 1) {
-        // thread = (query row, column half); one (maximum, sum) pair per head
-        float m[4], l[4];
-#pragma unroll
-        for (int p = 0; p < 4; ++p) { m[p] = kMasked; l[p] = 0.f; }
-        const int vis = row + a.q_offset;
-        bool ok = true;
-        for (int i = 0; i < n_it && ok; ++i) {
-            const int kt = kt_lo + i;
-            const bool open = kt * kWRows + kWRows - 1 <= a.q_offset && (kt + 1) * kWRows <= a.Tkv;
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                if (p >= P) break;
-                ok = mbar_wait(smem_u32(&mma_bar[p]), (unsigned)(i & 1), &abort_s);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                const int j0 = kt * kWRows + half * 64;
-#pragma unroll 1
-                for (int cb = 0; cb < 2; ++cb) {
-                    uint32_t v[32];
-                    tmem_ld32(tmem_lane + p * 128 + half * 64 + cb * 32, v);
-                    tmem_ld_wait();
-                    float cmax = kMasked;
-                    if (open) {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) cmax = fmaxf(cmax, __uint_as_float(v[e]));
-                        cmax *= a.c;
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int j = j0 + cb * 32 + e;
-                            if (j <= vis && j < a.Tkv) cmax = fmaxf(cmax, __uint_as_float(v[e]) * a.c);
-                        }
-                    }
-                    const float m_new = fmaxf(m[p], cmax);
-                    float acc0 = 0.f, acc1 = 0.f;
-                    if (open) {
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2) {
-                            acc0 += ex2f(fmaf(__uint_as_float(v[e]), a.c, -m_new));
-                            acc1 += ex2f(fmaf(__uint_as_float(v[e + 1]), a.c, -m_new));
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const int j = j0 + cb * 32 + e;
-                            if (j <= vis && j < a.Tkv) acc0 += ex2f(fmaf(__uint_as_float(v[e]), a.c, -m_new));
-                        }
-                    }
-                    l[p] = l[p] * ex2f(m[p] - m_new) + (acc0 + acc1);
-                    m[p] = m_new;
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&free_bar[p]));
-            }
-        }
-        if (!ok) {
-            abort_s = 1;
-            atomicExch(a.status, 1u);
-        }
-        // the two column halves of a row meet, then one partial per (key range, head, query)
-#pragma unroll
-        for (int p = 0; p < 4; ++p)
-            if (half == 1) { part_s[p][row][0] = m[p]; part_s[p][row][1] = l[p]; }
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kWThreads) : "memory");
-        if (half == 0 && row < a.Tq) {
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-                if (p >= P) break;
-                const float om = part_s[p][row][0], ol = part_s[p][row][1];
-                const float mm = fmaxf(m[p], om);
-                const float ll = l[p] * ex2f(m[p] - mm) + ol * ex2f(om - mm);
-                ra.lse_part[((size_t)blockIdx.x * a.B * Hq + head0 + p) * a.Tq + row] = make_float2(mm, ll);
-            }
-        }
-    } else {
-        // log-sum-exps of every (head, query) of this KV head from the partials of all key ranges
-        for (int n = tid; n < 4 * 128; n += kWThreads) {
-            const int p = n >> 7, c = n & 127, g = c >> 5, rr = 32 * p + (c & 31);
-            float out = -kMasked;                     // no such query: probability 0
-            if (g < G && rr < a.Tq) {
-                float mm = kMasked, ll = 0.f;
-                for (int sidx = 0; sidx < ra.n_split; ++sidx) {
-                    const float2 pr = ra.lse_part[((size_t)sidx * a.B * Hq + head0 + g) * a.Tq + rr];
-                    const float mn = fmaxf(mm, pr.x);
-                    ll = ll * ex2f(mm - mn) + pr.y * ex2f(pr.x - mn);
-                    mm = mn;
-                }
-                if (ll > 0.f) out = mm + log2f(ll);
-            }
-            lse_res[n] = out;
-        }
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kWThreads) : "memory");
-        const float inv_g = 1.0f / (float)G;
-        bool ok = true;
-        for (int i = 0; i < n_it; ++i) {     // (a warp that gave up keeps walking: the named barrier below counts it)
-            const int kt = kt_lo + i, j = kt * kWRows + row;
-            float s_sum = 0.f, s_max = 0.f, s_sq = 0.f;
-#pragma unroll 1
-            for (int p = 0; p < P && ok; ++p) {
-                ok = mbar_wait(smem_u32(&mma_bar[p]), (unsigned)(i & 1), &abort_s);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tc_fence_after();
-                float mean[16];
-#pragma unroll
-                for (int e = 0; e < 16; ++e) mean[e] = 0.f;
-                const int r_base = 32 * p + half * 16;
-                const bool open = kt * kWRows + kWRows - 1 <= 32 * p + a.q_offset;
-                const float *ls = lse_res + p * 128 + half * 16;
-                for (int g = 0; g < G; ++g) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem_lane + p * 128 + g * 32 + half * 16, v);
-                    float lg[16];
-#pragma unroll
-                    for (int e4 = 0; e4 < 4; ++e4) {
-                        const float4 f = *reinterpret_cast<const float4 *>(ls + g * 32 + 4 * e4);
-                        lg[4 * e4] = f.x; lg[4 * e4 + 1] = f.y; lg[4 * e4 + 2] = f.z; lg[4 * e4 + 3] = f.w;
-                    }
-                    tmem_ld_wait();
-                    if (open) {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e) mean[e] += ex2f(fmaf(__uint_as_float(v[e]), a.c, -lg[e]));
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 16; ++e)
-                            if (j <= r_base + e + a.q_offset) mean[e] += ex2f(fmaf(__uint_as_float(v[e]), a.c, -lg[e]));
-                    }
-                }
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&free_bar[p]));
-#pragma unroll
-                for (int e = 0; e < 16; ++e) {
-                    const float mg = mean[e] * inv_g;
-                    s_sum += mg;
-                    s_max = fmaxf(s_max, mg);
-                    s_sq = fmaf(mg, mg, s_sq);
-                }
-            }
-            // the two query halves of a key meet (double-buffered by the parity of the key tile), then the key's statistics
-            float *ps = &part_s[(i & 1) * 2][0][0];
-            if (half == 1) { ps[row * 2] = s_sum; ps[row * 2 + 1] = s_max; ps[2 * kWRows + row * 2] = s_sq; }
-            asm volatile("bar.sync 1, %0;\n" ::"n"(kWThreads) : "memory");
-            if (ok && half == 0 && j < a.Tkv) {
-                const size_t o = (size_t)bh * a.Tkv + j;
-                a.sum_attn[o] = s_sum + ps[row * 2];
-                a.max_attn[o] = fmaxf(s_max, ps[row * 2 + 1]);
-                a.sum_sq[o] = s_sq + ps[2 * kWRows + row * 2];
-            }
-        }
-        if (!ok) {
-            abort_s = 1;
-            atomicExch(a.status, 1u);
-        }
-    }
-    tmem_free(tmem, 512, warp);
-}
-
 int pick_rb(int G) { return 32 * G <= 256 ? 32 : 16; }
 
 size_t lse_bytes(int B, int H, int G, int Tq) { return (((size_t)B * H * G * Tq * sizeof(float)) + 255) & ~(size_t)255; }
-
-// the window form applies when a KV head's queries fit four resident tiles
-bool window_form(int G, int Tq) { return Tq <= 128 && G <= 4; }
-size_t res_part_bytes(int B, int H, int G, int Tq) {
-    return window_form(G, Tq) ? (size_t)kResSplitsMax * B * H * G * Tq * sizeof(float2) : 0;
-}
 
 // cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link the driver directly)
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
@@ -948,7 +686,7 @@ extern "C" {
 
 size_t odmkv_window_stats_workspace_bytes(int B, int H, int G, int Tq) {
     if (B <= 0 || H <= 0 || G <= 0 || Tq <= 0) return 0;
-    return lse_bytes(B, H, G, Tq) + 256 + res_part_bytes(B, H, G, Tq);
+    return lse_bytes(B, H, G, Tq) + 256;
 }
 
 size_t odmkv_window_stats_status_offset(int B, int H, int G, int Tq) { return lse_bytes(B, H, G, Tq); }
@@ -987,38 +725,6 @@ int odmkv_window_attn_stats(const void *Q, const void *K, int dtype, int B, int 
                      make_map(&maps.k_tile, K, a.bf16, (long long)B * H, Tkv, kWRows, 1);
     g_last_path = tma ? 1 : 0;
     const dim3 grid1((Tq + kWRows - 1) / kWRows, B * H * G), grid2((Tkv + kWRows - 1) / kWRows, B * H);
-    if (tma && window_form(G, Tq)) {
-        // queries resident, keys streamed once per pass; key ranges sized for about three CTAs per SM over the kernel
-        g_last_path = 2;
-        int sms = 148;
-        int dev = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        const long long n_keys = Tkv < (long long)Tq + q_offset ? Tkv : (long long)Tq + q_offset;
-        const int n_kt = (int)((n_keys + kWRows - 1) / kWRows);
-        int S = (3 * sms + B * H - 1) / (B * H);
-        if (S > n_kt / 4) S = n_kt / 4;
-        if (S > kResSplitsMax) S = kResSplitsMax;
-        if (S < 1) S = 1;
-        ResArgs ra;
-        ra.lse_part = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(workspace) + lse_bytes(B, H, G, Tq) + 256);
-        ra.n_split = S;
-        if ((long long)n_kt * kWRows < Tkv) {   // keys no query sees: their statistics are zero
-            const size_t nb = (size_t)B * H * Tkv * sizeof(float);
-            if ((e = cudaMemsetAsync(sum_attn, 0, nb, st)) != cudaSuccess) return (int)e;
-            if ((e = cudaMemsetAsync(max_attn, 0, nb, st)) != cudaSuccess) return (int)e;
-            if ((e = cudaMemsetAsync(sum_sq_attn, 0, nb, st)) != cudaSuccess) return (int)e;
-        }
-        if ((e = allow_smem(win_resident_kernel<1>, kResSmem)) != cudaSuccess) return (int)e;
-        if ((e = allow_smem(win_resident_kernel<2>, kResSmem)) != cudaSuccess) return (int)e;
-        const dim3 grid(S, B * H);
-        timing_begin("window_lse", st);
-        win_resident_kernel<1><<<grid, kTmaThreads, kResSmem, st>>>(a, ra, maps);
-        timing_end(st);
-        timing_begin("window_cols", st);
-        win_resident_kernel<2><<<grid, kTmaThreads, kResSmem, st>>>(a, ra, maps);
-        timing_end(st);
-        return launch_status();
-    }
     timing_begin("window_lse", st);
     if (tma) {
         if ((e = allow_smem(win_lse_kernel<true>, smem1)) != cudaSuccess) return (int)e;
