@@ -79,6 +79,7 @@ class GraphedDecoder:
         self.ids = None
         self.pos = None
         self._warm = False
+        self._expected = None
         self.captures = 0
         self.replays = 0
         self.eager_steps = 0
@@ -106,6 +107,10 @@ class GraphedDecoder:
     def _room(self) -> int:
         press = self.press
         return min(press.buffer_size - 1 - press._buffer_counts.get(i, 0) for i, _ in self._layer_states())
+
+    def _signature(self):
+        """What the captured step assumes about every state: lengths and the identity of the chunk list."""
+        return [(st.seq_len, st.tail_len, st.tail_start, tuple(id(c) for c in st.chunks)) for _, st in self._layer_states()]
 
     def drop_graph(self) -> None:
         """Forget the captured step (after anything that changes a state: a flush, a rewind, a new prefill)."""
@@ -157,6 +162,7 @@ class GraphedDecoder:
         press._buffer_start_seqs.clear()
         press._buffer_start_seqs.update(starts)
         self.graph = graph
+        self._expected = self._signature()
         self.captures += 1
 
     # -- the step ----------------------------------------------------------------------------
@@ -168,6 +174,8 @@ class GraphedDecoder:
             self._warm = True
             self.eager_steps += 1
             return self._forward(tokens)
+        if self.graph is not None and self._signature() != self._expected:
+            self.drop_graph()            # someone changed a state in between (a rewind, an eager step): capture again
         if self.graph is None or self.ids.shape != tokens.shape:
             self.drop_graph()
             self._capture(tokens)
@@ -179,4 +187,5 @@ class GraphedDecoder:
             st.advance_host(1)
             self.press._buffer_counts[i] = self.press._buffer_counts.get(i, 0) + 1
         self.replays += 1
+        self._expected = self._signature()
         return self.logits
