@@ -191,8 +191,20 @@ __global__ void __launch_bounds__(kDecThreads) decode_main_kernel(const DecodeCh
     const int BH = a.B * a.H, G = a.G;
     for (int e = tid; e < kD * GP; e += kDecThreads) {
         int i = e / GP, g = e % GP;
-        qs[e] = g < G ? a.qrot[((size_t)bh * G + g) * kD + i] : 0.f;
-        qx[e] = g < G ? a.qf[((size_t)bh * G + g) * kD + i] : 0.f;
+        const size_t qi = ((size_t)bh * G + g) * kD + i;
+        if (a.q_raw) {   // exact rows and tail only: the plain queries straight from the caller's tensor
+            float v = 0.f;
+            if (g < G) {
+                if (a.q_dtype == kF16) v = __half2float(reinterpret_cast<const __half *>(a.q_raw)[qi]);
+                else if (a.q_dtype == kBF16) v = __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(a.q_raw)[qi]);
+                else v = reinterpret_cast<const float *>(a.q_raw)[qi];
+            }
+            qs[e] = 0.f;
+            qx[e] = v;
+        } else {
+            qs[e] = g < G ? a.qrot[qi] : 0.f;
+            qx[e] = g < G ? a.qf[qi] : 0.f;
+        }
     }
     for (int e = tid; e < 4 * 256; e += kDecThreads) lut[e] = a.codebooks[e];
     __syncthreads();
@@ -417,7 +429,7 @@ int odmkv_decode_attn(const void *q, int q_dtype, const odmkv_chunk *chunks, int
     DecodeArgs a;
     a.qrot = ws.qrot; a.qf = ws.qf; a.tail_k = tail_k; a.tail_v = tail_v; a.codebooks = codebooks;
     a.part_ml = ws.part_ml; a.part_acc = ws.part_acc; a.tail_len = tail_len; a.tail_cap = tail_cap;
-    a.tail_len_dev = nullptr; a.tail_len_add = 0;
+    a.tail_len_dev = nullptr; a.tail_len_add = 0; a.q_raw = nullptr; a.q_dtype = 0;
     a.B = B; a.H = H; a.G = G; a.nsplit = n_splits; a.slot_base = 0; a.nslots = n_splits; a.class_mask = 0x7e; a.scale = scale;
     timing_begin("decode_main", st);
     launch_decode_cuda_core(dc, a, cache_dtype, st);

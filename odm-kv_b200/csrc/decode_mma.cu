@@ -568,13 +568,21 @@ static int decode_attn_mma_impl(const void *q, int q_dtype, const odmkv_chunk *c
     if (workspace_bytes < decode_ws_layout(B, H, G, nslots, &ws, (unsigned char *)workspace)) return ODMKV_ERR_WORKSPACE;
     cudaStream_t st = (cudaStream_t)stream;
     const int BH = B * H;
+    // Without 8-bit codes the exact / tail kernel needs no rotated query: it is forked before the rotation and runs
+    // beside it and the start of the tensor-core kernel.
+    bool has8 = false;
+    for (int i = 0; i < n_chunks; ++i) has8 = has8 || chunks[i].cap[4] > 0;
+    SideStream *ss = side_stream();
+    // (only while its CTAs are few: with many units they would hold up a noticeable part of the tensor-core grid)
+    long long side_tok = tail_len;
+    for (int i = 0; i < n_chunks; ++i) side_tok += ((long long)chunks[i].cap[4] + chunks[i].cap[5]) / ((long long)B * H) + 1;
+    const long long side_ctas = (long long)B * H * ((side_tok + 127) / 128 < 8 ? (side_tok + 127) / 128 : 8);
+    const bool early_side = ss && !has8 && 2 * side_ctas <= num_sms_cached();
+    if (early_side) cudaEventRecord(ss->fork, st);
     timing_begin("decode_rotate", st);
     launch_rotate_q(q, q_dtype, pi_k, ws, BH * G, st);
     timing_end(st);
-    {
-        SideStream *fk = side_stream();
-        if (fk) cudaEventRecord(fk->fork, st);
-    }
+    if (ss && !early_side) cudaEventRecord(ss->fork, st);
     MmaArgs m;
     m.qrot = ws.qrot; m.codebooks = codebooks; m.part_ml = ws.part_ml; m.part_acc = ws.part_acc;
     // grid: one CTA pair per SM, fewer when the cache is short (at least ~32 tiles per CTA) or when the caller's
@@ -612,33 +620,30 @@ static int decode_attn_mma_impl(const void *q, int q_dtype, const odmkv_chunk *c
     a.tail_len_dev = tail_len_dev; a.tail_len_add = tail_len_add;
     a.B = B; a.H = H; a.G = G; a.nsplit = ns_side; a.slot_base = n_splits; a.nslots = nslots;
     a.class_mask = (1 << 4) | (1 << 5) | (1 << 6); a.scale = scale;
-    // The exact / tail kernel only needs the rotated queries, so it runs beside the tensor-core kernel: the two are
-    // forked after the rotation and joined before the merge.  The tensor-core kernel fills every SM's registers, so
-    // whichever of the two is launched second starts when CTAs of the first retire.  For a long tensor-core kernel the
-    // small kernel goes second and slips into its tail; for a short one (small batch, short context) that would put
-    // the small kernel's whole latency behind it, so there the small kernel goes first and only delays a few CTAs.
-    SideStream *ss = side_stream();
-    const bool side_first = ss && total_tiles < 100ll * n_cta;   // under about 20 us of tensor-core kernel
-    cudaStream_t st_main = side_first ? ss->stream : st, st_side = side_first || !ss ? st : ss->stream;
-    if (ss && !side_first) cudaStreamWaitEvent(ss->stream, ss->fork, 0);
-    if (side_first) {
-        timing_begin("decode_side", st_side);
-        launch_decode_cuda_core(dc, a, cache_dtype, st_side);
-        timing_end(st_side);
+    a.q_raw = early_side ? q : nullptr; a.q_dtype = q_dtype;
+    if (early_side) a.class_mask = (1 << 5) | (1 << 6);
+    // The exact / tail kernel runs on a second stream, joined before the merge.  The tensor-core kernel fills every SM's
+    // registers, so the small kernel either starts before it (forked before the rotation, when it does not need the
+    // rotated queries) or slips into its tail as CTAs retire.
+    auto launch_side = [&]() {
         cudaStreamWaitEvent(ss->stream, ss->fork, 0);
-    }
-    timing_begin("decode_main", st_main);
-    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st_main>>>(dc, m);
-    else decode_mma_kernel<2><<<grid, kMmaThreads, kStageBytes, st_main>>>(dc, m);
-    timing_end(st_main);
-    if (!side_first) {
-        timing_begin("decode_side", st_side);
-        launch_decode_cuda_core(dc, a, cache_dtype, st_side);
-        timing_end(st_side);
-    }
-    if (ss) {
+        timing_begin("decode_side", ss->stream);
+        launch_decode_cuda_core(dc, a, cache_dtype, ss->stream);
+        timing_end(ss->stream);
         cudaEventRecord(ss->join, ss->stream);
+    };
+    if (early_side) launch_side();
+    timing_begin("decode_main", st);
+    if (G <= 4) decode_mma_kernel<1><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
+    else decode_mma_kernel<2><<<grid, kMmaThreads, kStageBytes, st>>>(dc, m);
+    timing_end(st);
+    if (ss && !early_side) launch_side();
+    if (ss) {
         cudaStreamWaitEvent(st, ss->join, 0);
+    } else {
+        timing_begin("decode_side", st);
+        launch_decode_cuda_core(dc, a, cache_dtype, st);
+        timing_end(st);
     }
     timing_begin("decode_merge", st);
     launch_decode_merge(ws, pi_v, BH, G, nslots, out, out_dtype, lse, st, n_splits, (int)n_cta);

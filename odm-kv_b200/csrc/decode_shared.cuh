@@ -30,6 +30,8 @@ struct DecodeArgs {
     int tail_len, tail_cap;
     const int32_t *tail_len_dev;   // when set: the tail length is read from device memory (plus tail_len_add), bounded by tail_cap
     int tail_len_add;
+    const void *q_raw;             // when set: the caller's queries (dtype q_dtype), read directly instead of qf / qrot --
+    int q_dtype;                   // for a launch that must not wait for the rotation kernel (no 8-bit codes in it)
     int B, H, G;
     int nsplit;        // CTAs per (b, h) of this launch
     int slot_base;     // first partial slot this launch writes
