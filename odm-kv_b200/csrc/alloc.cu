@@ -611,10 +611,12 @@ __global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, 
         for (int k = 0; k < kMaxL; ++k) lamb[k] = k < cfg.K ? __fmul_rn(lam32, cfg.bits32[k]) : 0.f;
         const int nh = prp->env.nh;
         if (tid < kMaxL) sh_counts[tid] = 0;
-        // ---- band edges by binary search (coarse index in shared memory, then the stride around it)
-        if (nh > 1 && tid < 2 * (nh - 1)) {
-            const int v = tid >> 1;
-            const bool upper = tid & 1;
+        // ---- band edges: one warp per edge; coarse index in shared memory, then the stride around it is narrowed
+        //      by 32 probes at a time (two dependent loads for a stride of 256 instead of eight)
+        if (nh > 1 && (tid >> 5) < 2 * (nh - 1)) {
+            const int w = tid >> 5, lane = tid & 31;
+            const int v = w >> 1;
+            const bool upper = w & 1;
             const float x = upper ? prp->env.hi[v] : prp->env.lo[v];
             int lo = 0, hi = nc;   // first coarse entry that is >= x (lower) or > x (upper)
             while (lo < hi) {
@@ -624,13 +626,31 @@ __global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, 
             }
             int a = lo > 0 ? (lo - 1) * stride : 0, b = lo < nc ? lo * stride : na;
             if (b > na) b = na;
-            while (a < b) {
-                const int mid = (a + b) >> 1;
-                const float kv = __uint_as_float(keys[mid]);
-                const bool go = upper ? (kv <= x) : (kv < x);
-                if (go) a = mid + 1; else b = mid;
+            // the edge (first key that is not "before x") lies in [a, b]; keys are sorted, so the probes answer
+            // true ... true false ... false
+            while (b - a > 32) {
+                const int step = (b - a + 31) >> 5;
+                const int pos = a + lane * step;
+                bool go = false;
+                if (pos < b) {
+                    const float kv = __uint_as_float(keys[pos]);
+                    go = upper ? (kv <= x) : (kv < x);
+                }
+                const int cnt = __popc(__ballot_sync(0xffffffffu, go));
+                if (cnt == 0) { b = a; break; }
+                const int nb = a + cnt * step;
+                a = a + (cnt - 1) * step + 1;
+                if (nb < b) b = nb;
             }
-            sh_edge[tid] = a;
+            {
+                bool go = false;
+                if (a + lane < b) {
+                    const float kv = __uint_as_float(keys[a + lane]);
+                    go = upper ? (kv <= x) : (kv < x);
+                }
+                a += __popc(__ballot_sync(0xffffffffu, go));
+            }
+            if (lane == 0) sh_edge[w] = a;
         }
         __syncthreads();
         // ---- pieces between the bands and the exact ranges inside them
