@@ -595,8 +595,17 @@ __global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, 
     __shared__ int sh_rng[2 * kMaxL + 2];   // exact ranges [start, end)
     __shared__ int sh_nr, sh_phase;
     const int p = blockIdx.x, tid = threadIdx.x;
-    AllocProblem *prp = ws.prob + p;
-    unsigned long long *acc = ws.acc + (size_t)p * kAccLen;
+    // the problem's state and its 16 counters live in shared memory for the whole solve (some 66 dependent steps, each
+    // of which would otherwise wait for several round trips to global memory) and go back at the end
+    __shared__ AllocProblem pr_s;
+    __shared__ unsigned long long acc_s[kAccHead];
+    AllocProblem *const prp_g = ws.prob + p;
+    unsigned long long *const acc_g = ws.acc + (size_t)p * kAccLen;
+    if (tid == 0) pr_s = *prp_g;
+    if (tid < kAccHead) acc_s[tid] = acc_g[tid];
+    __syncthreads();
+    AllocProblem *prp = &pr_s;
+    unsigned long long *acc = acc_s;
     const unsigned *keys = ws.keys_out + (size_t)p * n;
     const int na = prp->n_sorted;
     const int stride = na > kCoarse ? (na + kCoarse - 1) / kCoarse : 1;
@@ -688,6 +697,8 @@ __global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, 
         if (tid == 0) sh_phase = prp->phase;
         __syncthreads();
     }
+    if (tid == 0) *prp_g = pr_s;
+    if (tid < kAccHead) acc_g[tid] = acc_s[tid];
 }
 
 // blocks per problem of a pass: enough to fill the GPU a few times over, never more than one chunk each
