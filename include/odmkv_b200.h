@@ -165,6 +165,9 @@ typedef struct odmkv_chunk {
  *   pi_k, pi_v [128, 128] fp32 row-major (y = pi x);  codebooks [4][256] fp32 ascending
  *   (level index li uses the first 2^bits(li) entries). `chunk` is a HOST struct. */
 size_t odmkv_quantize_workspace_bytes(const int32_t *cap /* host int32[6], slots per class */);
+/* Status of the tensor-core quantise kernel (16-bit caches): 0 when none of its bounded waits has expired on the current
+ * device since the library was loaded, 1 otherwise (the codes of that call are invalid); synchronises the device. */
+int odmkv_quantize_status(void);
 int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
                         const float *pi_v, const float *codebooks, const odmkv_chunk *chunk,
                         const void *plan_workspace, void *workspace, size_t workspace_bytes, void *stream);

@@ -104,6 +104,7 @@ _PROTOTYPES = {
     "odmkv_decode_attn_noalloc": (c_int, [c_void_p, c_int, POINTER(Chunk), c_int, c_int, c_void_p, c_void_p, c_int, c_int,
                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p,
                                           c_int, POINTER(c_float), c_void_p]),
+    "odmkv_quantize_status": (c_int, []),
     "odmkv_window_stats_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "odmkv_window_stats_status_offset": (c_size_t, [c_int, c_int, c_int, c_int]),
     "odmkv_window_stats_last_path": (c_int, []),

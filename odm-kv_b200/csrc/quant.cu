@@ -637,6 +637,400 @@ __global__ void __launch_bounds__(512, 1) quantize_kernel(const QuantArgs a) {
     }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Quantise kernel on the fifth-generation tensor cores (16-bit caches).
+//
+// Same arithmetic and the same emitted bytes as quantize_kernel above, another mapping.  A CTA (256 threads, two per
+// SM) takes whole plan tiles of 128 tokens of one side (keys or values); two threads own a token row, 64 coordinates
+// each, and keep them in registers from the global load to the normalisation:
+//   norm     the ascending fp32 FMA chain of squares runs over the first thread's half, then over the second's
+//            (the partial sum is handed over through shared memory), IEEE square root;
+//   divide   x / (norm + 1e-10) as fp32(fp64(x) * fp64(1 / den)) (see quantize_kernel), split into fp16 high and
+//            low limbs, written straight into tensor memory (tcgen05.st: a thread's row is its tensor-memory lane) as
+//            the A operand;
+//   rotate   y = x Pi^T as three tcgen05 products (high x high, high x low, low x high; M 128, N 128, K 128 in
+//            eight steps each) with the limbs of Pi in shared memory (K-major, 128-byte swizzle), fp32 accumulator in
+//            tensor memory: 24 tensor-core instructions per 128 tokens instead of 3 072 mma.sync plus their
+//            ldmatrix traffic;
+//   decide   the thread reads its 64 accumulator columns (tcgen05.ld), takes the fp16 decision against the midpoints
+//            and packs its half row; coordinates inside the margin of a midpoint are queued;
+//   exact    queued coordinates are recomputed with the fp32 chain and the exact rule (the row is re-read from
+//            global memory, which just delivered it) and patched into the packed row; 8-bit rows, whose every
+//            coordinate is exact work, go to global memory directly;
+//   copy-out packed rows, norms, positions; exact-class rows from the registers that still hold them.
+// The error of the tensor-core rotation against the chain obeys the bound at kTcMarginBits (three limb products,
+// fp32 accumulation of 24 steps), so the margin and with it the emitted codes are the same.
+// ----------------------------------------------------------------------------------------------
+namespace umma {
+
+constexpr int kThreads = 256;
+constexpr int kUQueueCap = 1024;
+constexpr int kPkLd = 80;                        // bytes per packed row in shared memory (64 used by a 4-bit row)
+constexpr int kPiTileBytes = kD * kD * 2;        // one limb of the rotation, fp16
+constexpr unsigned kPolls = 1u << 12;
+constexpr unsigned kSuspendNs = 1000000u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void proxy_fence() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+// K-major, 128-byte swizzle, 1024 bytes between 8-row groups, descriptor version 1
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// fp32 accumulator, fp16 operands, both K-major, N = 128, M = 128
+constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(128 >> 3) << 17) | ((128u >> 4) << 24);
+// D (tensor memory) (+)= A (tensor memory: lane = row, one 32-bit column = two K elements) . B (shared memory)
+__device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d), "r"(a), "l"(bdesc), "r"(kIdesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, unsigned parity) {
+    for (unsigned it = 0; it < kPolls; ++it) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(bar), "r"(parity), "r"(kSuspendNs) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
+        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+        "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+          "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+          "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+          "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int DT>
+__device__ __forceinline__ float2 unpack16(uint32_t w) {
+    if constexpr (DT == kF16) return __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    else return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w));
+}
+
+constexpr size_t kSmemBytes = 2 * (size_t)kPiTileBytes + (size_t)kTile * kPkLd + 4 * 256 * sizeof(float) + kTile * sizeof(float) * 2 +
+                              kTile * sizeof(double) + (2 * kTile + 4 * kNumClasses + 16) * sizeof(int) + (size_t)kUQueueCap * 2 + 1024;
+
+}  // namespace umma
+
+template <int DT>
+__global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const QuantArgs a, unsigned *status) {
+    using namespace umma;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t mma_bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ LevelConst lc[3];
+    unsigned char *Ph = smem_raw;                                  // rotation, fp16 high limbs, [2 blocks][128 rows][128 bytes] swizzled
+    unsigned char *Pl = Ph + kPiTileBytes;                         // low limbs
+    unsigned char *PK = Pl + kPiTileBytes;                         // [128][kPkLd] packed rows
+    float *cb = reinterpret_cast<float *>(PK + kTile * kPkLd);     // [4][256]
+    float *nrm = cb + 4 * 256;                                     // [128]
+    float *part = nrm + kTile;                                     // [128] chain value after the first half
+    double *rinv = reinterpret_cast<double *>(part + kTile);       // [128]
+    int *cls = reinterpret_cast<int *>(rinv + kTile);              // [128]
+    int *slot = cls + kTile;                                       // [128]
+    int *wcnt = slot + kTile;                                      // [4][6]
+    int *tbase = wcnt + 4 * kNumClasses;                           // [8]
+    int *flags = tbase + 8;                                        // [0] any quantised row, [1] queue length
+    uint16_t *queue = reinterpret_cast<uint16_t *>(flags + 8);     // [kUQueueCap]
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row = (warp & 3) * 32 + lane, half = warp >> 2;      // token row of the tile, coordinate half
+    const int B = a.ch.B, H = a.ch.H, T = a.ch.T, BH = B * H;
+    const int side = blockIdx.x & 1;
+    const unsigned char *src = reinterpret_cast<const unsigned char *>(side ? a.V : a.K);
+    const float *pi = side ? a.pi_v : a.pi_k;
+
+    // ---- rotation limbs: element (j, i) of a limb sits in block i / 64 at j * 128 + ((i % 64) / 8 ^ (j % 8)) * 16 + (i % 8) * 2
+    for (int g = tid; g < kD * kD / 8; g += kThreads) {
+        const int j = g >> 4, c = g & 15;                          // row, 16-byte chunk (eight coordinates)
+        const float4 f0 = *reinterpret_cast<const float4 *>(pi + j * kD + 8 * c), f1 = *reinterpret_cast<const float4 *>(pi + j * kD + 8 * c + 4);
+        const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+        uint32_t hw[4], lw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __half2 h = __floats2half2_rn(f[2 * k], f[2 * k + 1]);
+            const float2 bk = __half22float2(h);
+            hw[k] = h2u(h);
+            lw[k] = h2u(__floats2half2_rn(f[2 * k] - bk.x, f[2 * k + 1] - bk.y));
+        }
+        const size_t off = (size_t)(c >> 3) * (kD * 128) + (size_t)j * 128 + (size_t)(((c & 7) ^ (j & 7)) * 16);
+        *reinterpret_cast<uint4 *>(Ph + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+        *reinterpret_cast<uint4 *>(Pl + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+    }
+    for (int g = tid; g < 4 * 256; g += kThreads) cb[g] = a.codebooks[g];
+    if (tid < 3 * 8) {
+        const int li = tid >> 3, j = tid & 7, half_k = 1 << (li + 1);   // K/2 for 2, 3, 4 bits
+        const float *cbl = a.codebooks + li * 256;
+        if (j < 7) {
+            __half m = __ushort_as_half((unsigned short)0x7c00);        // +inf: never exceeded, never near
+            if (j + 1 < half_k) m = __float2half_rn(0.5f * (cbl[half_k + j] + cbl[half_k + j + 1]));
+            lc[li].mid[j] = h2u(__half2half2(m));
+        } else {
+            lc[li].base = h2u(__half2half2(__float2half_rn(512.0f + (float)half_k - 0.5f)));
+        }
+    }
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(smem_u32(&mma_bar)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(&tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    proxy_fence();            // the limbs were written by ordinary stores and are read by the tensor cores
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t t_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t t_ah = t_lane + half * 32, t_al = t_lane + 64 + half * 32, t_d = t_lane + 128 + half * 64;
+
+    const long long n_work = (long long)BH * a.ntiles;
+    const long long w_step = gridDim.x >> 1;
+    unsigned n_mma = 0;          // products committed so far (parity of the barrier)
+    bool dead = false;
+    for (long long w = blockIdx.x >> 1; w < n_work; w += w_step) {
+        const int bh = (int)(w / a.ntiles), tile = (int)(w % a.ntiles);
+        const int t0 = tile * kTile;
+        const bool live = t0 + row < T;
+        // ---- this thread's 64 coordinates, kept as 32 packed words
+        uint32_t raw[32];
+        {
+            const uint4 *rp = reinterpret_cast<const uint4 *>(src + (((size_t)bh * T + t0 + row) * kD + 64 * half) * 2);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const uint4 v = live ? __ldg(rp + u) : make_uint4(0u, 0u, 0u, 0u);
+                raw[4 * u] = v.x; raw[4 * u + 1] = v.y; raw[4 * u + 2] = v.z; raw[4 * u + 3] = v.w;
+            }
+        }
+        if (tid == 0) { flags[0] = 0; flags[1] = 0; }
+        // ---- classes and slots of the plan tile (the slot of a token counts the tokens before it)
+        int c = -1, rank = 0;
+        if (tid < kTile) {
+            if (t0 + tid < T) c = class_of_bits(a.bits[(size_t)bh * T + t0 + tid]);
+#pragma unroll
+            for (int cc = 0; cc < kNumClasses; ++cc) {
+                unsigned m = __ballot_sync(0xffffffffu, c == cc);
+                if (c == cc) rank = __popc(m & ((1u << lane) - 1u));
+                if (lane == 0) wcnt[warp * kNumClasses + cc] = __popc(m);
+            }
+            if (tid < kNumClasses) tbase[tid] = a.ch.seg_start[tid * BH + bh] + a.tile_base[((size_t)bh * a.ntiles + tile) * kNumClasses + tid];
+        }
+        // ---- norm chain, first half of every row
+        float acc = 0.0f;
+        if (half == 0) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                const float2 f = unpack16<DT>(raw[k]);
+                acc = fmaf(f.x, f.x, acc);
+                acc = fmaf(f.y, f.y, acc);
+            }
+            part[row] = acc;
+        }
+        __syncthreads();
+        if (tid < kTile) {
+            int s = -1;
+            if (c >= 0) {
+                s = tbase[c] + rank;
+                for (int ww = 0; ww < warp; ++ww) s += wcnt[ww * kNumClasses + c];
+                if (c >= 1 && c <= 4) flags[0] = 1;
+            }
+            cls[tid] = c;
+            slot[tid] = s;
+        }
+        if (half == 1) {
+            acc = part[row];
+#pragma unroll
+            for (int k = 0; k < 32; ++k) {
+                const float2 f = unpack16<DT>(raw[k]);
+                acc = fmaf(f.x, f.x, acc);
+                acc = fmaf(f.y, f.y, acc);
+            }
+            const float nr = __fsqrt_rn(acc);
+            nrm[row] = nr;
+            rinv[row] = 1.0 / (double)__fadd_rn(nr, 1e-10f);
+        }
+        __syncthreads();
+        const bool any_q = flags[0] != 0;
+        const int cc = cls[row];
+        if (any_q) {
+            // ---- normalise, split into limbs, A operand into tensor memory
+            {
+                const double ri = rinv[row];
+                uint32_t hi[32], lo[32];
+#pragma unroll
+                for (int k = 0; k < 32; ++k) {
+                    const float2 f = unpack16<DT>(raw[k]);
+                    const float x0 = __double2float_rn(__dmul_rn((double)f.x, ri)), x1 = __double2float_rn(__dmul_rn((double)f.y, ri));
+                    const __half2 h = __floats2half2_rn(x0, x1);
+                    const float2 bk = __half22float2(h);
+                    hi[k] = h2u(h);
+                    lo[k] = h2u(__floats2half2_rn(x0 - bk.x, x1 - bk.y));
+                }
+                tmem_st32(t_ah, hi);
+                tmem_st32(t_al, lo);
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+            }
+            tc_fence_before();
+            __syncthreads();
+            if (warp == 0 && !dead) {
+                tc_fence_after();
+                uint32_t elected;
+                asm volatile("{\n.reg .pred P1;\nelect.sync _|P1, 0xffffffff;\nselp.u32 %0, 1, 0, P1;\n}\n" : "=r"(elected));
+                if (elected) {
+                    const uint32_t d = tmem + 128, ah = tmem, al = tmem + 64;
+                    const uint32_t ph = smem_u32(Ph), pl = smem_u32(Pl);
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const uint32_t bo = (ks >> 2) * (kD * 128) + (ks & 3) * 32;
+                        mma_ts(d, al + ks * 8, smem_desc(ph + bo), ks ? 1u : 0u);
+                        mma_ts(d, ah + ks * 8, smem_desc(pl + bo), 1u);
+                        mma_ts(d, ah + ks * 8, smem_desc(ph + bo), 1u);
+                    }
+                    mma_commit(smem_u32(&mma_bar));
+                }
+                __syncwarp();
+            }
+            if (!dead && !mbar_wait(smem_u32(&mma_bar), n_mma & 1)) {
+                dead = true;
+                atomicExch(status, 1u);
+            }
+            n_mma += 1;
+            tc_fence_after();
+            // ---- fp16 decision and packing of this thread's 64 coordinates (eight groups of eight).  The
+            //      tensor-memory loads are warp-wide instructions: every thread takes them, whatever its row's class.
+            const bool quant_row = cc >= 1 && cc <= 3;
+            const LevelConst &L = lc[quant_row ? cc - 1 : 0];
+            uint32_t mid[7];
+#pragma unroll
+            for (int j = 0; j < 7; ++j) mid[j] = L.mid[j];
+            const uint32_t base = L.base;
+            const int b = quant_row ? cc + 1 : 2;              // bits per code
+            unsigned char *dst = PK + row * kPkLd + half * 8 * b;
+#pragma unroll 1
+            for (int cbk = 0; cbk < 2; ++cbk) {
+                uint32_t v[32];
+                tmem_ld32(t_d + cbk * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (quant_row) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {              // eight coordinates -> b bytes
+                        uint32_t word = 0, bad = 0;
+#pragma unroll
+                        for (int nb = 0; nb < 4; ++nb) {
+                            const uint32_t y2 = h2u(__floats2half2_rn(__uint_as_float(v[8 * q + 2 * nb]), __uint_as_float(v[8 * q + 2 * nb + 1])));
+                            uint32_t ok;
+                            const uint32_t cf = cc == 3 ? decide_pair<7>(y2, mid, base, ok) : decide_pair<3>(y2, mid, base, ok);
+                            const uint32_t field = ((cf >> 1) & 15u) | (((cf >> 17) & 15u) << b);
+                            word |= field << (2 * b * nb);
+                            if ((ok & 0xffffu) != 0x3c00u) bad |= 1u << (2 * nb);
+                            if ((ok >> 16) != 0x3c00u) bad |= 2u << (2 * nb);
+                        }
+                        unsigned char *dq = dst + (cbk * 4 + q) * b;
+                        if (b == 2) *reinterpret_cast<uint16_t *>(dq) = (uint16_t)word;
+                        else if (b == 4) *reinterpret_cast<uint32_t *>(dq) = word;
+                        else { dq[0] = (unsigned char)word; dq[1] = (unsigned char)(word >> 8); dq[2] = (unsigned char)(word >> 16); }
+                        while (bad) {
+                            const int c8 = __ffs(bad) - 1;
+                            bad &= bad - 1;
+                            const int qi = atomicAdd(&flags[1], 1);
+                            if (qi < kUQueueCap) queue[qi] = (uint16_t)((row << 7) | (64 * half + 32 * cbk + 8 * q + c8));
+                        }
+                    }
+                }
+            }
+            if (cc == 4) {   // 8 bits: the centroid spacing is within the margin, every coordinate is exact work
+                for (int c8 = 0; c8 < 64; ++c8) {
+                    const int qi = atomicAdd(&flags[1], 1);
+                    if (qi < kUQueueCap) queue[qi] = (uint16_t)((row << 7) | (64 * half + c8));
+                }
+            }
+            tc_fence_before();
+            __syncthreads();
+            // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain over the re-read row
+            const int qn = flags[1];
+            const bool redo_all = qn > kUQueueCap;   // queue overflow: every coordinate of the tile is exact work
+            const int n_fix = redo_all ? kTile * kD : qn;
+            for (int e = tid; e < n_fix; e += kThreads) {
+                const int r = redo_all ? (e >> 7) : (queue[e] >> 7), col = redo_all ? (e & 127) : (queue[e] & 127);
+                const int li = cls[r] - 1;
+                if (li < 0 || li > 3) continue;
+                const uint4 *xr = reinterpret_cast<const uint4 *>(src + ((size_t)bh * T + t0 + r) * kD * 2);
+                const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);
+                const double ri = rinv[r];
+                float y = 0.0f;
+#pragma unroll 4
+                for (int i = 0; i < kD / 8; ++i) {
+                    const uint4 xv = __ldg(xr + i);
+                    const float4 p0 = __ldg(pr + 2 * i), p1 = __ldg(pr + 2 * i + 1);
+                    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                    const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float2 f = unpack16<DT>(xw[k]);
+                        y = fmaf(__double2float_rn(__dmul_rn((double)f.x, ri)), pp[2 * k], y);
+                        y = fmaf(__double2float_rn(__dmul_rn((double)f.y, ri)), pp[2 * k + 1], y);
+                    }
+                }
+                const int code = nearest_centroid(y, cb + li * 256, 1 << bits_of_qlevel(li));
+                if (li == 3) {
+                    uint8_t *rows8 = side ? a.ch.v_codes[3] : a.ch.k_codes[3];
+                    rows8[(size_t)slot[r] * 128 + col] = (uint8_t)code;
+                } else {
+                    patch_code(reinterpret_cast<uint32_t *>(PK + r * kPkLd), qbits(li), col, (uint32_t)code);
+                }
+            }
+            __syncthreads();
+        }
+        // ---- copy-out: this thread's half row
+        {
+            const int s = slot[row];
+            const int t_abs = a.ch.t_offset + t0 + row;
+            if (cc >= 1 && cc <= 3) {
+                const int li = cc - 1, nw = 2 * qbits(li);       // words per half row
+                uint8_t *rows = side ? a.v_scratch[li] : a.k_scratch[li];
+                uint32_t *dst = reinterpret_cast<uint32_t *>(rows + (size_t)s * 16 * qbits(li)) + half * nw;
+                const uint32_t *srcw = reinterpret_cast<const uint32_t *>(PK + row * kPkLd) + half * nw;
+                for (int k = 0; k < nw; ++k) dst[k] = srcw[k];
+            }
+            if (cc >= 1 && cc <= 4 && half == 0) {
+                const int li = cc - 1;
+                (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[row];
+                if (side == 0) a.ch.pos[li][s] = t_abs;
+            } else if (cc == 5) {
+                uint4 *drow = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + ((size_t)s * kD + 64 * half) * 2);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) drow[u] = make_uint4(raw[4 * u], raw[4 * u + 1], raw[4 * u + 2], raw[4 * u + 3]);
+                if (half == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
+            } else if (cc == 0 && side == 0 && half == 0) {
+                a.ch.evicted_pos[s] = t_abs;
+            }
+        }
+        __syncthreads();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(256u) : "memory");
+}
+
 // zero the padding slots between a segment's last token and the next 16-slot boundary
 template <int DT>
 __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *k_scratch0, uint8_t *k_scratch1, uint8_t *k_scratch2,
@@ -1005,6 +1399,20 @@ int odmkv_pack_plan(const int32_t *bits, int B, int H, int T, int32_t *seg_start
     return launch_status();
 }
 
+// status word of the tcgen05 quantise kernel: set to 1 when a bounded wait on the tensor cores expired
+__device__ unsigned g_quant_status;
+static unsigned *quant_status_ptr() {
+    static unsigned *ptrs[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_quant_status) != cudaSuccess) return nullptr;
+        ptrs[dev] = reinterpret_cast<unsigned *>(p);
+    }
+    return ptrs[dev];
+}
+
 static int check_chunk(const odmkv_chunk *ch) {
     if (!ch || !ch->seg_start || !ch->seg_count) return ODMKV_ERR_ARG;
     if (ch->B <= 0 || ch->H <= 0 || ch->T < 0 || (long long)ch->B * ch->H > 65535) return ODMKV_ERR_SHAPE;
@@ -1021,6 +1429,14 @@ size_t odmkv_quantize_workspace_bytes(const int32_t *cap) {
     size_t n = 0;
     for (int li = 0; li < 3; ++li) n += 2 * (((size_t)(cap[li + 1] > 0 ? cap[li + 1] : 0) * 16 * qbits(li) + 255) / 256 * 256);
     return n + 256;
+}
+
+// 0 when no tensor-core wait of odmkv_quantize_pack has expired on the current device since the library was loaded
+// (synchronises the device); 1 otherwise (the packed codes of that call are invalid); negative on a CUDA error
+int odmkv_quantize_status(void) {
+    unsigned v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_quant_status, sizeof(v)) != cudaSuccess) return -1;
+    return v != 0 ? 1 : 0;
 }
 
 int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *bits, const float *pi_k,
@@ -1063,7 +1479,20 @@ int odmkv_quantize_pack(const void *K, const void *V, int dtype, const int32_t *
     timing_begin("quantize", st);                                                                            \
     quantize_kernel<DT><<<grid, 512, kQuantKernelSmem, st>>>(a);                                                   \
     timing_end(st);
-    if (dtype == kF16) { ODMKV_LAUNCH_Q(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_Q(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
+    // 16-bit caches take the tcgen05 kernel (whole plan tiles, two CTAs per SM, even CTAs keys / odd CTAs values)
+    const long long n_tiles_side = (long long)BH * a.ntiles;
+    const int grid_u = 2 * (int)(n_tiles_side < num_sms() ? n_tiles_side : num_sms());
+    unsigned *qstatus = quant_status_ptr();
+#define ODMKV_LAUNCH_QU(DT)                                                                                  \
+    if (!qstatus) return ODMKV_ERR_UNSUPPORTED;                                                              \
+    e = cudaFuncSetAttribute(quantize_umma_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)umma::kSmemBytes); \
+    if (e != cudaSuccess) return (int)e;                                                                     \
+    fill_padding_kernel<DT><<<pad_grid, 128, 0, st>>>(*chunk, a.k_scratch[0], a.k_scratch[1], a.k_scratch[2], a.v_scratch[0], a.v_scratch[1], a.v_scratch[2]);  \
+    timing_begin("quantize", st);                                                                            \
+    quantize_umma_kernel<DT><<<grid_u, umma::kThreads, umma::kSmemBytes, st>>>(a, qstatus);                    \
+    timing_end(st);
+    if (dtype == kF16) { ODMKV_LAUNCH_QU(kF16) } else if (dtype == kBF16) { ODMKV_LAUNCH_QU(kBF16) } else { ODMKV_LAUNCH_Q(kF32) }
+#undef ODMKV_LAUNCH_QU
 #undef ODMKV_LAUNCH_Q
     // 2/3/4-bit banks: linear scratch -> tile layout
     for (int li = 0; li < 3; ++li) {
