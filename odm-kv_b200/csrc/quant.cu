@@ -977,7 +977,7 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
                 const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);
                 const double ri = rinv[r];
                 float y = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
                 for (int i = 0; i < kD / 8; ++i) {
                     const uint4 xv = __ldg(xr + i);
                     const float4 p0 = __ldg(pr + 2 * i), p1 = __ldg(pr + 2 * i + 1);
