@@ -733,11 +733,11 @@ constexpr size_t kSmemBytes = 2 * (size_t)kPiTileBytes + (size_t)kTile * kPkLd +
 template <int DT>
 __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const QuantArgs a, unsigned *status) {
     using namespace umma;
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    extern __shared__ __align__(1024) unsigned char smem_umma[];
     __shared__ __align__(8) uint64_t mma_bar;
     __shared__ uint32_t tmem_slot;
     __shared__ LevelConst lc[3];
-    unsigned char *Ph = smem_raw;                                  // rotation, fp16 high limbs, [2 blocks][128 rows][128 bytes] swizzled
+    unsigned char *Ph = smem_umma;                                  // rotation, fp16 high limbs, [2 blocks][128 rows][128 bytes] swizzled
     unsigned char *Pl = Ph + kPiTileBytes;                         // low limbs
     unsigned char *PK = Pl + kPiTileBytes;                         // [128][kPkLd] packed rows
     float *cb = reinterpret_cast<float *>(PK + kTile * kPkLd);     // [4][256]
