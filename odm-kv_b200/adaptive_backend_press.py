@@ -224,6 +224,8 @@ class TurboQuantPerTokenBackendPress:
         status = getattr(self.scorer, "last_status", None)
         if status is not None and int(status.item()) != 0:   # already synchronised by the read-back above
             raise ops._lib.OdmkvError("the scorer reported an expired bounded wait: the scores of this layer are invalid")
+        if bits.is_cuda and ops.quantize_status() != 0:      # the layers packed so far (the device is idle here anyway)
+            raise ops._lib.OdmkvError("the quantise kernel reported an expired bounded wait: packed codes are invalid")
         for row_idx in range(B * H_kv):
             h = row_idx % H_kv
             row = counts[row_idx]
@@ -530,8 +532,12 @@ class TurboQuantPerTokenBackendPress:
         finally:
             for h in hooks:
                 h.remove()
+            used = bool(self._states)
             # the eviction mask and packed state stay on the modules: they must keep acting during decode
             # steps issued outside the context manager; the next fresh prefill clears them.
             self._hooked_layer_indices, self._last_hooked_layer_idx, self._layer_modules = [], None, {}
             self._reset_prefill_state()
             self._states, self._buffer_counts, self._buffer_start_seqs = {}, {}, {}
+        # a normal exit: the packing of the last layers has not been checked yet (this synchronises once)
+        if used and torch.cuda.is_available() and ops.quantize_status() != 0:
+            raise ops._lib.OdmkvError("the quantise kernel reported an expired bounded wait: packed codes are invalid")

@@ -127,6 +127,15 @@ def window_attn_stats(Q: torch.Tensor, K: torch.Tensor, scale: Optional[float] =
     return tuple(outs)
 
 
+def quantize_status() -> int:
+    """0 while no bounded wait of the tensor-core quantise kernel has expired on the current device since the library
+    was loaded, 1 afterwards (the codes of that call are invalid).  Synchronises the device."""
+    rc = int(lib().odmkv_quantize_status())
+    if rc < 0:
+        raise OdmkvError("odmkv_quantize_status: the status word could not be read")
+    return rc
+
+
 # ---------------------------------------------------------------------------------------------
 # allocator
 # ---------------------------------------------------------------------------------------------
