@@ -807,20 +807,23 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
     const long long w_step = gridDim.x >> 1;
     unsigned n_mma = 0;          // products committed so far (parity of the barrier)
     bool dead = false;
+    // this thread's 64 coordinates of the current tile, kept as 32 packed words; the next tile's are fetched as soon as
+    // the current ones have been normalised, so that their latency runs under the decision and the recomputation
+    uint32_t raw[32];
+    auto load_raw = [&](long long w2) {
+        const int bh2 = (int)(w2 / a.ntiles), tl2 = (int)(w2 % a.ntiles);
+        const bool live2 = w2 < n_work && tl2 * kTile + row < T;
+        const uint4 *rp = reinterpret_cast<const uint4 *>(src + (((size_t)bh2 * T + (size_t)tl2 * kTile + row) * kD + 64 * half) * 2);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const uint4 v = live2 ? __ldg(rp + u) : make_uint4(0u, 0u, 0u, 0u);
+            raw[4 * u] = v.x; raw[4 * u + 1] = v.y; raw[4 * u + 2] = v.z; raw[4 * u + 3] = v.w;
+        }
+    };
+    load_raw(blockIdx.x >> 1);
     for (long long w = blockIdx.x >> 1; w < n_work; w += w_step) {
         const int bh = (int)(w / a.ntiles), tile = (int)(w % a.ntiles);
         const int t0 = tile * kTile;
-        const bool live = t0 + row < T;
-        // ---- this thread's 64 coordinates, kept as 32 packed words
-        uint32_t raw[32];
-        {
-            const uint4 *rp = reinterpret_cast<const uint4 *>(src + (((size_t)bh * T + t0 + row) * kD + 64 * half) * 2);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const uint4 v = live ? __ldg(rp + u) : make_uint4(0u, 0u, 0u, 0u);
-                raw[4 * u] = v.x; raw[4 * u + 1] = v.y; raw[4 * u + 2] = v.z; raw[4 * u + 3] = v.w;
-            }
-        }
         if (tid == 0) { flags[0] = 0; flags[1] = 0; }
         // ---- classes and slots of the plan tile (the slot of a token counts the tokens before it)
         int c = -1, rank = 0;
@@ -871,6 +874,12 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
         __syncthreads();
         const bool any_q = flags[0] != 0;
         const int cc = cls[row];
+        if (cc == 5) {   // exact class: the row goes out as it came in
+            const int s = slot[row];
+            uint4 *drow = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + ((size_t)s * kD + 64 * half) * 2);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) drow[u] = make_uint4(raw[4 * u], raw[4 * u + 1], raw[4 * u + 2], raw[4 * u + 3]);
+        }
         if (any_q) {
             // ---- normalise, split into limbs, A operand into tensor memory
             {
@@ -889,6 +898,7 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
                 tmem_st32(t_al, lo);
                 asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
             }
+            load_raw(w + w_step);
             tc_fence_before();
             __syncthreads();
             if (warp == 0 && !dead) {
@@ -999,6 +1009,8 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
                 }
             }
             __syncthreads();
+        } else {
+            load_raw(w + w_step);
         }
         // ---- copy-out: this thread's half row
         {
@@ -1016,9 +1028,6 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
                 (side ? a.ch.v_norm[li] : a.ch.k_norm[li])[s] = nrm[row];
                 if (side == 0) a.ch.pos[li][s] = t_abs;
             } else if (cc == 5) {
-                uint4 *drow = reinterpret_cast<uint4 *>(reinterpret_cast<unsigned char *>(side ? a.ch.exact_v : a.ch.exact_k) + ((size_t)s * kD + 64 * half) * 2);
-#pragma unroll
-                for (int u = 0; u < 8; ++u) drow[u] = make_uint4(raw[4 * u], raw[4 * u + 1], raw[4 * u + 2], raw[4 * u + 3]);
                 if (half == 0 && side == 0) a.ch.exact_pos[s] = t_abs;
             } else if (cc == 0 && side == 0 && half == 0) {
                 a.ch.evicted_pos[s] = t_abs;
