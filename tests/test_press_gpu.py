@@ -279,3 +279,61 @@ def test_graphed_decode_steps_match_eager_steps(pkg, cuda):
     for s, (a, b) in enumerate(zip(lg, le)):
         err = (a - b).abs().max() / b.abs().max()
         assert err < 2e-2, (s, err)     # bf16 model: different split counts of the tail kernel reorder a few sums
+
+
+@torch.no_grad()
+def test_padded_batch_takes_the_masked_route(pkg, cuda):
+    """A batch with left padding: the attention mask hides keys, the packed decode kernels take no mask, so the
+    wrapper must keep the reference's route (fake keys over the evicted positions, stock attention with the mask,
+    kvquant/attention_patch.py:13-55) -- for the dense-in-sync cache and for the packed-only cache, which
+    dequantises on that route.  Without the mask the same step goes through the packed kernels and differs on the
+    padded sample only."""
+    from transformers import DynamicCache
+    model = tiny_llama(cuda, dtype=torch.bfloat16)
+    B, T, pad = 2, 300, 100
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, 512, (B, T), generator=g).to(cuda)
+    nxt = torch.randint(0, 512, (B, 1), generator=g).to(cuda)
+    mask = torch.ones(B, T, dtype=torch.long, device=cuda)
+    mask[1, :pad] = 0
+    mask1 = torch.cat([mask, torch.ones(B, 1, dtype=torch.long, device=cuda)], dim=1)
+
+    def run(packed, decode_mask, packed_kernels):
+        press = make_press(pkg)
+        press.packed_cache = packed
+        cache = DynamicCache()
+        calls = {"n": 0}
+        with press(model):
+            model.model(input_ids=ids, attention_mask=mask, past_key_values=cache)
+            for layer in model.model.layers:
+                layer.self_attn._odmkv_decode = packed_kernels
+            real = {}
+            for i, st in press._states.items():      # count the packed decode calls of this step
+                real[i] = st.decode_attention
+
+                def counted(*a, _f=real[i], **k):
+                    calls["n"] += 1
+                    return _f(*a, **k)
+
+                st.decode_attention = counted
+            logits = model(input_ids=nxt, attention_mask=decode_mask, past_key_values=cache).logits.float()
+            for i, st in press._states.items():
+                st.decode_attention = real[i]
+            for layer in model.model.layers:
+                layer.self_attn._odmkv_decode = True
+        return logits, calls["n"]
+
+    ref, n_ref = run(False, mask1, False)            # the reference's route, packed kernels switched off
+    got, n_got = run(False, mask1, True)             # packed kernels allowed: the mask must keep them out
+    assert n_ref == 0 and n_got == 0
+    assert torch.equal(got, ref)
+    pk, n_pk = run(True, mask1, True)                # packed-only cache: dequantise, fake keys, stock attention
+    assert n_pk == 0
+    err = (pk - ref).abs().max() / ref.abs().max()
+    assert err < 5e-2, err
+    open_, n_open = run(False, None, True)           # no mask at the decode step: the packed kernels answer
+    assert n_open == len(model.model.layers)
+    e0 = (open_[0] - ref[0]).abs().max() / ref[0].abs().max()
+    e1 = (open_[1] - ref[1]).abs().max() / ref[1].abs().max()
+    assert e0 < 5e-2, e0                             # the unpadded sample sees the same keys either way
+    assert e1 > 2 * e0, (e0, e1)                     # the padded sample attends 100 more keys without the mask
