@@ -975,37 +975,68 @@ __global__ void __launch_bounds__(umma::kThreads, 2) quantize_umma_kernel(const 
             }
             tc_fence_before();
             __syncthreads();
-            // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain over the re-read row
+            // ---- exact recomputation of the queued coordinates: ascending fp32 FMA chain over the re-read row.  Four
+            //      lanes share a coordinate: each fetches and normalises a quarter of the row (the conversions are the
+            //      bulk of the work and run side by side), then the chain walks through the quarters in ascending
+            //      order, its running value handed from lane to lane -- the same sequence of fused multiply-adds as
+            //      one thread would execute.
             const int qn = flags[1];
             const bool redo_all = qn > kUQueueCap;   // queue overflow: every coordinate of the tile is exact work
             const int n_fix = redo_all ? kTile * kD : qn;
-            for (int e = tid; e < n_fix; e += kThreads) {
-                const int r = redo_all ? (e >> 7) : (queue[e] >> 7), col = redo_all ? (e & 127) : (queue[e] & 127);
-                const int li = cls[r] - 1;
-                if (li < 0 || li > 3) continue;
-                const uint4 *xr = reinterpret_cast<const uint4 *>(src + ((size_t)bh * T + t0 + r) * kD * 2);
-                const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD);
-                const double ri = rinv[r];
-                float y = 0.0f;
-#pragma unroll 8
-                for (int i = 0; i < kD / 8; ++i) {
-                    const uint4 xv = __ldg(xr + i);
-                    const float4 p0 = __ldg(pr + 2 * i), p1 = __ldg(pr + 2 * i + 1);
-                    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-                    const float pp[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float2 f = unpack16<DT>(xw[k]);
-                        y = fmaf(__double2float_rn(__dmul_rn((double)f.x, ri)), pp[2 * k], y);
-                        y = fmaf(__double2float_rn(__dmul_rn((double)f.y, ri)), pp[2 * k + 1], y);
-                    }
+            const int sub = lane & 3;
+            for (int e0 = 0; e0 < n_fix; e0 += kThreads / 4) {     // same trip count for every thread of the CTA
+                const int e = e0 + (tid >> 2);
+                int r = 0, col = 0, li = -1;
+                if (e < n_fix) {
+                    r = redo_all ? (e >> 7) : (queue[e] >> 7);
+                    col = redo_all ? (e & 127) : (queue[e] & 127);
+                    li = cls[r] - 1;
                 }
-                const int code = nearest_centroid(y, cb + li * 256, 1 << bits_of_qlevel(li));
-                if (li == 3) {
-                    uint8_t *rows8 = side ? a.ch.v_codes[3] : a.ch.k_codes[3];
-                    rows8[(size_t)slot[r] * 128 + col] = (uint8_t)code;
+                const bool work = li >= 0 && li <= 3;
+                float xn[32], pv[32];
+                if (work) {
+                    const uint4 *xr = reinterpret_cast<const uint4 *>(src + (((size_t)bh * T + t0 + r) * kD + 32 * sub) * 2);
+                    const float4 *pr = reinterpret_cast<const float4 *>(pi + col * kD + 32 * sub);
+                    uint4 xv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) xv[u] = __ldg(xr + u);
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float4 p = __ldg(pr + u);
+                        pv[4 * u] = p.x; pv[4 * u + 1] = p.y; pv[4 * u + 2] = p.z; pv[4 * u + 3] = p.w;
+                    }
+                    const double ri = rinv[r];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t xw[4] = {xv[u].x, xv[u].y, xv[u].z, xv[u].w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float2 f = unpack16<DT>(xw[k]);
+                            xn[8 * u + 2 * k] = __double2float_rn(__dmul_rn((double)f.x, ri));
+                            xn[8 * u + 2 * k + 1] = __double2float_rn(__dmul_rn((double)f.y, ri));
+                        }
+                    }
                 } else {
-                    patch_code(reinterpret_cast<uint32_t *>(PK + r * kPkLd), qbits(li), col, (uint32_t)code);
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) { xn[k] = 0.0f; pv[k] = 0.0f; }
+                }
+                float y = 0.0f;
+#pragma unroll
+                for (int st = 0; st < 4; ++st) {
+                    if (sub == st) {
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) y = fmaf(xn[k], pv[k], y);
+                    }
+                    y = __shfl_sync(0xffffffffu, y, (lane & ~3) | st);   // the next quarter continues from here
+                }
+                if (work && sub == 0) {
+                    const int code = nearest_centroid(y, cb + li * 256, 1 << bits_of_qlevel(li));
+                    if (li == 3) {
+                        uint8_t *rows8 = side ? a.ch.v_codes[3] : a.ch.k_codes[3];
+                        rows8[(size_t)slot[r] * 128 + col] = (uint8_t)code;
+                    } else {
+                        patch_code(reinterpret_cast<uint32_t *>(PK + r * kPkLd), qbits(li), col, (uint32_t)code);
+                    }
                 }
             }
             __syncthreads();
