@@ -665,7 +665,8 @@ namespace umma {
 
 constexpr int kThreads = 256;
 constexpr int kUQueueCap = 1024;
-constexpr int kPkLd = 80;                        // bytes per packed row in shared memory (64 used by a 4-bit row)
+constexpr int kPkLd = 84;                        // bytes per packed row in shared memory (64 used by a 4-bit row); 21 words:
+                                                 // the 32 rows of a warp fall into 32 different banks
 constexpr int kPiTileBytes = kD * kD * 2;        // one limb of the rotation, fp16
 constexpr unsigned kPolls = 1u << 12;
 constexpr unsigned kSuspendNs = 1000000u;
