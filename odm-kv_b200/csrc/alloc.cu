@@ -235,8 +235,186 @@ __device__ inline void setup_step(AllocProblem &pr, const AllocCfg &cfg) {
     pr.phase = 5;
 }
 
-// State update of one problem after a pass; called by a whole block (blockDim.x == kAllocThreads).
-__device__ void update_problem(AllocProblem *prp, unsigned long long *acc, const AllocCfg &cfg) {
+// level of one score by the reference's three-operation fp32 cost
+__device__ inline int exact_level(float s, const AllocCfg &cfg, const float *lamb) {
+    float best = __fadd_rn(__fmul_rn(s, cfg.eps32[0]), lamb[0]);
+    int arg = 0;
+#pragma unroll
+    for (int k = 1; k < kMaxL; ++k) {
+        if (k < cfg.K) {
+            const float c = __fadd_rn(__fmul_rn(s, cfg.eps32[k]), lamb[k]);
+            if (c < best) { best = c; arg = k; }
+        }
+    }
+    return arg;
+}
+
+// First index of the ascending keys[0, na) whose score is >= x (upper = false) or > x (upper = true).  Called by a
+// whole warp: 32 probes per round, so a million keys take four dependent loads.
+__device__ inline int warp_bound(const unsigned *__restrict__ keys, int na, float x, bool upper, int lane) {
+    int a = 0, b = na;
+    while (b - a > 32) {
+        const int step = (b - a + 31) >> 5;
+        const int pos = a + lane * step;
+        bool go = false;
+        if (pos < b) {
+            const float kv = __uint_as_float(keys[pos]);
+            go = upper ? (kv <= x) : (kv < x);
+        }
+        const int cnt = __popc(__ballot_sync(0xffffffffu, go));   // the probes answer true ... true false ... false
+        if (cnt == 0) { b = a; break; }
+        const int nb = a + cnt * step;
+        a = a + (cnt - 1) * step + 1;
+        if (nb < b) b = nb;
+    }
+    bool go = false;
+    if (a + lane < b) {
+        const float kv = __uint_as_float(keys[a + lane]);
+        go = upper ? (kv <= x) : (kv < x);
+    }
+    return a + __popc(__ballot_sync(0xffffffffu, go));
+}
+
+// Selection of a gap-closure step from the sorted scores (single-device path; blockDim.x == kAllocThreads).
+// The step moves the sel_k candidates of level sel_level with the smallest keys (score, index) -- the largest when
+// the direction is "promote".  The level of a score depends on its value only, and the levels of this step's
+// candidates are still those of the final assignment (earlier steps moved tokens between other levels), so in the
+// ascending order of the scores the candidates are: whole pieces of the cost envelope whose level is sel_level, plus
+// the scores inside the bands around the breakpoints for which the three-operation cost says so.  Walking through
+// these segments gives the score x of the sel_k-th candidate and the number k' of candidates with exactly that score
+// that belong to the selection, which is what two histogram passes over the 32 score bits of the keys find.  When
+// every candidate with score x is selected, the index bits need no passes either: the cut is (x, largest index).
+// On anything unexpected (no valid envelope, a band of more than 65 536 scores, counts that do not add up) the state
+// is left alone and the histogram passes do the selection.
+constexpr int kSelMaxExact = 1 << 16;
+constexpr int kSelSegs = 2 * kMaxL + 2;
+
+__device__ void sorted_select(AllocProblem *prp, const unsigned *__restrict__ keys, const AllocCfg &cfg) {
+    __shared__ Envelope env;
+    __shared__ int sg_a[kSelSegs], sg_b[kSelSegs], sg_level[kSelSegs], sg_cnt[kSelSegs];
+    __shared__ int sh_edge[2 * kMaxL];
+    __shared__ int sh_ns, sh_seg, sh_pos, sh_lb, sh_ub, sh_wsum[kAllocThreads / 32];
+    __shared__ long long sh_rem;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int na = prp->n_sorted, L = prp->sel_level;
+    const bool inv = prp->dir < 0;
+    const long long k = prp->sel_k;
+    const float lam32 = (float)prp->lam;
+    float lamb[kMaxL];
+#pragma unroll
+    for (int j = 0; j < kMaxL; ++j) lamb[j] = j < cfg.K ? __fmul_rn(lam32, cfg.bits32[j]) : 0.f;
+    if (tid == 0) build_envelope(cfg, lamb, env);
+    __syncthreads();
+    const int nh = env.nh;
+    if (nh == 0 || na <= 0) return;
+    for (int e = warp; e < 2 * (nh - 1); e += kAllocThreads / 32) {
+        const bool upper = e & 1;
+        const int r = warp_bound(keys, na, upper ? env.hi[e >> 1] : env.lo[e >> 1], upper, lane);
+        if (lane == 0) sh_edge[e] = r;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int ns = 0, cursor = 0;
+        for (int v = 0; v + 1 < nh; ++v) {
+            const int i_lo = sh_edge[2 * v], i_hi = sh_edge[2 * v + 1];
+            if (i_lo > cursor) {
+                sg_a[ns] = cursor; sg_b[ns] = i_lo; sg_level[ns] = env.level[v];
+                sg_cnt[ns] = env.level[v] == L ? i_lo - cursor : 0;
+                ++ns; cursor = i_lo;
+            }
+            if (i_hi > cursor) { sg_a[ns] = cursor; sg_b[ns] = i_hi; sg_level[ns] = -1; sg_cnt[ns] = 0; ++ns; cursor = i_hi; }
+        }
+        if (na > cursor) {
+            sg_a[ns] = cursor; sg_b[ns] = na; sg_level[ns] = env.level[nh - 1];
+            sg_cnt[ns] = env.level[nh - 1] == L ? na - cursor : 0;
+            ++ns;
+        }
+        sh_ns = ns;
+    }
+    __syncthreads();
+    const int ns = sh_ns;
+    for (int sgi = 0; sgi < ns; ++sgi) {
+        if (sg_level[sgi] >= 0) continue;
+        if (sg_b[sgi] - sg_a[sgi] > kSelMaxExact) return;
+        int c = 0;
+        for (int i = sg_a[sgi] + tid; i < sg_b[sgi]; i += kAllocThreads) c += exact_level(__uint_as_float(keys[i]), cfg, lamb) == L ? 1 : 0;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (lane == 0 && c) atomicAdd(&sg_cnt[sgi], c);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        long long rem = k;
+        int seg = -1;
+        for (int q = 0; q < ns; ++q) {
+            const int sgi = inv ? ns - 1 - q : q;
+            if (rem <= (long long)sg_cnt[sgi]) { seg = sgi; break; }
+            rem -= (long long)sg_cnt[sgi];
+        }
+        sh_seg = seg;
+        sh_rem = rem;
+        sh_pos = -1;
+        if (seg >= 0 && sg_level[seg] >= 0) sh_pos = inv ? sg_b[seg] - (int)rem : sg_a[seg] + (int)rem - 1;
+    }
+    __syncthreads();
+    const int seg = sh_seg;
+    if (seg < 0) return;
+    if (sg_level[seg] < 0) {
+        // the candidate sits inside a band: walk through it in key order, one block-wide step of 256 scores at a time
+        const int a = sg_a[seg], b = sg_b[seg];
+        long long rem = sh_rem;
+        bool found = false;
+        for (int c0 = 0; c0 < b - a; c0 += kAllocThreads) {
+            const int off = c0 + tid;
+            const int i = inv ? b - 1 - off : a + off;
+            const bool hit = off < b - a && exact_level(__uint_as_float(keys[i]), cfg, lamb) == L;
+            const unsigned bal = __ballot_sync(0xffffffffu, hit);
+            if (lane == 0) sh_wsum[warp] = __popc(bal);
+            __syncthreads();
+            int before = 0, total = 0;
+            for (int w2 = 0; w2 < kAllocThreads / 32; ++w2) {
+                if (w2 < warp) before += sh_wsum[w2];
+                total += sh_wsum[w2];
+            }
+            if (rem <= (long long)total) {
+                if (hit && before + __popc(bal & ((1u << lane) - 1u)) + 1 == (int)rem) sh_pos = i;
+                found = true;
+            }
+            __syncthreads();
+            if (found) break;
+            rem -= (long long)total;
+        }
+        if (!found) return;
+    }
+    const int pos = sh_pos;
+    if (pos < 0 || pos >= na) return;
+    const unsigned xb = keys[pos];
+    if (warp < 2) {
+        const int r = warp_bound(keys, na, __uint_as_float(xb), warp == 1, lane);
+        if (lane == 0) { if (warp == 1) sh_ub = r; else sh_lb = r; }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int lb = sh_lb, ub = sh_ub;
+        const long long take = inv ? (long long)(ub - pos) : (long long)(pos - lb + 1);   // of the ub - lb candidates with score x
+        const unsigned long long top = inv ? (unsigned long long)(unsigned)(~xb) : (unsigned long long)xb;
+        if (take >= 1 && take <= (long long)(ub - lb)) {
+            if (take == (long long)(ub - lb)) {
+                prp->sel_prefix = (top << 32) | 0xffffffffull;   // all of them: no cut among equal scores
+                prp->sel_pass = 4;
+                prp->phase = 4;
+            } else {
+                prp->sel_prefix = top;
+                prp->sel_k = take;
+                prp->sel_pass = 2;
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// State update of one problem after a pass; called by a whole block (blockDim.x == kAllocThreads).  With the sorted
+// scores of the problem at hand (`keys`), a gap-closure step that has just been set up is resolved from them.
+__device__ void update_problem(AllocProblem *prp, unsigned long long *acc, const AllocCfg &cfg, const unsigned *keys = nullptr) {
     __shared__ unsigned long long part[kAllocThreads];
     __shared__ int sh_phase;
     const int tid = threadIdx.x;
@@ -332,6 +510,12 @@ __device__ void update_problem(AllocProblem *prp, unsigned long long *acc, const
         if (tid < kAccHead) acc[tid] = 0ull;
     }
     __syncthreads();
+    if (keys != nullptr) {
+        __shared__ int sh_select;
+        if (tid == 0) sh_select = prp->phase == 3 && prp->sel_pass == 0;
+        __syncthreads();
+        if (sh_select) sorted_select(prp, keys, cfg);
+    }
 }
 
 __device__ inline unsigned long long make_key(float s, long long gidx, bool invert) {
@@ -562,7 +746,7 @@ __global__ void __launch_bounds__(kAllocThreads, 3) alloc_pass_kernel(const floa
         if (sh_last) {
             __threadfence();
             if (tid == 0) prp->ticket = 0;
-            update_problem(prp, acc, cfg);
+            update_problem(prp, acc, cfg, cfg.K > 1 ? ws.keys_out + (size_t)p * n : nullptr);   // this form runs after the sort
         }
     }
 }
