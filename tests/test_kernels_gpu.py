@@ -186,6 +186,33 @@ def test_allocate_bits_bit_exact_vs_oracle_heavy_tails(pkg, orc, cuda, golden, n
         assert abs(reports[p]["gap_before"] - info[p].gap_before) < 1e-9
 
 
+@pytest.mark.parametrize("n,target,nvals", [(30000, 2.0, 40), (30000, 3.0, 12), (70000, 5.5, 25), (5000, 2.5, 3)])
+def test_allocate_bits_bit_exact_on_score_ladders(pkg, orc, cuda, golden, n, target, nvals):
+    """Scores drawn from a few distinct values: the bisection ends with one value on a breakpoint of the cost lines
+    (inside the band that is evaluated with the full formula), every level is a handful of long runs of equal scores,
+    and the gap closure cuts inside such a run -- the cases in which the selection from the sorted scores has to walk a
+    band and hand the cut among equal scores to the index passes."""
+    eps = eps_of(golden["kats"])
+    rng = np.random.default_rng(int(n + 100 * target + nvals))
+    P = 3
+    ladder = (10.0 ** rng.uniform(-6, 1, size=nvals)).astype(np.float32)
+    s = np.stack([ladder[rng.integers(0, nvals, size=n)] for _ in range(P)])
+    s[2] = np.sort(s[2])[::-1]                    # descending: the index order of equal scores matters for the cut
+    sink = np.zeros(n, np.uint8)
+    sink[:4] = 1
+    info = [orc.AllocInfo() for _ in range(P)]
+    want = np.stack([orc.optimal_scores_to_bits(s[p], LEVELS, target, eps, sink.astype(bool), eviction_cost=0.5, info=info[p])
+                     for p in range(P)])
+    bits, rep = pkg.ops.allocate_bits(torch.from_numpy(np.ascontiguousarray(s)).to(cuda), torch.from_numpy(sink).to(cuda), LEVELS,
+                                      alloc_eps(eps), target)
+    got = bits.cpu().numpy()
+    reports = pkg.ops.read_reports(rep)
+    for p in range(P):
+        assert np.array_equal(got[p], want[p]), f"problem {p}: {(got[p] != want[p]).sum()} of {n} differ"
+        assert reports[p]["done"] and reports[p]["moved"] == info[p].moved
+        assert reports[p]["ties_lambda"] == info[p].ties_lambda and reports[p]["ties_cut"] == info[p].ties_cut
+
+
 def test_allocate_bits_edge_cases(pkg, orc, cuda, golden):
     eps = eps_of(golden["kats"])
     # nan / inf / negative scores, all-sink mask, constant scores (every cut is a tie), single level
