@@ -96,7 +96,10 @@ size_t odmkv_alloc_workspace_bytes(int P, int n);
  *   sink_mask [n] uint8 or NULL (shared by all problems; nonzero = pinned to sink_bits)
  *   levels    host int[K] ascending candidate widths, eps host float64[K] (eviction cost already
  *             applied to the 0 level, i.e. allocator.py:550-552 done by the caller)
- *   bits      [P, n] int32 out;  reports [P] out (device) */
+ *   bits      [P, n] int32 out;  reports [P] out (device)
+ * With more than one problem the per-problem sorts run on up to eight helper streams of the library, forked from
+ * and joined back into `stream` with events; the first call on a device creates them (host objects only) and must
+ * not be made while `stream` is being captured.  One call at a time per device. */
 int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, int n, const int *levels,
                         const double *eps, int K, double target_avg_bits, int sink_bits, int32_t *bits,
                         odmkv_alloc_report *reports, void *workspace, size_t workspace_bytes, void *stream);

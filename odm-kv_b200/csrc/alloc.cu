@@ -16,6 +16,7 @@
 #include "common.cuh"
 
 #include <cub/device/device_radix_sort.cuh>
+#include <mutex>
 
 namespace odmkv {
 
@@ -26,6 +27,7 @@ constexpr int kAccLen = kAccHead + kHistBins;
 constexpr int kEvalRounds = 74;              // 1 + 8 widenings + 64 halvings + 1 final
 constexpr int kAllocThreads = 256;
 constexpr int kPerThread = 8;
+constexpr int kSortLanes = 8;                // sorts of different problems in flight at once (helper streams)
 
 struct AllocCfg {
     float eps32[kMaxL];
@@ -125,7 +127,7 @@ struct AllocWs {
     uint8_t *chosen;             // [P][n]
     AllocCfg *cfg;               // device copy (for the stepwise entry points)
     unsigned *keys_in, *keys_out;   // [P][n] sanitised scores as ordered keys (sinks = 0xffffffff), unsorted / ascending
-    void *sort_temp;             // scratch of the radix sort
+    void *sort_temp;             // scratch of the radix sort, kSortLanes slices of sort_temp_bytes
     size_t sort_temp_bytes;
     // host-side header kept at the start of the workspace is mirrored in AllocHeader
 };
@@ -144,7 +146,8 @@ inline size_t alloc_ws_layout(int P, int n, AllocWs *ws, unsigned char *base) {
     size_t o_acc = take(sizeof(unsigned long long) * (size_t)P * kAccLen), o_ch = take((size_t)P * n);
     size_t sort_bytes = 0;
     cub::DeviceRadixSort::SortKeys(nullptr, sort_bytes, (const unsigned *)nullptr, (unsigned *)nullptr, n);
-    size_t o_ki = take((size_t)P * n * 4), o_ko = take((size_t)P * n * 4), o_st = take(sort_bytes);
+    sort_bytes = (sort_bytes + 255) / 256 * 256;
+    size_t o_ki = take((size_t)P * n * 4), o_ko = take((size_t)P * n * 4), o_st = take(sort_bytes * kSortLanes);
     (void)o_hdr;
     if (ws && base) {
         ws->keys_in = (unsigned *)(base + o_ki); ws->keys_out = (unsigned *)(base + o_ko);
@@ -951,6 +954,29 @@ static int make_cfg(const int *levels, const double *eps, int K, double target, 
     return ODMKV_OK;
 }
 
+// Helper streams on which the sorts of different problems run side by side (a sort of 1 M keys is five short
+// kernels that leave most of the GPU idle).  Created on the first call on a device (host objects, no device memory);
+// that call must not be made while a stream is being captured.
+struct SortLanes { cudaStream_t stream[kSortLanes]; cudaEvent_t fork, join[kSortLanes]; bool ok; };
+static SortLanes *sort_lanes() {
+    static SortLanes table[64] = {};
+    static bool tried[64] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!tried[dev]) {
+        tried[dev] = true;
+        SortLanes &l = table[dev];
+        bool ok = cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming) == cudaSuccess;
+        for (int j = 0; j < kSortLanes && ok; ++j)
+            ok = cudaStreamCreateWithFlags(&l.stream[j], cudaStreamNonBlocking) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&l.join[j], cudaEventDisableTiming) == cudaSuccess;
+        l.ok = ok;
+    }
+    return table[dev].ok ? &table[dev] : nullptr;
+}
+
 static inline int closure_rounds(int K) { return K > 1 ? 5 * (K - 1) : 0; }
 
 // host-side mirror of what a stepwise caller needs between calls
@@ -1002,9 +1028,26 @@ int odmkv_allocate_bits(const float *scores, const uint8_t *sink_mask, int P, in
         int kb = (n + 256 * 8 - 1) / (256 * 8);
         if (kb > 1024) kb = 1024;
         alloc_keys_kernel<<<dim3(kb, P), 256, 0, st>>>(scores, sink_mask, n, ws);
+        // problem p is sorted on lane p % kSortLanes (its own stream and slice of the scratch); the lanes start after
+        // the keys are written and the caller's stream goes on when all of them are done
+        SortLanes *lanes = P > 1 ? sort_lanes() : nullptr;
+        const int nl = lanes ? (P < kSortLanes ? P : kSortLanes) : 0;
+        if (lanes) {
+            cudaError_t e = cudaEventRecord(lanes->fork, st);
+            for (int j = 0; j < nl && e == cudaSuccess; ++j) e = cudaStreamWaitEvent(lanes->stream[j], lanes->fork, 0);
+            if (e != cudaSuccess) return (int)e;
+        }
         for (int p = 0; p < P; ++p) {
+            const int j = lanes ? p % kSortLanes : 0;
             size_t tb = ws.sort_temp_bytes;
-            cudaError_t e = cub::DeviceRadixSort::SortKeys(ws.sort_temp, tb, ws.keys_in + (size_t)p * n, ws.keys_out + (size_t)p * n, n, 0, 32, st);
+            cudaError_t e = cub::DeviceRadixSort::SortKeys((unsigned char *)ws.sort_temp + (size_t)j * ws.sort_temp_bytes, tb,
+                                                           ws.keys_in + (size_t)p * n, ws.keys_out + (size_t)p * n, n, 0, 32,
+                                                           lanes ? lanes->stream[j] : st);
+            if (e != cudaSuccess) return (int)e;
+        }
+        for (int j = 0; j < nl; ++j) {
+            cudaError_t e = cudaEventRecord(lanes->join[j], lanes->stream[j]);
+            if (e == cudaSuccess) e = cudaStreamWaitEvent(st, lanes->join[j], 0);
             if (e != cudaSuccess) return (int)e;
         }
         alloc_solve_kernel<<<P, kSolveThreads, 0, st>>>(ws, n, cfg);
