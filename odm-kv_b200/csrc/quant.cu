@@ -1112,33 +1112,68 @@ __global__ void fill_padding_kernel(const odmkv_chunk ch, uint8_t *k_scratch0, u
     }
 }
 
+// NB bits (at most 32) at a compile-time bit offset of a little-endian word array held in registers
+template <int NB>
+__device__ __forceinline__ uint32_t extract_bits(const uint32_t *w, int off) {
+    const int wi = off >> 5, sh = off & 31;
+    const uint32_t v = (sh + NB <= 32) ? (w[wi] >> sh) : __funnelshift_r(w[wi], w[wi + 1], sh);
+    return NB == 32 ? v : (v & ((NB == 32 ? 0u : (1u << (NB & 31))) - 1u));
+}
+// OR a field of NB bits into a zero-initialised word array at a compile-time bit offset
+template <int NB>
+__device__ __forceinline__ void insert_bits(uint32_t *out, int off, uint32_t field) {
+    const int wi = off >> 5, sh = off & 31;
+    out[wi] |= field << sh;
+    if (sh + NB > 32) out[wi + 1] |= field >> (32 - sh);
+}
+
 // re-tile the codes of one 2/3/4-bit bank: linear scratch rows -> tensor-core tile layout
-// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes; KEYS selects the field map)
+// (one warp per tile of 16 slots; lane (g, t) assembles its own 8*b bytes; KEYS selects the field map).
+// A lane's source bits are few whole words, so it loads them once and moves the fields between registers:
+//   keys:   the 32 coordinates 32 t .. 32 t + 31 of slots g and g + 8 are b consecutive words of either row; field
+//           4 s + 2 odd + hi of the output is pair 2 s + odd of slot g + 8 hi;
+//   values: coordinate 16 m + g + 8 a of a row sits at bit b g of its group 2 m + a of 8 b bits, so a lane shifts
+//           every group of the four rows 2 t, 2 t + 1, 2 t + 8, 2 t + 9 by the same amount.
 template <int B, bool KEYS>
 __global__ void retile_kernel(const uint8_t *__restrict__ rows, uint8_t *__restrict__ bank, int ntiles) {
-    constexpr int LI = B - 2;
     const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    constexpr uint32_t kMask = (1u << B) - 1u;
     for (int tile = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); tile < ntiles; tile += gridDim.x * (blockDim.x >> 5)) {
         uint32_t out[2 * B];
 #pragma unroll
         for (int w = 0; w < 2 * B; ++w) out[w] = 0;
+        const uint32_t *tile_rows = reinterpret_cast<const uint32_t *>(rows + (size_t)tile * 16 * 16 * B);   // 4 B words per row
+        if (KEYS) {
+            uint32_t c[2][B];
 #pragma unroll
-        for (int f = 0; f < 32; ++f) {
-            uint32_t field;
-            if (KEYS) {
-                const int s = f >> 2, odd = (f >> 1) & 1, hi = f & 1;
-                const long long slot = (long long)tile * 16 + g + 8 * hi;
-                const int dim = 32 * t + 4 * s + 2 * odd;
-                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot, dim + 1) << B);
-            } else {
-                const int m = f >> 2, hi = (f >> 1) & 1, a = f & 1;
-                const int dim = 16 * m + g + 8 * a;
-                const long long slot = (long long)tile * 16 + 2 * t + 8 * hi;
-                field = (uint32_t)linear_code(rows, LI, slot, dim) | ((uint32_t)linear_code(rows, LI, slot + 1, dim) << B);
+            for (int hi = 0; hi < 2; ++hi)
+#pragma unroll
+                for (int w = 0; w < B; ++w) c[hi][w] = __ldg(tile_rows + (g + 8 * hi) * 4 * B + B * t + w);
+#pragma unroll
+            for (int f = 0; f < 32; ++f) {
+                const int pair = f >> 1, hi = f & 1;   // pair = 2 s + odd
+                insert_bits<2 * B>(out, 2 * B * f, extract_bits<2 * B>(c[hi], 2 * B * pair));
             }
-            const int off = f * 2 * B, w = off >> 5, sh = off & 31;
-            out[w] |= field << sh;
-            if (sh + 2 * B > 32) out[w + 1] |= field >> (32 - sh);
+        } else {
+            const int sh = B * g;
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+                uint32_t ra[4 * B], rb[4 * B];
+                const uint4 *pa = reinterpret_cast<const uint4 *>(tile_rows + (2 * t + 8 * hi) * 4 * B);
+                const uint4 *pb = reinterpret_cast<const uint4 *>(tile_rows + (2 * t + 8 * hi + 1) * 4 * B);
+#pragma unroll
+                for (int u = 0; u < B; ++u) {
+                    const uint4 va = __ldg(pa + u), vb = __ldg(pb + u);
+                    ra[4 * u] = va.x; ra[4 * u + 1] = va.y; ra[4 * u + 2] = va.z; ra[4 * u + 3] = va.w;
+                    rb[4 * u] = vb.x; rb[4 * u + 1] = vb.y; rb[4 * u + 2] = vb.z; rb[4 * u + 3] = vb.w;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {            // j = 2 m + a
+                    const uint32_t ga = extract_bits<8 * B>(ra, 8 * B * j), gb = extract_bits<8 * B>(rb, 8 * B * j);
+                    const uint32_t field = ((ga >> sh) & kMask) | (((gb >> sh) & kMask) << B);
+                    insert_bits<2 * B>(out, 2 * B * (4 * (j >> 1) + 2 * hi + (j & 1)), field);
+                }
+            }
         }
         uint32_t *dst = reinterpret_cast<uint32_t *>(bank + (size_t)tile * 256 * B + (size_t)lane * 8 * B);
 #pragma unroll
