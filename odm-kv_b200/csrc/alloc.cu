@@ -36,6 +36,7 @@ struct AllocCfg {
     int K;
     int sink_bits;
     double target;
+    double inv_da[kMaxL * kMaxL];   // 1 / (eps32[i] - eps32[j]) in fp64 (0 where the slopes are equal)
 };
 
 // Breakpoints of the lower envelope of the K cost lines  s -> eps32[k] * s + lamb[k]  over s >= 0 (exact real
@@ -51,55 +52,70 @@ struct Envelope {
     int nh;                       // number of envelope pieces; 0 = use the full formula for every score
 };
 
+// (Where two cost lines cross is computed as a product with the precomputed reciprocal of the slope difference, a
+// relative change of 2^-52 against the quotient; the bands are eleven orders of magnitude wider.  Every loop over
+// levels is unrolled over kMaxL so that the lines stay in registers: this routine sits on the critical path of each
+// of the 66 dependent steps of a solve.)
 __device__ inline void build_envelope(const AllocCfg &cfg, const float *lamb, Envelope &env) {
     const int K = cfg.K;
     double a[kMaxL], c[kMaxL];
-    for (int k = 0; k < K; ++k) { a[k] = (double)cfg.eps32[k]; c[k] = (double)lamb[k]; }
-    bool on[kMaxL];
-    for (int k = 0; k < K; ++k) on[k] = false;
+#pragma unroll
+    for (int k = 0; k < kMaxL; ++k) { a[k] = (double)cfg.eps32[k]; c[k] = (double)lamb[k]; }
     int cur = 0;
-    for (int k = 1; k < K; ++k)
-        if (c[k] < c[cur] || (c[k] == c[cur] && a[k] < a[cur])) cur = k;
-    double tau[kMaxL];
+    double a_cur = a[0], c_cur = c[0];
+#pragma unroll
+    for (int k = 1; k < kMaxL; ++k)
+        if (k < K && (c[k] < c_cur || (c[k] == c_cur && a[k] < a_cur))) { cur = k; a_cur = a[k]; c_cur = c[k]; }
+    const double h0 = c_cur;                       // the envelope at s = 0
+    unsigned on = 0u;
+    double tau[kMaxL], fv[kMaxL];                  // breakpoint v and the envelope's value there
+#pragma unroll
+    for (int v = 0; v < kMaxL; ++v) { tau[v] = 0.0; fv[v] = 0.0; }
     int nh = 0;
     double s_cur = 0.0;
     bool ok = true;
-    while (true) {
+    for (int it = 0; it <= kMaxL; ++it) {
         env.level[nh] = cur;
-        on[cur] = true;
+        on |= 1u << cur;
         int nxt = -1;
-        double best = 0.0;
-        for (int k = 0; k < K; ++k) {
-            if (k == cur || !(a[k] < a[cur])) continue;
-            const double sx = (c[k] - c[cur]) / (a[cur] - a[k]);
-            if (sx < s_cur) continue;
-            if (nxt < 0 || sx < best || (sx == best && a[k] < a[nxt])) { nxt = k; best = sx; }
+        double best = 0.0, a_nxt = 0.0, c_nxt = 0.0;
+#pragma unroll
+        for (int k = 0; k < kMaxL; ++k) {
+            if (k < K && k != cur && a[k] < a_cur) {
+                const double sx = (c[k] - c_cur) * cfg.inv_da[cur * kMaxL + k];
+                if (!(sx < s_cur) && (nxt < 0 || sx < best || (sx == best && a[k] < a_nxt))) { nxt = k; best = sx; a_nxt = a[k]; c_nxt = c[k]; }
+            }
         }
         if (nxt < 0) { ++nh; break; }
-        const double f = a[cur] * best + c[cur];
-        const double dc = fabs(c[nxt] - c[cur]);
+        const double f = a_cur * best + c_cur;
+        const double dc = fabs(c_nxt - c_cur);
         double band = dc > 0.0 ? 64.0 * 1.1920928955078125e-07 * fabs(f) / dc : 1.0;
         if (band < 1e-5) band = 1e-5;
         if (!(band <= 1e-2) || !(best > 0.0) || !(best < 1e37)) ok = false;
-        tau[nh] = best;
+#pragma unroll
+        for (int v = 0; v < kMaxL; ++v) if (v == nh) { tau[v] = best; fv[v] = f; }
         env.lo[nh] = (float)(best * (1.0 - band) * (1.0 - 1e-7));
         env.hi[nh] = (float)(best * (1.0 + band) * (1.0 + 1e-7));
         ++nh;
         s_cur = best;
-        cur = nxt;
+        cur = nxt; a_cur = a_nxt; c_cur = c_nxt;
         if (nh >= kMaxL) { ok = false; break; }
     }
     // levels off the envelope must stay clear of it at every breakpoint (their gap is smallest there or at s = 0)
-    for (int k = 0; k < K && ok; ++k) {
-        if (on[k]) continue;
-        for (int v = 0; v + 1 < nh; ++v) {
-            const double h = a[env.level[v]] * tau[v] + c[env.level[v]];
-            const double h_next = v + 2 < nh ? a[env.level[v + 1]] * tau[v + 1] + c[env.level[v + 1]] : h;
-            const double gk = a[k] * tau[v] + c[k];
-            if (!(gk - h > 1e-4 * fmax(fabs(h), fabs(h_next)))) ok = false;   // 1e-4 >> 2^-22: holds along the whole piece
+#pragma unroll
+    for (int k = 0; k < kMaxL; ++k) {
+        if (k < K && !((on >> k) & 1u)) {
+#pragma unroll
+            for (int v = 0; v + 1 < kMaxL; ++v) {
+                if (v + 1 < nh) {
+                    const double h = fv[v];
+                    const double h_next = v + 2 < nh ? fv[v + 1] : h;
+                    const double gk = a[k] * tau[v] + c[k];
+                    if (!(gk - h > 1e-4 * fmax(fabs(h), fabs(h_next)))) ok = false;   // 1e-4 >> 2^-22: holds along the whole piece
+                }
+            }
+            if (!(c[k] - h0 > 1e-4 * fabs(h0)) && !(c[k] > h0 && h0 == 0.0)) ok = false;
         }
-        const double h0 = c[env.level[0]];
-        if (!(c[k] - h0 > 1e-4 * fabs(h0)) && !(c[k] > h0 && h0 == 0.0)) ok = false;
     }
     env.nh = ok ? nh : 0;
 }
@@ -945,6 +961,11 @@ static int make_cfg(const int *levels, const double *eps, int K, double target, 
         cfg->eps32[k] = (float)eps[k];
     }
     for (int k = K; k < kMaxL; ++k) { cfg->levels[k] = 0; cfg->bits32[k] = 0.f; cfg->eps32[k] = 0.f; }
+    for (int i = 0; i < kMaxL; ++i)
+        for (int j = 0; j < kMaxL; ++j) {
+            const double d = (double)cfg->eps32[i] - (double)cfg->eps32[j];
+            cfg->inv_da[i * kMaxL + j] = d != 0.0 ? 1.0 / d : 0.0;
+        }
     cfg->K = K;
     cfg->sink_bits = sink_bits;
     double t = target;
