@@ -788,7 +788,7 @@ __global__ void alloc_keys_kernel(const float *__restrict__ scores, const uint8_
     if ((threadIdx.x & 31) == 0 && live) atomicAdd(&ws.prob[p].n_sorted, (int)live);
 }
 
-constexpr int kSolveThreads = 1024;
+constexpr int kSolveThreads = 512;
 constexpr int kCoarse = 4096;
 
 __global__ void __launch_bounds__(kSolveThreads) alloc_solve_kernel(AllocWs ws, int n, const AllocCfg cfg) {
