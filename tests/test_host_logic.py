@@ -169,3 +169,25 @@ def test_packed_chunk_deepcopy_rebuilds_c_view():
     view = dup.c_struct()
     assert view.k_codes[0] == dup.k_codes[0].data_ptr() != ch.k_codes[0].data_ptr()
     assert view.cap[1] == 16 and view.T == 16
+
+
+def test_mask_predicates_of_the_attention_wrapper(pkg):
+    """The packed decode kernels take no mask: the wrapper may use them only when the mask hides no key from a single
+    query, and the per-query packed route of a multi-token pass only when nothing but the causal part is masked."""
+    ap = pkg.attention_patch
+    B, T, q = 2, 9, 3
+    assert ap._mask_is_open(None) and ap._causal_or_open(None, q)
+    full = torch.ones(B, 1, 1, T, dtype=torch.bool)
+    assert ap._mask_is_open(full) and ap._mask_is_open(torch.zeros(B, 1, 1, T))
+    padded = full.clone()
+    padded[1, ..., :4] = False                       # left padding of sample 1
+    assert not ap._mask_is_open(padded)
+    additive = torch.zeros(B, 1, 1, T)
+    additive[1, ..., :4] = torch.finfo(torch.float32).min
+    assert not ap._mask_is_open(additive)
+    causal = torch.ones(B, 1, q, T, dtype=torch.bool)
+    causal[..., -q:] = torch.tril(torch.ones(q, q, dtype=torch.bool))
+    assert ap._causal_or_open(causal, q) and not ap._mask_is_open(causal)
+    causal_padded = causal.clone()
+    causal_padded[1, ..., :4] = False
+    assert not ap._causal_or_open(causal_padded, q)
